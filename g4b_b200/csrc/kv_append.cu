@@ -1,0 +1,205 @@
+// KV-cache append and decode-state advance.
+//
+// Replaces g4b/kernels/add_kv_to_cache.py:83-159 (ring scatter with optional weight-less
+// RMS norm and cast on store) and g4b/kernels/advance_decode_state.py:31-63. Adds the paged
+// destination (16-token pages addressed through a block table), which the reference does
+// not have.
+//
+// Both kernels are launch-bound at decode sizes (512 rows of 512 B) and pure streaming at
+// prefill sizes: one warp per (slot, kv head, token) row, 16-byte vector accesses.
+#include "common.cuh"
+#include <type_traits>
+
+namespace g4b {
+
+struct AppendParams {
+  const void* x;
+  void* cache;
+  const void* cache_offsets;
+  const float* x_rsos;
+  const uint8_t* user_phase;
+  const int32_t* block_tables;
+  int64_t xs0, xs1, xs2;        // x strides (elements)
+  int64_t rs0, rs1, rs2;        // x_rsos strides
+  int64_t off_stride, phase_stride;
+  int64_t bt_stride0, bt_stride1;
+  int B, G, Tq, D;
+  int T;                        // ring length (ring mode)
+  int page_size, page_shift;    // paged mode
+  int num_pages, max_pages;
+  int offsets_are_i64;
+  int phase;
+  float eps;
+  int32_t* status;
+};
+
+template <typename T> __device__ __forceinline__ float ld_f(const T* p) {
+  return ElemTraits<T>::to_float(*p);
+}
+
+// One warp per row.  VEC = elements per lane per iteration (8).
+template <typename TX, typename TC, bool kSameBits>
+__global__ void __launch_bounds__(256) kv_append_kernel(AppendParams p) {
+  const int warps_per_block = blockDim.x >> 5;
+  const int64_t row = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int64_t rows = (int64_t)p.B * p.G * p.Tq;
+  if (row >= rows) return;
+  const int t = (int)(row % p.Tq);
+  const int g = (int)((row / p.Tq) % p.G);
+  const int b = (int)(row / ((int64_t)p.Tq * p.G));
+
+  if (p.user_phase != nullptr && p.user_phase[b * p.phase_stride] != (uint8_t)p.phase) return;
+
+  int64_t off;
+  if (p.offsets_are_i64) off = ((const int64_t*)p.cache_offsets)[b * p.off_stride];
+  else off = ((const int32_t*)p.cache_offsets)[b * p.off_stride];
+
+  TC* dst;
+  if (p.block_tables != nullptr) {
+    const int64_t pos = off + t;
+    const int64_t pg = pos >> p.page_shift;
+    if (pos < 0 || pg >= p.max_pages) {  // refuse to write outside the block table
+      if (lane == 0) atomicCAS(p.status, 0, 0x100 | 1);
+      return;
+    }
+    const int32_t page = p.block_tables[b * p.bt_stride0 + pg * p.bt_stride1];
+    if (page < 0 || page >= p.num_pages) {
+      if (lane == 0) atomicCAS(p.status, 0, 0x100 | 2);
+      return;
+    }
+    const int r = (int)(pos & (p.page_size - 1));
+    dst = (TC*)p.cache + (((int64_t)page * p.G + g) * p.page_size + r) * p.D;
+  } else {
+    int64_t r = (off + t) % p.T;
+    if (r < 0) r += p.T;
+    dst = (TC*)p.cache + (((int64_t)b * p.G + g) * p.T + r) * p.D;
+  }
+  const TX* src = (const TX*)p.x + b * p.xs0 + g * p.xs1 + t * p.xs2;
+
+  if constexpr (kSameBits) {
+    // same element type, no norm: move bits untouched
+    if (p.x_rsos == nullptr) {
+      constexpr int V = 16 / sizeof(TX);
+      const bool aligned = ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0 && (p.D % V) == 0;
+      if (aligned) {
+        for (int d = lane * V; d < p.D; d += 32 * V)
+          *(uint4*)(dst + d) = *(const uint4*)(src + d);
+      } else {
+        for (int d = lane; d < p.D; d += 32) dst[d] = (TC)src[d];
+      }
+      return;
+    }
+  }
+  float r = 1.0f;
+  const bool norm = p.x_rsos != nullptr;
+  if (norm) r = rsqrtf(p.x_rsos[b * p.rs0 + g * p.rs1 + t * p.rs2] / (float)p.D + p.eps);
+  const bool vec_ok = (p.D % 8) == 0 && (((uintptr_t)src) & (8 * sizeof(TX) - 1)) == 0 &&
+                      (((uintptr_t)dst) & (8 * sizeof(TC) - 1)) == 0;
+  if (vec_ok) {
+    // 8 elements per lane per pass: 16- or 32-byte loads, 16- or 32-byte stores
+    for (int d = lane * 8; d < p.D; d += 256) {
+      alignas(32) TX in[8];
+      alignas(32) TC out[8];
+      if constexpr (sizeof(TX) == 4) {
+        *(uint4*)&in[0] = *(const uint4*)(src + d);
+        *(uint4*)&in[4] = *(const uint4*)(src + d + 4);
+      } else {
+        *(uint4*)&in[0] = *(const uint4*)(src + d);
+      }
+#pragma unroll
+      for (int i = 0; i < 8; ++i) {
+        float v = ElemTraits<TX>::to_float(in[i]);
+        if (norm) v *= r;
+        out[i] = ElemTraits<TC>::from_float(v);
+      }
+      if constexpr (sizeof(TC) == 4) {
+        *(uint4*)(dst + d) = *(const uint4*)&out[0];
+        *(uint4*)(dst + d + 4) = *(const uint4*)&out[4];
+      } else {
+        *(uint4*)(dst + d) = *(const uint4*)&out[0];
+      }
+    }
+    return;
+  }
+  for (int d = lane; d < p.D; d += 32) {
+    float v = ld_f(src + d);
+    if (norm) v *= r;
+    dst[d] = ElemTraits<TC>::from_float(v);
+  }
+}
+
+template <typename TX, typename TC>
+static int launch_typed(const AppendParams& p, cudaStream_t st) {
+  const int64_t rows = (int64_t)p.B * p.G * p.Tq;
+  if (rows == 0) return G4B_OK;
+  const int wpb = 8;
+  const int64_t blocks = (rows + wpb - 1) / wpb;
+  if (blocks > 0x7fffffffLL) return fail(G4B_ERR_UNSUPPORTED, "kv_append: too many rows");
+  constexpr bool same = std::is_same<TX, TC>::value;
+  kv_append_kernel<TX, TC, same><<<(unsigned)blocks, wpb * 32, 0, st>>>(p);
+  G4B_CUDA_CHECK(cudaGetLastError());
+  return G4B_OK;
+}
+
+int launch_kv_append(const G4bAppendArgs& a, cudaStream_t st) {
+  AppendParams p{};
+  p.x = a.x.ptr; p.cache = a.cache.ptr; p.cache_offsets = a.cache_offsets.ptr;
+  p.x_rsos = (const float*)a.x_rsos.ptr;
+  p.user_phase = (const uint8_t*)a.user_phase.ptr;
+  p.block_tables = (const int32_t*)a.block_tables.ptr;
+  p.xs0 = a.x.stride[0]; p.xs1 = a.x.stride[1]; p.xs2 = a.x.stride[2];
+  p.rs0 = a.x_rsos.stride[0]; p.rs1 = a.x_rsos.stride[1]; p.rs2 = a.x_rsos.stride[2];
+  p.off_stride = a.cache_offsets.stride[0];
+  p.phase_stride = a.user_phase.stride[0];
+  p.bt_stride0 = a.block_tables.stride[0]; p.bt_stride1 = a.block_tables.stride[1];
+  p.B = (int)a.x.shape[0]; p.G = (int)a.x.shape[1]; p.Tq = (int)a.x.shape[2]; p.D = (int)a.x.shape[3];
+  p.offsets_are_i64 = a.cache_offsets.dtype == G4B_I64;
+  p.phase = a.phase; p.eps = a.rmsnorm_eps;
+  p.status = device_status_ptr();
+  if (p.status == nullptr) return G4B_ERR_CUDA;
+  if (p.block_tables != nullptr) {
+    p.page_size = a.page_size;
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < a.page_size) ++p.page_shift;
+    p.num_pages = (int)a.cache.shape[0];
+    p.max_pages = (int)a.block_tables.shape[1];
+    p.T = 0;
+  } else {
+    p.T = (int)a.cache.shape[2];
+  }
+  int rc = G4B_ERR_BAD_DTYPE;
+  G4B_DISPATCH_FLOAT(a.x.dtype, TX,
+    G4B_DISPATCH_FLOAT(a.cache.dtype, TC, rc = launch_typed<TX, TC>(p, st)));
+  if (rc == G4B_ERR_BAD_DTYPE) return fail(rc, "kv_append: x/cache dtypes must be f32, f16 or bf16");
+  return rc;
+}
+
+// ---------------------------------------------------------------------------------------
+// advance_decode_state
+// ---------------------------------------------------------------------------------------
+__global__ void advance_kernel(int32_t* in_tok, const int32_t* out_tok, int32_t* cache_offsets,
+                               int32_t* time_dim_sizes, const uint8_t* user_phase, int B,
+                               int64_t in_s1, int64_t out_s0, int64_t off_s, int64_t time_s,
+                               int64_t phase_s) {
+  const int b = blockIdx.x * blockDim.x + threadIdx.x;
+  if (b >= B) return;
+  if (user_phase[b * phase_s] != (uint8_t)G4B_PHASE_DECODE) return;
+  in_tok[b * in_s1] = out_tok[b * out_s0];
+  cache_offsets[b * off_s] += 1;
+  time_dim_sizes[b * time_s] += 1;
+}
+
+int launch_advance(const G4bAdvanceArgs& a, cudaStream_t st) {
+  const int B = (int)a.input_token_ids.shape[1];
+  if (B == 0) return G4B_OK;
+  advance_kernel<<<(B + 255) / 256, 256, 0, st>>>(
+      (int32_t*)a.input_token_ids.ptr, (const int32_t*)a.out_token_ids.ptr,
+      (int32_t*)a.cache_offsets.ptr, (int32_t*)a.time_dim_sizes.ptr,
+      (const uint8_t*)a.user_phase.ptr, B, a.input_token_ids.stride[1], a.out_token_ids.stride[0],
+      a.cache_offsets.stride[0], a.time_dim_sizes.stride[0], a.user_phase.stride[0]);
+  G4B_CUDA_CHECK(cudaGetLastError());
+  return G4B_OK;
+}
+
+}  // namespace g4b

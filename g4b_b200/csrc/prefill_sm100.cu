@@ -1,0 +1,593 @@
+// Flash-attention forward for Tq > 1 (prefill chunks), head dim 256, f16 / bf16, on the
+// 5th-generation tensor cores: tcgen05.mma with accumulators in tensor memory, operands
+// staged in shared memory by TMA, online softmax in registers.
+//
+// Replaces _attn_kernel / _attn_inner of the reference (g4b/kernels/fa2.py:37-136, 256-480)
+// for the prefill phase: ring-buffer KV cache (fa2.py:52-55,75), GQA (fa2.py:337), causal
+// and full stages (fa2.py:354-435), per-slot phase skip (fa2.py:333-335); adds the softmax
+// scale and the per-query sliding window of scripts/reference_impl.py:437-443.
+//
+// One CTA = 128 query rows of one query head.  Six warps:
+//   warp 0      producer: TMA loads of Q (once) and of K / V chunks into a 5-stage ring
+//   warp 1      one thread issues every tcgen05.mma; the warp owns the TMEM allocation
+//   warps 2..5  softmax: thread r owns query row r (TMEM lane r), so row max / row sum
+//               need no shuffles; also rescale O when a maximum moved and write the output
+//
+// TMEM (512 columns x 128 lanes x 32 bit):  O[128 x 256] f32 in columns 0..255,
+// S0 / S1 [128 x 128] f32 in columns 256..383 / 384..511.  P (f16/bf16) overwrites the
+// first 64 columns of its S buffer and is the A operand of the P.V product from TMEM.
+//
+// Per 128-key tile j:   S(j) = Q K(j)^T  (16 MMAs 128x128x16, A and B from smem, K-major)
+//                        O  += P(j) V(j)  ( 8 MMAs 128x256x16, A from TMEM, B MN-major smem)
+// issued in the order QK(0) QK(1) PV(0) QK(2) PV(1) ... so the tensor pipe works on
+// QK(j+1) / PV(j-1) while the softmax warps turn S(j) into P(j).
+//
+// Shared memory: Q 64 KB (4 slabs of [128 rows x 64 d], 128-byte swizzle) + 5 x 32 KB ring.
+// A K chunk is half the head dim of a tile ([128 keys x 128 d], 2 slabs); a V chunk is
+// half the keys of a tile ([64 keys x 256 d], 4 slabs).
+#include "common.cuh"
+#include "sm100_ptx.cuh"
+
+#include <cudaTypedefs.h>
+
+namespace g4b {
+
+namespace {
+
+constexpr int kBM = 128;          // query rows per CTA
+constexpr int kBN = 128;          // keys per S tile
+constexpr int kHD = 256;          // head dim
+constexpr int kStages = 5;
+constexpr int kChunkBytes = 32768;
+constexpr int kQBytes = kBM * kHD * 2;
+constexpr int kThreads = 192;
+constexpr int kSmemBytes = 1024 /*align slack*/ + kQBytes + kStages * kChunkBytes + 256 /*barriers*/;
+
+constexpr uint32_t kColO = 0, kColS0 = 256, kColS1 = 384;
+
+enum : int32_t {
+  kErrQFull = 0x301, kErrKvEmpty = 0x302, kErrKvFull = 0x303, kErrSFull = 0x304,
+  kErrPFull = 0x305, kErrPvDone = 0x306,
+};
+
+struct PrefillParams {
+  void* o;
+  const void* k; const void* v;              // raw cache pointers (manual fallback loads)
+  const int32_t* time_dim_sizes; const uint8_t* user_phase;
+  int64_t o_s0, o_s1, o_s2;
+  int64_t time_stride, phase_stride;
+  int B, H, G, Tq, T;
+  int ctx_window, sliding_window, phase, causal;
+  int o_dtype;
+  float scale_log2;
+  int32_t* status;
+};
+
+struct Barriers {
+  uint64_t q_full;
+  uint64_t kv_full[kStages];
+  uint64_t kv_empty[kStages];
+  uint64_t s_full[2];
+  uint64_t p_full[2];
+  uint64_t pv_done;
+  uint32_t tmem_base;
+  uint32_t pad;
+};
+
+__device__ __forceinline__ void record(int32_t* status, int32_t code) { atomicCAS(status, 0, code); }
+
+// Copies rows [row0, row0 + nrows) of a chunk with ordinary loads, applying the 128-byte
+// swizzle by hand; rows whose logical key is outside [0, window) are written as zeros.
+// Used for the tile that crosses the end of the ring buffer and for V rows past the window
+// (which may hold anything, and 0 x NaN would poison the accumulator).
+//   slab_rows: rows per slab (128 for K chunks, 64 for V chunks); d0: first head-dim element;
+//   nslabs: 64-element slabs in the chunk.
+template <typename T>
+__device__ __forceinline__ void manual_chunk(uint8_t* dst, const T* cache_bg, int ring_start, int Trows,
+                                             int key0, int nrows, int window, int d0, int nslabs,
+                                             int slab_rows, int lane) {
+  const int chunks_per_row = nslabs * 8;   // 16-byte pieces per row
+  for (int idx = lane; idx < nrows * chunks_per_row; idx += 32) {
+    const int r = idx / chunks_per_row, ch = idx % chunks_per_row;
+    const int key = key0 + r;
+    uint4 val = make_uint4(0u, 0u, 0u, 0u);
+    if (key >= 0 && key < window) {
+      int pr = ring_start + key;
+      if (pr >= Trows) pr -= Trows;
+      val = *reinterpret_cast<const uint4*>(cache_bg + (int64_t)pr * kHD + d0 + ch * 8);
+    }
+    const int slab = ch >> 3, c16 = ch & 7;
+    uint8_t* p = dst + slab * (slab_rows * 128) + r * 128 + ((c16 ^ (r & 7)) << 4);
+    *reinterpret_cast<uint4*>(p) = val;
+  }
+}
+
+template <typename T> struct PackT;
+template <> struct PackT<__nv_bfloat16> {
+  static constexpr uint32_t kFmt = 1;
+  __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+  }
+};
+template <> struct PackT<__half> {
+  static constexpr uint32_t kFmt = 0;
+  __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
+    uint32_t r;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
+    return r;
+  }
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kThreads, 1)
+prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
+               const __grid_constant__ CUtensorMap v_map, PrefillParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int bh = blockIdx.x;
+  const int b = bh / p.H, h = bh % p.H;
+  const int g = h / (p.H / p.G);
+  const int q_tile = (int)gridDim.y - 1 - (int)blockIdx.y;   // heaviest (latest) tiles first
+  const int m0 = q_tile * kBM;
+
+  if (p.user_phase != nullptr && p.user_phase[b * p.phase_stride] != (uint8_t)p.phase) return;
+  {
+    // an earlier CTA gave up on a wait: drain the grid.  One thread reads so all agree.
+    __shared__ int s_abort;
+    if (threadIdx.x == 0) s_abort = *reinterpret_cast<volatile int32_t*>(p.status);
+    __syncthreads();
+    if (s_abort != 0) return;
+  }
+
+  // ---- geometry of this CTA's key range (fa2.py:52-64) ----
+  const int time = p.time_dim_sizes[b * p.time_stride];
+  const int window = min(time, p.ctx_window);
+  const int ring_start = max(time - p.ctx_window, 0) % p.T;
+  const int q_t_base = window - p.Tq;                    // logical position of query row 0
+  const int rows_valid = min(kBM, p.Tq - m0);
+  const int qpos_min = q_t_base + m0;
+  const int qpos_max = q_t_base + m0 + rows_valid - 1;
+  const int key_hi = p.causal ? min(window, qpos_max + 1) : window;
+  const int key_lo = p.sliding_window > 0 ? max(0, qpos_min - p.sliding_window + 1) : 0;
+  const int tile_lo = key_lo / kBN;
+  const int n_tiles = key_hi > key_lo ? (key_hi + kBN - 1) / kBN - tile_lo : 0;
+
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  uint8_t* sQ = smem;
+  uint8_t* sRing = smem + kQBytes;
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + kQBytes + kStages * kChunkBytes);
+
+  if (n_tiles <= 0) {
+    // no visible key for any row of this tile: the output rows are defined as zero
+    if (warp >= 2) {
+      const int r = (warp & 3) * 32 + lane;
+      if (r < rows_valid) {
+        const int64_t off = b * p.o_s0 + h * p.o_s1 + (int64_t)(m0 + r) * p.o_s2;
+        for (int d = 0; d < kHD; ++d) {
+          if (p.o_dtype == G4B_F32) ((float*)p.o)[off + d] = 0.f;
+          else ((uint16_t*)p.o)[off + d] = 0;
+        }
+      }
+    }
+    return;
+  }
+
+  const uint32_t bar_q = ptx::smem_u32(&bars->q_full);
+  const uint32_t bar_pv = ptx::smem_u32(&bars->pv_done);
+  if (threadIdx.x == 0) {
+    ptx::mbar_init(bar_q, 1);
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&bars->kv_full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->kv_empty[s]), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&bars->s_full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->p_full[s]), 128);
+    }
+    ptx::mbar_init(bar_pv, 1);
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&q_map);
+    ptx::prefetch_tensormap(&k_map);
+    ptx::prefetch_tensormap(&v_map);
+  }
+  if (warp == 1) {
+    ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), 512);
+    ptx::tmem_relinquish();
+  }
+  ptx::tc_fence_before();
+  __syncthreads();
+  ptx::tc_fence_after();
+  const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+
+  if (warp == 0) {
+    // =============================== producer ===============================
+    const T* kbg = (const T*)p.k + ((int64_t)b * p.G + g) * p.T * kHD;
+    const T* vbg = (const T*)p.v + ((int64_t)b * p.G + g) * p.T * kHD;
+    const int bg = b * p.G + g;
+    if (lane == 0) {
+      ptx::mbar_arrive_expect_tx(bar_q, kQBytes);
+      for (int s = 0; s < 4; ++s)
+        ptx::tma_load_4d(ptx::smem_u32(sQ + s * 16384), &q_map, bar_q, s * 64, m0, h, b);
+    }
+    uint32_t cc = 0;   // chunk counter over the ring
+    bool ok = true;
+    // lane 0 waits for the stage to drain; the verdict is shared so the warp stays converged
+    auto wait_empty = [&](int st, uint32_t c) -> bool {
+      int w = 1;
+      if (lane == 0) w = ptx::mbar_wait(ptx::smem_u32(&bars->kv_empty[st]), ((c / kStages) & 1) ^ 1) ? 1 : 0;
+      w = __shfl_sync(0xffffffffu, w, 0);
+      if (!w) { if (lane == 0) record(p.status, kErrKvEmpty); ok = false; }
+      return w != 0;
+    };
+    // chunk order = MMA consumption order: K(0) K(1) V(0) K(2) V(1) ... K(n-1) V(n-2) V(n-1)
+    auto load_k = [&](int j) {
+      const int key0 = (tile_lo + j) * kBN;
+      int pr0 = ring_start + key0;
+      if (pr0 >= p.T) pr0 -= p.T;
+      const int live = min(kBN, window - key0);          // keys of this tile inside the window
+      const bool wraps = pr0 + live > p.T;
+      for (int kc = 0; kc < 2 && ok; ++kc, ++cc) {
+        const int st = cc % kStages;
+        const uint32_t full = ptx::smem_u32(&bars->kv_full[st]);
+        if (!wait_empty(st, cc)) break;
+        uint8_t* dst = sRing + st * kChunkBytes;
+        if (!wraps) {
+          if (lane == 0) {
+            ptx::mbar_arrive_expect_tx(full, kChunkBytes);
+            for (int s = 0; s < 2; ++s)
+              ptx::tma_load_3d(ptx::smem_u32(dst + s * 16384), &k_map, full, kc * 128 + s * 64, pr0, bg);
+          }
+        } else {
+          manual_chunk<T>(dst, kbg, ring_start, p.T, key0, kBN, window, kc * 128, 2, 128, lane);
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(full);
+        }
+        __syncwarp();
+      }
+    };
+    auto load_v = [&](int j) {
+      const int key0t = (tile_lo + j) * kBN;
+      for (int vc = 0; vc < 2 && ok; ++vc, ++cc) {
+        const int key0 = key0t + vc * 64;
+        int pr0 = ring_start + key0;
+        if (pr0 >= p.T) pr0 -= p.T;
+        const int live = min(64, window - key0);
+        // rows past the window must read as zero; rows past the ring end must wrap
+        const bool manual = live < 64 || pr0 + 64 > p.T;
+        const int st = cc % kStages;
+        const uint32_t full = ptx::smem_u32(&bars->kv_full[st]);
+        if (!wait_empty(st, cc)) break;
+        uint8_t* dst = sRing + st * kChunkBytes;
+        if (!manual) {
+          if (lane == 0) {
+            ptx::mbar_arrive_expect_tx(full, kChunkBytes);
+            for (int s = 0; s < 4; ++s)
+              ptx::tma_load_3d(ptx::smem_u32(dst + s * 8192), &v_map, full, s * 64, pr0, bg);
+          }
+        } else {
+          manual_chunk<T>(dst, vbg, ring_start, p.T, key0, 64, window, 0, 4, 64, lane);
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(full);
+        }
+        __syncwarp();
+      }
+    };
+    load_k(0);
+    if (n_tiles > 1) load_k(1);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      load_v(j);
+      if (j + 2 < n_tiles) load_k(j + 2);
+    }
+  } else if (warp == 1) {
+    // =============================== MMA issuer ===============================
+    if (lane == 0) {
+      constexpr uint32_t idesc_qk = ptx::make_idesc_f16(PackT<T>::kFmt, 128, 128, 0, 0);
+      constexpr uint32_t idesc_pv = ptx::make_idesc_f16(PackT<T>::kFmt, 128, 256, 0, 1);
+      const uint32_t sQ_u = ptx::smem_u32(sQ), sRing_u = ptx::smem_u32(sRing);
+      bool ok = ptx::mbar_wait(bar_q, 0);
+      if (!ok) record(p.status, kErrQFull);
+      ptx::tc_fence_after();
+      uint32_t cc = 0;
+      auto issue_qk = [&](int j) {
+        const uint32_t d_tmem = tmem + ((j & 1) ? kColS1 : kColS0);
+        for (int kc = 0; kc < 2 && ok; ++kc, ++cc) {
+          const int st = cc % kStages;
+          if (!ptx::mbar_wait(ptx::smem_u32(&bars->kv_full[st]), (cc / kStages) & 1)) {
+            record(p.status, kErrKvFull); ok = false; break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t kb = sRing_u + st * kChunkBytes;
+#pragma unroll
+          for (int k16 = 0; k16 < 8; ++k16) {
+            const uint32_t a_addr = sQ_u + (kc * 2 + (k16 >> 2)) * 16384 + (k16 & 3) * 32;
+            const uint32_t b_addr = kb + (k16 >> 2) * 16384 + (k16 & 3) * 32;
+            ptx::mma_ss(d_tmem, ptx::make_smem_desc_sw128(a_addr, 16, 1024),
+                        ptx::make_smem_desc_sw128(b_addr, 16, 1024), idesc_qk, (kc | k16) != 0);
+          }
+          ptx::tc_commit(ptx::smem_u32(&bars->kv_empty[st]));
+        }
+        if (ok) ptx::tc_commit(ptx::smem_u32(&bars->s_full[j & 1]));
+      };
+      auto issue_pv = [&](int j) {
+        if (!ptx::mbar_wait(ptx::smem_u32(&bars->p_full[j & 1]), (j >> 1) & 1)) {
+          record(p.status, kErrPFull); ok = false; return;
+        }
+        ptx::tc_fence_after();
+        const uint32_t p_tmem = tmem + ((j & 1) ? kColS1 : kColS0);
+        for (int vc = 0; vc < 2 && ok; ++vc, ++cc) {
+          const int st = cc % kStages;
+          if (!ptx::mbar_wait(ptx::smem_u32(&bars->kv_full[st]), (cc / kStages) & 1)) {
+            record(p.status, kErrKvFull); ok = false; break;
+          }
+          ptx::tc_fence_after();
+          const uint32_t vb = sRing_u + st * kChunkBytes;
+#pragma unroll
+          for (int k16 = 0; k16 < 4; ++k16) {
+            // 16 keys = 8 packed columns of P; 16 rows of every V slab = 2048 bytes
+            ptx::mma_ts(tmem + kColO, p_tmem + vc * 32 + k16 * 8,
+                        ptx::make_smem_desc_sw128(vb + k16 * 2048, 8192, 1024), idesc_pv,
+                        (j | vc | k16) != 0);
+          }
+          ptx::tc_commit(ptx::smem_u32(&bars->kv_empty[st]));
+        }
+        if (ok) ptx::tc_commit(bar_pv);
+      };
+      if (ok) issue_qk(0);
+      if (ok && n_tiles > 1) issue_qk(1);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        issue_pv(j);
+        if (ok && j + 2 < n_tiles) issue_qk(j + 2);
+      }
+    }
+    __syncwarp();
+  } else {
+    // =============================== softmax / epilogue ===============================
+    const int lane_base = (warp & 3) * 32;
+    const int r = lane_base + lane;                       // query row = TMEM lane
+    const uint32_t trow = tmem + ((uint32_t)lane_base << 16);
+    const int qpos = q_t_base + m0 + r;
+    const int hi_r = p.causal ? min(window, qpos + 1) : window;
+    const int lo_r = p.sliding_window > 0 ? max(0, qpos - p.sliding_window + 1) : 0;
+    float m_used = -INFINITY;   // reference maximum the accumulated O and l are scaled by
+    float l_run = 0.f;
+    bool ok = true;
+
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      const uint32_t s_col = (j & 1) ? kColS1 : kColS0;
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(ptx::smem_u32(&bars->s_full[j & 1]), (j >> 1) & 1))) {
+        record(p.status, kErrSFull); ok = false; break;
+      }
+      ptx::tc_fence_after();
+      const int kbase = (tile_lo + j) * kBN;
+      // warp-uniform: does any row of this CTA need element masks in this tile?
+      const bool need_mask = (p.causal && kbase + kBN - 1 > qpos_min) || (kbase + kBN > window) ||
+                             (kbase < key_lo) ||
+                             (p.sliding_window > 0 && kbase < qpos_max - p.sliding_window + 1);
+      uint32_t sraw[4][32];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) ptx::tmem_ld32(trow + s_col + q4 * 32, sraw[q4]);
+      ptx::tc_wait_ld();
+      float mx = -INFINITY;
+      if (need_mask) {
+        const int nlo = lo_r - kbase, nhi = hi_r - kbase;
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) {
+            const int n = q4 * 32 + i;
+            float x = __uint_as_float(sraw[q4][i]);
+            x = (n >= nlo && n < nhi) ? x : -INFINITY;
+            sraw[q4][i] = __float_as_uint(x);
+            mx = fmaxf(mx, x);
+          }
+      } else {
+#pragma unroll
+        for (int q4 = 0; q4 < 4; ++q4)
+#pragma unroll
+          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sraw[q4][i]));
+      }
+      const float m_blk = mx * p.scale_log2;
+      // Lazy rescale: keep the old reference maximum unless the new one is more than 2^8
+      // above it (p stays <= 256, exact enough in f32 sums and representable in f16/bf16).
+      float alpha = 1.f;
+      bool rescale = false;
+      if (m_blk > m_used + 8.f) {
+        rescale = (m_used != -INFINITY);
+        alpha = rescale ? ptx::ex2_approx(m_used - m_blk) : 1.f;
+        m_used = m_blk;
+      }
+      const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+      float sum = 0.f;
+      uint32_t pk[2][32];
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4)
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = ptx::ex2_approx(fmaf(__uint_as_float(sraw[q4][i]), p.scale_log2, neg_m));
+          const float p1 = ptx::ex2_approx(fmaf(__uint_as_float(sraw[q4][i + 1]), p.scale_log2, neg_m));
+          sum += p0 + p1;
+          pk[q4 >> 1][(q4 & 1) * 16 + (i >> 1)] = PackT<T>::pack(p0, p1);
+        }
+      l_run = l_run * alpha + sum;
+      ptx::tmem_st32(trow + s_col, pk[0]);
+      ptx::tmem_st32(trow + s_col + 32, pk[1]);
+      // O may only be touched once PV(j-1) has drained; waiting every tile keeps the phase
+      // bookkeeping trivial and is off the critical path (PV(j) queues behind QK(j+1) anyway).
+      if (j > 0) {
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(bar_pv, (j - 1) & 1))) { record(p.status, kErrPvDone); ok = false; }
+        ptx::tc_fence_after();
+        if (ok && __any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+          for (int c8 = 0; c8 < 8; ++c8) {
+            uint32_t ov[32];
+            ptx::tmem_ld32(trow + kColO + c8 * 32, ov);
+            ptx::tc_wait_ld();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+            ptx::tmem_st32(trow + kColO + c8 * 32, ov);
+          }
+        }
+      }
+      ptx::tc_wait_st();
+      ptx::tc_fence_before();
+      ptx::mbar_arrive(ptx::smem_u32(&bars->p_full[j & 1]));
+    }
+
+    // ---- epilogue: O / l -> global ----
+    if (ok) {
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(bar_pv, (n_tiles - 1) & 1))) { record(p.status, kErrPvDone); ok = false; }
+      ptx::tc_fence_after();
+    }
+    if (ok) {
+      const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
+      const bool row_ok = r < rows_valid;
+      const int64_t off = b * p.o_s0 + h * p.o_s1 + (int64_t)(m0 + r) * p.o_s2;
+#pragma unroll 1
+      for (int c8 = 0; c8 < 8; ++c8) {
+        uint32_t ov[32];
+        ptx::tmem_ld32(trow + kColO + c8 * 32, ov);
+        ptx::tc_wait_ld();
+        if (row_ok) {
+          if (p.o_dtype == G4B_F32) {
+            float4* dst = reinterpret_cast<float4*>((float*)p.o + off + c8 * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i)
+              dst[i] = make_float4(__uint_as_float(ov[4 * i]) * inv_l, __uint_as_float(ov[4 * i + 1]) * inv_l,
+                                   __uint_as_float(ov[4 * i + 2]) * inv_l, __uint_as_float(ov[4 * i + 3]) * inv_l);
+          } else {
+            uint4* dst = reinterpret_cast<uint4*>((T*)p.o + off + c8 * 32);
+#pragma unroll
+            for (int i = 0; i < 4; ++i) {
+              uint4 w;
+              w.x = PackT<T>::pack(__uint_as_float(ov[8 * i + 0]) * inv_l, __uint_as_float(ov[8 * i + 1]) * inv_l);
+              w.y = PackT<T>::pack(__uint_as_float(ov[8 * i + 2]) * inv_l, __uint_as_float(ov[8 * i + 3]) * inv_l);
+              w.z = PackT<T>::pack(__uint_as_float(ov[8 * i + 4]) * inv_l, __uint_as_float(ov[8 * i + 5]) * inv_l);
+              w.w = PackT<T>::pack(__uint_as_float(ov[8 * i + 6]) * inv_l, __uint_as_float(ov[8 * i + 7]) * inv_l);
+              dst[i] = w;
+            }
+          }
+        }
+      }
+    }
+  }
+
+  // ---- teardown: every thread arrives here, on success and after a failed wait ----
+  ptx::tc_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    ptx::tc_fence_after();
+    ptx::tmem_dealloc(tmem, 512);
+  }
+}
+
+// ---------------------------------------------------------------------------------------
+// host side: tensor maps + launch
+// ---------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  if (fn == nullptr) {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = (EncodeTiledFn)ptr;
+  }
+  return fn;
+}
+
+static int encode_map(CUtensorMap* map, int dtype, int rank, void* base, const uint64_t* dims,
+                      const uint64_t* strides_bytes, const uint32_t* box, const char* what) {
+  EncodeTiledFn fn = encode_fn();
+  if (fn == nullptr) return fail(G4B_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
+  cuuint64_t gdim[5]; cuuint64_t gstr[4]; cuuint32_t bx[5]; cuuint32_t es[5];
+  for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
+  for (int i = 0; i < rank - 1; ++i) gstr[i] = strides_bytes[i];
+  const CUtensorMapDataType dt = dtype == G4B_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  CUresult r = fn(map, dt, (cuuint32_t)rank, base, gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r != CUDA_SUCCESS) return fail(G4B_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
+  return G4B_OK;
+}
+
+template <typename T>
+static int launch_typed(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const PrefillParams& p,
+                        dim3 grid, cudaStream_t st) {
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  G4B_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    G4B_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    attr_set[dev] = true;
+  }
+  prefill_kernel<T><<<grid, kThreads, kSmemBytes, st>>>(qm, km, vm, p);
+  G4B_CUDA_CHECK(cudaGetLastError());
+  return G4B_OK;
+}
+
+}  // namespace
+
+int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
+  if (a.block_tables.ptr != nullptr)
+    return fail(G4B_ERR_UNSUPPORTED, "prefill over a paged cache is not built yet; use the ring layout");
+  if (a.q.dtype != a.k_cache.dtype)
+    return fail(G4B_ERR_BAD_DTYPE, "prefill: q must have the cache dtype (f16 or bf16)");
+  if (a.o.dtype != a.q.dtype && a.o.dtype != G4B_F32)
+    return fail(G4B_ERR_BAD_DTYPE, "prefill: o must have the q dtype or be f32");
+  const int64_t B = a.q.shape[0], H = a.q.shape[1], Tq = a.q.shape[2], D = a.q.shape[3];
+  const int64_t G = a.k_cache.shape[1], T = a.k_cache.shape[2];
+  if (B == 0 || Tq == 0) return G4B_OK;
+  const int esz = 2;
+  for (int i = 0; i < 3; ++i) {
+    if ((a.q.stride[i] * esz) % 16 != 0) return fail(G4B_ERR_BAD_STRIDE, "prefill: q strides must be multiples of 16 bytes");
+  }
+  if (((uintptr_t)a.q.ptr) & 15) return fail(G4B_ERR_BAD_STRIDE, "prefill: q must be 16-byte aligned");
+  const int osz = dtype_size(a.o.dtype);
+  for (int i = 0; i < 3; ++i)
+    if ((a.o.stride[i] * osz) % 16 != 0) return fail(G4B_ERR_BAD_STRIDE, "prefill: o strides must be multiples of 16 bytes");
+  if (((uintptr_t)a.o.ptr) & 15) return fail(G4B_ERR_BAD_STRIDE, "prefill: o must be 16-byte aligned");
+  const int64_t n_q_tiles = (Tq + kBM - 1) / kBM;
+  if (B * H > 0x7fffffffLL || n_q_tiles > 65535) return fail(G4B_ERR_UNSUPPORTED, "prefill: grid too large");
+
+  CUtensorMap qm, km, vm;
+  int rc;
+  {
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)Tq, (uint64_t)H, (uint64_t)B};
+    const uint64_t strides[3] = {(uint64_t)a.q.stride[2] * esz, (uint64_t)a.q.stride[1] * esz, (uint64_t)a.q.stride[0] * esz};
+    const uint32_t box[4] = {64, (uint32_t)kBM, 1, 1};
+    if ((rc = encode_map(&qm, a.q.dtype, 4, a.q.ptr, dims, strides, box, "q"))) return rc;
+  }
+  {
+    const uint64_t dims[3] = {(uint64_t)D, (uint64_t)T, (uint64_t)(B * G)};
+    const uint64_t strides[2] = {(uint64_t)D * esz, (uint64_t)T * D * esz};
+    const uint32_t boxk[3] = {64, (uint32_t)kBN, 1};
+    const uint32_t boxv[3] = {64, 64, 1};
+    if ((rc = encode_map(&km, a.k_cache.dtype, 3, a.k_cache.ptr, dims, strides, boxk, "k_cache"))) return rc;
+    if ((rc = encode_map(&vm, a.v_cache.dtype, 3, a.v_cache.ptr, dims, strides, boxv, "v_cache"))) return rc;
+  }
+  PrefillParams p{};
+  p.o = a.o.ptr; p.k = a.k_cache.ptr; p.v = a.v_cache.ptr;
+  p.time_dim_sizes = (const int32_t*)a.time_dim_sizes.ptr;
+  p.user_phase = (const uint8_t*)a.user_phase.ptr;
+  p.o_s0 = a.o.stride[0]; p.o_s1 = a.o.stride[1]; p.o_s2 = a.o.stride[2];
+  p.time_stride = a.time_dim_sizes.stride[0]; p.phase_stride = a.user_phase.stride[0];
+  p.B = (int)B; p.H = (int)H; p.G = (int)G; p.Tq = (int)Tq; p.T = (int)T;
+  p.ctx_window = a.ctx_window_size; p.sliding_window = a.sliding_window; p.phase = a.phase;
+  p.causal = a.stage == G4B_STAGE_CAUSAL;
+  p.o_dtype = a.o.dtype;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.status = device_status_ptr();
+  if (p.status == nullptr) return G4B_ERR_CUDA;
+  dim3 grid((unsigned)(B * H), (unsigned)n_q_tiles, 1);
+  if (a.q.dtype == G4B_BF16) return launch_typed<__nv_bfloat16>(qm, km, vm, p, grid, st);
+  return launch_typed<__half>(qm, km, vm, p, grid, st);
+}
+
+}  // namespace g4b

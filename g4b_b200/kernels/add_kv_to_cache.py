@@ -1,0 +1,41 @@
+"""add_kv_to_cache: the reference's call signature (g4b/kernels/add_kv_to_cache.py:162-170)
+over the CUDA library, plus the paged destination."""
+from __future__ import annotations
+
+import ctypes
+
+from g4b_b200 import _cabi
+
+
+def add_kv_to_cache(
+    x,
+    cache,
+    cache_offsets,
+    rmsnorm_eps: float,
+    x_rsos=None,
+    user_phase=None,
+    phase: int = 0,
+    *,
+    block_tables=None,
+    page_size: int = 16,
+    stream=None,
+):
+    """``cache[b, g, (cache_offsets[b] + t) % T, :] = x[b, g, t, :]`` cast to the cache dtype,
+    times ``rsqrt(x_rsos[b,g,t] / D + rmsnorm_eps)`` when ``x_rsos`` is given
+    (add_kv_to_cache.py:148-158).  With ``block_tables [B,max_pages]`` the cache is a page pool
+    ``[num_pages,G,page_size,D]`` and token ``p = cache_offsets[b] + t`` goes to page
+    ``block_tables[b, p // page_size]``, row ``p % page_size``.  Slots whose ``user_phase``
+    differs from ``phase`` are skipped.  Returns None."""
+    assert isinstance(phase, int)
+    a = _cabi.G4bAppendArgs()
+    a.x = _cabi.as_tensor(x)
+    a.cache = _cabi.as_tensor(cache)
+    a.cache_offsets = _cabi.as_tensor(cache_offsets)
+    a.x_rsos = _cabi.as_tensor(x_rsos)
+    a.user_phase = _cabi.as_tensor(user_phase)
+    a.block_tables = _cabi.as_tensor(block_tables)
+    a.rmsnorm_eps = float(rmsnorm_eps)
+    a.phase = int(phase)
+    a.page_size = int(page_size)
+    _cabi.check(_cabi.load().g4b_kv_append(ctypes.byref(a), ctypes.c_void_p(_cabi.current_stream(stream))))
+    return None

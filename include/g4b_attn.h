@@ -1,0 +1,187 @@
+/*
+ * g4b_attn.h -- C ABI of libg4b_attn.so: the attention hot path of the g4b Gemma
+ * inference engine (flash-attention prefill, paged / ring KV-cache append, single-token
+ * split-KV decode with log-sum-exp combine) as hand-written CUDA for sm_100a.
+ *
+ * Every entry point takes plain structs of pointers, sizes and element strides, launches
+ * on the stream it is given, allocates nothing on the device, never synchronises the
+ * host, never aborts, and returns 0 or a negative G4B_ERR_* code. The message for the
+ * last failure on the calling thread is available from g4b_last_error_string().
+ *
+ * Each declaration cites the interface of the reference (barnii77/g4b) that it replaces.
+ */
+#ifndef G4B_ATTN_H_
+#define G4B_ATTN_H_
+
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define G4B_ABI_VERSION 1
+
+/* element types (g4b/tensor.py dtypes that reach this path) */
+enum G4bDtype {
+  G4B_F32 = 0,
+  G4B_F16 = 1,
+  G4B_BF16 = 2,
+  G4B_I32 = 3,
+  G4B_I64 = 4,
+  G4B_U8 = 5
+};
+
+/* per-slot phase encoding, g4b/kernels/fa2.py:26-31 */
+enum G4bPhase { G4B_PHASE_UNALLOCATED = 0, G4B_PHASE_PREFILL = 1, G4B_PHASE_DECODE = 2 };
+
+/* masking stage, g4b/kernels/fa2.py:14-16 */
+enum G4bStage { G4B_STAGE_FULL = 1, G4B_STAGE_CAUSAL = 3 };
+
+enum G4bStatus {
+  G4B_OK = 0,
+  G4B_ERR_BAD_ARG = -1,      /* null pointer, bad rank, inconsistent shapes            */
+  G4B_ERR_BAD_DTYPE = -2,    /* dtype combination no kernel is built for               */
+  G4B_ERR_BAD_STRIDE = -3,   /* innermost stride != 1, non-contiguous cache, alignment */
+  G4B_ERR_UNSUPPORTED = -4,  /* shape outside what the kernels cover (e.g. head dim)   */
+  G4B_ERR_CUDA = -5,         /* a CUDA runtime / driver call failed                    */
+  G4B_ERR_DEVICE_WAIT = -6,  /* a bounded in-kernel wait ran out (see g4b_device_status) */
+  G4B_ERR_TOO_LARGE = -7     /* size beyond a stated fixed maximum                     */
+};
+
+/*
+ * A strided view, the C form of what g4b/kernels/utils.py:113-122 unpacks from any
+ * object with .shape/.stride/.dtype/.data_ptr(): base pointer, shape and strides in
+ * ELEMENTS, rank <= 5.  ptr == NULL means "argument not given".
+ */
+typedef struct G4bTensor {
+  void* ptr;
+  int64_t shape[5];
+  int64_t stride[5];
+  int32_t ndim;
+  int32_t dtype; /* enum G4bDtype */
+} G4bTensor;
+
+/*
+ * Arguments of one attention call; the C form of
+ *   flash_attention(q, k_cache, v_cache, o, time_dim_sizes, user_phase, ctx_window_size,
+ *                   phase, partial_o, partial_l, partial_m, *, stage)
+ * (g4b/kernels/fa2.py:634-652).
+ *
+ *  q, o          [B, H, Tq, D] views, last stride 1 (fa2.py:312-314)
+ *  ring mode     k_cache, v_cache [B, G, T, D] contiguous (fa2.py:315-320); logical key j
+ *                of slot b lives in row (ring_start + j) % T (fa2.py:52-55,75)
+ *  paged mode    block_tables.ptr != NULL: k_cache, v_cache are page pools
+ *                [num_pages, G, page_size, D] contiguous, block_tables int32 [B, max_pages];
+ *                logical key j lives in page block_tables[b, j / page_size], row
+ *                j % page_size (not in the reference, which has a ring buffer only)
+ *  time_dim_sizes int32 [B]: context length of slot b including this step's tokens
+ *  user_phase    uint8 [B] or absent: slot b is skipped unless user_phase[b] == phase
+ *                (fa2.py:333-335)
+ *  ctx_window_size  number of most recent keys the cache exposes (fa2.py:53-54)
+ *  sliding_window   0, or W: query at absolute position p also ignores keys at positions
+ *                <= p - W (scripts/reference_impl.py:440-441).  0 keeps the reference
+ *                kernel's chunk-shared lower bound only (fa2.py:58-64).
+ *  scale         multiplies q.k before the softmax; the reference uses 1.0 (fa2.py:89)
+ *  partial_*     split-KV workspace [S, B, H, Tq, D] / [S, B, H, Tq] (fa2.py:438-472);
+ *                partial_o f32/f16/bf16, partial_l and partial_m f32, m in log2 units
+ *  num_kv_splits 0 = the reference's static policy (fa2.py:201-212), else forced
+ */
+typedef struct G4bAttnArgs {
+  G4bTensor q, k_cache, v_cache, o;
+  G4bTensor time_dim_sizes, user_phase;
+  G4bTensor partial_o, partial_l, partial_m;
+  G4bTensor block_tables;
+  int32_t ctx_window_size;
+  int32_t phase;
+  int32_t stage;
+  int32_t page_size;
+  int32_t sliding_window;
+  int32_t num_kv_splits;
+  float scale;
+  int32_t reserved;
+} G4bAttnArgs;
+
+/* replaces flash_attention() as a whole (fa2.py:634-715): picks the prefill or the
+ * decode kernel, the split count, and runs the combine when splits > 1. */
+int g4b_flash_attention(const G4bAttnArgs* args, void* cuda_stream);
+
+/* replaces the launch of _attn_kernel for Tq > 1 (fa2.py:256-480, 672-690):
+ * tcgen05 / TMEM / TMA flash-attention forward, head dim 256, f16 or bf16. */
+int g4b_attn_prefill(const G4bAttnArgs* args, void* cuda_stream);
+
+/* replaces the launch of _attn_kernel for Tq == 1 (fa2.py:256-480 with
+ * NUM_KV_SPLITS >= 1): streams K/V once from HBM; writes o when the split count is 1,
+ * else un-normalised partials (fa2.py:438-472) and leaves the merge to the caller. */
+int g4b_attn_decode(const G4bAttnArgs* args, void* cuda_stream);
+
+/* replaces _reduce_split_kv_kernel (fa2.py:546-631): log-sum-exp merge of the first
+ * num_splits partials into o.  Also merges partials gathered from other GPUs. */
+typedef struct G4bCombineArgs {
+  G4bTensor partial_o, partial_l, partial_m, o;
+  G4bTensor user_phase; /* optional uint8 [B]: rows of slots with user_phase[b] != phase keep o */
+  int32_t num_splits;
+  int32_t phase;
+} G4bCombineArgs;
+int g4b_attn_combine(const G4bCombineArgs* args, void* cuda_stream);
+
+/* The split count g4b_flash_attention would use; the reference's policy in
+ * _prune_invalid_configs (fa2.py:186-225). */
+int g4b_select_kv_splits(int ctx_window_size, int max_kv_splits, int phase, int tq);
+
+/*
+ * replaces add_kv_to_cache(x, cache, cache_offsets, rmsnorm_eps, x_rsos, user_phase,
+ * phase) (g4b/kernels/add_kv_to_cache.py:162-186):
+ *   cache[b, g, (cache_offsets[b] + t) % T, :] = cast(x[b, g, t, :] * r)
+ * with r = rsqrt(x_rsos[b,g,t] / D + eps) when x_rsos is given, else 1
+ * (add_kv_to_cache.py:148-158).  Paged mode (block_tables given): row cache_offsets[b]+t
+ * of the sequence goes to page block_tables[b, p / page_size], row p % page_size.
+ * cache_offsets may be int32 or int64.  Slots with user_phase[b] != phase are skipped.
+ */
+typedef struct G4bAppendArgs {
+  G4bTensor x;             /* [B, G, Tq, D] view, last stride 1; f32, f16 or bf16 */
+  G4bTensor cache;         /* ring [B, G, T, D] or pool [num_pages, G, page_size, D] */
+  G4bTensor cache_offsets; /* [B] int32 or int64 */
+  G4bTensor x_rsos;        /* optional [B, G, Tq] f32 view */
+  G4bTensor user_phase;    /* optional uint8 [B] */
+  G4bTensor block_tables;  /* optional int32 [B, max_pages] */
+  float rmsnorm_eps;
+  int32_t phase;
+  int32_t page_size;
+  int32_t reserved;
+} G4bAppendArgs;
+int g4b_kv_append(const G4bAppendArgs* args, void* cuda_stream);
+
+/*
+ * replaces advance_decode_state(input_token_ids, out_token_ids, cache_offsets,
+ * time_dim_sizes, user_phase) (g4b/kernels/advance_decode_state.py:31-80): for every slot
+ * in the decode phase, input_token_ids[0,b] = out_token_ids[b,0], cache_offsets[b] += 1,
+ * time_dim_sizes[b] += 1.
+ */
+typedef struct G4bAdvanceArgs {
+  G4bTensor input_token_ids; /* int32 [>=1, B] */
+  G4bTensor out_token_ids;   /* int32 [B, >=1] */
+  G4bTensor cache_offsets;   /* int32 [B] */
+  G4bTensor time_dim_sizes;  /* int32 [B] */
+  G4bTensor user_phase;      /* uint8 [B] */
+} G4bAdvanceArgs;
+int g4b_advance_decode_state(const G4bAdvanceArgs* args, void* cuda_stream);
+
+/* Message of the last failing call on this thread ("" if none). No reference counterpart:
+ * the reference raises Python exceptions from its wrappers (fa2.py:656-657). */
+const char* g4b_last_error_string(void);
+
+/* ABI version of the loaded library (G4B_ABI_VERSION). */
+int g4b_abi_version(void);
+
+/*
+ * Reads (and clears) the device-side status word of the current device after
+ * synchronising the given stream: 0, or a code naming the bounded wait that gave up
+ * inside a kernel.  Kernels never trap; a wait that runs out makes the kernel return
+ * early and record its position here.  No reference counterpart.
+ */
+int g4b_device_status(void* cuda_stream, int32_t* status_out);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* G4B_ATTN_H_ */

@@ -1,0 +1,178 @@
+"""Flash-attention prefill (tcgen05 kernel) on the GPU, through the C ABI, against the oracle
+and the reference-generated golden fixtures.  Tolerance: |a-b| <= 2e-3 + 1e-2 |b|."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from g4b_b200.kernels import fa2
+from g4b_b200.kernels.add_kv_to_cache import add_kv_to_cache
+from helpers import assert_close, make_ring_case, orc, randn
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+
+
+def run(case, cuda, *, scale=1 / 16, stage=fa2.STAGE_CAUSAL, sliding_window=None, phase_t=None,
+        o_dtype=None, o_init=None, phase=fa2.PHASE_PREFILL):
+    q_phys, k, v, time = (case[n].to(cuda) for n in ("q_phys", "k", "v", "time"))
+    B, Tq, H, D = q_phys.shape
+    o_phys = (torch.zeros(B, Tq, H, D, dtype=o_dtype or q_phys.dtype, device=cuda)
+              if o_init is None else o_init.to(cuda))
+    ph = None if phase_t is None else phase_t.to(cuda)
+    fa2.flash_attention(q_phys.permute(0, 2, 1, 3), k, v, o_phys.permute(0, 2, 1, 3), time, ph,
+                        case["ctx_window"], phase, stage=stage, scale=scale, sliding_window=sliding_window)
+    return o_phys.permute(0, 2, 1, 3).cpu()
+
+
+def oracle(case, *, scale=1 / 16, stage=fa2.STAGE_CAUSAL, sliding_window=None, phase_t=None, o_init=None,
+           phase=fa2.PHASE_PREFILL):
+    o0 = torch.zeros_like(case["q"], dtype=torch.float32) if o_init is None else o_init.permute(0, 2, 1, 3)
+    return orc.flash_attention(case["q"], case["k"], case["v"], o0, case["time"], phase_t, case["ctx_window"],
+                               phase, stage=stage, scale=scale, sliding_window=sliding_window)
+
+
+@pytest.mark.parametrize("name", ["prefill_causal", "prefill_causal_unscaled", "prefill_swa", "prefill_chunked"])
+def test_prefill_matches_reference_golden(cuda, name):
+    """The committed outputs of the reference's LayerKVCache, reproduced by append + attention
+    on the GPU (fp16; the fixture inputs are fp16-exact)."""
+    z = np.load(GOLD / f"{name}.npz")
+    q = torch.from_numpy(z["q"])          # [H,Tq,D] fp16
+    k_all, v_all = torch.from_numpy(z["k_all"]), torch.from_numpy(z["v_all"])
+    H, Tq, D = q.shape
+    G, n_all, _ = k_all.shape
+    is_swa, window = bool(z["is_swa"]), int(z["window"])
+    T = 64
+    k_cache = torch.zeros(1, G, T, D, dtype=torch.float16, device=cuda)
+    v_cache = torch.zeros_like(k_cache)
+    off = torch.zeros(1, dtype=torch.int32, device=cuda)
+    add_kv_to_cache(k_all[None].to(cuda), k_cache, off, 1e-6)
+    add_kv_to_cache(v_all[None].to(cuda), v_cache, off, 1e-6)
+    o = torch.zeros(1, H, Tq, D, dtype=torch.float16, device=cuda)
+    time = torch.tensor([n_all], dtype=torch.int32, device=cuda)
+    ctx_window = min(T, window + Tq - 1) if is_swa else T
+    fa2.flash_attention(q[None].to(cuda), k_cache, v_cache, o, time, None, ctx_window, 1,
+                        scale=float(z["scale"]), sliding_window=window if is_swa else None)
+    assert_close(o[0].cpu(), torch.from_numpy(z["out"]), name)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H,G,Tq,T", [(2, 8, 2, 256, 1024), (1, 16, 4, 128, 512), (2, 4, 2, 200, 333)])
+def test_prefill_chunk_over_ring_cache(cuda, dtype, B, H, G, Tq, T):
+    """A prefill chunk attending to a longer (for odd slots: wrapped) ring cache --
+    tests/compare_scripts/test_fa2.py:61-64 scaled down, incl. a ragged Tq and an odd T."""
+    case = make_ring_case(40, B=B, H=H, G=G, Tq=Tq, T=T, dtype=dtype,
+                          times=[T if b % 2 == 0 else T + 17 for b in range(B)])
+    assert_close(run(case, cuda), oracle(case), "prefill over ring")
+
+
+def test_prefill_reference_scale(cuda):
+    case = make_ring_case(41, B=1, H=8, G=2, Tq=256, T=256, dtype=torch.float16)
+    assert_close(run(case, cuda, scale=1.0), oracle(case, scale=1.0), "prefill scale 1")
+
+
+@pytest.mark.parametrize("Tq", [1, 37, 128, 129, 640])
+def test_prefill_fresh_causal_lengths(cuda, Tq):
+    """Whole-prompt prefill into an empty cache (time == Tq), ragged lengths incl. Tq == 1 run
+    through the prefill kernel."""
+    case = make_ring_case(42, B=2, H=8, G=2, Tq=Tq, T=640, dtype=torch.bfloat16, times=[Tq, Tq])
+    q_phys, k, v, time = (case[n].to(cuda) for n in ("q_phys", "k", "v", "time"))
+    o_phys = torch.zeros_like(q_phys)
+    import ctypes
+    from g4b_b200 import _cabi
+    a = fa2._attn_args(q_phys.permute(0, 2, 1, 3), k, v, o_phys.permute(0, 2, 1, 3), time, None, 640, 1,
+                       None, None, None, fa2.STAGE_CAUSAL, 1 / 16, None, None, 16, None)
+    _cabi.check(_cabi.load().g4b_attn_prefill(ctypes.byref(a), ctypes.c_void_p(_cabi.current_stream())))
+    assert_close(o_phys.permute(0, 2, 1, 3).cpu(), oracle(case), f"fresh prefill Tq={Tq}")
+
+
+@pytest.mark.parametrize("Tq,W", [(1024, 128), (1024, 100), (700, 512), (384, 1)])
+def test_prefill_sliding_window_per_query(cuda, Tq, W):
+    """Per-query window (scripts/reference_impl.py:440-441): key visible iff 0 <= q_pos - k_pos < W."""
+    case = make_ring_case(43, B=2, H=8, G=2, Tq=Tq, T=Tq, dtype=torch.bfloat16, times=[Tq, Tq])
+    assert_close(run(case, cuda, sliding_window=W), oracle(case, sliding_window=W), f"swa W={W}")
+
+
+def test_prefill_chunk_shared_window(cuda):
+    """The reference kernel's own SWA form: the cache exposes W + t - 1 keys and every query
+    of the chunk sees back to the first of them (fa2.py:52-67)."""
+    Tq, W, T = 128, 256, 512
+    case = make_ring_case(44, B=2, H=8, G=2, Tq=Tq, T=T, dtype=torch.float16, ctx_window=W + Tq - 1,
+                          times=[W + Tq - 1, 2000])
+    assert_close(run(case, cuda), oracle(case), "chunk-shared window")
+
+
+def test_prefill_stage_full(cuda):
+    # test_fa2.py:78: non-causal, Tq == Tcache == window
+    case = make_ring_case(45, B=2, H=16, G=4, Tq=256, T=256, dtype=torch.float16, times=[256, 256])
+    assert_close(run(case, cuda, stage=fa2.STAGE_FULL), oracle(case, stage=fa2.STAGE_FULL), "stage full")
+
+
+def test_prefill_skips_slots_off_phase_and_f32_output(cuda):
+    case = make_ring_case(46, B=3, H=8, G=2, Tq=128, T=256, dtype=torch.bfloat16, times=[256, 200, 128])
+    phase_t = torch.tensor([1, 2, 1], dtype=torch.uint8)
+    gen = torch.Generator().manual_seed(2)
+    o_init = randn(gen, 3, 128, 8, 256)
+    got = run(case, cuda, phase_t=phase_t, o_init=o_init)
+    want = oracle(case, phase_t=phase_t, o_init=o_init)
+    assert_close(got, want, "phase skip + f32 o", abs_tol=1e-3)
+    assert torch.equal(got[1], o_init.permute(0, 2, 1, 3)[1])
+
+
+def test_prefill_window_tail_rows_may_hold_garbage(cuda):
+    """Cache rows past the context are never multiplied in: fill them with NaN."""
+    case = make_ring_case(47, B=1, H=8, G=2, Tq=100, T=512, dtype=torch.bfloat16, times=[300])
+    case["k"][:, :, 300:] = float("nan")
+    case["v"][:, :, 300:] = float("nan")
+    got = run(case, cuda)
+    case["k"][:, :, 300:] = 0
+    case["v"][:, :, 300:] = 0
+    assert_close(got, oracle(case), "garbage tail")
+
+
+def test_prefill_full_size_rows(cuda):
+    """Benchmark shape (B4 S8192 H8 G2 D256 bf16, causal, scale 1/16): sampled rows against
+    the oracle, and invariance of every row to what lies after it in the cache."""
+    gen = torch.Generator().manual_seed(48)
+    B, S, H, G, D = 4, 8192, 8, 2, 256
+    q_phys = randn(gen, B, S, H, D, dtype=torch.bfloat16)
+    k = randn(gen, B, G, S, D, dtype=torch.bfloat16)
+    v = randn(gen, B, G, S, D, dtype=torch.bfloat16)
+    time = torch.full((B,), S, dtype=torch.int32)
+    qd, kd, vd = q_phys.to(cuda), k.to(cuda), v.to(cuda)
+    o = torch.zeros_like(qd)
+    fa2.flash_attention(qd.permute(0, 2, 1, 3), kd, vd, o.permute(0, 2, 1, 3), time.to(cuda), None, S, 1, scale=1 / 16)
+    got = o.permute(0, 2, 1, 3).cpu()
+    rows = [0, 1, 127, 128, 129, 4095, 4096, 5000, 8190, 8191]
+    for b in range(B):
+        for r in rows:
+            want = orc.attention_core(q_phys[b, r:r + 1].permute(1, 0, 2), k[b, :, :r + 1], v[b, :, :r + 1], scale=1 / 16)
+            assert_close(got[b, :, r:r + 1], want, f"b={b} row={r}")
+    # causality: scrambling keys after position 4096 leaves rows <= 4096 bit-identical
+    kd[:, :, 4097:] = torch.flip(kd[:, :, 4097:], dims=[2])
+    vd[:, :, 4097:] = -vd[:, :, 4097:]
+    o2 = torch.zeros_like(qd)
+    fa2.flash_attention(qd.permute(0, 2, 1, 3), kd, vd, o2.permute(0, 2, 1, 3), time.to(cuda), None, S, 1, scale=1 / 16)
+    assert torch.equal(o2[:, :4097], o[:, :4097])
+    assert not torch.equal(o2[:, 4097:], o[:, 4097:])
+
+
+def test_prefill_sliding_window_full_size_rows(cuda):
+    """Config shape B2 S32768 W512: sampled rows, each against its own 512-key window."""
+    gen = torch.Generator().manual_seed(49)
+    B, S, H, G, D, W = 2, 32768, 8, 2, 256, 512
+    q_phys = randn(gen, B, S, H, D, dtype=torch.bfloat16)
+    k = randn(gen, B, G, S, D, dtype=torch.bfloat16)
+    v = randn(gen, B, G, S, D, dtype=torch.bfloat16)
+    time = torch.full((B,), S, dtype=torch.int32)
+    qd = q_phys.to(cuda)
+    o = torch.zeros_like(qd)
+    fa2.flash_attention(qd.permute(0, 2, 1, 3), k.to(cuda), v.to(cuda), o.permute(0, 2, 1, 3), time.to(cuda), None,
+                        S, 1, scale=1 / 16, sliding_window=W)
+    got = o.permute(0, 2, 1, 3).cpu()
+    for b in range(B):
+        for r in [0, 5, 511, 512, 513, 1000, 16384, 32767]:
+            lo = max(0, r - W + 1)
+            want = orc.attention_core(q_phys[b, r:r + 1].permute(1, 0, 2), k[b, :, lo:r + 1], v[b, :, lo:r + 1], scale=1 / 16)
+            assert_close(got[b, :, r:r + 1], want, f"b={b} row={r}")
