@@ -1,0 +1,519 @@
+"""Benchmark of the attention hot path on synthetic inputs of the reference's headline shapes.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
+
+Prints ONE JSON line.  Workloads (shapes of the five benchmark configurations):
+    prefill_causal  B4 S8192 H8 G2 D256 bf16, causal, scale 1/16          (default)
+    prefill_swa     B2 S32768 W512, per-query sliding window
+    decode_paged    256 sequences, ctx ~ U[1024,32768], fp16 KV in shuffled 16-token pages,
+                    one step = append the new token's K/V + attention
+    decode_long     1 sequence of 131072 tokens, bf16 paged KV; with N > 1 the KV range is
+                    split across GPUs and the (acc, l, m) partials are all-gathered by NCCL
+A step is one pass of the hot path over one batch.  ``value`` has inputs resident in HBM;
+``e2e`` goes through the public Python operators with pinned host buffers, host<->device
+copies inside the timed region.  With N > 1 every rank runs the same per-GPU batch (weak
+scaling; requests, heads and sequences are independent) except decode_long, which splits one
+sequence (strong scaling).  ``--impl reference`` times the CPU oracle (a port of the
+reference's torch attention) on the host cores on a bounded sample of the same workload.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch  # noqa: E402
+
+H, G, D, PAGE = 8, 2, 256, 16
+SCALE = 1.0 / 16.0
+
+
+# ------------------------------------------------------------------------------------------
+# helpers
+# ------------------------------------------------------------------------------------------
+def measured_peaks():
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        d = json.loads(p.read_text())
+        return dict(hbm=float(d["hbm_gbs"]), tensor=float(d["bf16_tflops"]),
+                    tensor_sustained=float(d.get("bf16_tflops_sustained", d["bf16_tflops"])), source="measured")
+    return dict(hbm=6650.0, tensor=1590.0, tensor_sustained=1400.0, source="fallback")
+
+
+class ClockSampler:
+    """Polls SM clock and throttle reasons through NVML while the timed region runs."""
+
+    def __init__(self, index: int):
+        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self._stop = threading.Event()
+        self._thread = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            self._h = pynvml.nvmlDeviceGetHandleByIndex(index)
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(self._h, pynvml.NVML_CLOCK_SM))
+        except Exception:  # NVML missing: report no clocks rather than fail the bench
+            self._nv = None
+
+    def _run(self):
+        nv = self._nv
+        names = {
+            "hw_slowdown": getattr(nv, "nvmlClocksEventReasonHwSlowdown", 0x8),
+            "hw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonHwThermalSlowdown", 0x40),
+            "sw_thermal_slowdown": getattr(nv, "nvmlClocksEventReasonSwThermalSlowdown", 0x20),
+            "sw_power_cap": getattr(nv, "nvmlClocksEventReasonSwPowerCap", 0x4),
+        }
+        while not self._stop.is_set():
+            try:
+                self.samples.append(int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM)))
+                try:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksEventReasons(self._h))
+                except Exception:
+                    mask = int(nv.nvmlDeviceGetCurrentClocksThrottleReasons(self._h))
+                for k, bit in names.items():
+                    if mask & bit:
+                        self.reasons.add(k)
+            except Exception:
+                pass
+            time.sleep(0.004)
+
+    def start(self):
+        if self._nv is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join()
+        s = sorted(self.samples)
+        return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
+                "reasons": sorted(self.reasons), "samples": len(s)}
+
+
+def dist_env():
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    return rank, world, local
+
+
+def barrier_sync(world):
+    if world > 1:
+        torch.distributed.barrier()
+    torch.cuda.synchronize()
+
+
+def max_over_ranks(ms: float, world: int, dev) -> float:
+    if world == 1:
+        return ms
+    t = torch.tensor([ms], dtype=torch.float64, device=dev)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
+    return float(t.item())
+
+
+def timed_region(step_fn, steps, warmup, world, dev, sampler=None):
+    """W warm-up steps, then exactly K steps between CUDA events on the launching stream,
+    bracketed by barrier + synchronize; returns the max over ranks in ms."""
+    for _ in range(warmup):
+        step_fn()
+    barrier_sync(world)
+    if sampler is not None:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(steps):
+        step_fn()
+    e1.record()
+    barrier_sync(world)
+    ms = e0.elapsed_time(e1)
+    return max_over_ranks(ms, world, dev)
+
+
+# ------------------------------------------------------------------------------------------
+# workloads
+# ------------------------------------------------------------------------------------------
+def prefill_flops(B, S, window=None):
+    if window is None:
+        pairs = S * (S + 1) // 2
+    else:
+        pairs = window * (window + 1) // 2 + (S - window) * window
+    return 4.0 * B * H * D * pairs
+
+
+class PrefillWorkload:
+    """Configs 2 and 3: q [B,S,H,D] physical (passed as the [B,H,S,D] view), caches [B,G,S,D]."""
+
+    def __init__(self, name, dev, seed):
+        from g4b_b200.kernels import fa2
+
+        self.fa2 = fa2
+        self.name = name
+        self.B, self.S, self.window = (4, 8192, None) if name == "prefill_causal" else (2, 32768, 512)
+        self.dtype = torch.bfloat16
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        B, S = self.B, self.S
+        # pinned host copies: source of the e2e leg's per-step uploads
+        self.h_q = torch.randn(B, S, H, D, generator=gen).to(self.dtype).pin_memory()
+        self.h_k = torch.randn(B, G, S, D, generator=gen).to(self.dtype).pin_memory()
+        self.h_v = torch.randn(B, G, S, D, generator=gen).to(self.dtype).pin_memory()
+        self.h_o = torch.empty(B, S, H, D, dtype=self.dtype).pin_memory()
+        self.q, self.k, self.v = self.h_q.to(dev), self.h_k.to(dev), self.h_v.to(dev)
+        self.o = torch.empty_like(self.q)
+        self.time = torch.full((B,), S, dtype=torch.int32, device=dev)
+        self.units = prefill_flops(B, S, self.window)          # FLOPs per step
+        self.metric, self.unit, self.bound = "prefill_attn_tflops", "TFLOP/s", "tensor"
+        self.launches_per_step = 1
+        self.h2d = (self.h_q.numel() + self.h_k.numel() + self.h_v.numel()) * 2
+        self.d2h = self.h_o.numel() * 2
+        self.config = {"workload": name, "batch_per_gpu": B, "seq_len": S, "q_heads": H, "kv_heads": G,
+                       "head_dim": D, "window": self.window, "scale": SCALE,
+                       "l2": "inputs (%d MB) larger than L2" % ((self.h2d + self.d2h) >> 20)}
+
+    def step(self):
+        self.fa2.flash_attention(self.q.permute(0, 2, 1, 3), self.k, self.v, self.o.permute(0, 2, 1, 3), self.time,
+                                 None, self.S, self.fa2.PHASE_PREFILL, scale=SCALE, sliding_window=self.window)
+
+    def e2e_step(self):
+        self.q.copy_(self.h_q, non_blocking=True)
+        self.k.copy_(self.h_k, non_blocking=True)
+        self.v.copy_(self.h_v, non_blocking=True)
+        self.step()
+        self.h_o.copy_(self.o, non_blocking=True)
+
+    def value_from(self, ms_per_step, world):
+        return self.units * world / (ms_per_step * 1e-3) / 1e12
+
+    def cpu_sample(self, budget_s=15.0):
+        """Oracle on host cores: batch item 0, all heads, in 1024-query blocks; more items
+        while the budget lasts.  Returns (TFLOP/s, description)."""
+        from oracle import attention_oracle as orc
+
+        q = self.h_q.float().permute(0, 2, 1, 3)
+        k, v = self.h_k.float(), self.h_v.float()
+        S = self.S if self.window is None else 8192     # bounded sample of the long SWA sequence
+        done, t0 = 0, time.perf_counter()
+        while done < self.B and (done == 0 or time.perf_counter() - t0 < budget_s / 2):
+            orc.attention_core(q[done][:, :S], k[done][:, :S], v[done][:, :S], scale=SCALE, causal=True,
+                               sliding_window=self.window)
+            done += 1
+        dt = time.perf_counter() - t0
+        flops = prefill_flops(done, S, self.window)
+        return flops / dt / 1e12, f"{done} of {self.B} batch items, first {S} tokens, fp32, 1024-query blocks"
+
+
+class DecodeWorkload:
+    """Configs 4 and 5: paged KV with shuffled block tables; a step appends the new token's
+    K and V rows and runs decode attention (split-KV + combine)."""
+
+    def __init__(self, name, dev, seed, rank=0, world=1, sequences=256):
+        from g4b_b200.kernels import fa2
+        from g4b_b200.kernels.add_kv_to_cache import add_kv_to_cache
+
+        self.fa2, self.append = fa2, add_kv_to_cache
+        self.name, self.dev, self.rank, self.world = name, dev, rank, world
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        if name == "decode_paged":
+            self.dtype = torch.float16
+            self.lens = torch.randint(1024, 32769, (sequences,), generator=gen, dtype=torch.int64)
+            self.splits = 16
+        else:
+            self.dtype = torch.bfloat16
+            self.lens = torch.tensor([131072], dtype=torch.int64)
+            self.splits = 128
+        self.long_split = name == "decode_long" and world > 1
+        lens = self.lens
+        B = len(lens)
+        self.B = B
+        pages_per = (lens + PAGE - 1) // PAGE
+        if self.long_split:
+            # this rank holds (and is handed block-table entries for) only its page range
+            from g4b_b200 import dist as gdist
+
+            rng = gdist.split_pages(int(pages_per[0]), world, rank)
+            local_pages = torch.tensor([len(rng)])
+            self.local_lens = torch.tensor([min(int(lens[0]), rng.stop * PAGE) - rng.start * PAGE])
+            self.splits = max(8, 128 // world)
+        else:
+            local_pages, self.local_lens = pages_per, lens
+        num_pages = int(local_pages.sum())
+        gdev = torch.Generator(device=dev).manual_seed(seed + 1 + rank)
+        self.k_pool = torch.randn(num_pages, G, PAGE, D, generator=gdev, device=dev, dtype=torch.float32).to(self.dtype) \
+            if num_pages * G * PAGE * D < (1 << 28) else self._big_randn(num_pages, gdev)
+        self.v_pool = torch.randn(num_pages, G, PAGE, D, generator=gdev, device=dev, dtype=torch.float32).to(self.dtype) \
+            if num_pages * G * PAGE * D < (1 << 28) else self._big_randn(num_pages, gdev)
+        perm = torch.randperm(num_pages, generator=gen).to(torch.int32)
+        max_pages = int(local_pages.max())
+        bt = torch.zeros(B, max_pages, dtype=torch.int32)
+        at = 0
+        for b in range(B):
+            n = int(local_pages[b])
+            bt[b, :n] = perm[at:at + n]
+            at += n
+        self.h_bt = bt
+        self.bt = bt.to(dev)
+        self.max_len = max_pages * PAGE
+        self.time = self.local_lens.to(torch.int32).to(dev)
+        self.off = (self.local_lens - 1).to(torch.int32).to(dev)
+        self.h_q = torch.randn(B, H, 1, D, generator=gen).to(self.dtype).pin_memory()
+        self.h_kn = torch.randn(B, G, 1, D, generator=gen).to(self.dtype).pin_memory()
+        self.h_vn = torch.randn(B, G, 1, D, generator=gen).to(self.dtype).pin_memory()
+        self.h_o = torch.empty(B, H, 1, D, dtype=self.dtype).pin_memory()
+        self.q, self.kn, self.vn = self.h_q.to(dev), self.h_kn.to(dev), self.h_vn.to(dev)
+        self.o = torch.empty_like(self.q)
+        S = self.splits
+        self.packed = torch.empty(S, B, H, 1, D + 2, device=dev, dtype=torch.float32)
+        self.po, self.pl, self.pm = self.packed[..., :D], self.packed[..., D], self.packed[..., D + 1]
+        if self.long_split:
+            self.gathered = torch.empty(world * S, B, H, 1, D + 2, device=dev, dtype=torch.float32)
+        kv_bytes = float(self.local_lens.sum()) * G * D * 2 * 2
+        self.units = kv_bytes                                    # K/V bytes per step (this rank)
+        self.metric, self.unit, self.bound = "decode_attn_hbm_gbs", "GB/s", "hbm"
+        self.launches_per_step = 4                               # 2 appends + decode + combine
+        self.h2d = (self.h_q.numel() + self.h_kn.numel() + self.h_vn.numel()) * 2
+        self.d2h = self.h_o.numel() * 2
+        self.config = {"workload": name, "sequences": B, "ctx_sum": int(lens.sum()), "ctx_min": int(lens.min()),
+                       "ctx_max": int(lens.max()), "page_size": PAGE, "kv_dtype": str(self.dtype).replace("torch.", ""),
+                       "kv_splits": self.splits, "scale": SCALE,
+                       "l2": "K/V (%d MB per GPU) larger than L2" % (int(kv_bytes) >> 20) if kv_bytes > 200e6
+                       else "K/V (%d MB per GPU) fits L2: flushed between steps" % (int(kv_bytes) >> 20)}
+        self.flush = None
+        if kv_bytes <= 200e6:
+            self.flush = torch.empty(256 << 20, dtype=torch.uint8, device=dev)
+
+    def _big_randn(self, num_pages, gdev):
+        out = torch.empty(num_pages, G, PAGE, D, device=self.dev, dtype=self.dtype)
+        chunk = 1 << 14
+        for s in range(0, num_pages, chunk):
+            e = min(num_pages, s + chunk)
+            out[s:e] = torch.randn(e - s, G, PAGE, D, generator=gdev, device=self.dev, dtype=torch.float32).to(self.dtype)
+        return out
+
+    def step(self):
+        if self.flush is not None:
+            self.flush.zero_()                                   # evict K/V from L2 between steps
+        last = (not self.long_split) or self.rank == self.world - 1
+        if last:   # the new token's row lives on the rank that owns the tail of the sequence
+            self.append(self.kn, self.k_pool, self.off, 1e-6, block_tables=self.bt, page_size=PAGE)
+            self.append(self.vn, self.v_pool, self.off, 1e-6, block_tables=self.bt, page_size=PAGE)
+        if not self.long_split:
+            self.fa2.flash_attention(self.q, self.k_pool, self.v_pool, self.o, self.time, None, self.max_len,
+                                     self.fa2.PHASE_DECODE, self.po, self.pl, self.pm, scale=SCALE,
+                                     block_tables=self.bt, page_size=PAGE, num_kv_splits=self.splits)
+            return
+        from g4b_b200 import dist as gdist
+
+        self.fa2.attention_decode_partials(self.q, self.k_pool, self.v_pool, self.o, self.time, None, self.max_len,
+                                           self.fa2.PHASE_DECODE, self.po, self.pl, self.pm, self.splits, scale=SCALE,
+                                           block_tables=self.bt, page_size=PAGE)
+        gdist.gather_packed(self.packed, out=self.gathered)
+        go, gl, gm = gdist.unpack_gathered(self.gathered)
+        self.fa2.combine_partials(go, gl, gm, self.o, self.world * self.splits)
+
+    def e2e_step(self):
+        self.q.copy_(self.h_q, non_blocking=True)
+        self.kn.copy_(self.h_kn, non_blocking=True)
+        self.vn.copy_(self.h_vn, non_blocking=True)
+        self.step()
+        self.h_o.copy_(self.o, non_blocking=True)
+
+    def value_from(self, ms_per_step, world):
+        total = self.units * (1 if self.long_split else world)
+        if self.long_split:
+            total = float(self.lens.sum()) * G * D * 2 * 2
+        return total / (ms_per_step * 1e-3) / 1e9
+
+    def cpu_sample(self, budget_s=15.0):
+        from oracle import attention_oracle as orc
+
+        n = min(8, self.B)
+        idx = list(range(n))
+        kp, vp = self.k_pool.cpu(), self.v_pool.cpu()
+        t0 = time.perf_counter()
+        touched = 0
+        for b in idx:
+            L = int(self.local_lens[b])
+            k = orc.gather_pages(kp, self.h_bt[b], L, PAGE)
+            v = orc.gather_pages(vp, self.h_bt[b], L, PAGE)
+            orc.attention_core(self.h_q[b].float(), k, v, scale=SCALE)
+            touched += L * G * D * 2 * 2
+        dt = time.perf_counter() - t0
+        return touched / dt / 1e9, f"{n} of {self.B} sequences ({touched >> 20} MB of K/V), page gather + fp32 attention"
+
+
+def make_workload(name, dev, rank, world, sequences=256):
+    seeds = {"prefill_causal": 1, "prefill_swa": 2, "decode_paged": 3, "decode_long": 4}
+    if name.startswith("prefill"):
+        return PrefillWorkload(name, dev, seeds[name] + 100 * rank)
+    return DecodeWorkload(name, dev, seeds[name] + (0 if name == "decode_long" else 100 * rank), rank, world,
+                          sequences)
+
+
+# ------------------------------------------------------------------------------------------
+# arms
+# ------------------------------------------------------------------------------------------
+def run_ours(args):
+    rank, world, local = dist_env()
+    if args.gpus != world and world == 1 and args.gpus > 1:
+        raise SystemExit("launch N > 1 with torchrun (one rank per GPU)")
+    dev = torch.device(f"cuda:{local}")
+    torch.cuda.set_device(dev)
+    if world > 1:
+        torch.distributed.init_process_group("nccl", device_id=dev)
+    import __graft_entry__
+
+    if rank == 0:
+        __graft_entry__.build()
+    if world > 1:
+        torch.distributed.barrier()
+    from g4b_b200 import _cabi
+
+    peaks = measured_peaks()
+    wl = make_workload(args.workload, dev, rank, world, args.sequences)
+    sampler = ClockSampler(local) if rank == 0 else None
+    ms = timed_region(wl.step, args.steps, args.warmup, world, dev, sampler)
+    clocks = sampler.stop() if sampler is not None else None
+    ms_step = ms / args.steps
+    value = wl.value_from(ms_step, world)
+
+    # end to end: pinned host inputs -> device -> operators -> pinned host result, every step
+    ms_e2e = timed_region(wl.e2e_step, args.steps, args.warmup, world, dev) / args.steps
+    e2e_value = wl.value_from(ms_e2e, world)
+    status = _cabi.device_status()
+    if status != 0:
+        raise SystemExit(f"device status word {status:#x}: a kernel gave up on a bounded wait")
+
+    peak = peaks["tensor"] if wl.bound == "tensor" else peaks["hbm"]
+    per_gpu = value / (1 if getattr(wl, "long_split", False) else world)
+    out = {
+        "metric": wl.metric, "value": round(value, 3), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+        "warmup": args.warmup, "ms_per_step": round(ms_step, 5), "higher_is_better": True,
+        "scaling": "strong" if getattr(wl, "long_split", False) else "weak", "vs_baseline": None,
+        "dtype": "bf16" if wl.dtype == torch.bfloat16 else "f16", "data": "synthetic (seeded N(0,1))",
+        "config": wl.config,
+        "e2e": {"value": round(e2e_value, 3), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
+                "d2h_bytes_per_step": wl.d2h, "ms_per_step": round(ms_e2e, 5)},
+        "gpu_launches": wl.launches_per_step * args.steps,
+        "roofline": {"bound": wl.bound, "achieved": round(per_gpu, 3), "peak": peak, "unit": wl.unit,
+                     "frac": round(per_gpu / peak, 4), "traffic": None,
+                     "peak_source": peaks["source"] + (" burst" if wl.bound == "tensor" else " copy")},
+        "clocks": clocks,
+    }
+    if rank == 0 and world == 1 and not args.no_cpu:
+        v, sample = wl.cpu_sample()
+        out["cpu_baseline"] = {"value": round(v, 5), "unit": wl.unit, "cores": torch.get_num_threads(),
+                               "kind": "port", "sample": sample}
+    if rank == 0 and world == 1 and args.workload == "prefill_causal" and not args.no_decode:
+        # the metric has a decode half: report it in the same line
+        del wl
+        torch.cuda.empty_cache()
+        dw = make_workload("decode_paged", dev, rank, world)
+        dms = timed_region(dw.step, max(5, args.steps // 2), max(3, args.warmup), world, dev) / max(5, args.steps // 2)
+        dv = dw.value_from(dms, world)
+        cv, csample = dw.cpu_sample() if not args.no_cpu else (None, None)
+        out["decode"] = {"metric": dw.metric, "value": round(dv, 2), "unit": dw.unit, "ms_per_step": round(dms, 5),
+                         "config": dw.config,
+                         "roofline": {"bound": "hbm", "achieved": round(dv, 2), "peak": peaks["hbm"], "unit": "GB/s",
+                                      "frac": round(dv / peaks["hbm"], 4), "traffic": None,
+                                      "peak_source": peaks["source"] + " copy"},
+                         "cpu_baseline": None if cv is None else {"value": round(cv, 4), "unit": "GB/s",
+                                                                  "cores": torch.get_num_threads(), "kind": "port",
+                                                                  "sample": csample}}
+    if rank == 0:
+        print(json.dumps(out))
+    if world > 1:
+        torch.distributed.destroy_process_group()
+
+
+def run_reference(args):
+    """The reference's CPU attention (oracle port of scripts/reference_impl.py's LayerKVCache
+    math) on the host cores, bounded sample per step.  Rank 0 only."""
+    rank, world, _ = dist_env()
+    if rank != 0:
+        return
+    torch.set_num_threads(os.cpu_count() or 1)
+    name = args.workload
+
+    # build the same inputs on the host only (no GPU needed for this arm)
+    from oracle import attention_oracle as orc
+
+    gen = torch.Generator().manual_seed(1)
+    if name.startswith("prefill"):
+        # bounded sample: ~1 s of host work per step so K + W steps end within minutes
+        S, window = (4096, None) if name == "prefill_causal" else (8192, 512)
+        q = torch.randn(H, S, D, generator=gen).to(torch.bfloat16).float()
+        k = torch.randn(G, S, D, generator=gen).to(torch.bfloat16).float()
+        v = torch.randn(G, S, D, generator=gen).to(torch.bfloat16).float()
+        units = prefill_flops(1, S, window)
+        fn = lambda: orc.attention_core(q, k, v, scale=SCALE, causal=True, sliding_window=window)
+        metric, unit, div = "prefill_attn_tflops", "TFLOP/s", 1e12
+        sample = f"1 batch item, {S} tokens, all {H} heads per step, fp32, 1024-query blocks"
+    else:
+        L = 32768 if name == "decode_paged" else 131072
+        n_pages = L // PAGE
+        kp = torch.randn(n_pages, G, PAGE, D, generator=gen).to(torch.float16)
+        vp = torch.randn(n_pages, G, PAGE, D, generator=gen).to(torch.float16)
+        bt = torch.randperm(n_pages, generator=gen).to(torch.int32)
+        q = torch.randn(H, 1, D, generator=gen)
+        units = float(L) * G * D * 2 * 2
+
+        def fn():
+            kk = orc.gather_pages(kp, bt, L, PAGE)
+            vv = orc.gather_pages(vp, bt, L, PAGE)
+            return orc.attention_core(q, kk, vv, scale=SCALE)
+
+        metric, unit, div = "decode_attn_hbm_gbs", "GB/s", 1e9
+        sample = f"1 sequence of {L} tokens per step, page gather + fp32 attention"
+    for _ in range(args.warmup):
+        fn()
+    t0 = time.perf_counter()
+    for _ in range(args.steps):
+        fn()
+    dt = (time.perf_counter() - t0) / args.steps
+    value = units / dt / div
+    out = {
+        "impl": "reference", "metric": metric, "value": round(value, 5), "unit": unit, "n_gpus": args.gpus,
+        "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded N(0,1))",
+        "config": {"workload": name},
+        "cpu_baseline": {"value": round(value, 5), "unit": unit, "cores": torch.get_num_threads(), "kind": "port",
+                         "sample": sample},
+        "e2e": {"value": round(value, 5), "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }
+    print(json.dumps(out))
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--warmup", type=int, default=5)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="prefill_causal",
+                    choices=["prefill_causal", "prefill_swa", "decode_paged", "decode_long"])
+    ap.add_argument("--sequences", type=int, default=256,
+                    help="decode_paged only: number of sequences (256 = the benchmark configuration; "
+                         "smaller values are for profiler captures)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
+    ap.add_argument("--no-decode", action="store_true", help="skip the decode half of the default line")
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -44,6 +44,7 @@ constexpr int kD = 256;
 
 template <typename T> struct Mma;
 template <> struct Mma<__nv_bfloat16> {
+  static constexpr bool kSplitP = true;
   __device__ static __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                              uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -56,8 +57,13 @@ template <> struct Mma<__nv_bfloat16> {
     __nv_bfloat162 t = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&t);
   }
+  // sum of the two rounded values a packed register holds
+  __device__ static __forceinline__ float sum2(uint32_t v) {
+    return __uint_as_float(v << 16) + __uint_as_float(v & 0xffff0000u);
+  }
 };
 template <> struct Mma<__half> {
+  static constexpr bool kSplitP = false;
   __device__ static __forceinline__ void run(float (&d)[4], uint32_t a0, uint32_t a1, uint32_t a2,
                                              uint32_t a3, uint32_t b0, uint32_t b1) {
     asm volatile(
@@ -69,6 +75,10 @@ template <> struct Mma<__half> {
   __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
     __half2 t = __floats2half2_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&t);
+  }
+  __device__ static __forceinline__ float sum2(uint32_t v) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v));
+    return f.x + f.y;
   }
 };
 
@@ -151,7 +161,6 @@ __device__ __forceinline__ void block_step(WarpState& st, const uint32_t (&qf)[8
   float pr[4];
 #pragma unroll
   for (int e = 0; e < 4; ++e) pr[e] = exp2f(sv[e] - m_use);
-  st.l_run = st.l_run * alpha + (pr[0] + pr[1]) + (pr[2] + pr[3]);
   if (__any_sync(0xffffffffu, moved)) {
     // O^T columns are heads 2c, 2c+1: fetch their factors from the rows that own them
     const float a0 = __shfl_sync(0xffffffffu, alpha, (2 * c) * 4);
@@ -163,6 +172,17 @@ __device__ __forceinline__ void block_step(WarpState& st, const uint32_t (&qf)[8
   }
   const uint32_t pb0 = Mma<T>::pack(pr[0], pr[1]);
   const uint32_t pb1 = Mma<T>::pack(pr[2], pr[3]);
+  // row sum over the ROUNDED probabilities the tensor instruction multiplies, so numerator
+  // and denominator stay consistent (exact for a single visible key)
+  st.l_run = st.l_run * alpha + Mma<T>::sum2(pb0) + Mma<T>::sum2(pb1);
+  // bf16 keeps 8 significant bits of p: feed the rounding residue through a second product
+  // (P = P_hi + P_lo) so the weights carry ~16 bits, like the f16 path's 11
+  uint32_t pl0 = 0u, pl1 = 0u;
+  if constexpr (Mma<T>::kSplitP) {
+    pl0 = Mma<T>::pack(pr[0] - __uint_as_float(pb0 << 16), pr[1] - __uint_as_float(pb0 & 0xffff0000u));
+    pl1 = Mma<T>::pack(pr[2] - __uint_as_float(pb1 << 16), pr[3] - __uint_as_float(pb1 & 0xffff0000u));
+    st.l_run += Mma<T>::sum2(pl0) + Mma<T>::sum2(pl1);
+  }
   // ---------------- O^T += V^T P^T ----------------
 #pragma unroll
   for (int i = 0; i < 4; ++i) {
@@ -177,6 +197,7 @@ __device__ __forceinline__ void block_step(WarpState& st, const uint32_t (&qf)[8
       const uint32_t a2 = __byte_perm(v2[e2], v3[e2], 0x5410);
       const uint32_t a3 = __byte_perm(v2[e2], v3[e2], 0x7632);
       Mma<T>::run(st.oacc[i * 4 + e2], a0, a1, a2, a3, pb0, pb1);
+      if constexpr (Mma<T>::kSplitP) Mma<T>::run(st.oacc[i * 4 + e2], a0, a1, a2, a3, pl0, pl1);
     }
   }
 }

@@ -14,7 +14,7 @@
 //               need no shuffles; also rescale O when a maximum moved and write the output
 //
 // TMEM (512 columns x 128 lanes x 32 bit):  O[128 x 256] f32 in columns 0..255,
-// S0 / S1 [128 x 128] f32 in columns 256..383 / 384..511.  P (f16/bf16) overwrites the
+// S0 / S1 [128 x 128] f32 in columns 256..383 / 384..511.  P (always f16) overwrites the
 // first 64 columns of its S buffer and is the A operand of the P.V product from TMEM.
 //
 // Per 128-key tile j:   S(j) = Q K(j)^T  (16 MMAs 128x128x16, A and B from smem, K-major)
@@ -105,6 +105,10 @@ __device__ __forceinline__ void manual_chunk(uint8_t* dst, const T* cache_bg, in
 template <typename T> struct PackT;
 template <> struct PackT<__nv_bfloat16> {
   static constexpr uint32_t kFmt = 1;
+  // sum of the two rounded values a packed register holds
+  __device__ static __forceinline__ float sum2(uint32_t v) {
+    return __uint_as_float(v << 16) + __uint_as_float(v & 0xffff0000u);
+  }
   __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
@@ -113,6 +117,10 @@ template <> struct PackT<__nv_bfloat16> {
 };
 template <> struct PackT<__half> {
   static constexpr uint32_t kFmt = 0;
+  __device__ static __forceinline__ float sum2(uint32_t v) {
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v));
+    return f.x + f.y;
+  }
   __device__ static __forceinline__ uint32_t pack(float lo, float hi) {
     uint32_t r;
     asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(r) : "f"(hi), "f"(lo));
@@ -286,7 +294,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     // =============================== MMA issuer ===============================
     if (lane == 0) {
       constexpr uint32_t idesc_qk = ptx::make_idesc_f16(PackT<T>::kFmt, 128, 128, 0, 0);
-      constexpr uint32_t idesc_pv = ptx::make_idesc_f16(PackT<T>::kFmt, 128, 256, 0, 1);
+      // P is always f16 (11 significant bits; it never exceeds 2^8 here), V keeps the cache type
+      constexpr uint32_t idesc_pv = ptx::make_idesc_f16_ab(0, PackT<T>::kFmt, 128, 256, 0, 1);
       const uint32_t sQ_u = ptx::smem_u32(sQ), sRing_u = ptx::smem_u32(sRing);
       bool ok = ptx::mbar_wait(bar_q, 0);
       if (!ok) record(p.status, kErrQFull);
@@ -409,8 +418,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         for (int i = 0; i < 32; i += 2) {
           const float p0 = ptx::ex2_approx(fmaf(__uint_as_float(sraw[q4][i]), p.scale_log2, neg_m));
           const float p1 = ptx::ex2_approx(fmaf(__uint_as_float(sraw[q4][i + 1]), p.scale_log2, neg_m));
-          sum += p0 + p1;
-          pk[q4 >> 1][(q4 & 1) * 16 + (i >> 1)] = PackT<T>::pack(p0, p1);
+          // the row sum is taken over the ROUNDED probabilities the tensor core will multiply,
+          // so numerator and denominator stay consistent (exact for a single visible key)
+          const uint32_t packed = PackT<__half>::pack(p0, p1);
+          sum += PackT<__half>::sum2(packed);
+          pk[q4 >> 1][(q4 & 1) * 16 + (i >> 1)] = packed;
         }
       l_run = l_run * alpha + sum;
       ptx::tmem_st32(trow + s_col, pk[0]);

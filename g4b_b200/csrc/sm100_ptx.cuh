@@ -154,6 +154,13 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(uint32_t fmt, uint32_t m, 
          | ((m >> 4) << 24);    // m_dim
 }
 
+// Same with separate A and B element formats (both 16-bit).
+__host__ __device__ constexpr uint32_t make_idesc_f16_ab(uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n,
+                                                         uint32_t a_mn_major, uint32_t b_mn_major) {
+  return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) |
+         ((n >> 3) << 17) | ((m >> 4) << 24);
+}
+
 // ---- TMEM <-> registers: each thread moves 32 consecutive 32-bit columns of its lane ----
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
   asm volatile(

@@ -1,0 +1,95 @@
+"""Multi-GPU partitioning of the attention path: one process per GPU.
+
+The reference is single-GPU (one ``Device(0)``, g4b/__main__.py:46); everything here is new.
+Three of the four sharded workloads need no communication at all (requests, kv heads and
+sequences are independent).  Only single-sequence long-context decode exchanges data: every
+rank attends to its contiguous share of the KV pages and the per-rank (acc, l, m) partials --
+the reference's split-KV format (g4b/kernels/fa2.py:438-472) -- are all-gathered (NCCL over
+NVLink) and merged by the same combine kernel that merges intra-GPU splits
+(fa2.py:546-631).  The gathered partials are ordinary local memory when the kernel reads
+them.
+"""
+from __future__ import annotations
+
+from typing import Sequence
+
+
+def shard_requests(num_requests: int, world_size: int, rank: int) -> range:
+    """Contiguous, balanced share of independent requests for ``rank``."""
+    base, extra = divmod(num_requests, world_size)
+    start = rank * base + min(rank, extra)
+    return range(start, start + base + (1 if rank < extra else 0))
+
+
+def shard_request_heads(num_requests: int, kv_heads: int, world_size: int, rank: int) -> list[tuple[int, int]]:
+    """(request, kv head) units of ``rank`` when there are more GPUs than requests: units are
+    independent because a query head only reads its own kv head."""
+    units = [(r, g) for r in range(num_requests) for g in range(kv_heads)]
+    return [units[i] for i in shard_requests(len(units), world_size, rank)]
+
+
+def balance_sequences(context_lens: Sequence[int], world_size: int) -> list[list[int]]:
+    """Greedy longest-first assignment of sequences to GPUs so that KV bytes (proportional to
+    context length) balance.  Returns the sequence indices of every rank."""
+    order = sorted(range(len(context_lens)), key=lambda i: -int(context_lens[i]))
+    loads = [0] * world_size
+    out: list[list[int]] = [[] for _ in range(world_size)]
+    for i in order:
+        r = min(range(world_size), key=lambda j: (loads[j], j))
+        out[r].append(i)
+        loads[r] += int(context_lens[i])
+    for part in out:
+        part.sort()
+    return out
+
+
+def split_pages(num_pages: int, world_size: int, rank: int) -> range:
+    """Contiguous page range of ``rank`` for one long sequence split across GPUs."""
+    return shard_requests(num_pages, world_size, rank)
+
+
+def gather_partials(local_o, local_l, local_m, group=None):
+    """All-gathers one (acc, l, m) partial per rank into split-major buffers.
+
+    local_o [B,H,Tq,D], local_l / local_m [B,H,Tq] (f32; m in log2 units; acc un-normalised)
+    -> partial_o [W,B,H,Tq,D], partial_l / partial_m [W,B,H,Tq], identical on every rank and
+    ready for ``g4b_b200.kernels.fa2.combine_partials``.  Works on any torch.distributed
+    backend (NCCL on GPUs, gloo on CPU tensors).
+    """
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    po = torch.empty((world, *local_o.shape), dtype=local_o.dtype, device=local_o.device)
+    pl = torch.empty((world, *local_l.shape), dtype=local_l.dtype, device=local_l.device)
+    pm = torch.empty((world, *local_m.shape), dtype=local_m.dtype, device=local_m.device)
+    dist.all_gather_into_tensor(po, local_o.contiguous(), group=group)
+    dist.all_gather_into_tensor(pl, local_l.contiguous(), group=group)
+    dist.all_gather_into_tensor(pm, local_m.contiguous(), group=group)
+    return po, pl, pm
+
+
+def pack_partial(o, l, m):
+    """One message instead of three: [B,H,Tq,D+2] = (acc | l | m)."""
+    import torch
+
+    return torch.cat([o, l.unsqueeze(-1), m.unsqueeze(-1)], dim=-1).contiguous()
+
+
+def gather_packed(packed, out=None, group=None):
+    """All-gather of ``pack_partial`` messages -> [W,B,H,Tq,D+2]; ``out`` may be preallocated
+    (e.g. for CUDA-graph capture)."""
+    import torch
+    import torch.distributed as dist
+
+    world = dist.get_world_size(group)
+    if out is None:
+        out = torch.empty((world, *packed.shape), dtype=packed.dtype, device=packed.device)
+    dist.all_gather_into_tensor(out, packed, group=group)
+    return out
+
+
+def unpack_gathered(gathered):
+    """[W,B,H,Tq,D+2] -> strided views (partial_o, partial_l, partial_m) for the combine kernel."""
+    d = gathered.shape[-1] - 2
+    return gathered[..., :d], gathered[..., d], gathered[..., d + 1]
