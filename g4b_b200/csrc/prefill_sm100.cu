@@ -7,14 +7,16 @@
 // and full stages (fa2.py:354-435), per-slot phase skip (fa2.py:333-335); adds the softmax
 // scale and the per-query sliding window of scripts/reference_impl.py:437-443.
 //
-// One CTA = 128 query rows of one query head.  Six warps:
+// One CTA = 128 query rows of one query head.  Ten warps:
 //   warp 0      producer: TMA loads of Q (once) and of K / V chunks into a 5-stage ring
 //   warp 1      one thread issues every tcgen05.mma; the warp owns the TMEM allocation
-//   warps 2..5  softmax: thread r owns query row r (TMEM lane r), so row max / row sum
-//               need no shuffles; also rescale O when a maximum moved and write the output
+//   warps 2..9  softmax, two warpgroups: a thread owns query row r (TMEM lane r) for one
+//               half of a tile's 128 keys, so row max / row sum need no shuffles, only one
+//               shared-memory exchange with the partner warp; they also rescale O when a
+//               maximum moved and write the output (each half of the head dim)
 //
 // TMEM (512 columns x 128 lanes x 32 bit):  O[128 x 256] f32 in columns 0..255,
-// S0 / S1 [128 x 128] f32 in columns 256..383 / 384..511.  P (always f16) overwrites the
+// S0 / S1 [128 x 128] f32 in columns 256..383 / 384..511.  P (f16/bf16) overwrites the
 // first 64 columns of its S buffer and is the A operand of the P.V product from TMEM.
 //
 // Per 128-key tile j:   S(j) = Q K(j)^T  (16 MMAs 128x128x16, A and B from smem, K-major)
@@ -40,14 +42,15 @@ constexpr int kHD = 256;          // head dim
 constexpr int kStages = 5;
 constexpr int kChunkBytes = 32768;
 constexpr int kQBytes = kBM * kHD * 2;
-constexpr int kThreads = 192;
-constexpr int kSmemBytes = 1024 /*align slack*/ + kQBytes + kStages * kChunkBytes + 256 /*barriers*/;
+constexpr int kThreads = 320;      // producer warp, MMA warp, 2 softmax warpgroups
+constexpr int kXchgBytes = 2 * 2 * kBM * 4;   // row maxima: [tile parity][column half][row]
+constexpr int kSmemBytes = kQBytes + kStages * kChunkBytes + 256 /*barriers*/ + kXchgBytes;
 
 constexpr uint32_t kColO = 0, kColS0 = 256, kColS1 = 384;
 
 enum : int32_t {
   kErrQFull = 0x301, kErrKvEmpty = 0x302, kErrKvFull = 0x303, kErrSFull = 0x304,
-  kErrPFull = 0x305, kErrPvDone = 0x306,
+  kErrPFull = 0x305, kErrPvDone = 0x306, kErrSmemAlign = 0x307, kErrPair = 0x308,
 };
 
 struct PrefillParams {
@@ -70,8 +73,9 @@ struct Barriers {
   uint64_t s_full[2];
   uint64_t p_full[2];
   uint64_t pv_done;
+  uint64_t pair[4];        // one per softmax warp pair (64 arrivals): shared-memory exchanges
   uint32_t tmem_base;
-  uint32_t pad;
+  int32_t abort_flag;
 };
 
 __device__ __forceinline__ void record(int32_t* status, int32_t code) { atomicCAS(status, 0, code); }
@@ -105,6 +109,11 @@ __device__ __forceinline__ void manual_chunk(uint8_t* dst, const T* cache_bg, in
 template <typename T> struct PackT;
 template <> struct PackT<__nv_bfloat16> {
   static constexpr uint32_t kFmt = 1;
+  // 8 significant bits: rows that see only a few keys get their probabilities as a
+  // (rounded + residue) pair, multiplied by two MMAs
+  static constexpr bool kSplitP = true;
+  __device__ static __forceinline__ float lo_val(uint32_t v) { return __uint_as_float(v << 16); }
+  __device__ static __forceinline__ float hi_val(uint32_t v) { return __uint_as_float(v & 0xffff0000u); }
   // sum of the two rounded values a packed register holds
   __device__ static __forceinline__ float sum2(uint32_t v) {
     return __uint_as_float(v << 16) + __uint_as_float(v & 0xffff0000u);
@@ -117,6 +126,9 @@ template <> struct PackT<__nv_bfloat16> {
 };
 template <> struct PackT<__half> {
   static constexpr uint32_t kFmt = 0;
+  static constexpr bool kSplitP = false;
+  __device__ static __forceinline__ float lo_val(uint32_t v) { return __low2float(*reinterpret_cast<const __half2*>(&v)); }
+  __device__ static __forceinline__ float hi_val(uint32_t v) { return __high2float(*reinterpret_cast<const __half2*>(&v)); }
   __device__ static __forceinline__ float sum2(uint32_t v) {
     const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&v));
     return f.x + f.y;
@@ -132,7 +144,7 @@ template <typename T>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                const __grid_constant__ CUtensorMap v_map, PrefillParams p) {
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int bh = blockIdx.x;
   const int b = bh / p.H, h = bh % p.H;
@@ -141,12 +153,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
   const int m0 = q_tile * kBM;
 
   if (p.user_phase != nullptr && p.user_phase[b * p.phase_stride] != (uint8_t)p.phase) return;
+  uint8_t* smem = smem_raw;
+  uint8_t* sQ = smem;
+  uint8_t* sRing = smem + kQBytes;
+  Barriers* bars = reinterpret_cast<Barriers*>(smem + kQBytes + kStages * kChunkBytes);
+  float* xchg = reinterpret_cast<float*>(smem + kQBytes + kStages * kChunkBytes + 256);
   {
     // an earlier CTA gave up on a wait: drain the grid.  One thread reads so all agree.
-    __shared__ int s_abort;
-    if (threadIdx.x == 0) s_abort = *reinterpret_cast<volatile int32_t*>(p.status);
+    // The swizzled tiles need the buffer on a 1024-byte boundary: refuse to run otherwise.
+    if (threadIdx.x == 0) {
+      int32_t a = *reinterpret_cast<volatile int32_t*>(p.status);
+      if (a == 0 && (ptx::smem_u32(smem_raw) & 1023u) != 0) { record(p.status, kErrSmemAlign); a = kErrSmemAlign; }
+      bars->abort_flag = a;
+    }
     __syncthreads();
-    if (s_abort != 0) return;
+    if (bars->abort_flag != 0) return;
   }
 
   // ---- geometry of this CTA's key range (fa2.py:52-64) ----
@@ -159,17 +180,16 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
   const int qpos_max = q_t_base + m0 + rows_valid - 1;
   const int key_hi = p.causal ? min(window, qpos_max + 1) : window;
   const int key_lo = p.sliding_window > 0 ? max(0, qpos_min - p.sliding_window + 1) : 0;
+  // CTA-uniform: some row of this tile may see fewer than 64 keys in all
+  const bool few_keys = qpos_min < 64 || (p.sliding_window > 0 && p.sliding_window < 64);
+  const bool precise = PackT<T>::kSplitP && few_keys;
   const int tile_lo = key_lo / kBN;
   const int n_tiles = key_hi > key_lo ? (key_hi + kBN - 1) / kBN - tile_lo : 0;
 
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
-  uint8_t* sQ = smem;
-  uint8_t* sRing = smem + kQBytes;
-  Barriers* bars = reinterpret_cast<Barriers*>(smem + kQBytes + kStages * kChunkBytes);
 
   if (n_tiles <= 0) {
     // no visible key for any row of this tile: the output rows are defined as zero
-    if (warp >= 2) {
+    if (warp >= 2 && warp < 6) {
       const int r = (warp & 3) * 32 + lane;
       if (r < rows_valid) {
         const int64_t off = b * p.o_s0 + h * p.o_s1 + (int64_t)(m0 + r) * p.o_s2;
@@ -192,9 +212,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     }
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(ptx::smem_u32(&bars->s_full[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->p_full[s]), 128);
+      ptx::mbar_init(ptx::smem_u32(&bars->p_full[s]), 256);
     }
     ptx::mbar_init(bar_pv, 1);
+    for (int s = 0; s < 4; ++s) ptx::mbar_init(ptx::smem_u32(&bars->pair[s]), 64);
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&q_map);
     ptx::prefetch_tensormap(&k_map);
@@ -294,8 +315,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     // =============================== MMA issuer ===============================
     if (lane == 0) {
       constexpr uint32_t idesc_qk = ptx::make_idesc_f16(PackT<T>::kFmt, 128, 128, 0, 0);
-      // P is always f16 (11 significant bits; it never exceeds 2^8 here), V keeps the cache type
-      constexpr uint32_t idesc_pv = ptx::make_idesc_f16_ab(0, PackT<T>::kFmt, 128, 256, 0, 1);
+      constexpr uint32_t idesc_pv = ptx::make_idesc_f16(PackT<T>::kFmt, 128, 256, 0, 1);
       const uint32_t sQ_u = ptx::smem_u32(sQ), sRing_u = ptx::smem_u32(sRing);
       bool ok = ptx::mbar_wait(bar_q, 0);
       if (!ok) record(p.status, kErrQFull);
@@ -340,6 +360,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
             ptx::mma_ts(tmem + kColO, p_tmem + vc * 32 + k16 * 8,
                         ptx::make_smem_desc_sw128(vb + k16 * 2048, 8192, 1024), idesc_pv,
                         (j | vc | k16) != 0);
+            if (precise)   // residue of the probabilities, in the upper half of the S buffer
+              ptx::mma_ts(tmem + kColO, p_tmem + 64 + vc * 32 + k16 * 8,
+                          ptx::make_smem_desc_sw128(vb + k16 * 2048, 8192, 1024), idesc_pv, 1u);
           }
           ptx::tc_commit(ptx::smem_u32(&bars->kv_empty[st]));
         }
@@ -355,14 +378,28 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     __syncwarp();
   } else {
     // =============================== softmax / epilogue ===============================
+    // Two warpgroups share every row: warps 2..5 own the first 64 keys of a tile (and O
+    // columns 0..127), warps 6..9 the other 64 (O columns 128..255).  A warp and its partner
+    // (warp + 4, same TMEM lanes) trade row maxima through shared memory.
+    const int half = (warp - 2) >> 2;
     const int lane_base = (warp & 3) * 32;
     const int r = lane_base + lane;                       // query row = TMEM lane
     const uint32_t trow = tmem + ((uint32_t)lane_base << 16);
+    const uint32_t pair_bar = ptx::smem_u32(&bars->pair[warp & 3]);   // barrier of the warp pair
+    uint32_t pair_phase = 0;
+    // bounded rendezvous of the two warps that share these rows (a named barrier would have
+    // no time limit); false when the partner never arrived
+    auto pair_sync = [&]() -> bool {
+      ptx::mbar_arrive(pair_bar);
+      const bool w = __all_sync(0xffffffffu, ptx::mbar_wait(pair_bar, pair_phase & 1));
+      ++pair_phase;
+      return w;
+    };
     const int qpos = q_t_base + m0 + r;
     const int hi_r = p.causal ? min(window, qpos + 1) : window;
     const int lo_r = p.sliding_window > 0 ? max(0, qpos - p.sliding_window + 1) : 0;
     float m_used = -INFINITY;   // reference maximum the accumulated O and l are scaled by
-    float l_run = 0.f;
+    float l_run = 0.f;          // this thread's half of the row sum
     bool ok = true;
 
     for (int j = 0; j < n_tiles && ok; ++j) {
@@ -376,29 +413,35 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       const bool need_mask = (p.causal && kbase + kBN - 1 > qpos_min) || (kbase + kBN > window) ||
                              (kbase < key_lo) ||
                              (p.sliding_window > 0 && kbase < qpos_max - p.sliding_window + 1);
-      uint32_t sraw[4][32];
-#pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4) ptx::tmem_ld32(trow + s_col + q4 * 32, sraw[q4]);
+      uint32_t sraw[2][32];
+      ptx::tmem_ld32(trow + s_col + half * 64, sraw[0]);
+      ptx::tmem_ld32(trow + s_col + half * 64 + 32, sraw[1]);
       ptx::tc_wait_ld();
-      float mx = -INFINITY;
+      float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
-        const int nlo = lo_r - kbase, nhi = hi_r - kbase;
+        const int nlo = lo_r - kbase - half * 64, nhi = hi_r - kbase - half * 64;
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4)
+        for (int q2 = 0; q2 < 2; ++q2)
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const int n = q4 * 32 + i;
-            float x = __uint_as_float(sraw[q4][i]);
+            const int n = q2 * 32 + i;
+            float x = __uint_as_float(sraw[q2][i]);
             x = (n >= nlo && n < nhi) ? x : -INFINITY;
-            sraw[q4][i] = __float_as_uint(x);
-            mx = fmaxf(mx, x);
+            sraw[q2][i] = __float_as_uint(x);
+            mx4[i & 3] = fmaxf(mx4[i & 3], x);
           }
       } else {
 #pragma unroll
-        for (int q4 = 0; q4 < 4; ++q4)
+        for (int q2 = 0; q2 < 2; ++q2)
 #pragma unroll
-          for (int i = 0; i < 32; ++i) mx = fmaxf(mx, __uint_as_float(sraw[q4][i]));
+          for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sraw[q2][i]));
       }
+      float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
+      // trade the half-row maximum with the partner warp
+      float* xm = xchg + (j & 1) * (2 * kBM);
+      xm[half * kBM + r] = mx;
+      if (!pair_sync()) { record(p.status, kErrPair); ok = false; break; }
+      mx = fmaxf(mx, xm[(half ^ 1) * kBM + r]);
       const float m_blk = mx * p.scale_log2;
       // Lazy rescale: keep the old reference maximum unless the new one is more than 2^8
       // above it (p stays <= 256, exact enough in f32 sums and representable in f16/bf16).
@@ -410,23 +453,36 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         m_used = m_blk;
       }
       const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-      float sum = 0.f;
-      uint32_t pk[2][32];
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      uint32_t pk[32];
+      uint32_t plo[32];
 #pragma unroll
-      for (int q4 = 0; q4 < 4; ++q4)
+      for (int q2 = 0; q2 < 2; ++q2)
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
-          const float p0 = ptx::ex2_approx(fmaf(__uint_as_float(sraw[q4][i]), p.scale_log2, neg_m));
-          const float p1 = ptx::ex2_approx(fmaf(__uint_as_float(sraw[q4][i + 1]), p.scale_log2, neg_m));
-          // the row sum is taken over the ROUNDED probabilities the tensor core will multiply,
-          // so numerator and denominator stay consistent (exact for a single visible key)
-          const uint32_t packed = PackT<__half>::pack(p0, p1);
-          sum += PackT<__half>::sum2(packed);
-          pk[q4 >> 1][(q4 & 1) * 16 + (i >> 1)] = packed;
+          const float p0 = ptx::ex2_approx(fmaf(__uint_as_float(sraw[q2][i]), p.scale_log2, neg_m));
+          const float p1 = ptx::ex2_approx(fmaf(__uint_as_float(sraw[q2][i + 1]), p.scale_log2, neg_m));
+          const uint32_t packed = PackT<T>::pack(p0, p1);
+          pk[q2 * 16 + (i >> 1)] = packed;
+          if (few_keys) {
+            // rows that see only a few keys: sum the ROUNDED probabilities the tensor core
+            // multiplies, so numerator and denominator agree (exact for one visible key) ...
+            sum4[(i >> 1) & 3] += PackT<T>::sum2(packed);
+            if constexpr (PackT<T>::kSplitP) {
+              // ... and give bf16 its rounding residue back through a second product
+              const uint32_t lo = PackT<T>::pack(p0 - PackT<T>::lo_val(packed), p1 - PackT<T>::hi_val(packed));
+              sum4[(i >> 1) & 3] += PackT<T>::sum2(lo);
+              plo[q2 * 16 + (i >> 1)] = lo;
+            }
+          } else {
+            sum4[(i >> 1) & 3] += p0 + p1;
+          }
         }
-      l_run = l_run * alpha + sum;
-      ptx::tmem_st32(trow + s_col, pk[0]);
-      ptx::tmem_st32(trow + s_col + 32, pk[1]);
+      l_run = l_run * alpha + ((sum4[0] + sum4[1]) + (sum4[2] + sum4[3]));
+      ptx::tmem_st32(trow + s_col + half * 32, pk);
+      if constexpr (PackT<T>::kSplitP) {
+        if (few_keys) ptx::tmem_st32(trow + s_col + 64 + half * 32, plo);
+      }
       // O may only be touched once PV(j-1) has drained; waiting every tile keeps the phase
       // bookkeeping trivial and is off the critical path (PV(j) queues behind QK(j+1) anyway).
       if (j > 0) {
@@ -434,13 +490,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         ptx::tc_fence_after();
         if (ok && __any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
-          for (int c8 = 0; c8 < 8; ++c8) {
+          for (int c4 = 0; c4 < 4; ++c4) {
             uint32_t ov[32];
-            ptx::tmem_ld32(trow + kColO + c8 * 32, ov);
+            ptx::tmem_ld32(trow + kColO + half * 128 + c4 * 32, ov);
             ptx::tc_wait_ld();
 #pragma unroll
             for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
-            ptx::tmem_st32(trow + kColO + c8 * 32, ov);
+            ptx::tmem_st32(trow + kColO + half * 128 + c4 * 32, ov);
           }
         }
       }
@@ -454,24 +510,32 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(bar_pv, (n_tiles - 1) & 1))) { record(p.status, kErrPvDone); ok = false; }
       ptx::tc_fence_after();
     }
+    // the row sum is the sum of both halves (both scaled by the same m_used); the exchange
+    // uses the maxima buffer the last tile did not use
+    if (ok) {
+      float* xl = xchg + (n_tiles & 1) * (2 * kBM);
+      xl[half * kBM + r] = l_run;
+      if (!pair_sync()) { record(p.status, kErrPair); ok = false; }
+      l_run += xl[(half ^ 1) * kBM + r];
+    }
     if (ok) {
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
       const bool row_ok = r < rows_valid;
-      const int64_t off = b * p.o_s0 + h * p.o_s1 + (int64_t)(m0 + r) * p.o_s2;
+      const int64_t off = b * p.o_s0 + h * p.o_s1 + (int64_t)(m0 + r) * p.o_s2 + half * 128;
 #pragma unroll 1
-      for (int c8 = 0; c8 < 8; ++c8) {
+      for (int c4 = 0; c4 < 4; ++c4) {
         uint32_t ov[32];
-        ptx::tmem_ld32(trow + kColO + c8 * 32, ov);
+        ptx::tmem_ld32(trow + kColO + half * 128 + c4 * 32, ov);
         ptx::tc_wait_ld();
         if (row_ok) {
           if (p.o_dtype == G4B_F32) {
-            float4* dst = reinterpret_cast<float4*>((float*)p.o + off + c8 * 32);
+            float4* dst = reinterpret_cast<float4*>((float*)p.o + off + c4 * 32);
 #pragma unroll
             for (int i = 0; i < 8; ++i)
               dst[i] = make_float4(__uint_as_float(ov[4 * i]) * inv_l, __uint_as_float(ov[4 * i + 1]) * inv_l,
                                    __uint_as_float(ov[4 * i + 2]) * inv_l, __uint_as_float(ov[4 * i + 3]) * inv_l);
           } else {
-            uint4* dst = reinterpret_cast<uint4*>((T*)p.o + off + c8 * 32);
+            uint4* dst = reinterpret_cast<uint4*>((T*)p.o + off + c4 * 32);
 #pragma unroll
             for (int i = 0; i < 4; ++i) {
               uint4 w;

@@ -143,6 +143,7 @@ __device__ __forceinline__ uint64_t make_smem_desc_sw128(uint32_t smem_addr, uin
 }
 
 // Instruction descriptor for kind::f16: f32 accumulator, A/B both `fmt` (0 = f16, 1 = bf16).
+// A and B must have the SAME format: an f16 A with a bf16 B raised "illegal instruction" on B200.
 __host__ __device__ constexpr uint32_t make_idesc_f16(uint32_t fmt, uint32_t m, uint32_t n, uint32_t a_mn_major,
                                                       uint32_t b_mn_major) {
   return (1u << 4)              // c_format = f32
@@ -152,13 +153,6 @@ __host__ __device__ constexpr uint32_t make_idesc_f16(uint32_t fmt, uint32_t m, 
          | (b_mn_major << 16)   // b_major
          | ((n >> 3) << 17)     // n_dim
          | ((m >> 4) << 24);    // m_dim
-}
-
-// Same with separate A and B element formats (both 16-bit).
-__host__ __device__ constexpr uint32_t make_idesc_f16_ab(uint32_t a_fmt, uint32_t b_fmt, uint32_t m, uint32_t n,
-                                                         uint32_t a_mn_major, uint32_t b_mn_major) {
-  return (1u << 4) | (a_fmt << 7) | (b_fmt << 10) | (a_mn_major << 15) | (b_mn_major << 16) |
-         ((n >> 3) << 17) | ((m >> 4) << 24);
 }
 
 // ---- TMEM <-> registers: each thread moves 32 consecutive 32-bit columns of its lane ----
