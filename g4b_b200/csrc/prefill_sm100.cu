@@ -71,7 +71,8 @@ struct Barriers {
   uint64_t kv_full[kStages];
   uint64_t kv_empty[kStages];
   uint64_t s_full[2];
-  uint64_t p_full[2];
+  uint64_t p_a[2];          // first quarter-pairs of P(j) written (keys 0..31 and 64..95)
+  uint64_t p_b[2];          // the rest of P(j) written
   uint64_t pv_done;
   uint64_t pair[4];        // one per softmax warp pair (64 arrivals): shared-memory exchanges
   uint32_t tmem_base;
@@ -79,6 +80,18 @@ struct Barriers {
 };
 
 __device__ __forceinline__ void record(int32_t* status, int32_t code) { atomicCAS(status, 0, code); }
+
+// Optional timeline of one CTA (developer builds with -DG4B_TRACE only): SM cycle counter at
+// the main hand-over points of every tile, read back with g4b_debug_read_trace().
+#ifdef G4B_TRACE
+__device__ long long g_trace[128][16];
+#define G4B_TRACE_AT(tile, slot)                                                         \
+  do {                                                                                   \
+    if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (tile) < 128) g_trace[(tile)][(slot)] = clock64(); \
+  } while (0)
+#else
+#define G4B_TRACE_AT(tile, slot) do {} while (0)
+#endif
 
 // Copies rows [row0, row0 + nrows) of a chunk with ordinary loads, applying the 128-byte
 // swizzle by hand; rows whose logical key is outside [0, window) are written as zeros.
@@ -212,7 +225,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     }
     for (int s = 0; s < 2; ++s) {
       ptx::mbar_init(ptx::smem_u32(&bars->s_full[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->p_full[s]), 256);
+      ptx::mbar_init(ptx::smem_u32(&bars->p_a[s]), 256);
+      ptx::mbar_init(ptx::smem_u32(&bars->p_b[s]), 256);
     }
     ptx::mbar_init(bar_pv, 1);
     for (int s = 0; s < 4; ++s) ptx::mbar_init(ptx::smem_u32(&bars->pair[s]), 64);
@@ -313,67 +327,99 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     }
   } else if (warp == 1) {
     // =============================== MMA issuer ===============================
-    if (lane == 0) {
-      constexpr uint32_t idesc_qk = ptx::make_idesc_f16(PackT<T>::kFmt, 128, 128, 0, 0);
-      constexpr uint32_t idesc_pv = ptx::make_idesc_f16(PackT<T>::kFmt, 128, 256, 0, 1);
-      const uint32_t sQ_u = ptx::smem_u32(sQ), sRing_u = ptx::smem_u32(sRing);
-      bool ok = ptx::mbar_wait(bar_q, 0);
-      if (!ok) record(p.status, kErrQFull);
-      ptx::tc_fence_after();
-      uint32_t cc = 0;
-      auto issue_qk = [&](int j) {
-        const uint32_t d_tmem = tmem + ((j & 1) ? kColS1 : kColS0);
-        for (int kc = 0; kc < 2 && ok; ++kc, ++cc) {
-          const int st = cc % kStages;
-          if (!ptx::mbar_wait(ptx::smem_u32(&bars->kv_full[st]), (cc / kStages) & 1)) {
-            record(p.status, kErrKvFull); ok = false; break;
-          }
-          ptx::tc_fence_after();
-          const uint32_t kb = sRing_u + st * kChunkBytes;
-#pragma unroll
-          for (int k16 = 0; k16 < 8; ++k16) {
-            const uint32_t a_addr = sQ_u + (kc * 2 + (k16 >> 2)) * 16384 + (k16 & 3) * 32;
-            const uint32_t b_addr = kb + (k16 >> 2) * 16384 + (k16 & 3) * 32;
-            ptx::mma_ss(d_tmem, ptx::make_smem_desc_sw128(a_addr, 16, 1024),
-                        ptx::make_smem_desc_sw128(b_addr, 16, 1024), idesc_qk, (kc | k16) != 0);
-          }
-          ptx::tc_commit(ptx::smem_u32(&bars->kv_empty[st]));
-        }
-        if (ok) ptx::tc_commit(ptx::smem_u32(&bars->s_full[j & 1]));
-      };
-      auto issue_pv = [&](int j) {
-        if (!ptx::mbar_wait(ptx::smem_u32(&bars->p_full[j & 1]), (j >> 1) & 1)) {
-          record(p.status, kErrPFull); ok = false; return;
+    // The whole warp walks the loop (uniform control flow keeps addresses and descriptors in
+    // uniform registers); one elected lane issues each tcgen05 instruction.  Descriptors are
+    // a constant upper word plus a lower word that is a base and a compile-time offset.
+    constexpr uint32_t idesc_qk = ptx::make_idesc_f16(PackT<T>::kFmt, 128, 128, 0, 0);
+    constexpr uint32_t idesc_pv = ptx::make_idesc_f16(PackT<T>::kFmt, 128, 256, 0, 1);
+    constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024 B, version 1, SWIZZLE_128B
+    constexpr uint32_t kLoKMajor = 1u << 16;                                // LBO field unused (1)
+    constexpr uint32_t kLoVMajor = (8192u >> 4) << 16;                      // LBO 8192 B between 64-wide slabs
+    const uint32_t q_lo = (ptx::smem_u32(sQ) >> 4) | kLoKMajor;
+    const uint32_t ring_lo = ptx::smem_u32(sRing) >> 4;
+    auto wait_all = [&](uint32_t bar, uint32_t parity) -> bool {
+      return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity));
+    };
+    bool ok = wait_all(bar_q, 0);
+    if (!ok && lane == 0) record(p.status, kErrQFull);
+    ptx::tc_fence_after();
+    uint32_t cc = 0;
+    auto issue_qk = [&](int j) {
+      const uint32_t d_tmem = tmem + ((j & 1) ? kColS1 : kColS0);
+      for (int kc = 0; kc < 2 && ok; ++kc, ++cc) {
+        const int st = cc % kStages;
+        if (!wait_all(ptx::smem_u32(&bars->kv_full[st]), (cc / kStages) & 1)) {
+          if (lane == 0) record(p.status, kErrKvFull);
+          ok = false; break;
         }
         ptx::tc_fence_after();
-        const uint32_t p_tmem = tmem + ((j & 1) ? kColS1 : kColS0);
-        for (int vc = 0; vc < 2 && ok; ++vc, ++cc) {
-          const int st = cc % kStages;
-          if (!ptx::mbar_wait(ptx::smem_u32(&bars->kv_full[st]), (cc / kStages) & 1)) {
-            record(p.status, kErrKvFull); ok = false; break;
-          }
-          ptx::tc_fence_after();
-          const uint32_t vb = sRing_u + st * kChunkBytes;
+        const uint32_t k_lo = (ring_lo + st * (kChunkBytes >> 4)) | kLoKMajor;
+        const uint32_t a_lo = q_lo + kc * (2 * 16384 >> 4);
+        if (ptx::elect_one()) {
 #pragma unroll
-          for (int k16 = 0; k16 < 4; ++k16) {
-            // 16 keys = 8 packed columns of P; 16 rows of every V slab = 2048 bytes
-            ptx::mma_ts(tmem + kColO, p_tmem + vc * 32 + k16 * 8,
-                        ptx::make_smem_desc_sw128(vb + k16 * 2048, 8192, 1024), idesc_pv,
-                        (j | vc | k16) != 0);
-            if (precise)   // residue of the probabilities, in the upper half of the S buffer
-              ptx::mma_ts(tmem + kColO, p_tmem + 64 + vc * 32 + k16 * 8,
-                          ptx::make_smem_desc_sw128(vb + k16 * 2048, 8192, 1024), idesc_pv, 1u);
+          for (int k16 = 0; k16 < 8; ++k16) {
+            const uint32_t off = ((k16 >> 2) * 16384 + (k16 & 3) * 32) >> 4;
+            ptx::mma_ss(d_tmem, ptx::desc64(a_lo + off, kDescHi), ptx::desc64(k_lo + off, kDescHi), idesc_qk,
+                        (kc | k16) != 0);
           }
           ptx::tc_commit(ptx::smem_u32(&bars->kv_empty[st]));
         }
-        if (ok) ptx::tc_commit(bar_pv);
-      };
-      if (ok) issue_qk(0);
-      if (ok && n_tiles > 1) issue_qk(1);
-      for (int j = 0; j < n_tiles && ok; ++j) {
-        issue_pv(j);
-        if (ok && j + 2 < n_tiles) issue_qk(j + 2);
+        __syncwarp();
       }
+      if (ok && ptx::elect_one()) ptx::tc_commit(ptx::smem_u32(&bars->s_full[j & 1]));
+      __syncwarp();
+      G4B_TRACE_AT(j, 0);   // QK(j) issued
+    };
+    auto issue_pv = [&](int j) {
+      // both V chunks first (they landed long ago), then P in the order the softmax warps
+      // finish it: keys 0..31 and 64..95, then 32..63 and 96..127
+      uint32_t v_lo[2];
+      int st2[2];
+      for (int vc = 0; vc < 2 && ok; ++vc, ++cc) {
+        st2[vc] = cc % kStages;
+        if (!wait_all(ptx::smem_u32(&bars->kv_full[st2[vc]]), (cc / kStages) & 1)) {
+          if (lane == 0) record(p.status, kErrKvFull);
+          ok = false; return;
+        }
+        v_lo[vc] = (ring_lo + st2[vc] * (kChunkBytes >> 4)) | kLoVMajor;
+      }
+      const uint32_t p_tmem = tmem + ((j & 1) ? kColS1 : kColS0);
+      G4B_TRACE_AT(j, 3);   // V chunks of tile j seen by the issuer
+      for (int part = 0; part < 2 && ok; ++part) {
+        const uint32_t bar = ptx::smem_u32(part == 0 ? &bars->p_a[j & 1] : &bars->p_b[j & 1]);
+        if (!wait_all(bar, (j >> 1) & 1)) {
+          if (lane == 0) record(p.status, kErrPFull);
+          ok = false; return;
+        }
+        ptx::tc_fence_after();
+        G4B_TRACE_AT(j, 1 + part);   // P part A / B seen by the issuer
+        if (ptx::elect_one()) {
+#pragma unroll
+          for (int vc = 0; vc < 2; ++vc) {
+#pragma unroll
+            for (int kk = 0; kk < 2; ++kk) {
+              const int k16 = part * 2 + kk;
+              // 16 keys = 8 packed columns of P; 16 rows of every V slab = 2048 bytes
+              const uint64_t vdesc = ptx::desc64(v_lo[vc] + (k16 * 2048 >> 4), kDescHi);
+              ptx::mma_ts(tmem + kColO, p_tmem + vc * 32 + k16 * 8, vdesc, idesc_pv, (j | part | vc | kk) != 0);
+              if (precise)   // residue of the probabilities, in the upper half of the S buffer
+                ptx::mma_ts(tmem + kColO, p_tmem + 64 + vc * 32 + k16 * 8, vdesc, idesc_pv, 1u);
+            }
+          }
+          if (part == 1) {
+            ptx::tc_commit(ptx::smem_u32(&bars->kv_empty[st2[0]]));
+            ptx::tc_commit(ptx::smem_u32(&bars->kv_empty[st2[1]]));
+            ptx::tc_commit(bar_pv);
+          }
+        }
+        __syncwarp();
+      }
+    };
+    if (ok) issue_qk(0);
+    if (ok && n_tiles > 1) issue_qk(1);
+    for (int j = 0; j < n_tiles && ok; ++j) {
+      issue_pv(j);
+      if (ok && j + 2 < n_tiles) issue_qk(j + 2);
     }
     __syncwarp();
   } else {
@@ -408,6 +454,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         record(p.status, kErrSFull); ok = false; break;
       }
       ptx::tc_fence_after();
+      if (warp == 2) G4B_TRACE_AT(j, 8);   // S(j) seen by the softmax warp
       const int kbase = (tile_lo + j) * kBN;
       // warp-uniform: does any row of this CTA need element masks in this tile?
       const bool need_mask = (p.causal && kbase + kBN - 1 > qpos_min) || (kbase + kBN > window) ||
@@ -417,6 +464,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       ptx::tmem_ld32(trow + s_col + half * 64, sraw[0]);
       ptx::tmem_ld32(trow + s_col + half * 64 + 32, sraw[1]);
       ptx::tc_wait_ld();
+      if (warp == 2) G4B_TRACE_AT(j, 9);   // S(j) in registers
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
         const int nlo = lo_r - kbase - half * 64, nhi = hi_r - kbase - half * 64;
@@ -437,24 +485,79 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           for (int i = 0; i < 32; ++i) mx4[i & 3] = fmaxf(mx4[i & 3], __uint_as_float(sraw[q2][i]));
       }
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
-      // trade the half-row maximum with the partner warp
+      // publish the half-row maximum for the partner warp; collect the partner's later
       float* xm = xchg + (j & 1) * (2 * kBM);
       xm[half * kBM + r] = mx;
-      if (!pair_sync()) { record(p.status, kErrPair); ok = false; break; }
+      ptx::mbar_arrive(pair_bar);
+
+      const uint32_t bar_pa = ptx::smem_u32(&bars->p_a[j & 1]);
+      const uint32_t bar_pb = ptx::smem_u32(&bars->p_b[j & 1]);
+      uint32_t pk[32];
+      // Optimistic path: the reference maximum rarely moves (it only has to stay within 2^8
+      // of the true one), so start exponentiating against the current one while the maxima
+      // are still being traded, and fall back only if the new maximum is out of range.
+      bool fast = !few_keys && __all_sync(0xffffffffu, m_used != -INFINITY);
+      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
+      if (fast) {
+        const float neg_m = -m_used;
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = ptx::ex2_approx(fmaf(__uint_as_float(sraw[0][i]), p.scale_log2, neg_m));
+          const float p1 = ptx::ex2_approx(fmaf(__uint_as_float(sraw[0][i + 1]), p.scale_log2, neg_m));
+          sum4[(i >> 1) & 3] += p0 + p1;
+          pk[i >> 1] = PackT<T>::pack(p0, p1);
+        }
+      }
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(pair_bar, pair_phase & 1))) {
+        record(p.status, kErrPair); ok = false; break;
+      }
+      ++pair_phase;
+      if (warp == 2) G4B_TRACE_AT(j, 10);  // partner's maximum received
       mx = fmaxf(mx, xm[(half ^ 1) * kBM + r]);
       const float m_blk = mx * p.scale_log2;
+      const bool exceed = m_blk > m_used + 8.f;
+      if (fast && __any_sync(0xffffffffu, exceed)) fast = false;   // same verdict in the partner warp
+
+      if (fast) {
+        // first 32 keys of this half are final: let the P.V product start on them
+        ptx::tmem_st16(trow + s_col + half * 32, pk);
+        ptx::tc_wait_st();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(bar_pa);
+        if (warp == 2) G4B_TRACE_AT(j, 11);  // P part A published
+        const float neg_m = -m_used;
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = ptx::ex2_approx(fmaf(__uint_as_float(sraw[1][i]), p.scale_log2, neg_m));
+          const float p1 = ptx::ex2_approx(fmaf(__uint_as_float(sraw[1][i + 1]), p.scale_log2, neg_m));
+          sum4[(i >> 1) & 3] += p0 + p1;
+          pk[16 + (i >> 1)] = PackT<T>::pack(p0, p1);
+        }
+        ptx::tmem_st16(trow + s_col + half * 32 + 16, pk + 16);
+        l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        ptx::tc_wait_st();
+        ptx::tc_fence_before();
+        ptx::mbar_arrive(bar_pb);
+        if (warp == 2) G4B_TRACE_AT(j, 12);  // P part B published
+        // keep the PV-done phase bookkeeping in step (no stall: PV(j-1) ended long ago)
+        if (j > 0 && !__all_sync(0xffffffffu, ptx::mbar_wait(bar_pv, (j - 1) & 1))) {
+          record(p.status, kErrPvDone); ok = false;
+        }
+        continue;
+      }
+
+      // ---- general path: new reference maximum, few-keys rows, first tile ----
       // Lazy rescale: keep the old reference maximum unless the new one is more than 2^8
       // above it (p stays <= 256, exact enough in f32 sums and representable in f16/bf16).
       float alpha = 1.f;
       bool rescale = false;
-      if (m_blk > m_used + 8.f) {
+      if (exceed) {
         rescale = (m_used != -INFINITY);
         alpha = rescale ? ptx::ex2_approx(m_used - m_blk) : 1.f;
         m_used = m_blk;
       }
       const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
-      float sum4[4] = {0.f, 0.f, 0.f, 0.f};
-      uint32_t pk[32];
+      sum4[0] = sum4[1] = sum4[2] = sum4[3] = 0.f;
       uint32_t plo[32];
 #pragma unroll
       for (int q2 = 0; q2 < 2; ++q2)
@@ -483,8 +586,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       if constexpr (PackT<T>::kSplitP) {
         if (few_keys) ptx::tmem_st32(trow + s_col + 64 + half * 32, plo);
       }
-      // O may only be touched once PV(j-1) has drained; waiting every tile keeps the phase
-      // bookkeeping trivial and is off the critical path (PV(j) queues behind QK(j+1) anyway).
+      // O may only be touched once PV(j-1) has drained
       if (j > 0) {
         if (!__all_sync(0xffffffffu, ptx::mbar_wait(bar_pv, (j - 1) & 1))) { record(p.status, kErrPvDone); ok = false; }
         ptx::tc_fence_after();
@@ -502,7 +604,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       }
       ptx::tc_wait_st();
       ptx::tc_fence_before();
-      ptx::mbar_arrive(ptx::smem_u32(&bars->p_full[j & 1]));
+      ptx::mbar_arrive(bar_pa);
+      ptx::mbar_arrive(bar_pb);
     }
 
     // ---- epilogue: O / l -> global ----
@@ -609,6 +712,12 @@ static int launch_typed(const CUtensorMap& qm, const CUtensorMap& km, const CUte
 }
 
 }  // namespace
+
+#ifdef G4B_TRACE
+extern "C" int g4b_debug_read_trace(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 128 * 16);
+}
+#endif
 
 int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   if (a.block_tables.ptr != nullptr)
