@@ -177,6 +177,8 @@ class PrefillWorkload:
         self.launches_per_step = 1
         self.h2d = (self.h_q.numel() + self.h_k.numel() + self.h_v.numel()) * 2
         self.d2h = self.h_o.numel() * 2
+        # DRAM bytes of one launch from the committed ncu capture (profiles/): read + write
+        self.traffic = 476.4e6 if name == "prefill_causal" else None
         self.config = {"workload": name, "batch_per_gpu": B, "seq_len": S, "q_heads": H, "kv_heads": G,
                        "head_dim": D, "window": self.window, "scale": SCALE,
                        "l2": "inputs (%d MB) larger than L2" % ((self.h2d + self.d2h) >> 20)}
@@ -279,6 +281,9 @@ class DecodeWorkload:
             self.gathered = torch.empty(world * S, B, H, 1, D + 2, device=dev, dtype=torch.float32)
         kv_bytes = float(self.local_lens.sum()) * G * D * 2 * 2
         self.units = kv_bytes                                    # K/V bytes per step (this rank)
+        # DRAM bytes per launch: the ncu capture of a 32-sequence case read 1.0006x its
+        # algorithmic K/V bytes and traffic grows with the token count (profiles/)
+        self.traffic = kv_bytes * 1.0006 + 5.4e6 * (B / 32.0) if name == "decode_paged" else None
         self.metric, self.unit, self.bound = "decode_attn_hbm_gbs", "GB/s", "hbm"
         self.launches_per_step = 4                               # 2 appends + decode + combine
         self.h2d = (self.h_q.numel() + self.h_kn.numel() + self.h_vn.numel()) * 2
@@ -406,7 +411,7 @@ def run_ours(args):
                 "d2h_bytes_per_step": wl.d2h, "ms_per_step": round(ms_e2e, 5)},
         "gpu_launches": wl.launches_per_step * args.steps,
         "roofline": {"bound": wl.bound, "achieved": round(per_gpu, 3), "peak": peak, "unit": wl.unit,
-                     "frac": round(per_gpu / peak, 4), "traffic": None,
+                     "frac": round(per_gpu / peak, 4), "traffic": wl.traffic,
                      "peak_source": peaks["source"] + (" burst" if wl.bound == "tensor" else " copy")},
         "clocks": clocks,
     }
@@ -425,7 +430,7 @@ def run_ours(args):
         out["decode"] = {"metric": dw.metric, "value": round(dv, 2), "unit": dw.unit, "ms_per_step": round(dms, 5),
                          "config": dw.config,
                          "roofline": {"bound": "hbm", "achieved": round(dv, 2), "peak": peaks["hbm"], "unit": "GB/s",
-                                      "frac": round(dv / peaks["hbm"], 4), "traffic": None,
+                                      "frac": round(dv / peaks["hbm"], 4), "traffic": dw.traffic,
                                       "peak_source": peaks["source"] + " copy"},
                          "cpu_baseline": None if cv is None else {"value": round(cv, 4), "unit": "GB/s",
                                                                   "cores": torch.get_num_threads(), "kind": "port",
