@@ -76,6 +76,7 @@ EXPORTS = {
     "g4b_flash_attention": (ctypes.c_int, [ctypes.POINTER(G4bAttnArgs), ctypes.c_void_p]),
     "g4b_attn_prefill": (ctypes.c_int, [ctypes.POINTER(G4bAttnArgs), ctypes.c_void_p]),
     "g4b_attn_decode": (ctypes.c_int, [ctypes.POINTER(G4bAttnArgs), ctypes.c_void_p]),
+    "g4b_attn_decode_static_scratch": (ctypes.c_int, [ctypes.POINTER(G4bAttnArgs), ctypes.c_void_p]),
     "g4b_attn_combine": (ctypes.c_int, [ctypes.POINTER(G4bCombineArgs), ctypes.c_void_p]),
     "g4b_select_kv_splits": (ctypes.c_int, [ctypes.c_int] * 4),
     "g4b_kv_append": (ctypes.c_int, [ctypes.POINTER(G4bAppendArgs), ctypes.c_void_p]),

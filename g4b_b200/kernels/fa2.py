@@ -125,3 +125,18 @@ def combine_partials(partial_o, partial_l, partial_m, o, num_splits, *, user_pha
     c.num_splits = int(num_splits)
     c.phase = int(phase)
     _cabi.check(_cabi.load().g4b_attn_combine(ctypes.byref(c), ctypes.c_void_p(_cabi.current_stream(stream))))
+
+
+def decode_attention_static_scratch(q, k_cache, v_cache, o, time_dim_sizes, user_phase, ctx_window_size, phase, *,
+                                    scale=1.0, sliding_window=None, block_tables=None, page_size=16,
+                                    num_kv_splits=None, stage=STAGE_CAUSAL, stream=None):
+    """Tq == 1 attention with split-KV for callers that may not allocate device memory (a
+    serving loop with a memory budget fixed at load, a plugin inside an engine that owns every
+    buffer): the split workspace is a fixed 8 MiB array inside the library instead of
+    caller-provided partial buffers.  Limits: head dim 256, at most 16 splits and
+    splits * B * H <= 8192, else ValueError.  Calls share that array, so run them on one stream
+    (or otherwise ordered); the first call on a device should precede any stream capture."""
+    a = _attn_args(q, k_cache, v_cache, o, time_dim_sizes, user_phase, ctx_window_size, phase,
+                   None, None, None, stage, scale, sliding_window, block_tables, page_size, num_kv_splits)
+    _cabi.check(_cabi.load().g4b_attn_decode_static_scratch(ctypes.byref(a),
+                                                            ctypes.c_void_p(_cabi.current_stream(stream))))

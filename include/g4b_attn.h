@@ -166,6 +166,23 @@ typedef struct G4bAdvanceArgs {
 } G4bAdvanceArgs;
 int g4b_advance_decode_state(const G4bAdvanceArgs* args, void* cuda_stream);
 
+/*
+ * Tq == 1 attention with split-KV and merge, for callers that cannot allocate device memory
+ * (a serving loop whose memory was fixed at load time, a plugin inside an engine that owns
+ * every allocation).  It has no counterpart in the reference, whose caller always brings the
+ * partial buffers (g4b/models/gemma4e.py:819-821).  Same arguments as g4b_flash_attention,
+ * except that partial_o / partial_l / partial_m must be absent: the split-KV workspace is a
+ * fixed array inside the library (8192 rows of 258 floats, 8.06 MiB per GPU, held until the
+ * process exits).  Limits: head dim 256, at most 16 splits, splits * B * H <= 8192; anything
+ * larger returns G4B_ERR_TOO_LARGE.  Allocates nothing.  The first call on each device looks
+ * up the array's device address (cudaGetSymbolAddress) and should therefore be made once
+ * before any stream capture on that device.  All calls share the one array, which keeps the
+ * previous call's contents: nothing needs clearing (every entry the merge reads is written
+ * first by the same call), but two calls that overlap on the GPU race on it -- keep them on
+ * one stream or order them.
+ */
+int g4b_attn_decode_static_scratch(const G4bAttnArgs* args, void* cuda_stream);
+
 /* Message of the last failing call on this thread ("" if none). No reference counterpart:
  * the reference raises Python exceptions from its wrappers (fa2.py:656-657). */
 const char* g4b_last_error_string(void);
