@@ -63,33 +63,35 @@ def gather_partials(local_o, local_l, local_m, group=None):
     po = torch.empty((world, *local_o.shape), dtype=local_o.dtype, device=local_o.device)
     pl = torch.empty((world, *local_l.shape), dtype=local_l.dtype, device=local_l.device)
     pm = torch.empty((world, *local_m.shape), dtype=local_m.dtype, device=local_m.device)
-    dist.all_gather_into_tensor(po, local_o.contiguous(), group=group)
-    dist.all_gather_into_tensor(pl, local_l.contiguous(), group=group)
-    dist.all_gather_into_tensor(pm, local_m.contiguous(), group=group)
+    # inputs get a leading split dim of 1 so the output is their concatenation along dim 0
+    # (the only form every backend accepts)
+    dist.all_gather_into_tensor(po, local_o.contiguous().unsqueeze(0), group=group)
+    dist.all_gather_into_tensor(pl, local_l.contiguous().unsqueeze(0), group=group)
+    dist.all_gather_into_tensor(pm, local_m.contiguous().unsqueeze(0), group=group)
     return po, pl, pm
 
 
 def pack_partial(o, l, m):
-    """One message instead of three: [B,H,Tq,D+2] = (acc | l | m)."""
+    """One message instead of three: [...,D+2] = (acc | l | m)."""
     import torch
 
     return torch.cat([o, l.unsqueeze(-1), m.unsqueeze(-1)], dim=-1).contiguous()
 
 
 def gather_packed(packed, out=None, group=None):
-    """All-gather of ``pack_partial`` messages -> [W,B,H,Tq,D+2]; ``out`` may be preallocated
-    (e.g. for CUDA-graph capture)."""
+    """All-gather of packed partials [S,B,H,Tq,D+2] -> [W*S,B,H,Tq,D+2] (rank-major, i.e. the
+    concatenation along the split dim); ``out`` may be preallocated."""
     import torch
     import torch.distributed as dist
 
     world = dist.get_world_size(group)
     if out is None:
-        out = torch.empty((world, *packed.shape), dtype=packed.dtype, device=packed.device)
+        out = torch.empty((world * packed.shape[0], *packed.shape[1:]), dtype=packed.dtype, device=packed.device)
     dist.all_gather_into_tensor(out, packed, group=group)
     return out
 
 
 def unpack_gathered(gathered):
-    """[W,B,H,Tq,D+2] -> strided views (partial_o, partial_l, partial_m) for the combine kernel."""
+    """[S,B,H,Tq,D+2] -> strided views (partial_o, partial_l, partial_m) for the combine kernel."""
     d = gathered.shape[-1] - 2
     return gathered[..., :d], gathered[..., d], gathered[..., d + 1]
