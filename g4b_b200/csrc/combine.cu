@@ -19,40 +19,87 @@ struct CombineParams {
   int S, B, H, Tq, D, phase;
 };
 
+constexpr int kCombineThreads = 256;
+constexpr int kCombineMaxSplits = 1024;   // weights of one row live in shared memory
+
+// One block per (b, h, t) row.  Phase 1: the threads share out the splits, find the row
+// maximum and turn every split's (m, l) into a weight 2^(m_s - m) and the row sum.  Phase 2:
+// the block is (split group) x (pair of head-dim elements); each thread accumulates its
+// splits with independent loads, and the groups are summed through shared memory.
 template <typename TP, typename TO>
-__global__ void __launch_bounds__(128) combine_kernel(CombineParams p) {
-  // one block per (b, h, t) row; thread handles 2 consecutive d per pass
+__global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams p) {
+  __shared__ float s_w[kCombineMaxSplits];
+  __shared__ float s_red[kCombineThreads / 32];
+  __shared__ float s_acc[kCombineThreads][2];
   int64_t row = blockIdx.x;
   const int t = (int)(row % p.Tq); row /= p.Tq;
   const int h = (int)(row % p.H);
   const int b = (int)(row / p.H);
   if (p.user_phase != nullptr && p.user_phase[b * p.phase_stride] != (uint8_t)p.phase) return;
+  const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  const int64_t ml_off = b * p.pm_s[1] + h * p.pm_s[2] + t * p.pm_s[3];
+  const int64_t l_off = b * p.pl_s[1] + h * p.pl_s[2] + t * p.pl_s[3];
 
+  // ---- phase 1 ----
   float m = -INFINITY;
-  for (int s = 0; s < p.S; ++s)
-    m = fmaxf(m, p.pm[s * p.pm_s[0] + b * p.pm_s[1] + h * p.pm_s[2] + t * p.pm_s[3]]);
-  float l = 0.f;
-  for (int s = 0; s < p.S; ++s) {
-    const float ms = p.pm[s * p.pm_s[0] + b * p.pm_s[1] + h * p.pm_s[2] + t * p.pm_s[3]];
-    const float ls = p.pl[s * p.pl_s[0] + b * p.pl_s[1] + h * p.pl_s[2] + t * p.pl_s[3]];
-    if (ms != -INFINITY) l += ls * exp2f(ms - m);
+  for (int s = tid; s < p.S; s += kCombineThreads) {
+    const float ms = p.pm[s * p.pm_s[0] + ml_off];
+    s_w[s] = ms;
+    m = fmaxf(m, ms);
   }
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (lane == 0) s_red[warp] = m;
+  __syncthreads();
+  m = s_red[0];
+  for (int w = 1; w < kCombineThreads / 32; ++w) m = fmaxf(m, s_red[w]);
+  __syncthreads();
+  float l = 0.f;
+  for (int s = tid; s < p.S; s += kCombineThreads) {
+    const float ms = s_w[s];
+    const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
+    s_w[s] = w;
+    if (w != 0.f) l += p.pl[s * p.pl_s[0] + l_off] * w;
+  }
+  for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+  if (lane == 0) s_red[warp] = l;
+  __syncthreads();
+  l = 0.f;
+  for (int w = 0; w < kCombineThreads / 32; ++w) l += s_red[w];
   const float inv_l = l > 0.f ? 1.0f / l : 0.f;
 
+  // ---- phase 2 ----
   const TP* po = (const TP*)p.po + b * p.po_s[1] + h * p.po_s[2] + t * p.po_s[3];
   TO* o = (TO*)p.o + b * p.o_s[0] + h * p.o_s[1] + t * p.o_s[2];
-  for (int d = threadIdx.x * 2; d < p.D; d += blockDim.x * 2) {
+  const int pairs = (p.D + 1) / 2;
+  // as many split groups as fit: pairs * groups <= threads (groups >= 1)
+  int groups = kCombineThreads / pairs;
+  if (groups < 1) groups = 1;
+  if (groups > p.S) groups = p.S;
+  for (int d0 = 0; d0 < pairs; d0 += kCombineThreads / groups) {
+    const int per = kCombineThreads / groups;          // pairs handled per pass
+    const int grp = tid / per, pi = d0 + tid % per;
     float a0 = 0.f, a1 = 0.f;
-    for (int s = 0; s < p.S; ++s) {
-      const float ms = p.pm[s * p.pm_s[0] + b * p.pm_s[1] + h * p.pm_s[2] + t * p.pm_s[3]];
-      if (ms == -INFINITY) continue;
-      const float w = exp2f(ms - m);
-      const TP* src = po + s * p.po_s[0] + d;
-      a0 += ElemTraits<TP>::to_float(src[0]) * w;
-      if (d + 1 < p.D) a1 += ElemTraits<TP>::to_float(src[1]) * w;
+    if (grp < groups && pi < pairs) {
+      const int d = 2 * pi;
+      const bool two = d + 1 < p.D;
+#pragma unroll 4
+      for (int s = grp; s < p.S; s += groups) {
+        const float w = s_w[s];
+        if (w == 0.f) continue;
+        const TP* src = po + s * p.po_s[0] + d;
+        a0 += ElemTraits<TP>::to_float(src[0]) * w;
+        if (two) a1 += ElemTraits<TP>::to_float(src[1]) * w;
+      }
     }
-    o[d] = ElemTraits<TO>::from_float(a0 * inv_l);
-    if (d + 1 < p.D) o[d + 1] = ElemTraits<TO>::from_float(a1 * inv_l);
+    __syncthreads();
+    s_acc[tid][0] = a0; s_acc[tid][1] = a1;
+    __syncthreads();
+    if (grp == 0 && pi < pairs) {
+      for (int g2 = 1; g2 < groups; ++g2) { a0 += s_acc[g2 * per + tid][0]; a1 += s_acc[g2 * per + tid][1]; }
+      const int d = 2 * pi;
+      o[d] = ElemTraits<TO>::from_float(a0 * inv_l);
+      if (d + 1 < p.D) o[d + 1] = ElemTraits<TO>::from_float(a1 * inv_l);
+    }
   }
 }
 
@@ -69,10 +116,11 @@ int launch_combine(const G4bCombineArgs& a, cudaStream_t st) {
   const int64_t rows = (int64_t)p.B * p.H * p.Tq;
   if (rows == 0) return G4B_OK;
   if (rows > 0x7fffffffLL) return fail(G4B_ERR_UNSUPPORTED, "combine: too many rows");
+  if (p.S > kCombineMaxSplits) return fail(G4B_ERR_TOO_LARGE, "combine: at most %d splits", kCombineMaxSplits);
   bool launched = false;
   G4B_DISPATCH_FLOAT(a.partial_o.dtype, TP,
     G4B_DISPATCH_FLOAT(a.o.dtype, TO,
-      combine_kernel<TP, TO><<<(unsigned)rows, 128, 0, st>>>(p); launched = true));
+      combine_kernel<TP, TO><<<(unsigned)rows, kCombineThreads, 0, st>>>(p); launched = true));
   if (!launched) return fail(G4B_ERR_BAD_DTYPE, "combine: partial_o/o dtypes must be f32, f16 or bf16");
   G4B_CUDA_CHECK(cudaGetLastError());
   return G4B_OK;

@@ -218,9 +218,11 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 2) decode_kernel(DecodePara
   // ---- key range of this split (fa2.py:52-67, with block-aligned split boundaries) ----
   const int time = p.time_dim_sizes[b * p.time_stride];
   const int window = min(time, p.ctx_window);
-  int lo_all = 0;
-  if (p.sliding_window > 0) lo_all = max(0, window - p.sliding_window);
-  const int hi_all = window;
+  // Ring mode counts keys from the oldest one the cache exposes; a paged cache is addressed
+  // by absolute position, so there the exposed window is just another lower bound.
+  int lo_all = kPaged ? time - window : 0;
+  const int hi_all = kPaged ? time : window;
+  if (p.sliding_window > 0) lo_all = max(lo_all, hi_all - p.sliding_window);
   const int lo_al = lo_all & ~15;
   const int nblk = hi_all > lo_al ? (hi_all - lo_al + 15) >> 4 : 0;
   const int bps = (nblk + p.num_splits - 1) / p.num_splits;   // blocks per split
@@ -234,13 +236,23 @@ __global__ void __launch_bounds__(kDecodeWarps * 32, 2) decode_kernel(DecodePara
   if (gi < R) {
     const int h = g * R + gi;
     const int64_t qoff = b * p.q_s0 + h * p.q_s1;
+    const bool q_is_t = p.q_dtype == ElemTraits<T>::kDtype;
+    if (q_is_t && ((reinterpret_cast<uintptr_t>((const T*)p.q + qoff) & 15) == 0)) {
+      // same element type as the cache: the 16 bytes are the fragment registers as they are
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float f[8];
+      for (int i = 0; i < 8; ++i) {
+        const uint4 w = *reinterpret_cast<const uint4*>((const T*)p.q + qoff + 32 * i + 8 * c);
+        qf[i][0] = w.x; qf[i][1] = w.y; qf[i][2] = w.z; qf[i][3] = w.w;
+      }
+    } else {
 #pragma unroll
-      for (int e = 0; e < 8; ++e) f[e] = load_as_float(p.q, qoff + 32 * i + 8 * c + e, p.q_dtype);
+      for (int i = 0; i < 8; ++i) {
+        float f[8];
 #pragma unroll
-      for (int e = 0; e < 4; ++e) qf[i][e] = Mma<T>::pack(f[2 * e], f[2 * e + 1]);
+        for (int e = 0; e < 8; ++e) f[e] = load_as_float(p.q, qoff + 32 * i + 8 * c + e, p.q_dtype);
+#pragma unroll
+        for (int e = 0; e < 4; ++e) qf[i][e] = Mma<T>::pack(f[2 * e], f[2 * e + 1]);
+      }
     }
   }
 

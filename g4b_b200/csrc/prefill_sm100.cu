@@ -50,15 +50,17 @@ constexpr uint32_t kColO = 0, kColS0 = 256, kColS1 = 384;
 
 enum : int32_t {
   kErrQFull = 0x301, kErrKvEmpty = 0x302, kErrKvFull = 0x303, kErrSFull = 0x304,
-  kErrPFull = 0x305, kErrPvDone = 0x306, kErrSmemAlign = 0x307, kErrPair = 0x308,
+  kErrPFull = 0x305, kErrPvDone = 0x306, kErrSmemAlign = 0x307, kErrPair = 0x308, kErrBadPage = 0x309,
 };
 
 struct PrefillParams {
   void* o;
   const void* k; const void* v;              // raw cache pointers (manual fallback loads)
   const int32_t* time_dim_sizes; const uint8_t* user_phase;
+  const int32_t* block_tables;               // paged mode: [B, max_pages]; else null
   int64_t o_s0, o_s1, o_s2;
-  int64_t time_stride, phase_stride;
+  int64_t time_stride, phase_stride, bt_s0, bt_s1;
+  int page_shift, num_pages, max_pages;      // paged mode
   int B, H, G, Tq, T;
   int ctx_window, sliding_window, phase, causal;
   int o_dtype;
@@ -93,26 +95,47 @@ __device__ long long g_trace[128][16];
 #define G4B_TRACE_AT(tile, slot) do {} while (0)
 #endif
 
-// Copies rows [row0, row0 + nrows) of a chunk with ordinary loads, applying the 128-byte
-// swizzle by hand; rows whose logical key is outside [0, window) are written as zeros.
-// Used for the tile that crosses the end of the ring buffer and for V rows past the window
-// (which may hold anything, and 0 x NaN would poison the accumulator).
+// Where logical key `key` of this (slot, kv head) lives, or null if it is outside the
+// context (ring buffer or page pool).
+template <typename T>
+struct KeySource {
+  const T* base;            // ring: start of (b, g); paged: start of the pool
+  const int32_t* bt;        // paged: block table row of slot b
+  int64_t bt_s1;
+  int ring_start, Trows;    // ring
+  int G, g, page_shift, num_pages, max_pages;   // paged
+  int window;               // keys [0, window) exist
+  bool paged;
+  __device__ __forceinline__ const T* row(int key) const {
+    if (key < 0 || key >= window) return nullptr;
+    if (!paged) {
+      int pr = ring_start + key;
+      if (pr >= Trows) pr -= Trows;
+      return base + (int64_t)pr * kHD;
+    }
+    const int pg = key >> page_shift;
+    if (pg >= max_pages) return nullptr;
+    const int page = bt[pg * bt_s1];
+    if (page < 0 || page >= num_pages) return nullptr;
+    return base + ((((int64_t)page * G + g) << page_shift) + (key & ((1 << page_shift) - 1))) * kHD;
+  }
+};
+
+// Copies `nrows` rows of a chunk with ordinary loads, applying the 128-byte swizzle by hand;
+// rows whose key is outside the context are written as zeros.  Used for the tile that crosses
+// the end of the ring buffer and for V rows past the context (which may hold anything, and
+// 0 x NaN would poison the accumulator).
 //   slab_rows: rows per slab (128 for K chunks, 64 for V chunks); d0: first head-dim element;
 //   nslabs: 64-element slabs in the chunk.
 template <typename T>
-__device__ __forceinline__ void manual_chunk(uint8_t* dst, const T* cache_bg, int ring_start, int Trows,
-                                             int key0, int nrows, int window, int d0, int nslabs,
-                                             int slab_rows, int lane) {
+__device__ __forceinline__ void manual_chunk(uint8_t* dst, const KeySource<T>& src, int key0, int nrows, int d0,
+                                             int nslabs, int slab_rows, int lane) {
   const int chunks_per_row = nslabs * 8;   // 16-byte pieces per row
   for (int idx = lane; idx < nrows * chunks_per_row; idx += 32) {
     const int r = idx / chunks_per_row, ch = idx % chunks_per_row;
-    const int key = key0 + r;
     uint4 val = make_uint4(0u, 0u, 0u, 0u);
-    if (key >= 0 && key < window) {
-      int pr = ring_start + key;
-      if (pr >= Trows) pr -= Trows;
-      val = *reinterpret_cast<const uint4*>(cache_bg + (int64_t)pr * kHD + d0 + ch * 8);
-    }
+    const T* rp = src.row(key0 + r);
+    if (rp != nullptr) val = *reinterpret_cast<const uint4*>(rp + d0 + ch * 8);
     const int slab = ch >> 3, c16 = ch & 7;
     uint8_t* p = dst + slab * (slab_rows * 128) + r * 128 + ((c16 ^ (r & 7)) << 4);
     *reinterpret_cast<uint4*>(p) = val;
@@ -184,17 +207,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
   }
 
   // ---- geometry of this CTA's key range (fa2.py:52-64) ----
+  // Ring mode counts keys from the oldest one the cache exposes (fa2.py:52-56).  A paged cache
+  // is addressed by absolute position: all `time` keys are addressable (so 128-key tiles
+  // start on page boundaries) and the exposed window is just another lower bound.
+  const bool paged = p.block_tables != nullptr;
   const int time = p.time_dim_sizes[b * p.time_stride];
-  const int window = min(time, p.ctx_window);
-  const int ring_start = max(time - p.ctx_window, 0) % p.T;
+  const int window = paged ? time : min(time, p.ctx_window);
+  const int win_lo = paged ? max(0, time - p.ctx_window) : 0;
+  const int ring_start = paged ? 0 : max(time - p.ctx_window, 0) % p.T;
   const int q_t_base = window - p.Tq;                    // logical position of query row 0
   const int rows_valid = min(kBM, p.Tq - m0);
   const int qpos_min = q_t_base + m0;
   const int qpos_max = q_t_base + m0 + rows_valid - 1;
   const int key_hi = p.causal ? min(window, qpos_max + 1) : window;
-  const int key_lo = p.sliding_window > 0 ? max(0, qpos_min - p.sliding_window + 1) : 0;
+  const int key_lo = p.sliding_window > 0 ? max(win_lo, qpos_min - p.sliding_window + 1) : win_lo;
   // CTA-uniform: some row of this tile may see fewer than 64 keys in all
-  const bool few_keys = qpos_min < 64 || (p.sliding_window > 0 && p.sliding_window < 64);
+  const bool few_keys = qpos_min - win_lo < 64 || (p.sliding_window > 0 && p.sliding_window < 64);
   const bool precise = PackT<T>::kSplitP && few_keys;
   const int tile_lo = key_lo / kBN;
   const int n_tiles = key_hi > key_lo ? (key_hi + kBN - 1) / kBN - tile_lo : 0;
@@ -246,8 +274,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
 
   if (warp == 0) {
     // =============================== producer ===============================
-    const T* kbg = (const T*)p.k + ((int64_t)b * p.G + g) * p.T * kHD;
-    const T* vbg = (const T*)p.v + ((int64_t)b * p.G + g) * p.T * kHD;
+    KeySource<T> ksrc, vsrc;
+    ksrc.paged = paged; ksrc.window = window; ksrc.ring_start = ring_start; ksrc.Trows = p.T;
+    ksrc.G = p.G; ksrc.g = g; ksrc.page_shift = p.page_shift; ksrc.num_pages = p.num_pages;
+    ksrc.max_pages = p.max_pages; ksrc.bt = paged ? p.block_tables + b * p.bt_s0 : nullptr; ksrc.bt_s1 = p.bt_s1;
+    ksrc.base = paged ? (const T*)p.k : (const T*)p.k + ((int64_t)b * p.G + g) * p.T * kHD;
+    vsrc = ksrc;
+    vsrc.base = paged ? (const T*)p.v : (const T*)p.v + ((int64_t)b * p.G + g) * p.T * kHD;
     const int bg = b * p.G + g;
     if (lane == 0) {
       ptx::mbar_arrive_expect_tx(bar_q, kQBytes);
@@ -264,26 +297,60 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       if (!w) { if (lane == 0) record(p.status, kErrKvEmpty); ok = false; }
       return w != 0;
     };
+    // Paged mode: page ids of the 16-key groups [key0, key0 + 16 n), one per lane; -1 marks a
+    // group that must not be fetched by TMA (outside the table / the pool).
+    auto page_ids = [&](int key0, int n) -> int {
+      int id = -1;
+      if (lane < n) {
+        const int key = key0 + 16 * lane;
+        const int pg = key >> p.page_shift;
+        if (key < window && pg < p.max_pages) {
+          id = ksrc.bt[pg * p.bt_s1];
+          if (id < 0 || id >= p.num_pages) { record(p.status, kErrBadPage); id = -1; }
+        }
+      }
+      return id;
+    };
+    const int page_mask = (1 << p.page_shift) - 1;
     // chunk order = MMA consumption order: K(0) K(1) V(0) K(2) V(1) ... K(n-1) V(n-2) V(n-1)
     auto load_k = [&](int j) {
       const int key0 = (tile_lo + j) * kBN;
       int pr0 = ring_start + key0;
       if (pr0 >= p.T) pr0 -= p.T;
-      const int live = min(kBN, window - key0);          // keys of this tile inside the window
-      const bool wraps = pr0 + live > p.T;
+      const int live = min(kBN, window - key0);          // keys of this tile inside the context
+      bool manual;
+      int my_page = -1;
+      if (paged) {
+        my_page = page_ids(key0, 8);
+        // every 16-key group that holds live keys needs a page; K rows past the context are
+        // masked later, so their groups may come from any valid page (page 0)
+        const bool bad = lane < 8 && key0 + 16 * lane < window && my_page < 0;
+        manual = __any_sync(0xffffffffu, bad);
+        if (my_page < 0) my_page = 0;
+      } else {
+        manual = pr0 + live > p.T;                       // the tile crosses the end of the ring
+      }
       for (int kc = 0; kc < 2 && ok; ++kc, ++cc) {
         const int st = cc % kStages;
         const uint32_t full = ptx::smem_u32(&bars->kv_full[st]);
         if (!wait_empty(st, cc)) break;
         uint8_t* dst = sRing + st * kChunkBytes;
-        if (!wraps) {
-          if (lane == 0) {
-            ptx::mbar_arrive_expect_tx(full, kChunkBytes);
+        if (!manual) {
+          if (lane == 0) ptx::mbar_arrive_expect_tx(full, kChunkBytes);
+          __syncwarp();
+          if (!paged) {
+            if (lane == 0)
+              for (int s = 0; s < 2; ++s)
+                ptx::tma_load_3d(ptx::smem_u32(dst + s * 16384), &k_map, full, kc * 128 + s * 64, pr0, bg);
+          } else if (lane < 8) {
+            // lane i fetches its own 16-key group: 2 slabs of [16 rows x 64 d]
+            const int row = (key0 + 16 * lane) & page_mask;
             for (int s = 0; s < 2; ++s)
-              ptx::tma_load_3d(ptx::smem_u32(dst + s * 16384), &k_map, full, kc * 128 + s * 64, pr0, bg);
+              ptx::tma_load_4d(ptx::smem_u32(dst + s * 16384 + lane * 2048), &k_map, full, kc * 128 + s * 64, row, g,
+                               my_page);
           }
         } else {
-          manual_chunk<T>(dst, kbg, ring_start, p.T, key0, kBN, window, kc * 128, 2, 128, lane);
+          manual_chunk<T>(dst, ksrc, key0, kBN, kc * 128, 2, 128, lane);
           ptx::fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(full);
@@ -298,20 +365,31 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         int pr0 = ring_start + key0;
         if (pr0 >= p.T) pr0 -= p.T;
         const int live = min(64, window - key0);
-        // rows past the window must read as zero; rows past the ring end must wrap
-        const bool manual = live < 64 || pr0 + 64 > p.T;
+        // rows past the context must read as zero; rows past the ring end must wrap
+        bool manual = live < 64 || (!paged && pr0 + 64 > p.T);
+        int my_page = -1;
+        if (paged && !manual) {
+          my_page = page_ids(key0, 4);
+          manual = __any_sync(0xffffffffu, lane < 4 && my_page < 0);
+        }
         const int st = cc % kStages;
         const uint32_t full = ptx::smem_u32(&bars->kv_full[st]);
         if (!wait_empty(st, cc)) break;
         uint8_t* dst = sRing + st * kChunkBytes;
         if (!manual) {
-          if (lane == 0) {
-            ptx::mbar_arrive_expect_tx(full, kChunkBytes);
+          if (lane == 0) ptx::mbar_arrive_expect_tx(full, kChunkBytes);
+          __syncwarp();
+          if (!paged) {
+            if (lane == 0)
+              for (int s = 0; s < 4; ++s)
+                ptx::tma_load_3d(ptx::smem_u32(dst + s * 8192), &v_map, full, s * 64, pr0, bg);
+          } else if (lane < 4) {
+            const int row = (key0 + 16 * lane) & page_mask;
             for (int s = 0; s < 4; ++s)
-              ptx::tma_load_3d(ptx::smem_u32(dst + s * 8192), &v_map, full, s * 64, pr0, bg);
+              ptx::tma_load_4d(ptx::smem_u32(dst + s * 8192 + lane * 2048), &v_map, full, s * 64, row, g, my_page);
           }
         } else {
-          manual_chunk<T>(dst, vbg, ring_start, p.T, key0, 64, window, 0, 4, 64, lane);
+          manual_chunk<T>(dst, vsrc, key0, 64, 0, 4, 64, lane);
           ptx::fence_proxy_async_smem();
           __syncwarp();
           if (lane == 0) ptx::mbar_arrive(full);
@@ -443,7 +521,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     };
     const int qpos = q_t_base + m0 + r;
     const int hi_r = p.causal ? min(window, qpos + 1) : window;
-    const int lo_r = p.sliding_window > 0 ? max(0, qpos - p.sliding_window + 1) : 0;
+    const int lo_r = p.sliding_window > 0 ? max(win_lo, qpos - p.sliding_window + 1) : win_lo;
     float m_used = -INFINITY;   // reference maximum the accumulated O and l are scaled by
     float l_run = 0.f;          // this thread's half of the row sum
     bool ok = true;
@@ -720,8 +798,7 @@ extern "C" int g4b_debug_read_trace(long long* out) {
 #endif
 
 int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
-  if (a.block_tables.ptr != nullptr)
-    return fail(G4B_ERR_UNSUPPORTED, "prefill over a paged cache is not built yet; use the ring layout");
+  const bool paged = a.block_tables.ptr != nullptr;
   if (a.q.dtype != a.k_cache.dtype)
     return fail(G4B_ERR_BAD_DTYPE, "prefill: q must have the cache dtype (f16 or bf16)");
   if (a.o.dtype != a.q.dtype && a.o.dtype != G4B_F32)
@@ -749,13 +826,21 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
     const uint32_t box[4] = {64, (uint32_t)kBM, 1, 1};
     if ((rc = encode_map(&qm, a.q.dtype, 4, a.q.ptr, dims, strides, box, "q"))) return rc;
   }
-  {
+  if (!paged) {
     const uint64_t dims[3] = {(uint64_t)D, (uint64_t)T, (uint64_t)(B * G)};
     const uint64_t strides[2] = {(uint64_t)D * esz, (uint64_t)T * D * esz};
     const uint32_t boxk[3] = {64, (uint32_t)kBN, 1};
     const uint32_t boxv[3] = {64, 64, 1};
     if ((rc = encode_map(&km, a.k_cache.dtype, 3, a.k_cache.ptr, dims, strides, boxk, "k_cache"))) return rc;
     if ((rc = encode_map(&vm, a.v_cache.dtype, 3, a.v_cache.ptr, dims, strides, boxv, "v_cache"))) return rc;
+  } else {
+    // pool [num_pages, G, page, D]: one box = 16 rows of one (page, kv head), 64 elements wide
+    const uint64_t P = (uint64_t)a.k_cache.shape[2], NP = (uint64_t)a.k_cache.shape[0];
+    const uint64_t dims[4] = {(uint64_t)D, P, (uint64_t)G, NP};
+    const uint64_t strides[3] = {(uint64_t)D * esz, P * D * esz, (uint64_t)G * P * D * esz};
+    const uint32_t box[4] = {64, 16, 1, 1};
+    if ((rc = encode_map(&km, a.k_cache.dtype, 4, a.k_cache.ptr, dims, strides, box, "k pool"))) return rc;
+    if ((rc = encode_map(&vm, a.v_cache.dtype, 4, a.v_cache.ptr, dims, strides, box, "v pool"))) return rc;
   }
   PrefillParams p{};
   p.o = a.o.ptr; p.k = a.k_cache.ptr; p.v = a.v_cache.ptr;
@@ -763,7 +848,15 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   p.user_phase = (const uint8_t*)a.user_phase.ptr;
   p.o_s0 = a.o.stride[0]; p.o_s1 = a.o.stride[1]; p.o_s2 = a.o.stride[2];
   p.time_stride = a.time_dim_sizes.stride[0]; p.phase_stride = a.user_phase.stride[0];
-  p.B = (int)B; p.H = (int)H; p.G = (int)G; p.Tq = (int)Tq; p.T = (int)T;
+  p.B = (int)B; p.H = (int)H; p.G = (int)G; p.Tq = (int)Tq; p.T = paged ? 1 : (int)T;
+  if (paged) {
+    p.block_tables = (const int32_t*)a.block_tables.ptr;
+    p.bt_s0 = a.block_tables.stride[0]; p.bt_s1 = a.block_tables.stride[1];
+    p.page_shift = 0;
+    while ((1 << p.page_shift) < a.page_size) ++p.page_shift;
+    p.num_pages = (int)a.k_cache.shape[0];
+    p.max_pages = (int)a.block_tables.shape[1];
+  }
   p.ctx_window = a.ctx_window_size; p.sliding_window = a.sliding_window; p.phase = a.phase;
   p.causal = a.stage == G4B_STAGE_CAUSAL;
   p.o_dtype = a.o.dtype;

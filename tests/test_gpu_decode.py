@@ -124,6 +124,15 @@ def test_decode_paged_page_size_64_and_window(cuda):
     assert_close(got, want, "paged page 64 + window")
 
 
+def test_decode_paged_window_shorter_than_context(cuda):
+    """A paged cache keeps absolute positions: ctx_window_size < context exposes the tail."""
+    case = make_paged_case(36, lens=[1000, 300, 77], H=8, G=2, dtype=torch.float16)
+    got, _ = run_paged(case, cuda, ctx_window=200, splits=4, max_splits=4)
+    want = orc.flash_attention(case["q"], case["k_pool"], case["v_pool"], torch.zeros_like(case["q"], dtype=torch.float32),
+                               case["time"], None, 200, 2, scale=1 / 16, block_tables=case["block_tables"], page_size=16)
+    assert_close(got, want, "paged, window < context")
+
+
 def test_decode_partials_have_reference_format(cuda):
     """Partials written for S splits merge, with the oracle's combine (fa2.py:618-626), to the
     unsplit answer; the GPU combine agrees with the oracle's on the same partials."""

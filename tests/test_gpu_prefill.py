@@ -176,3 +176,77 @@ def test_prefill_sliding_window_full_size_rows(cuda):
             lo = max(0, r - W + 1)
             want = orc.attention_core(q_phys[b, r:r + 1].permute(1, 0, 2), k[b, :, lo:r + 1], v[b, :, lo:r + 1], scale=1 / 16)
             assert_close(got[b, :, r:r + 1], want, f"b={b} row={r}")
+
+
+# ------------------------------------------------------------------------------------------
+# prefill over a paged cache (not in the reference: block tables + 16-token pages)
+# ------------------------------------------------------------------------------------------
+def make_paged_prefill_case(seed, *, times, Tq, H, G, page_size=16, dtype=torch.bfloat16, poison=False):
+    from helpers import make_paged_case
+    case = make_paged_case(seed, lens=times, H=H, G=G, dtype=dtype, page_size=page_size)
+    gen = torch.Generator().manual_seed(seed + 1)
+    B = len(times)
+    case["q_phys"] = randn(gen, B, Tq, H, 256, dtype=dtype)
+    case["q"] = case["q_phys"].permute(0, 2, 1, 3)
+    if poison:   # rows past each sequence's length hold NaN: they must never be multiplied in
+        for b, n in enumerate(times):
+            last = int(case["block_tables"][b, (n - 1) // page_size])
+            r = n % page_size
+            if r:
+                case["k_pool"][last, :, r:] = float("nan")
+                case["v_pool"][last, :, r:] = float("nan")
+    return case
+
+
+def run_paged_prefill(case, cuda, *, ctx_window=None, sliding_window=None, stage=fa2.STAGE_CAUSAL):
+    q_phys = case["q_phys"].to(cuda)
+    o_phys = torch.zeros_like(q_phys)
+    fa2.flash_attention(q_phys.permute(0, 2, 1, 3), case["k_pool"].to(cuda), case["v_pool"].to(cuda),
+                        o_phys.permute(0, 2, 1, 3), case["time"].to(cuda), None, ctx_window or case["max_len"], 1,
+                        scale=1 / 16, sliding_window=sliding_window, block_tables=case["block_tables"].to(cuda),
+                        page_size=case["page_size"], stage=stage)
+    return o_phys.permute(0, 2, 1, 3).cpu()
+
+
+def oracle_paged_prefill(case, *, ctx_window=None, sliding_window=None, stage=fa2.STAGE_CAUSAL):
+    kp = torch.nan_to_num(case["k_pool"].float(), nan=0.0)
+    vp = torch.nan_to_num(case["v_pool"].float(), nan=0.0)
+    return orc.flash_attention(case["q"], kp, vp, torch.zeros_like(case["q"], dtype=torch.float32), case["time"], None,
+                               ctx_window or case["max_len"], 1, stage=stage, scale=1 / 16,
+                               sliding_window=sliding_window, block_tables=case["block_tables"],
+                               page_size=case["page_size"])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("times,Tq", [([128, 300, 1000], 128), ([200, 200], 200), ([640, 37 + 256, 513], 256)])
+def test_prefill_paged_chunk(cuda, dtype, times, Tq):
+    """The last Tq tokens of ragged contexts attend through shuffled block tables; partial
+    last pages hold NaN beyond the context."""
+    case = make_paged_prefill_case(60, times=times, Tq=Tq, H=8, G=2, dtype=dtype, poison=True)
+    assert_close(run_paged_prefill(case, cuda), oracle_paged_prefill(case), "paged prefill")
+
+
+def test_prefill_paged_windows_and_page_64(cuda):
+    case = make_paged_prefill_case(61, times=[1000, 777], Tq=384, H=16, G=4, page_size=64, dtype=torch.float16)
+    for kw in (dict(sliding_window=200), dict(ctx_window=500), dict(ctx_window=640, sliding_window=100),
+               dict(stage=fa2.STAGE_FULL)):
+        assert_close(run_paged_prefill(case, cuda, **kw), oracle_paged_prefill(case, **kw), f"paged prefill {kw}")
+
+
+def test_prefill_paged_bad_table_entry_is_reported(cuda):
+    from g4b_b200 import _cabi
+    case = make_paged_prefill_case(62, times=[256], Tq=128, H=8, G=2)
+    case["block_tables"][0, 3] = 10 ** 6
+    got = run_paged_prefill(case, cuda)
+    assert torch.isfinite(got).all()
+    assert _cabi.device_status() == 0x309
+
+
+def test_prefill_paged_equals_ring(cuda):
+    """Same keys through a ring cache and through pages: identical outputs."""
+    case = make_paged_prefill_case(63, times=[512, 512], Tq=512, H=8, G=2, dtype=torch.bfloat16)
+    paged = run_paged_prefill(case, cuda)
+    k = torch.stack([orc.gather_pages(case["k_pool"], case["block_tables"][b], 512, 16) for b in range(2)])
+    v = torch.stack([orc.gather_pages(case["v_pool"], case["block_tables"][b], 512, 16) for b in range(2)])
+    ring = dict(q_phys=case["q_phys"], q=case["q"], k=k.contiguous(), v=v.contiguous(), time=case["time"], ctx_window=512)
+    assert torch.equal(run(ring, cuda), paged)
