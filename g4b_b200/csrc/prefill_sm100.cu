@@ -31,6 +31,7 @@
 #include "sm100_ptx.cuh"
 
 #include <cudaTypedefs.h>
+#include <stdlib.h>
 
 namespace g4b {
 
@@ -91,8 +92,13 @@ __device__ long long g_trace[128][16];
   do {                                                                                   \
     if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (tile) < 128) g_trace[(tile)][(slot)] = clock64(); \
   } while (0)
+#define G4B_TRACE_PEER(tile, slot)                                                       \
+  do {                                                                                   \
+    if (blockIdx.x == 1 && blockIdx.y == 0 && lane == 0 && (tile) < 128) g_trace[(tile)][(slot)] = clock64(); \
+  } while (0)
 #else
 #define G4B_TRACE_AT(tile, slot) do {} while (0)
+#define G4B_TRACE_PEER(tile, slot) do {} while (0)
 #endif
 
 // Where logical key `key` of this (slot, kv head) lives, or null if it is outside the
@@ -176,7 +182,14 @@ template <> struct PackT<__half> {
   }
 };
 
-template <typename T>
+// kPair = false: one CTA per 128 query rows (cta_group::1).
+// kPair = true : a cluster of two CTAs works on two query heads of the same kv head at the
+//   same query tile (rows 0..127 = the even head in CTA 0, rows 128..255 = the odd head in
+//   CTA 1) with cta_group::2 MMAs issued by CTA 0.  Both heads read the same K/V tiles, and
+//   each CTA stages only half of every tile (K: half the keys, V: half the head dim), so the
+//   ring covers twice the time and Q.K^T reads 96 instead of 128 bytes of shared memory per
+//   cycle -- the two things that starve the single-CTA form.
+template <typename T, bool kPair>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                const __grid_constant__ CUtensorMap v_map, PrefillParams p) {
@@ -187,24 +200,49 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
   const int g = h / (p.H / p.G);
   const int q_tile = (int)gridDim.y - 1 - (int)blockIdx.y;   // heaviest (latest) tiles first
   const int m0 = q_tile * kBM;
+  const uint32_t rank = kPair ? ptx::cluster_ctarank() : 0u;   // 0 = the CTA that issues the MMAs
+  const bool leader = rank == 0;
 
+  // both CTAs of a pair belong to the same slot: they leave together
   if (p.user_phase != nullptr && p.user_phase[b * p.phase_stride] != (uint8_t)p.phase) return;
   uint8_t* smem = smem_raw;
   uint8_t* sQ = smem;
   uint8_t* sRing = smem + kQBytes;
   Barriers* bars = reinterpret_cast<Barriers*>(smem + kQBytes + kStages * kChunkBytes);
   float* xchg = reinterpret_cast<float*>(smem + kQBytes + kStages * kChunkBytes + 256);
-  {
-    // an earlier CTA gave up on a wait: drain the grid.  One thread reads so all agree.
-    // The swizzled tiles need the buffer on a 1024-byte boundary: refuse to run otherwise.
-    if (threadIdx.x == 0) {
+  const uint32_t bar_q = ptx::smem_u32(&bars->q_full);
+  const uint32_t bar_pv = ptx::smem_u32(&bars->pv_done);
+  if (threadIdx.x == 0) {
+    // In a pair, the barriers the MMA issuer waits on live in CTA 0 and count both CTAs.
+    constexpr uint32_t kN = kPair ? 2u : 1u;
+    ptx::mbar_init(bar_q, kN);
+    for (int s = 0; s < kStages; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&bars->kv_full[s]), kN);
+      ptx::mbar_init(ptx::smem_u32(&bars->kv_empty[s]), 1);
+    }
+    for (int s = 0; s < 2; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&bars->s_full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&bars->p_a[s]), 8 * kN);   // one arrival per softmax warp
+      ptx::mbar_init(ptx::smem_u32(&bars->p_b[s]), 8 * kN);
+    }
+    ptx::mbar_init(bar_pv, 1);
+    for (int s = 0; s < 4; ++s) ptx::mbar_init(ptx::smem_u32(&bars->pair[s]), 2);   // one arrival per warp of the pair
+    ptx::fence_barrier_init();
+    ptx::prefetch_tensormap(&q_map);
+    ptx::prefetch_tensormap(&k_map);
+    ptx::prefetch_tensormap(&v_map);
+    // An earlier CTA gave up on a wait: drain the grid.  One thread reads so all agree (in a
+    // pair: CTA 0 decides for both).  The swizzled tiles need the buffer on a 1024-byte
+    // boundary: refuse to run otherwise.
+    if (leader) {
       int32_t a = *reinterpret_cast<volatile int32_t*>(p.status);
       if (a == 0 && (ptx::smem_u32(smem_raw) & 1023u) != 0) { record(p.status, kErrSmemAlign); a = kErrSmemAlign; }
       bars->abort_flag = a;
+      if constexpr (kPair) ptx::st_cluster_u32(ptx::map_to_cta(ptx::smem_u32(&bars->abort_flag), 1), (uint32_t)a);
     }
-    __syncthreads();
-    if (bars->abort_flag != 0) return;
   }
+  if constexpr (kPair) ptx::cluster_sync_all(); else __syncthreads();
+  if (*reinterpret_cast<volatile int32_t*>(&bars->abort_flag) != 0) return;
 
   // ---- geometry of this CTA's key range (fa2.py:52-64) ----
   // Ring mode counts keys from the oldest one the cache exposes (fa2.py:52-56).  A paged cache
@@ -243,34 +281,36 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     return;
   }
 
-  const uint32_t bar_q = ptx::smem_u32(&bars->q_full);
-  const uint32_t bar_pv = ptx::smem_u32(&bars->pv_done);
-  if (threadIdx.x == 0) {
-    ptx::mbar_init(bar_q, 1);
-    for (int s = 0; s < kStages; ++s) {
-      ptx::mbar_init(ptx::smem_u32(&bars->kv_full[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->kv_empty[s]), 1);
-    }
-    for (int s = 0; s < 2; ++s) {
-      ptx::mbar_init(ptx::smem_u32(&bars->s_full[s]), 1);
-      ptx::mbar_init(ptx::smem_u32(&bars->p_a[s]), 256);
-      ptx::mbar_init(ptx::smem_u32(&bars->p_b[s]), 256);
-    }
-    ptx::mbar_init(bar_pv, 1);
-    for (int s = 0; s < 4; ++s) ptx::mbar_init(ptx::smem_u32(&bars->pair[s]), 64);
-    ptx::fence_barrier_init();
-    ptx::prefetch_tensormap(&q_map);
-    ptx::prefetch_tensormap(&k_map);
-    ptx::prefetch_tensormap(&v_map);
-  }
   if (warp == 1) {
-    ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), 512);
-    ptx::tmem_relinquish();
+    if constexpr (kPair) {
+      ptx::tmem_alloc_pair(ptx::smem_u32(&bars->tmem_base), 512);
+      ptx::tmem_relinquish_pair();
+    } else {
+      ptx::tmem_alloc(ptx::smem_u32(&bars->tmem_base), 512);
+      ptx::tmem_relinquish();
+    }
   }
   ptx::tc_fence_before();
   __syncthreads();
   ptx::tc_fence_after();
   const uint32_t tmem = *reinterpret_cast<volatile uint32_t*>(&bars->tmem_base);
+  // where this CTA's arrivals for the MMA issuer go (CTA 0's copy of the barrier)
+  auto issuer_bar = [&](uint64_t* local) -> uint32_t {
+    const uint32_t a = ptx::smem_u32(local);
+    if constexpr (kPair) return ptx::map_to_cta(a, 0);
+    else return a;
+  };
+  // one arrival per warp: every lane has finished (and fenced) its own tensor-memory stores,
+  // the warp converges, one lane signals
+  auto arrive_issuer = [&](uint32_t bar) {
+    __syncwarp();
+    if (lane == 0) {
+      // P lives in tensor memory (ordered by tcgen05.wait::st + tcgen05.fence above), so the
+      // cross-CTA arrival needs no memory ordering of its own
+      if constexpr (kPair) ptx::mbar_arrive_cluster_relaxed(bar);
+      else ptx::mbar_arrive(bar);
+    }
+  };
 
   if (warp == 0) {
     // =============================== producer ===============================
@@ -282,10 +322,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     vsrc = ksrc;
     vsrc.base = paged ? (const T*)p.v : (const T*)p.v + ((int64_t)b * p.G + g) * p.T * kHD;
     const int bg = b * p.G + g;
+    // K/V tiles are re-read by every query tile of 4 heads: keep them in L2; Q is read once
+    const uint64_t pol_kv = ptx::policy_evict_last();
+    const uint64_t pol_q = ptx::policy_evict_first();
     if (lane == 0) {
-      ptx::mbar_arrive_expect_tx(bar_q, kQBytes);
-      for (int s = 0; s < 4; ++s)
-        ptx::tma_load_4d(ptx::smem_u32(sQ + s * 16384), &q_map, bar_q, s * 64, m0, h, b);
+      if constexpr (kPair) {
+        const uint32_t qb = issuer_bar(&bars->q_full);
+        ptx::mbar_arrive_expect_tx_cluster(qb, kQBytes);
+        for (int s = 0; s < 4; ++s)
+          ptx::tma_load_4d_pair(ptx::smem_u32(sQ + s * 16384), &q_map, qb, s * 64, m0, h, b, pol_q);
+      } else {
+        ptx::mbar_arrive_expect_tx(bar_q, kQBytes);
+        for (int s = 0; s < 4; ++s)
+          ptx::tma_load_4d_hint(ptx::smem_u32(sQ + s * 16384), &q_map, bar_q, s * 64, m0, h, b, pol_q);
+      }
     }
     uint32_t cc = 0;   // chunk counter over the ring
     bool ok = true;
@@ -341,13 +391,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           if (!paged) {
             if (lane == 0)
               for (int s = 0; s < 2; ++s)
-                ptx::tma_load_3d(ptx::smem_u32(dst + s * 16384), &k_map, full, kc * 128 + s * 64, pr0, bg);
+                ptx::tma_load_3d_hint(ptx::smem_u32(dst + s * 16384), &k_map, full, kc * 128 + s * 64, pr0, bg, pol_kv);
           } else if (lane < 8) {
             // lane i fetches its own 16-key group: 2 slabs of [16 rows x 64 d]
             const int row = (key0 + 16 * lane) & page_mask;
             for (int s = 0; s < 2; ++s)
-              ptx::tma_load_4d(ptx::smem_u32(dst + s * 16384 + lane * 2048), &k_map, full, kc * 128 + s * 64, row, g,
-                               my_page);
+              ptx::tma_load_4d_hint(ptx::smem_u32(dst + s * 16384 + lane * 2048), &k_map, full, kc * 128 + s * 64, row,
+                                    g, my_page, pol_kv);
           }
         } else {
           manual_chunk<T>(dst, ksrc, key0, kBN, kc * 128, 2, 128, lane);
@@ -382,11 +432,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           if (!paged) {
             if (lane == 0)
               for (int s = 0; s < 4; ++s)
-                ptx::tma_load_3d(ptx::smem_u32(dst + s * 8192), &v_map, full, s * 64, pr0, bg);
+                ptx::tma_load_3d_hint(ptx::smem_u32(dst + s * 8192), &v_map, full, s * 64, pr0, bg, pol_kv);
           } else if (lane < 4) {
             const int row = (key0 + 16 * lane) & page_mask;
             for (int s = 0; s < 4; ++s)
-              ptx::tma_load_4d(ptx::smem_u32(dst + s * 8192 + lane * 2048), &v_map, full, s * 64, row, g, my_page);
+              ptx::tma_load_4d_hint(ptx::smem_u32(dst + s * 8192 + lane * 2048), &v_map, full, s * 64, row, g, my_page,
+                                    pol_kv);
           }
         } else {
           manual_chunk<T>(dst, vsrc, key0, 64, 0, 4, 64, lane);
@@ -397,14 +448,202 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         __syncwarp();
       }
     };
-    load_k(0);
-    if (n_tiles > 1) load_k(1);
-    for (int j = 0; j < n_tiles && ok; ++j) {
-      load_v(j);
-      if (j + 2 < n_tiles) load_k(j + 2);
+    // ---- pair form: one 32 KB chunk per tile and operand.  K chunk = this CTA's 64 keys of
+    // the tile x 256 d (4 slabs of [64 rows x 64 d]); V chunk = all 128 keys x this CTA's 128
+    // head-dim columns (2 slabs of [128 rows x 64 d]).  Every CTA accounts for its own bytes
+    // on CTA 0's barrier (2 arrivals per phase).
+    auto load_k_pair = [&](int j) {
+      const int key0 = (tile_lo + j) * kBN + 64 * (int)rank;
+      int pr0 = ring_start + key0;
+      if (pr0 >= p.T) pr0 -= p.T;
+      const int live = min(64, window - key0);
+      bool manual;
+      int my_page = -1;
+      if (paged) {
+        my_page = page_ids(key0, 4);
+        manual = __any_sync(0xffffffffu, lane < 4 && key0 + 16 * lane < window && my_page < 0);
+        if (my_page < 0) my_page = 0;
+      } else {
+        manual = live > 0 && pr0 + live > p.T;
+      }
+      const int st = cc % kStages;
+      const uint32_t full = issuer_bar(&bars->kv_full[st]);
+      G4B_TRACE_AT(j, 7);
+      if (!wait_empty(st, cc)) return;
+      G4B_TRACE_AT(j, 5);   // K(j) slot free, loads go out
+      uint8_t* dst = sRing + st * kChunkBytes;
+      if (!manual) {
+        if (lane == 0) ptx::mbar_arrive_expect_tx_cluster(full, kChunkBytes);
+        __syncwarp();
+        if (!paged) {
+          if (lane == 0)
+            for (int s = 0; s < 4; ++s)
+              ptx::tma_load_3d_pair(ptx::smem_u32(dst + s * 8192), &k_map, full, s * 64, pr0, bg, pol_kv);
+        } else if (lane < 4) {
+          const int row = (key0 + 16 * lane) & page_mask;
+          for (int s = 0; s < 4; ++s)
+            ptx::tma_load_4d_pair(ptx::smem_u32(dst + s * 8192 + lane * 2048), &k_map, full, s * 64, row, g, my_page,
+                                  pol_kv);
+        }
+      } else {
+        manual_chunk<T>(dst, ksrc, key0, 64, 0, 4, 64, lane);
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(full);
+      }
+      __syncwarp();
+      ++cc;
+    };
+    auto load_v_pair = [&](int j) {
+      const int key0 = (tile_lo + j) * kBN;
+      const int d0 = 128 * (int)rank;
+      int pr0 = ring_start + key0;
+      if (pr0 >= p.T) pr0 -= p.T;
+      const int live = min(kBN, window - key0);
+      bool manual = live < kBN || (!paged && pr0 + kBN > p.T);
+      int my_page = -1;
+      if (paged && !manual) {
+        my_page = page_ids(key0, 8);
+        manual = __any_sync(0xffffffffu, lane < 8 && my_page < 0);
+      }
+      const int st = cc % kStages;
+      const uint32_t full = issuer_bar(&bars->kv_full[st]);
+      G4B_TRACE_AT(j, 6);
+      if (!wait_empty(st, cc)) return;
+      G4B_TRACE_AT(j, 4);   // V(j) slot free, loads go out
+      uint8_t* dst = sRing + st * kChunkBytes;
+      if (!manual) {
+        if (lane == 0) ptx::mbar_arrive_expect_tx_cluster(full, kChunkBytes);
+        __syncwarp();
+        if (!paged) {
+          if (lane == 0)
+            for (int s = 0; s < 2; ++s)
+              ptx::tma_load_3d_pair(ptx::smem_u32(dst + s * 16384), &v_map, full, d0 + s * 64, pr0, bg, pol_kv);
+        } else if (lane < 8) {
+          const int row = (key0 + 16 * lane) & page_mask;
+          for (int s = 0; s < 2; ++s)
+            ptx::tma_load_4d_pair(ptx::smem_u32(dst + s * 16384 + lane * 2048), &v_map, full, d0 + s * 64, row, g,
+                                  my_page, pol_kv);
+        }
+      } else {
+        manual_chunk<T>(dst, vsrc, key0, kBN, d0, 2, 128, lane);
+        ptx::fence_proxy_async_smem();
+        __syncwarp();
+        if (lane == 0) ptx::mbar_arrive_cluster(full);
+      }
+      __syncwarp();
+      ++cc;
+    };
+    if constexpr (kPair) {
+      load_k_pair(0);
+      if (n_tiles > 1 && ok) load_k_pair(1);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        load_v_pair(j);
+        if (ok && j + 2 < n_tiles) load_k_pair(j + 2);
+      }
+    } else {
+      load_k(0);
+      if (n_tiles > 1) load_k(1);
+      for (int j = 0; j < n_tiles && ok; ++j) {
+        load_v(j);
+        if (j + 2 < n_tiles) load_k(j + 2);
+      }
     }
   } else if (warp == 1) {
     // =============================== MMA issuer ===============================
+    if constexpr (kPair) {
+      // Pair form: only CTA 0 issues.  One MMA spans both CTAs: rows 0..127 of the 256-row
+      // tile (A operand, accumulator, P) are CTA 0's, rows 128..255 CTA 1's; the B operand is
+      // split between the two shared memories (K: keys 0..63 | 64..127, V: d 0..127 | 128..255)
+      // at the same offsets.  Completion is signalled to the barriers of both CTAs.
+      if (leader) {
+        constexpr uint32_t idesc_qk = ptx::make_idesc_f16(PackT<T>::kFmt, 256, 128, 0, 0);
+        constexpr uint32_t idesc_pv = ptx::make_idesc_f16(PackT<T>::kFmt, 256, 256, 0, 1);
+        constexpr uint32_t kDescHi = (1024u >> 4) | (1u << 14) | (2u << 29);   // SBO 1024 B, version 1, SWIZZLE_128B
+        constexpr uint32_t kLoKMajor = 1u << 16;
+        constexpr uint32_t kLoVMajor = (16384u >> 4) << 16;   // LBO: 64-wide slabs of 128 rows are 16 KB apart
+        const uint32_t q_lo = (ptx::smem_u32(sQ) >> 4) | kLoKMajor;
+        const uint32_t ring_lo = ptx::smem_u32(sRing) >> 4;
+        auto wait_all = [&](uint32_t bar, uint32_t parity) -> bool {
+          return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity));
+        };
+        auto commit_both = [&](uint64_t* local) {   // same barrier in CTA 0 and CTA 1
+          const uint32_t a = ptx::smem_u32(local);
+          ptx::tc_commit_pair(ptx::map_to_cta(a, 0));
+          ptx::tc_commit_pair(ptx::map_to_cta(a, 1));
+        };
+        bool ok = wait_all(bar_q, 0);
+        if (!ok && lane == 0) record(p.status, kErrQFull);
+        ptx::tc_fence_after();
+        uint32_t cc = 0;
+        auto issue_qk = [&](int j) {
+          const uint32_t d_tmem = tmem + ((j & 1) ? kColS1 : kColS0);
+          const int st = cc % kStages;
+          if (!wait_all(ptx::smem_u32(&bars->kv_full[st]), (cc / kStages) & 1)) {
+            if (lane == 0) record(p.status, kErrKvFull);
+            ok = false; return;
+          }
+          ptx::tc_fence_after();
+          const uint32_t k_lo = (ring_lo + st * (kChunkBytes >> 4)) | kLoKMajor;
+          if (ptx::elect_one()) {
+#pragma unroll
+            for (int k16 = 0; k16 < 16; ++k16) {
+              const uint32_t aoff = ((k16 >> 2) * 16384 + (k16 & 3) * 32) >> 4;   // Q: slabs of 128 rows
+              const uint32_t boff = ((k16 >> 2) * 8192 + (k16 & 3) * 32) >> 4;    // K: slabs of 64 rows
+              ptx::mma_ss_pair(d_tmem, ptx::desc64(q_lo + aoff, kDescHi), ptx::desc64(k_lo + boff, kDescHi), idesc_qk,
+                               k16 != 0);
+            }
+            commit_both(&bars->kv_empty[st]);
+            commit_both(&bars->s_full[j & 1]);
+          }
+          __syncwarp();
+          G4B_TRACE_AT(j, 0);   // QK(j) issued
+          ++cc;
+        };
+        auto issue_pv = [&](int j) {
+          const int st = cc % kStages;
+          if (!wait_all(ptx::smem_u32(&bars->kv_full[st]), (cc / kStages) & 1)) {
+            if (lane == 0) record(p.status, kErrKvFull);
+            ok = false; return;
+          }
+          const uint32_t v_lo = (ring_lo + st * (kChunkBytes >> 4)) | kLoVMajor;
+          const uint32_t p_tmem = tmem + ((j & 1) ? kColS1 : kColS0);
+          G4B_TRACE_AT(j, 3);   // V chunk of tile j seen by the issuer
+          for (int part = 0; part < 2 && ok; ++part) {
+            const uint32_t bar = ptx::smem_u32(part == 0 ? &bars->p_a[j & 1] : &bars->p_b[j & 1]);
+            if (!wait_all(bar, (j >> 1) & 1)) {
+              if (lane == 0) record(p.status, kErrPFull);
+              ok = false; return;
+            }
+            ptx::tc_fence_after();
+            G4B_TRACE_AT(j, 1 + part);   // P part A / B seen by the issuer
+            if (ptx::elect_one()) {
+#pragma unroll
+              for (int i = 0; i < 4; ++i) {
+                // part 0: keys 0..31 and 64..95 (k16 = 0,1,4,5); part 1: the rest
+                const int k16 = (i >> 1) * 4 + part * 2 + (i & 1);
+                const uint64_t vdesc = ptx::desc64(v_lo + (k16 * 2048 >> 4), kDescHi);
+                ptx::mma_ts_pair(tmem + kColO, p_tmem + k16 * 8, vdesc, idesc_pv, (j | part | i) != 0);
+                if (precise) ptx::mma_ts_pair(tmem + kColO, p_tmem + 64 + k16 * 8, vdesc, idesc_pv, 1u);
+              }
+              if (part == 1) {
+                commit_both(&bars->kv_empty[st]);
+                commit_both(&bars->pv_done);
+              }
+            }
+            __syncwarp();
+          }
+          ++cc;
+        };
+        if (ok) issue_qk(0);
+        if (ok && n_tiles > 1) issue_qk(1);
+        for (int j = 0; j < n_tiles && ok; ++j) {
+          issue_pv(j);
+          if (ok && j + 2 < n_tiles) issue_qk(j + 2);
+        }
+      }
+      __syncwarp();
+    } else {
     // The whole warp walks the loop (uniform control flow keeps addresses and descriptors in
     // uniform registers); one elected lane issues each tcgen05 instruction.  Descriptors are
     // a constant upper word plus a lower word that is a base and a compile-time offset.
@@ -500,6 +739,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       if (ok && j + 2 < n_tiles) issue_qk(j + 2);
     }
     __syncwarp();
+    }
   } else {
     // =============================== softmax / epilogue ===============================
     // Two warpgroups share every row: warps 2..5 own the first 64 keys of a tile (and O
@@ -514,7 +754,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     // bounded rendezvous of the two warps that share these rows (a named barrier would have
     // no time limit); false when the partner never arrived
     auto pair_sync = [&]() -> bool {
-      ptx::mbar_arrive(pair_bar);
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(pair_bar);
       const bool w = __all_sync(0xffffffffu, ptx::mbar_wait(pair_bar, pair_phase & 1));
       ++pair_phase;
       return w;
@@ -533,6 +774,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       }
       ptx::tc_fence_after();
       if (warp == 2) G4B_TRACE_AT(j, 8);   // S(j) seen by the softmax warp
+      if (warp == 2) G4B_TRACE_PEER(j, 13);
       const int kbase = (tile_lo + j) * kBN;
       // warp-uniform: does any row of this CTA need element masks in this tile?
       const bool need_mask = (p.causal && kbase + kBN - 1 > qpos_min) || (kbase + kBN > window) ||
@@ -566,10 +808,11 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       // publish the half-row maximum for the partner warp; collect the partner's later
       float* xm = xchg + (j & 1) * (2 * kBM);
       xm[half * kBM + r] = mx;
-      ptx::mbar_arrive(pair_bar);
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(pair_bar);
 
-      const uint32_t bar_pa = ptx::smem_u32(&bars->p_a[j & 1]);
-      const uint32_t bar_pb = ptx::smem_u32(&bars->p_b[j & 1]);
+      const uint32_t bar_pa = issuer_bar(&bars->p_a[j & 1]);   // in a pair: CTA 0's barrier
+      const uint32_t bar_pb = issuer_bar(&bars->p_b[j & 1]);
       uint32_t pk[32];
       // Optimistic path: the reference maximum rarely moves (it only has to stay within 2^8
       // of the true one), so start exponentiating against the current one while the maxima
@@ -601,8 +844,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         ptx::tmem_st16(trow + s_col + half * 32, pk);
         ptx::tc_wait_st();
         ptx::tc_fence_before();
-        ptx::mbar_arrive(bar_pa);
+        arrive_issuer(bar_pa);
         if (warp == 2) G4B_TRACE_AT(j, 11);  // P part A published
+        if (warp == 2) G4B_TRACE_PEER(j, 14);
         const float neg_m = -m_used;
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -615,8 +859,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
         ptx::tc_wait_st();
         ptx::tc_fence_before();
-        ptx::mbar_arrive(bar_pb);
+        arrive_issuer(bar_pb);
         if (warp == 2) G4B_TRACE_AT(j, 12);  // P part B published
+        if (warp == 2) G4B_TRACE_PEER(j, 15);
         // keep the PV-done phase bookkeeping in step (no stall: PV(j-1) ended long ago)
         if (j > 0 && !__all_sync(0xffffffffu, ptx::mbar_wait(bar_pv, (j - 1) & 1))) {
           record(p.status, kErrPvDone); ok = false;
@@ -682,8 +927,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       }
       ptx::tc_wait_st();
       ptx::tc_fence_before();
-      ptx::mbar_arrive(bar_pa);
-      ptx::mbar_arrive(bar_pb);
+      arrive_issuer(bar_pa);
+      arrive_issuer(bar_pb);
     }
 
     // ---- epilogue: O / l -> global ----
@@ -702,6 +947,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     if (ok) {
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
       const bool row_ok = r < rows_valid;
+      const uint64_t pol_o = ptx::policy_evict_first();   // the output is not read again here
       const int64_t off = b * p.o_s0 + h * p.o_s1 + (int64_t)(m0 + r) * p.o_s2 + half * 128;
 #pragma unroll 1
       for (int c4 = 0; c4 < 4; ++c4) {
@@ -713,8 +959,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
             float4* dst = reinterpret_cast<float4*>((float*)p.o + off + c4 * 32);
 #pragma unroll
             for (int i = 0; i < 8; ++i)
-              dst[i] = make_float4(__uint_as_float(ov[4 * i]) * inv_l, __uint_as_float(ov[4 * i + 1]) * inv_l,
-                                   __uint_as_float(ov[4 * i + 2]) * inv_l, __uint_as_float(ov[4 * i + 3]) * inv_l);
+              ptx::st_global_v4_hint(dst + i, make_uint4(__float_as_uint(__uint_as_float(ov[4 * i]) * inv_l),
+                                                         __float_as_uint(__uint_as_float(ov[4 * i + 1]) * inv_l),
+                                                         __float_as_uint(__uint_as_float(ov[4 * i + 2]) * inv_l),
+                                                         __float_as_uint(__uint_as_float(ov[4 * i + 3]) * inv_l)), pol_o);
           } else {
             uint4* dst = reinterpret_cast<uint4*>((T*)p.o + off + c4 * 32);
 #pragma unroll
@@ -724,7 +972,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
               w.y = PackT<T>::pack(__uint_as_float(ov[8 * i + 2]) * inv_l, __uint_as_float(ov[8 * i + 3]) * inv_l);
               w.z = PackT<T>::pack(__uint_as_float(ov[8 * i + 4]) * inv_l, __uint_as_float(ov[8 * i + 5]) * inv_l);
               w.w = PackT<T>::pack(__uint_as_float(ov[8 * i + 6]) * inv_l, __uint_as_float(ov[8 * i + 7]) * inv_l);
-              dst[i] = w;
+              ptx::st_global_v4_hint(dst + i, w, pol_o);
             }
           }
         }
@@ -735,7 +983,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
   // ---- teardown: every thread arrives here, on success and after a failed wait ----
   ptx::tc_fence_before();
   __syncthreads();
-  if (warp == 1) {
+  if constexpr (kPair) {
+    // CTA 0's MMAs read this CTA's shared and tensor memory: leave together
+    ptx::cluster_sync_all();
+    if (warp == 1) {
+      ptx::tc_fence_after();
+      ptx::tmem_dealloc_pair(tmem, 512);
+    }
+  } else if (warp == 1) {
     ptx::tc_fence_after();
     ptx::tmem_dealloc(tmem, 512);
   }
@@ -774,19 +1029,37 @@ static int encode_map(CUtensorMap* map, int dtype, int rank, void* base, const u
   return G4B_OK;
 }
 
-template <typename T>
-static int launch_typed(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const PrefillParams& p,
-                        dim3 grid, cudaStream_t st) {
+template <typename T, bool kPair>
+static int launch_variant(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const PrefillParams& p,
+                          dim3 grid, cudaStream_t st) {
   static bool attr_set[64] = {false};
   int dev = 0;
   G4B_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    G4B_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<T>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    G4B_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<T, kPair>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     attr_set[dev] = true;
   }
-  prefill_kernel<T><<<grid, kThreads, kSmemBytes, st>>>(qm, km, vm, p);
-  G4B_CUDA_CHECK(cudaGetLastError());
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = kPair ? 2 : 1;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  G4B_CUDA_CHECK(cudaLaunchKernelEx(&cfg, prefill_kernel<T, kPair>, qm, km, vm, p));
   return G4B_OK;
+}
+
+template <typename T>
+static int launch_typed(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const PrefillParams& p,
+                        dim3 grid, bool pair, cudaStream_t st) {
+  if (pair) return launch_variant<T, true>(qm, km, vm, p, grid, st);
+  return launch_variant<T, false>(qm, km, vm, p, grid, st);
 }
 
 }  // namespace
@@ -818,6 +1091,10 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   const int64_t n_q_tiles = (Tq + kBM - 1) / kBM;
   if (B * H > 0x7fffffffLL || n_q_tiles > 65535) return fail(G4B_ERR_UNSUPPORTED, "prefill: grid too large");
 
+  // Two heads of one kv head per CTA pair when the head counts allow it; G4B_PREFILL_SINGLE_CTA=1
+  // forces the one-CTA form (for comparisons).
+  static const bool force_single = []() { const char* e = getenv("G4B_PREFILL_SINGLE_CTA"); return e && e[0] == '1'; }();
+  const bool pair = !force_single && (H % 2 == 0) && ((H / G) % 2 == 0);
   CUtensorMap qm, km, vm;
   int rc;
   {
@@ -829,8 +1106,10 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   if (!paged) {
     const uint64_t dims[3] = {(uint64_t)D, (uint64_t)T, (uint64_t)(B * G)};
     const uint64_t strides[2] = {(uint64_t)D * esz, (uint64_t)T * D * esz};
-    const uint32_t boxk[3] = {64, (uint32_t)kBN, 1};
-    const uint32_t boxv[3] = {64, 64, 1};
+    // one CTA: K boxes of a whole tile (128 keys), V boxes of half a tile; a pair: K boxes of
+    // this CTA's 64 keys, V boxes of all 128 keys (of this CTA's half of the head dim)
+    const uint32_t boxk[3] = {64, pair ? 64u : (uint32_t)kBN, 1};
+    const uint32_t boxv[3] = {64, pair ? (uint32_t)kBN : 64u, 1};
     if ((rc = encode_map(&km, a.k_cache.dtype, 3, a.k_cache.ptr, dims, strides, boxk, "k_cache"))) return rc;
     if ((rc = encode_map(&vm, a.v_cache.dtype, 3, a.v_cache.ptr, dims, strides, boxv, "v_cache"))) return rc;
   } else {
@@ -864,8 +1143,8 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   p.status = device_status_ptr();
   if (p.status == nullptr) return G4B_ERR_CUDA;
   dim3 grid((unsigned)(B * H), (unsigned)n_q_tiles, 1);
-  if (a.q.dtype == G4B_BF16) return launch_typed<__nv_bfloat16>(qm, km, vm, p, grid, st);
-  return launch_typed<__half>(qm, km, vm, p, grid, st);
+  if (a.q.dtype == G4B_BF16) return launch_typed<__nv_bfloat16>(qm, km, vm, p, grid, pair, st);
+  return launch_typed<__half>(qm, km, vm, p, grid, pair, st);
 }
 
 }  // namespace g4b
