@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the prefill kernel uses:
-// mbarrier, TMA (cp.async.bulk.tensor, never multicast), tcgen05 MMA / TMEM.
+// mbarrier, TMA (cp.async.bulk.tensor; every load lands in the issuing CTA only), tcgen05 MMA / TMEM.
 // Every wait is bounded: it gives up after a wall-clock limit and reports failure instead
 // of spinning forever, so a protocol bug costs a wrong answer plus a status code, not a
 // hung GPU.
@@ -63,7 +63,7 @@ __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity) {
   return true;
 }
 
-// ---- TMA: tiled bulk tensor loads into this CTA's shared memory (no multicast) ----
+// ---- TMA: tiled bulk tensor loads into this CTA's own shared memory ----
 __device__ __forceinline__ void tma_load_3d(uint32_t dst, const CUtensorMap* map, uint32_t bar, int c0,
                                             int c1, int c2) {
   asm volatile(
