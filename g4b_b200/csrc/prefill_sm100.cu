@@ -51,7 +51,7 @@ constexpr uint32_t kColO = 0, kColS0 = 256, kColS1 = 384;
 
 enum : int32_t {
   kErrQFull = 0x301, kErrKvEmpty = 0x302, kErrKvFull = 0x303, kErrSFull = 0x304,
-  kErrPFull = 0x305, kErrPvDone = 0x306, kErrSmemAlign = 0x307, kErrPair = 0x308, kErrBadPage = 0x309,
+  kErrPFull = 0x305, kErrPvDone = 0x306, kErrSmemAlign = 0x307, kErrPair = 0x308, kErrBadPage = 0x309, kErrQEmpty = 0x30a, kErrOFree = 0x30b,
 };
 
 struct PrefillParams {
@@ -63,6 +63,7 @@ struct PrefillParams {
   int64_t time_stride, phase_stride, bt_s0, bt_s1;
   int page_shift, num_pages, max_pages;      // paged mode
   int B, H, G, Tq, T;
+  int n_q_tiles;                             // ceil(Tq / 128)
   int ctx_window, sliding_window, phase, causal;
   int o_dtype;
   float scale_log2;
@@ -77,6 +78,8 @@ struct Barriers {
   uint64_t p_a[2];          // first quarter-pairs of P(j) written (keys 0..31 and 64..95)
   uint64_t p_b[2];          // the rest of P(j) written
   uint64_t pv_done;
+  uint64_t q_empty;        // last Q.K^T of a work item done: the Q buffer may be refilled
+  uint64_t o_free;         // the softmax warps have read O out of tensor memory
   uint64_t pair[4];        // one per softmax warp pair (64 arrivals): shared-memory exchanges
   uint32_t tmem_base;
   int32_t abort_flag;
@@ -88,18 +91,51 @@ __device__ __forceinline__ void record(int32_t* status, int32_t code) { atomicCA
 // the main hand-over points of every tile, read back with g4b_debug_read_trace().
 #ifdef G4B_TRACE
 __device__ long long g_trace[128][16];
+__device__ long long g_item_trace[128][16];
 #define G4B_TRACE_AT(tile, slot)                                                         \
   do {                                                                                   \
-    if (blockIdx.x == 0 && blockIdx.y == 0 && lane == 0 && (tile) < 128) g_trace[(tile)][(slot)] = clock64(); \
+    if (blockIdx.x == 0 && n_done == 0 && lane == 0 && (tile) < 128) g_trace[(tile)][(slot)] = clock64(); \
   } while (0)
-#define G4B_TRACE_PEER(tile, slot)                                                       \
+// per work item (row = item count of worker 0)
+#define G4B_ITEM_AT(slot)                                                                \
   do {                                                                                   \
-    if (blockIdx.x == 1 && blockIdx.y == 0 && lane == 0 && (tile) < 128) g_trace[(tile)][(slot)] = clock64(); \
+    if (blockIdx.x == 0 && lane == 0 && n_done < 128) g_item_trace[n_done][(slot)] = clock64(); \
   } while (0)
 #else
 #define G4B_TRACE_AT(tile, slot) do {} while (0)
-#define G4B_TRACE_PEER(tile, slot) do {} while (0)
+#define G4B_ITEM_AT(slot) do {} while (0)
 #endif
+
+// Geometry of one work item = 128 query rows of one head (fa2.py:52-64).  Ring mode counts
+// keys from the oldest one the cache exposes (fa2.py:52-56).  A paged cache is addressed by
+// absolute position: all `time` keys are addressable (so 128-key tiles start on page
+// boundaries) and the exposed window is just another lower bound.  Items are ordered with
+// the latest (heaviest) query tiles first; in a CTA pair the two CTAs take heads 2u and 2u+1.
+#define G4B_ITEM_GEOMETRY(item)                                                                      \
+  const int unit_ = (item) % units_per_level;                                                         \
+  const int q_tile = p.n_q_tiles - 1 - (item) / units_per_level;                                      \
+  const int bh = kPair ? 2 * unit_ + (int)rank : unit_;                                               \
+  const int b = bh / p.H, h = bh % p.H;                                                               \
+  const int g = h / (p.H / p.G);                                                                      \
+  const int m0 = q_tile * kBM;                                                                        \
+  const bool active = p.user_phase == nullptr || p.user_phase[b * p.phase_stride] == (uint8_t)p.phase; \
+  const bool paged = p.block_tables != nullptr;                                                       \
+  const int time = p.time_dim_sizes[b * p.time_stride];                                               \
+  const int window = paged ? time : min(time, p.ctx_window);                                          \
+  const int win_lo = paged ? max(0, time - p.ctx_window) : 0;                                         \
+  const int ring_start = paged ? 0 : max(time - p.ctx_window, 0) % p.T;                               \
+  const int q_t_base = window - p.Tq; /* logical position of query row 0 */                           \
+  const int rows_valid = min(kBM, p.Tq - m0);                                                         \
+  const int qpos_min = q_t_base + m0;                                                                 \
+  const int qpos_max = q_t_base + m0 + rows_valid - 1;                                                \
+  const int key_hi = p.causal ? min(window, qpos_max + 1) : window;                                   \
+  const int key_lo = p.sliding_window > 0 ? max(win_lo, qpos_min - p.sliding_window + 1) : win_lo;    \
+  /* uniform over the item: some row may see fewer than 64 keys in all */                             \
+  const bool few_keys = qpos_min - win_lo < 64 || (p.sliding_window > 0 && p.sliding_window < 64);    \
+  const bool precise = PackT<T>::kSplitP && few_keys;                                                 \
+  const int tile_lo = key_lo / kBN;                                                                   \
+  const int n_tiles = (active && key_hi > key_lo) ? (key_hi + kBN - 1) / kBN - tile_lo : 0;           \
+  (void)ring_start; (void)precise; (void)few_keys; (void)g; (void)h; (void)tile_lo; (void)qpos_max
 
 // Where logical key `key` of this (slot, kv head) lives, or null if it is outside the
 // context (ring buffer or page pool).
@@ -195,16 +231,22 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
                const __grid_constant__ CUtensorMap v_map, PrefillParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int bh = blockIdx.x;
-  const int b = bh / p.H, h = bh % p.H;
-  const int g = h / (p.H / p.G);
-  const int q_tile = (int)gridDim.y - 1 - (int)blockIdx.y;   // heaviest (latest) tiles first
-  const int m0 = q_tile * kBM;
   const uint32_t rank = kPair ? ptx::cluster_ctarank() : 0u;   // 0 = the CTA that issues the MMAs
   const bool leader = rank == 0;
 
-  // both CTAs of a pair belong to the same slot: they leave together
-  if (p.user_phase != nullptr && p.user_phase[b * p.phase_stride] != (uint8_t)p.phase) return;
+  // Persistent: a worker (a CTA, or a CTA pair) walks a static list of work items, so barrier
+  // set-up, the tensor-memory allocation and the launch gap are paid once, and the producer
+  // runs ahead into the next item while the current one drains.  Round r hands item
+  // r * workers + w to worker w, alternating the direction so heavy and light items pair up.
+  const int units_per_level = kPair ? (p.B * p.H) / 2 : p.B * p.H;   // (slot, head[s]) units per query tile
+  const int n_items = p.n_q_tiles * units_per_level;
+  const int n_workers = kPair ? (int)gridDim.x / 2 : (int)gridDim.x;
+  const int worker = kPair ? (int)blockIdx.x / 2 : (int)blockIdx.x;
+  auto item_of_round = [&](int round) -> int {
+    const int pos = (round & 1) ? n_workers - 1 - worker : worker;
+    const int item = round * n_workers + pos;
+    return item < n_items ? item : -1;
+  };
   uint8_t* smem = smem_raw;
   uint8_t* sQ = smem;
   uint8_t* sRing = smem + kQBytes;
@@ -226,6 +268,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       ptx::mbar_init(ptx::smem_u32(&bars->p_b[s]), 8 * kN);
     }
     ptx::mbar_init(bar_pv, 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->q_empty), 1);
+    ptx::mbar_init(ptx::smem_u32(&bars->o_free), 8 * kN);
     for (int s = 0; s < 4; ++s) ptx::mbar_init(ptx::smem_u32(&bars->pair[s]), 2);   // one arrival per warp of the pair
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&q_map);
@@ -243,43 +287,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
   }
   if constexpr (kPair) ptx::cluster_sync_all(); else __syncthreads();
   if (*reinterpret_cast<volatile int32_t*>(&bars->abort_flag) != 0) return;
-
-  // ---- geometry of this CTA's key range (fa2.py:52-64) ----
-  // Ring mode counts keys from the oldest one the cache exposes (fa2.py:52-56).  A paged cache
-  // is addressed by absolute position: all `time` keys are addressable (so 128-key tiles
-  // start on page boundaries) and the exposed window is just another lower bound.
-  const bool paged = p.block_tables != nullptr;
-  const int time = p.time_dim_sizes[b * p.time_stride];
-  const int window = paged ? time : min(time, p.ctx_window);
-  const int win_lo = paged ? max(0, time - p.ctx_window) : 0;
-  const int ring_start = paged ? 0 : max(time - p.ctx_window, 0) % p.T;
-  const int q_t_base = window - p.Tq;                    // logical position of query row 0
-  const int rows_valid = min(kBM, p.Tq - m0);
-  const int qpos_min = q_t_base + m0;
-  const int qpos_max = q_t_base + m0 + rows_valid - 1;
-  const int key_hi = p.causal ? min(window, qpos_max + 1) : window;
-  const int key_lo = p.sliding_window > 0 ? max(win_lo, qpos_min - p.sliding_window + 1) : win_lo;
-  // CTA-uniform: some row of this tile may see fewer than 64 keys in all
-  const bool few_keys = qpos_min - win_lo < 64 || (p.sliding_window > 0 && p.sliding_window < 64);
-  const bool precise = PackT<T>::kSplitP && few_keys;
-  const int tile_lo = key_lo / kBN;
-  const int n_tiles = key_hi > key_lo ? (key_hi + kBN - 1) / kBN - tile_lo : 0;
-
-
-  if (n_tiles <= 0) {
-    // no visible key for any row of this tile: the output rows are defined as zero
-    if (warp >= 2 && warp < 6) {
-      const int r = (warp & 3) * 32 + lane;
-      if (r < rows_valid) {
-        const int64_t off = b * p.o_s0 + h * p.o_s1 + (int64_t)(m0 + r) * p.o_s2;
-        for (int d = 0; d < kHD; ++d) {
-          if (p.o_dtype == G4B_F32) ((float*)p.o)[off + d] = 0.f;
-          else ((uint16_t*)p.o)[off + d] = 0;
-        }
-      }
-    }
-    return;
-  }
 
   if (warp == 1) {
     if constexpr (kPair) {
@@ -314,6 +321,17 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
 
   if (warp == 0) {
     // =============================== producer ===============================
+    // K/V tiles are re-read by every query tile of 4 heads: keep them in L2; Q is read once
+    const uint64_t pol_kv = ptx::policy_evict_last();
+    const uint64_t pol_q = ptx::policy_evict_first();
+    uint32_t cc = 0;   // chunk counter over the ring (runs on across work items)
+    int n_done = 0;    // work items this worker has gone through
+    bool ok = true;
+    for (int round = 0; round * n_workers < n_items && ok; ++round) {
+    const int item = item_of_round(round);
+    if (item < 0) continue;
+    G4B_ITEM_GEOMETRY(item);
+    if (n_tiles <= 0) continue;
     KeySource<T> ksrc, vsrc;
     ksrc.paged = paged; ksrc.window = window; ksrc.ring_start = ring_start; ksrc.Trows = p.T;
     ksrc.G = p.G; ksrc.g = g; ksrc.page_shift = p.page_shift; ksrc.num_pages = p.num_pages;
@@ -322,9 +340,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     vsrc = ksrc;
     vsrc.base = paged ? (const T*)p.v : (const T*)p.v + ((int64_t)b * p.G + g) * p.T * kHD;
     const int bg = b * p.G + g;
-    // K/V tiles are re-read by every query tile of 4 heads: keep them in L2; Q is read once
-    const uint64_t pol_kv = ptx::policy_evict_last();
-    const uint64_t pol_q = ptx::policy_evict_first();
+    G4B_ITEM_AT(0);   // producer reaches the item
+    {
+      // the Q buffer is free once the last Q.K^T of the previous item has run
+      int w = 1;
+      if (lane == 0 && n_done > 0) w = ptx::mbar_wait(ptx::smem_u32(&bars->q_empty), (n_done - 1) & 1) ? 1 : 0;
+      w = __shfl_sync(0xffffffffu, w, 0);
+      if (!w) { if (lane == 0) record(p.status, kErrQEmpty); ok = false; break; }
+    }
+    G4B_ITEM_AT(1);   // Q buffer free, Q load goes out
     if (lane == 0) {
       if constexpr (kPair) {
         const uint32_t qb = issuer_bar(&bars->q_full);
@@ -337,8 +361,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           ptx::tma_load_4d_hint(ptx::smem_u32(sQ + s * 16384), &q_map, bar_q, s * 64, m0, h, b, pol_q);
       }
     }
-    uint32_t cc = 0;   // chunk counter over the ring
-    bool ok = true;
     // lane 0 waits for the stage to drain; the verdict is shared so the warp stays converged
     auto wait_empty = [&](int st, uint32_t c) -> bool {
       int w = 1;
@@ -549,6 +571,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         if (j + 2 < n_tiles) load_k(j + 2);
       }
     }
+    ++n_done;
+    }   // work items
   } else if (warp == 1) {
     // =============================== MMA issuer ===============================
     if constexpr (kPair) {
@@ -572,12 +596,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           ptx::tc_commit_pair(ptx::map_to_cta(a, 0));
           ptx::tc_commit_pair(ptx::map_to_cta(a, 1));
         };
-        bool ok = wait_all(bar_q, 0);
-        if (!ok && lane == 0) record(p.status, kErrQFull);
-        ptx::tc_fence_after();
+        bool ok = true;
         uint32_t cc = 0;
+        int tg = 0;       // tiles issued so far: S buffer and barrier phases run on across items
+        int n_done = 0;
+        for (int round = 0; round * n_workers < n_items && ok; ++round) {
+        const int item = item_of_round(round);
+        if (item < 0) continue;
+        G4B_ITEM_GEOMETRY(item);
+        if (n_tiles <= 0) continue;
+        G4B_ITEM_AT(2);   // issuer reaches the item
+        ok = wait_all(bar_q, n_done & 1);
+        if (!ok) { if (lane == 0) record(p.status, kErrQFull); break; }
+        ptx::tc_fence_after();
+        G4B_ITEM_AT(3);   // Q seen by the issuer
         auto issue_qk = [&](int j) {
-          const uint32_t d_tmem = tmem + ((j & 1) ? kColS1 : kColS0);
+          const int t = tg + j;
+          const uint32_t d_tmem = tmem + ((t & 1) ? kColS1 : kColS0);
           const int st = cc % kStages;
           if (!wait_all(ptx::smem_u32(&bars->kv_full[st]), (cc / kStages) & 1)) {
             if (lane == 0) record(p.status, kErrKvFull);
@@ -594,7 +629,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
                                k16 != 0);
             }
             commit_both(&bars->kv_empty[st]);
-            commit_both(&bars->s_full[j & 1]);
+            commit_both(&bars->s_full[t & 1]);
+            if (j == n_tiles - 1) commit_both(&bars->q_empty);   // last use of this item's Q
           }
           __syncwarp();
           G4B_TRACE_AT(j, 0);   // QK(j) issued
@@ -606,12 +642,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
             if (lane == 0) record(p.status, kErrKvFull);
             ok = false; return;
           }
+          const int t = tg + j;
           const uint32_t v_lo = (ring_lo + st * (kChunkBytes >> 4)) | kLoVMajor;
-          const uint32_t p_tmem = tmem + ((j & 1) ? kColS1 : kColS0);
+          const uint32_t p_tmem = tmem + ((t & 1) ? kColS1 : kColS0);
           G4B_TRACE_AT(j, 3);   // V chunk of tile j seen by the issuer
+          if (j == 0 && n_done > 0) {
+            // the first product of an item overwrites O: the previous item's O must have been read
+            if (!wait_all(ptx::smem_u32(&bars->o_free), (n_done - 1) & 1)) {
+              if (lane == 0) record(p.status, kErrOFree);
+              ok = false; return;
+            }
+            ptx::tc_fence_after();
+          }
           for (int part = 0; part < 2 && ok; ++part) {
-            const uint32_t bar = ptx::smem_u32(part == 0 ? &bars->p_a[j & 1] : &bars->p_b[j & 1]);
-            if (!wait_all(bar, (j >> 1) & 1)) {
+            const uint32_t bar = ptx::smem_u32(part == 0 ? &bars->p_a[t & 1] : &bars->p_b[t & 1]);
+            if (!wait_all(bar, (t >> 1) & 1)) {
               if (lane == 0) record(p.status, kErrPFull);
               ok = false; return;
             }
@@ -641,6 +686,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           issue_pv(j);
           if (ok && j + 2 < n_tiles) issue_qk(j + 2);
         }
+        G4B_ITEM_AT(4);   // last P.V of the item issued
+        tg += n_tiles;
+        ++n_done;
+        }   // work items
       }
       __syncwarp();
     } else {
@@ -657,12 +706,21 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     auto wait_all = [&](uint32_t bar, uint32_t parity) -> bool {
       return __all_sync(0xffffffffu, ptx::mbar_wait(bar, parity));
     };
-    bool ok = wait_all(bar_q, 0);
-    if (!ok && lane == 0) record(p.status, kErrQFull);
-    ptx::tc_fence_after();
+    bool ok = true;
     uint32_t cc = 0;
+    int tg = 0;       // tiles issued so far: S buffer and barrier phases run on across items
+    int n_done = 0;
+    for (int round = 0; round * n_workers < n_items && ok; ++round) {
+    const int item = item_of_round(round);
+    if (item < 0) continue;
+    G4B_ITEM_GEOMETRY(item);
+    if (n_tiles <= 0) continue;
+    ok = wait_all(bar_q, n_done & 1);
+    if (!ok) { if (lane == 0) record(p.status, kErrQFull); break; }
+    ptx::tc_fence_after();
     auto issue_qk = [&](int j) {
-      const uint32_t d_tmem = tmem + ((j & 1) ? kColS1 : kColS0);
+      const int t = tg + j;
+      const uint32_t d_tmem = tmem + ((t & 1) ? kColS1 : kColS0);
       for (int kc = 0; kc < 2 && ok; ++kc, ++cc) {
         const int st = cc % kStages;
         if (!wait_all(ptx::smem_u32(&bars->kv_full[st]), (cc / kStages) & 1)) {
@@ -683,7 +741,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         }
         __syncwarp();
       }
-      if (ok && ptx::elect_one()) ptx::tc_commit(ptx::smem_u32(&bars->s_full[j & 1]));
+      if (ok && ptx::elect_one()) {
+        ptx::tc_commit(ptx::smem_u32(&bars->s_full[t & 1]));
+        if (j == n_tiles - 1) ptx::tc_commit(ptx::smem_u32(&bars->q_empty));   // last use of this item's Q
+      }
       __syncwarp();
       G4B_TRACE_AT(j, 0);   // QK(j) issued
     };
@@ -700,11 +761,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         }
         v_lo[vc] = (ring_lo + st2[vc] * (kChunkBytes >> 4)) | kLoVMajor;
       }
-      const uint32_t p_tmem = tmem + ((j & 1) ? kColS1 : kColS0);
+      const int t = tg + j;
+      const uint32_t p_tmem = tmem + ((t & 1) ? kColS1 : kColS0);
       G4B_TRACE_AT(j, 3);   // V chunks of tile j seen by the issuer
+      if (j == 0 && n_done > 0) {
+        // the first product of an item overwrites O: the previous item's O must have been read
+        if (!wait_all(ptx::smem_u32(&bars->o_free), (n_done - 1) & 1)) {
+          if (lane == 0) record(p.status, kErrOFree);
+          ok = false; return;
+        }
+        ptx::tc_fence_after();
+      }
       for (int part = 0; part < 2 && ok; ++part) {
-        const uint32_t bar = ptx::smem_u32(part == 0 ? &bars->p_a[j & 1] : &bars->p_b[j & 1]);
-        if (!wait_all(bar, (j >> 1) & 1)) {
+        const uint32_t bar = ptx::smem_u32(part == 0 ? &bars->p_a[t & 1] : &bars->p_b[t & 1]);
+        if (!wait_all(bar, (t >> 1) & 1)) {
           if (lane == 0) record(p.status, kErrPFull);
           ok = false; return;
         }
@@ -738,6 +808,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       issue_pv(j);
       if (ok && j + 2 < n_tiles) issue_qk(j + 2);
     }
+    tg += n_tiles;
+    ++n_done;
+    }   // work items
     __syncwarp();
     }
   } else {
@@ -760,21 +833,39 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       ++pair_phase;
       return w;
     };
+    bool ok = true;
+    int tg = 0;       // tiles seen so far: S buffer and barrier phases run on across items
+    int n_done = 0;
+    for (int round = 0; round * n_workers < n_items && ok; ++round) {
+    const int item = item_of_round(round);
+    if (item < 0) continue;
+    G4B_ITEM_GEOMETRY(item);
+    if (n_tiles <= 0) {
+      // no visible key for any row of this tile: the output rows are defined as zero
+      if (active && half == 0 && r < rows_valid) {
+        const int64_t off = b * p.o_s0 + h * p.o_s1 + (int64_t)(m0 + r) * p.o_s2;
+        for (int d = 0; d < kHD; ++d) {
+          if (p.o_dtype == G4B_F32) ((float*)p.o)[off + d] = 0.f;
+          else ((uint16_t*)p.o)[off + d] = 0;
+        }
+      }
+      continue;
+    }
     const int qpos = q_t_base + m0 + r;
     const int hi_r = p.causal ? min(window, qpos + 1) : window;
     const int lo_r = p.sliding_window > 0 ? max(win_lo, qpos - p.sliding_window + 1) : win_lo;
     float m_used = -INFINITY;   // reference maximum the accumulated O and l are scaled by
     float l_run = 0.f;          // this thread's half of the row sum
-    bool ok = true;
 
     for (int j = 0; j < n_tiles && ok; ++j) {
-      const uint32_t s_col = (j & 1) ? kColS1 : kColS0;
-      if (!__all_sync(0xffffffffu, ptx::mbar_wait(ptx::smem_u32(&bars->s_full[j & 1]), (j >> 1) & 1))) {
+      const int t = tg + j;
+      const uint32_t s_col = (t & 1) ? kColS1 : kColS0;
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(ptx::smem_u32(&bars->s_full[t & 1]), (t >> 1) & 1))) {
         record(p.status, kErrSFull); ok = false; break;
       }
       ptx::tc_fence_after();
       if (warp == 2) G4B_TRACE_AT(j, 8);   // S(j) seen by the softmax warp
-      if (warp == 2) G4B_TRACE_PEER(j, 13);
+      if (warp == 2 && j == 0) G4B_ITEM_AT(5);
       const int kbase = (tile_lo + j) * kBN;
       // warp-uniform: does any row of this CTA need element masks in this tile?
       const bool need_mask = (p.causal && kbase + kBN - 1 > qpos_min) || (kbase + kBN > window) ||
@@ -806,13 +897,15 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       }
       float mx = fmaxf(fmaxf(mx4[0], mx4[1]), fmaxf(mx4[2], mx4[3]));
       // publish the half-row maximum for the partner warp; collect the partner's later
-      float* xm = xchg + (j & 1) * (2 * kBM);
+      // exchange buffers alternate with every rendezvous of the pair (also across items), so a
+      // write can never overtake the partner's read of the exchange before last
+      float* xm = xchg + (pair_phase & 1) * (2 * kBM);
       xm[half * kBM + r] = mx;
       __syncwarp();
       if (lane == 0) ptx::mbar_arrive(pair_bar);
 
-      const uint32_t bar_pa = issuer_bar(&bars->p_a[j & 1]);   // in a pair: CTA 0's barrier
-      const uint32_t bar_pb = issuer_bar(&bars->p_b[j & 1]);
+      const uint32_t bar_pa = issuer_bar(&bars->p_a[t & 1]);   // in a pair: CTA 0's barrier
+      const uint32_t bar_pb = issuer_bar(&bars->p_b[t & 1]);
       uint32_t pk[32];
       // Optimistic path: the reference maximum rarely moves (it only has to stay within 2^8
       // of the true one), so start exponentiating against the current one while the maxima
@@ -846,7 +939,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         ptx::tc_fence_before();
         arrive_issuer(bar_pa);
         if (warp == 2) G4B_TRACE_AT(j, 11);  // P part A published
-        if (warp == 2) G4B_TRACE_PEER(j, 14);
         const float neg_m = -m_used;
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -861,9 +953,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         ptx::tc_fence_before();
         arrive_issuer(bar_pb);
         if (warp == 2) G4B_TRACE_AT(j, 12);  // P part B published
-        if (warp == 2) G4B_TRACE_PEER(j, 15);
         // keep the PV-done phase bookkeeping in step (no stall: PV(j-1) ended long ago)
-        if (j > 0 && !__all_sync(0xffffffffu, ptx::mbar_wait(bar_pv, (j - 1) & 1))) {
+        if (j > 0 && !__all_sync(0xffffffffu, ptx::mbar_wait(bar_pv, (t - 1) & 1))) {
           record(p.status, kErrPvDone); ok = false;
         }
         continue;
@@ -911,7 +1002,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       }
       // O may only be touched once PV(j-1) has drained
       if (j > 0) {
-        if (!__all_sync(0xffffffffu, ptx::mbar_wait(bar_pv, (j - 1) & 1))) { record(p.status, kErrPvDone); ok = false; }
+        if (!__all_sync(0xffffffffu, ptx::mbar_wait(bar_pv, (t - 1) & 1))) { record(p.status, kErrPvDone); ok = false; }
         ptx::tc_fence_after();
         if (ok && __any_sync(0xffffffffu, rescale)) {
 #pragma unroll 1
@@ -932,14 +1023,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     }
 
     // ---- epilogue: O / l -> global ----
+    if (warp == 2) G4B_ITEM_AT(6);   // all P of the item published
     if (ok) {
-      if (!__all_sync(0xffffffffu, ptx::mbar_wait(bar_pv, (n_tiles - 1) & 1))) { record(p.status, kErrPvDone); ok = false; }
+      if (!__all_sync(0xffffffffu, ptx::mbar_wait(bar_pv, (tg + n_tiles - 1) & 1))) { record(p.status, kErrPvDone); ok = false; }
       ptx::tc_fence_after();
     }
-    // the row sum is the sum of both halves (both scaled by the same m_used); the exchange
-    // uses the maxima buffer the last tile did not use
+    // the row sum is the sum of both halves (both scaled by the same m_used)
     if (ok) {
-      float* xl = xchg + (n_tiles & 1) * (2 * kBM);
+      float* xl = xchg + (pair_phase & 1) * (2 * kBM);
       xl[half * kBM + r] = l_run;
       if (!pair_sync()) { record(p.status, kErrPair); ok = false; }
       l_run += xl[(half ^ 1) * kBM + r];
@@ -949,13 +1040,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       const bool row_ok = r < rows_valid;
       const uint64_t pol_o = ptx::policy_evict_first();   // the output is not read again here
       const int64_t off = b * p.o_s0 + h * p.o_s1 + (int64_t)(m0 + r) * p.o_s2 + half * 128;
+      if (p.o_dtype == G4B_F32) {
 #pragma unroll 1
-      for (int c4 = 0; c4 < 4; ++c4) {
-        uint32_t ov[32];
-        ptx::tmem_ld32(trow + kColO + half * 128 + c4 * 32, ov);
-        ptx::tc_wait_ld();
-        if (row_ok) {
-          if (p.o_dtype == G4B_F32) {
+        for (int c4 = 0; c4 < 4; ++c4) {
+          uint32_t ov[32];
+          ptx::tmem_ld32(trow + kColO + half * 128 + c4 * 32, ov);
+          ptx::tc_wait_ld();
+          if (row_ok) {
             float4* dst = reinterpret_cast<float4*>((float*)p.o + off + c4 * 32);
 #pragma unroll
             for (int i = 0; i < 8; ++i)
@@ -963,21 +1054,42 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
                                                          __float_as_uint(__uint_as_float(ov[4 * i + 1]) * inv_l),
                                                          __float_as_uint(__uint_as_float(ov[4 * i + 2]) * inv_l),
                                                          __float_as_uint(__uint_as_float(ov[4 * i + 3]) * inv_l)), pol_o);
-          } else {
+          }
+        }
+        ptx::tc_fence_before();
+        arrive_issuer(issuer_bar(&bars->o_free));
+      } else {
+        // pull this thread's 128 accumulator columns out (normalised and packed: 64 registers),
+        // hand O back to the MMA issuer -- the next item's first P.V overwrites it -- then store
+        uint32_t pk[4][16];
+#pragma unroll
+        for (int c4 = 0; c4 < 4; ++c4) {
+          uint32_t ov[32];
+          ptx::tmem_ld32(trow + kColO + half * 128 + c4 * 32, ov);
+          ptx::tc_wait_ld();
+#pragma unroll
+          for (int i = 0; i < 16; ++i)
+            pk[c4][i] = PackT<T>::pack(__uint_as_float(ov[2 * i]) * inv_l, __uint_as_float(ov[2 * i + 1]) * inv_l);
+        }
+        ptx::tc_fence_before();
+        arrive_issuer(issuer_bar(&bars->o_free));
+        if (warp == 2) G4B_ITEM_AT(7);   // O read out
+        if (row_ok) {
+#pragma unroll
+          for (int c4 = 0; c4 < 4; ++c4) {
             uint4* dst = reinterpret_cast<uint4*>((T*)p.o + off + c4 * 32);
 #pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              uint4 w;
-              w.x = PackT<T>::pack(__uint_as_float(ov[8 * i + 0]) * inv_l, __uint_as_float(ov[8 * i + 1]) * inv_l);
-              w.y = PackT<T>::pack(__uint_as_float(ov[8 * i + 2]) * inv_l, __uint_as_float(ov[8 * i + 3]) * inv_l);
-              w.z = PackT<T>::pack(__uint_as_float(ov[8 * i + 4]) * inv_l, __uint_as_float(ov[8 * i + 5]) * inv_l);
-              w.w = PackT<T>::pack(__uint_as_float(ov[8 * i + 6]) * inv_l, __uint_as_float(ov[8 * i + 7]) * inv_l);
-              ptx::st_global_v4_hint(dst + i, w, pol_o);
-            }
+            for (int i = 0; i < 4; ++i)
+              ptx::st_global_v4_hint(dst + i, make_uint4(pk[c4][4 * i], pk[c4][4 * i + 1], pk[c4][4 * i + 2], pk[c4][4 * i + 3]),
+                                     pol_o);
           }
         }
       }
     }
+    if (warp == 2) G4B_ITEM_AT(8);   // item stored
+    tg += n_tiles;
+    ++n_done;
+    }   // work items
   }
 
   // ---- teardown: every thread arrives here, on success and after a failed wait ----
@@ -1065,9 +1177,13 @@ static int launch_typed(const CUtensorMap& qm, const CUtensorMap& km, const CUte
 }  // namespace
 
 #ifdef G4B_TRACE
+extern "C" int g4b_debug_read_item_trace(long long* out) {
+  return (int)cudaMemcpyFromSymbol(out, g_item_trace, sizeof(long long) * 128 * 16);
+}
 extern "C" int g4b_debug_read_trace(long long* out) {
   return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 128 * 16);
 }
+
 #endif
 
 int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
@@ -1089,7 +1205,7 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
     if ((a.o.stride[i] * osz) % 16 != 0) return fail(G4B_ERR_BAD_STRIDE, "prefill: o strides must be multiples of 16 bytes");
   if (((uintptr_t)a.o.ptr) & 15) return fail(G4B_ERR_BAD_STRIDE, "prefill: o must be 16-byte aligned");
   const int64_t n_q_tiles = (Tq + kBM - 1) / kBM;
-  if (B * H > 0x7fffffffLL || n_q_tiles > 65535) return fail(G4B_ERR_UNSUPPORTED, "prefill: grid too large");
+  if (B * H * n_q_tiles > 0x7fffffffLL) return fail(G4B_ERR_UNSUPPORTED, "prefill: too many work items");
 
   // Two heads of one kv head per CTA pair when the head counts allow it; G4B_PREFILL_SINGLE_CTA=1
   // forces the one-CTA form (for comparisons).
@@ -1128,6 +1244,7 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   p.o_s0 = a.o.stride[0]; p.o_s1 = a.o.stride[1]; p.o_s2 = a.o.stride[2];
   p.time_stride = a.time_dim_sizes.stride[0]; p.phase_stride = a.user_phase.stride[0];
   p.B = (int)B; p.H = (int)H; p.G = (int)G; p.Tq = (int)Tq; p.T = paged ? 1 : (int)T;
+  p.n_q_tiles = (int)n_q_tiles;
   if (paged) {
     p.block_tables = (const int32_t*)a.block_tables.ptr;
     p.bt_s0 = a.block_tables.stride[0]; p.bt_s1 = a.block_tables.stride[1];
@@ -1142,7 +1259,18 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   p.scale_log2 = a.scale * 1.4426950408889634f;
   p.status = device_status_ptr();
   if (p.status == nullptr) return G4B_ERR_CUDA;
-  dim3 grid((unsigned)(B * H), (unsigned)n_q_tiles, 1);
+  // persistent launch: one worker (CTA or CTA pair) per SM (pair of SMs), or fewer if there
+  // are fewer work items
+  static int sm_count[64] = {0};
+  int dev = 0;
+  G4B_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= 64) return fail(G4B_ERR_CUDA, "device index out of range");
+  if (sm_count[dev] == 0) G4B_CUDA_CHECK(cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
+  const int64_t n_items = n_q_tiles * (pair ? (B * H) / 2 : B * H);
+  int64_t workers = pair ? sm_count[dev] / 2 : sm_count[dev];
+  if (workers < 1) workers = 1;
+  if (workers > n_items) workers = n_items;
+  dim3 grid((unsigned)(pair ? 2 * workers : workers), 1, 1);
   if (a.q.dtype == G4B_BF16) return launch_typed<__nv_bfloat16>(qm, km, vm, p, grid, pair, st);
   return launch_typed<__half>(qm, km, vm, p, grid, pair, st);
 }
