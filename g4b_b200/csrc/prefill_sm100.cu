@@ -40,7 +40,7 @@ namespace {
 constexpr int kBM = 128;          // query rows per CTA
 constexpr int kBN = 128;          // keys per S tile
 constexpr int kHD = 256;          // head dim
-constexpr int kStages = 5;
+constexpr int kStages = 5;          // 32 KB ring slots in shared memory
 constexpr int kChunkBytes = 32768;
 constexpr int kQBytes = kBM * kHD * 2;
 constexpr int kThreads = 320;      // producer warp, MMA warp, 2 softmax warpgroups
@@ -225,12 +225,16 @@ template <> struct PackT<__half> {
 //   each CTA stages only half of every tile (K: half the keys, V: half the head dim), so the
 //   ring covers twice the time and Q.K^T reads 96 instead of 128 bytes of shared memory per
 //   cycle -- the two things that starve the single-CTA form.
-template <typename T, bool kPair>
+template <typename T, bool kPair, bool kStageOut>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                const __grid_constant__ CUtensorMap v_map, PrefillParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // Ring slots in use.  Short work items (sliding windows: ~5 tiles) gain more from coalesced
+  // output stores than from look-ahead: that variant uses 4 slots and the fifth becomes the
+  // staging buffer of the epilogue.
+  constexpr int kSt = kStageOut ? kStages - 1 : kStages;
   const uint32_t rank = kPair ? ptx::cluster_ctarank() : 0u;   // 0 = the CTA that issues the MMAs
   const bool leader = rank == 0;
 
@@ -258,7 +262,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     // In a pair, the barriers the MMA issuer waits on live in CTA 0 and count both CTAs.
     constexpr uint32_t kN = kPair ? 2u : 1u;
     ptx::mbar_init(bar_q, kN);
-    for (int s = 0; s < kStages; ++s) {
+    for (int s = 0; s < kSt; ++s) {
       ptx::mbar_init(ptx::smem_u32(&bars->kv_full[s]), kN);
       ptx::mbar_init(ptx::smem_u32(&bars->kv_empty[s]), 1);
     }
@@ -364,7 +368,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     // lane 0 waits for the stage to drain; the verdict is shared so the warp stays converged
     auto wait_empty = [&](int st, uint32_t c) -> bool {
       int w = 1;
-      if (lane == 0) w = ptx::mbar_wait(ptx::smem_u32(&bars->kv_empty[st]), ((c / kStages) & 1) ^ 1) ? 1 : 0;
+      if (lane == 0) w = ptx::mbar_wait(ptx::smem_u32(&bars->kv_empty[st]), ((c / kSt) & 1) ^ 1) ? 1 : 0;
       w = __shfl_sync(0xffffffffu, w, 0);
       if (!w) { if (lane == 0) record(p.status, kErrKvEmpty); ok = false; }
       return w != 0;
@@ -403,7 +407,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         manual = pr0 + live > p.T;                       // the tile crosses the end of the ring
       }
       for (int kc = 0; kc < 2 && ok; ++kc, ++cc) {
-        const int st = cc % kStages;
+        const int st = cc % kSt;
         const uint32_t full = ptx::smem_u32(&bars->kv_full[st]);
         if (!wait_empty(st, cc)) break;
         uint8_t* dst = sRing + st * kChunkBytes;
@@ -444,7 +448,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           my_page = page_ids(key0, 4);
           manual = __any_sync(0xffffffffu, lane < 4 && my_page < 0);
         }
-        const int st = cc % kStages;
+        const int st = cc % kSt;
         const uint32_t full = ptx::smem_u32(&bars->kv_full[st]);
         if (!wait_empty(st, cc)) break;
         uint8_t* dst = sRing + st * kChunkBytes;
@@ -488,7 +492,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       } else {
         manual = live > 0 && pr0 + live > p.T;
       }
-      const int st = cc % kStages;
+      const int st = cc % kSt;
       const uint32_t full = issuer_bar(&bars->kv_full[st]);
       G4B_TRACE_AT(j, 7);
       if (!wait_empty(st, cc)) return;
@@ -528,7 +532,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         my_page = page_ids(key0, 8);
         manual = __any_sync(0xffffffffu, lane < 8 && my_page < 0);
       }
-      const int st = cc % kStages;
+      const int st = cc % kSt;
       const uint32_t full = issuer_bar(&bars->kv_full[st]);
       G4B_TRACE_AT(j, 6);
       if (!wait_empty(st, cc)) return;
@@ -613,8 +617,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         auto issue_qk = [&](int j) {
           const int t = tg + j;
           const uint32_t d_tmem = tmem + ((t & 1) ? kColS1 : kColS0);
-          const int st = cc % kStages;
-          if (!wait_all(ptx::smem_u32(&bars->kv_full[st]), (cc / kStages) & 1)) {
+          const int st = cc % kSt;
+          if (!wait_all(ptx::smem_u32(&bars->kv_full[st]), (cc / kSt) & 1)) {
             if (lane == 0) record(p.status, kErrKvFull);
             ok = false; return;
           }
@@ -637,8 +641,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           ++cc;
         };
         auto issue_pv = [&](int j) {
-          const int st = cc % kStages;
-          if (!wait_all(ptx::smem_u32(&bars->kv_full[st]), (cc / kStages) & 1)) {
+          const int st = cc % kSt;
+          if (!wait_all(ptx::smem_u32(&bars->kv_full[st]), (cc / kSt) & 1)) {
             if (lane == 0) record(p.status, kErrKvFull);
             ok = false; return;
           }
@@ -722,8 +726,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       const int t = tg + j;
       const uint32_t d_tmem = tmem + ((t & 1) ? kColS1 : kColS0);
       for (int kc = 0; kc < 2 && ok; ++kc, ++cc) {
-        const int st = cc % kStages;
-        if (!wait_all(ptx::smem_u32(&bars->kv_full[st]), (cc / kStages) & 1)) {
+        const int st = cc % kSt;
+        if (!wait_all(ptx::smem_u32(&bars->kv_full[st]), (cc / kSt) & 1)) {
           if (lane == 0) record(p.status, kErrKvFull);
           ok = false; break;
         }
@@ -754,8 +758,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       uint32_t v_lo[2];
       int st2[2];
       for (int vc = 0; vc < 2 && ok; ++vc, ++cc) {
-        st2[vc] = cc % kStages;
-        if (!wait_all(ptx::smem_u32(&bars->kv_full[st2[vc]]), (cc / kStages) & 1)) {
+        st2[vc] = cc % kSt;
+        if (!wait_all(ptx::smem_u32(&bars->kv_full[st2[vc]]), (cc / kSt) & 1)) {
           if (lane == 0) record(p.status, kErrKvFull);
           ok = false; return;
         }
@@ -1074,7 +1078,31 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         ptx::tc_fence_before();
         arrive_issuer(issuer_bar(&bars->o_free));
         if (warp == 2) G4B_ITEM_AT(7);   // O read out
-        if (row_ok) {
+        if constexpr (kStageOut) {
+          // A lane owns a row, and rows are kilobytes apart in memory: stored directly, every
+          // 16-byte store touches its own line.  Instead the warp turns its [32 rows x 64
+          // columns] block through shared memory (4 KB per warp, 16-byte chunks XOR-swizzled by
+          // row so neither side has bank conflicts) and stores whole 128-byte row segments.
+          uint8_t* stage = sRing + (kStages - 1) * kChunkBytes + (warp - 2) * 4096;
+          const int64_t row_base = b * p.o_s0 + h * p.o_s1 + (int64_t)(m0 + lane_base) * p.o_s2 + half * 128;
+#pragma unroll
+          for (int cp = 0; cp < 2; ++cp) {
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const uint32_t* src = &pk[2 * cp + (c >> 2)][(c & 3) * 4];
+              *reinterpret_cast<uint4*>(stage + lane * 128 + ((c ^ (lane & 7)) << 4)) = make_uint4(src[0], src[1], src[2], src[3]);
+            }
+            __syncwarp();
+#pragma unroll
+            for (int i = 0; i < 8; ++i) {
+              const int rr = 4 * i + (lane >> 3), c = lane & 7;
+              const uint4 w = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((c ^ (rr & 7)) << 4));
+              if (lane_base + rr < rows_valid)
+                ptx::st_global_v4_hint((T*)p.o + row_base + (int64_t)rr * p.o_s2 + cp * 64 + c * 8, w, pol_o);
+            }
+            __syncwarp();
+          }
+        } else if (row_ok) {
 #pragma unroll
           for (int c4 = 0; c4 < 4; ++c4) {
             uint4* dst = reinterpret_cast<uint4*>((T*)p.o + off + c4 * 32);
@@ -1141,14 +1169,14 @@ static int encode_map(CUtensorMap* map, int dtype, int rank, void* base, const u
   return G4B_OK;
 }
 
-template <typename T, bool kPair>
+template <typename T, bool kPair, bool kStageOut>
 static int launch_variant(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const PrefillParams& p,
                           dim3 grid, cudaStream_t st) {
   static bool attr_set[64] = {false};
   int dev = 0;
   G4B_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    G4B_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<T, kPair>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    G4B_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<T, kPair, kStageOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -1163,15 +1191,16 @@ static int launch_variant(const CUtensorMap& qm, const CUtensorMap& km, const CU
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  G4B_CUDA_CHECK(cudaLaunchKernelEx(&cfg, prefill_kernel<T, kPair>, qm, km, vm, p));
+  G4B_CUDA_CHECK(cudaLaunchKernelEx(&cfg, prefill_kernel<T, kPair, kStageOut>, qm, km, vm, p));
   return G4B_OK;
 }
 
 template <typename T>
 static int launch_typed(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const PrefillParams& p,
-                        dim3 grid, bool pair, cudaStream_t st) {
-  if (pair) return launch_variant<T, true>(qm, km, vm, p, grid, st);
-  return launch_variant<T, false>(qm, km, vm, p, grid, st);
+                        dim3 grid, bool pair, bool stage_out, cudaStream_t st) {
+  if (pair && stage_out) return launch_variant<T, true, true>(qm, km, vm, p, grid, st);
+  if (pair) return launch_variant<T, true, false>(qm, km, vm, p, grid, st);
+  return launch_variant<T, false, false>(qm, km, vm, p, grid, st);
 }
 
 }  // namespace
@@ -1245,6 +1274,11 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   p.time_stride = a.time_dim_sizes.stride[0]; p.phase_stride = a.user_phase.stride[0];
   p.B = (int)B; p.H = (int)H; p.G = (int)G; p.Tq = (int)Tq; p.T = paged ? 1 : (int)T;
   p.n_q_tiles = (int)n_q_tiles;
+  // tiles per work item, from what the host knows (context lengths live on the device)
+  const int64_t est_tiles = a.sliding_window > 0 ? (a.sliding_window + 127) / 128 + 1 : (int64_t)a.ctx_window_size / 256 + 1;
+  // G4B_PREFILL_STAGE_OUT=0/1 overrides the choice (for tests that cover both forms at one size)
+  static const int force_stage = []() { const char* e = getenv("G4B_PREFILL_STAGE_OUT"); return e ? (e[0] == '1' ? 1 : 0) : -1; }();
+  const bool stage_out = pair && a.o.dtype != G4B_F32 && (force_stage >= 0 ? force_stage == 1 : est_tiles <= 12);
   if (paged) {
     p.block_tables = (const int32_t*)a.block_tables.ptr;
     p.bt_s0 = a.block_tables.stride[0]; p.bt_s1 = a.block_tables.stride[1];
@@ -1271,8 +1305,8 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   if (workers < 1) workers = 1;
   if (workers > n_items) workers = n_items;
   dim3 grid((unsigned)(pair ? 2 * workers : workers), 1, 1);
-  if (a.q.dtype == G4B_BF16) return launch_typed<__nv_bfloat16>(qm, km, vm, p, grid, pair, st);
-  return launch_typed<__half>(qm, km, vm, p, grid, pair, st);
+  if (a.q.dtype == G4B_BF16) return launch_typed<__nv_bfloat16>(qm, km, vm, p, grid, pair, stage_out, st);
+  return launch_typed<__half>(qm, km, vm, p, grid, pair, stage_out, st);
 }
 
 }  // namespace g4b
