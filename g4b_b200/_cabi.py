@@ -64,6 +64,19 @@ class G4bAppendArgs(ctypes.Structure):
     ]
 
 
+class G4bRopeAppendArgs(ctypes.Structure):
+    _fields_ = [
+        ("q", G4bTensor), ("k", G4bTensor), ("v", G4bTensor), ("q_out", G4bTensor), ("k_out", G4bTensor),
+        ("rope_freqs", G4bTensor), ("cache_offsets", G4bTensor),
+        ("q_rsos", G4bTensor), ("k_rsos", G4bTensor), ("v_rsos", G4bTensor),
+        ("q_norm_w", G4bTensor), ("k_norm_w", G4bTensor),
+        ("k_cache", G4bTensor), ("v_cache", G4bTensor),
+        ("user_phase", G4bTensor), ("block_tables", G4bTensor),
+        ("rmsnorm_eps", ctypes.c_float), ("phase", ctypes.c_int32), ("page_size", ctypes.c_int32),
+        ("norm_qk", ctypes.c_int32), ("norm_v", ctypes.c_int32), ("reserved", ctypes.c_int32),
+    ]
+
+
 class G4bAdvanceArgs(ctypes.Structure):
     _fields_ = [
         ("input_token_ids", G4bTensor), ("out_token_ids", G4bTensor), ("cache_offsets", G4bTensor),
@@ -80,6 +93,7 @@ EXPORTS = {
     "g4b_attn_combine": (ctypes.c_int, [ctypes.POINTER(G4bCombineArgs), ctypes.c_void_p]),
     "g4b_select_kv_splits": (ctypes.c_int, [ctypes.c_int] * 4),
     "g4b_kv_append": (ctypes.c_int, [ctypes.POINTER(G4bAppendArgs), ctypes.c_void_p]),
+    "g4b_rope_norm_append": (ctypes.c_int, [ctypes.POINTER(G4bRopeAppendArgs), ctypes.c_void_p]),
     "g4b_advance_decode_state": (ctypes.c_int, [ctypes.POINTER(G4bAdvanceArgs), ctypes.c_void_p]),
     "g4b_last_error_string": (ctypes.c_char_p, []),
     "g4b_abi_version": (ctypes.c_int, []),

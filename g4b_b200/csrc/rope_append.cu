@@ -1,0 +1,382 @@
+// Per-head RMS norm + rotary embedding of q and k, V norm, and the KV-cache append, in one
+// launch.
+//
+// Replaces the three launches the reference makes between the q/k/v projections and the
+// attention call (g4b/models/gemma4e.py:564-592): apply_rope (g4b/kernels/rope.py:8-39,
+// 123-211) and two add_kv_to_cache calls (g4b/kernels/add_kv_to_cache.py:83-159).  The
+// reference writes the rotated k back to its scratchpad and reads it again to append it;
+// here the row goes from registers to the cache, and q can leave in the 16-bit type the
+// prefill kernel wants.
+//
+// Pure streaming: one warp per (slot, token, head) row or per few heads of one token (the
+// sines and cosines of a token are shared by its heads), 16-byte accesses.  A lane holds the
+// elements [4l, 4l+4) and [D/2 + 4l, D/2 + 4l + 4) of the row, i.e. complete rotation pairs.
+#include "common.cuh"
+
+namespace g4b {
+namespace {
+
+constexpr int kMaxIter = 2;   // D/2 <= 256 elements: two passes of 32 lanes x 4
+
+struct RopeParams {
+  const void* q; const void* k; const void* v;
+  void* q_out; void* k_out;
+  const float* freqs;
+  const void* cache_offsets;
+  const float* q_rsos; const float* k_rsos; const float* v_rsos;
+  const float* q_w; const float* k_w;
+  void* k_cache; void* v_cache;
+  const uint8_t* user_phase;
+  const int32_t* block_tables;
+  int64_t qs[3], ks[3], vs[3], qos[3], kos[3];     // strides (elements) of dims 0..2
+  int64_t qrs[3], krs[3], vrs[3];
+  int64_t off_stride, phase_stride, bt_s0, bt_s1, freq_stride, qw_stride, kw_stride;
+  int in_dtype, q_out_dtype, k_out_dtype, cache_dtype;
+  int B, H, G, Tq, D;
+  int n_heads;                  // H + G (+ G with v)
+  int heads_per_warp;
+  int T;                        // ring length
+  int page_size, page_shift, num_pages, max_pages;
+  int offsets_are_i64, phase, norm_qk, norm_v;
+  float eps;
+  int32_t* status;
+};
+
+__device__ __forceinline__ float4 load4(const void* base, int dtype, int64_t idx) {
+  if (dtype == G4B_F32) return *reinterpret_cast<const float4*>((const float*)base + idx);
+  const uint2 raw = *reinterpret_cast<const uint2*>((const uint16_t*)base + idx);
+  float4 r;
+  if (dtype == G4B_F16) {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+    r = make_float4(a.x, a.y, b.x, b.y);
+  } else {
+    const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+    const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+    r = make_float4(a.x, a.y, b.x, b.y);
+  }
+  return r;
+}
+
+__device__ __forceinline__ void store4(void* base, int dtype, int64_t idx, float4 v) {
+  if (dtype == G4B_F32) {
+    *reinterpret_cast<float4*>((float*)base + idx) = v;
+    return;
+  }
+  uint2 raw;
+  if (dtype == G4B_F16) {
+    const __half2 a = __floats2half2_rn(v.x, v.y), b = __floats2half2_rn(v.z, v.w);
+    raw.x = *reinterpret_cast<const uint32_t*>(&a);
+    raw.y = *reinterpret_cast<const uint32_t*>(&b);
+  } else {
+    const __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+    raw.x = *reinterpret_cast<const uint32_t*>(&a);
+    raw.y = *reinterpret_cast<const uint32_t*>(&b);
+  }
+  *reinterpret_cast<uint2*>((uint16_t*)base + idx) = raw;
+}
+
+__device__ __forceinline__ float4 mul4(float4 a, float4 b) { return make_float4(a.x * b.x, a.y * b.y, a.z * b.z, a.w * b.w); }
+__device__ __forceinline__ float4 scale4(float4 a, float s) { return make_float4(a.x * s, a.y * s, a.z * s, a.w * s); }
+__device__ __forceinline__ float dot4(float4 a) { return a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w; }
+
+// Row of the cache that position `pos` of slot b, kv head g lands in; -1 after recording why not.
+__device__ __forceinline__ int64_t cache_row(const RopeParams& p, int b, int g, int64_t pos, int lane) {
+  if (p.block_tables != nullptr) {
+    const int64_t pg = pos >> p.page_shift;
+    if (pos < 0 || pg >= p.max_pages) {
+      if (lane == 0) atomicCAS(p.status, 0, 0x100 | 1);
+      return -1;
+    }
+    const int32_t page = p.block_tables[b * p.bt_s0 + pg * p.bt_s1];
+    if (page < 0 || page >= p.num_pages) {
+      if (lane == 0) atomicCAS(p.status, 0, 0x100 | 2);
+      return -1;
+    }
+    return ((int64_t)page * p.G + g) * p.page_size + (pos & (p.page_size - 1));
+  }
+  int64_t r = pos % p.T;
+  if (r < 0) r += p.T;
+  return ((int64_t)b * p.G + g) * p.T + r;
+}
+
+__global__ void __launch_bounds__(256) rope_norm_append_kernel(RopeParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int n_slots = (p.n_heads + p.heads_per_warp - 1) / p.heads_per_warp;
+  const int64_t row = warp / n_slots;
+  if (row >= (int64_t)p.B * p.Tq) return;
+  const int slot = (int)(warp % n_slots);
+  const int b = (int)(row / p.Tq), t = (int)(row % p.Tq);
+  const int half = p.D >> 1;
+
+  int64_t off;
+  if (p.offsets_are_i64) off = ((const int64_t*)p.cache_offsets)[b * p.off_stride];
+  else off = ((const int32_t*)p.cache_offsets)[b * p.off_stride];
+  const int64_t pos = off + t;
+  const bool in_phase = p.user_phase == nullptr || p.user_phase[b * p.phase_stride] == (uint8_t)p.phase;
+
+  const int h_begin = slot * p.heads_per_warp;
+  const int h_end = min(h_begin + p.heads_per_warp, p.n_heads);
+
+  // sines and cosines of this token, for the pairs this lane owns
+  float4 sn[kMaxIter], cs[kMaxIter];
+  const bool rotate = p.freqs != nullptr && h_begin < p.H + p.G;
+#pragma unroll
+  for (int it = 0; it < kMaxIter; ++it) {
+    const int d1 = it * 128 + lane * 4;
+    sn[it] = make_float4(0.f, 0.f, 0.f, 0.f);
+    cs[it] = make_float4(1.f, 1.f, 1.f, 1.f);
+    if (rotate && d1 < half) {
+      const float fp = (float)pos;
+      // theta is the fp32 product, as in the reference (rope.py:171) and its torch oracle
+      sincosf(fp * p.freqs[(d1 + 0) * p.freq_stride], &sn[it].x, &cs[it].x);
+      sincosf(fp * p.freqs[(d1 + 1) * p.freq_stride], &sn[it].y, &cs[it].y);
+      sincosf(fp * p.freqs[(d1 + 2) * p.freq_stride], &sn[it].z, &cs[it].z);
+      sincosf(fp * p.freqs[(d1 + 3) * p.freq_stride], &sn[it].w, &cs[it].w);
+    }
+  }
+
+  for (int hh = h_begin; hh < h_end; ++hh) {
+    // which tensor this head index belongs to: 0 q, 1 k, 2 v
+    const int kind = hh < p.H ? 0 : (hh < p.H + p.G ? 1 : 2);
+    const int h = kind == 0 ? hh : (kind == 1 ? hh - p.H : hh - p.H - p.G);
+    const void* src_base = kind == 0 ? p.q : (kind == 1 ? p.k : p.v);
+    const int64_t* ss = kind == 0 ? p.qs : (kind == 1 ? p.ks : p.vs);
+    const int64_t src_off = b * ss[0] + h * ss[1] + t * ss[2];
+
+    int64_t crow = -1;
+    void* cache = kind == 1 ? p.k_cache : (kind == 2 ? p.v_cache : nullptr);
+    if (cache != nullptr && in_phase) crow = cache_row(p, b, h, pos, lane);
+    void* out = nullptr;
+    int64_t out_off = 0;
+    int out_dtype = p.in_dtype;
+    if (kind == 0) {
+      if (p.q_out != nullptr) { out = p.q_out; out_dtype = p.q_out_dtype; out_off = b * p.qos[0] + h * p.qos[1] + t * p.qos[2]; }
+      else { out = const_cast<void*>(p.q); out_off = src_off; }
+    } else if (kind == 1) {
+      if (p.k_out != nullptr) { out = p.k_out; out_dtype = p.k_out_dtype; out_off = b * p.kos[0] + h * p.kos[1] + t * p.kos[2]; }
+      else if (p.k_cache == nullptr) { out = const_cast<void*>(p.k); out_off = src_off; }
+    }
+    if (out == nullptr && crow < 0) continue;    // nothing to write (warp-uniform)
+
+    float4 x1[kMaxIter], x2[kMaxIter];
+    float sumsq = 0.f;
+#pragma unroll
+    for (int it = 0; it < kMaxIter; ++it) {
+      const int d1 = it * 128 + lane * 4;
+      if (d1 < half) {
+        x1[it] = load4(src_base, p.in_dtype, src_off + d1);
+        x2[it] = load4(src_base, p.in_dtype, src_off + d1 + half);
+        sumsq += dot4(x1[it]) + dot4(x2[it]);
+      }
+    }
+    const bool norm = kind == 2 ? p.norm_v != 0 : p.norm_qk != 0;
+    if (norm) {
+      const float* rsos = kind == 0 ? p.q_rsos : (kind == 1 ? p.k_rsos : p.v_rsos);
+      const int64_t* rs = kind == 0 ? p.qrs : (kind == 1 ? p.krs : p.vrs);
+      if (rsos != nullptr) {
+        sumsq = rsos[b * rs[0] + h * rs[1] + t * rs[2]];
+      } else {
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sumsq += __shfl_xor_sync(0xffffffffu, sumsq, o);
+      }
+      const float inv = rsqrtf(sumsq / (float)p.D + p.eps);
+      const float* w = kind == 0 ? p.q_w : (kind == 1 ? p.k_w : nullptr);
+      const int64_t ws = kind == 0 ? p.qw_stride : p.kw_stride;
+#pragma unroll
+      for (int it = 0; it < kMaxIter; ++it) {
+        const int d1 = it * 128 + lane * 4;
+        if (d1 < half) {
+          if (w != nullptr) {
+            float4 w1, w2;
+            if (ws == 1) {
+              w1 = *reinterpret_cast<const float4*>(w + d1);
+              w2 = *reinterpret_cast<const float4*>(w + d1 + half);
+            } else {
+              w1 = make_float4(w[d1 * ws], w[(d1 + 1) * ws], w[(d1 + 2) * ws], w[(d1 + 3) * ws]);
+              w2 = make_float4(w[(d1 + half) * ws], w[(d1 + half + 1) * ws], w[(d1 + half + 2) * ws], w[(d1 + half + 3) * ws]);
+            }
+            // x * (inv * w): the reference's grouping (rope.py:33-34)
+            x1[it] = mul4(x1[it], scale4(w1, inv));
+            x2[it] = mul4(x2[it], scale4(w2, inv));
+          } else {
+            x1[it] = scale4(x1[it], inv);
+            x2[it] = scale4(x2[it], inv);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int it = 0; it < kMaxIter; ++it) {
+      const int d1 = it * 128 + lane * 4;
+      if (d1 < half) {
+        float4 y1 = x1[it], y2 = x2[it];
+        if (kind != 2 && p.freqs != nullptr) {
+          const float4 a = x1[it], c = x2[it], s = sn[it], co = cs[it];
+          y1 = make_float4(co.x * a.x - s.x * c.x, co.y * a.y - s.y * c.y, co.z * a.z - s.z * c.z, co.w * a.w - s.w * c.w);
+          y2 = make_float4(co.x * c.x + s.x * a.x, co.y * c.y + s.y * a.y, co.z * c.z + s.z * a.z, co.w * c.w + s.w * a.w);
+        }
+        if (out != nullptr) {
+          store4(out, out_dtype, out_off + d1, y1);
+          store4(out, out_dtype, out_off + d1 + half, y2);
+        }
+        if (crow >= 0) {
+          store4(cache, p.cache_dtype, crow * p.D + d1, y1);
+          store4(cache, p.cache_dtype, crow * p.D + d1 + half, y2);
+        }
+      }
+    }
+  }
+}
+
+int check_view(const G4bTensor& t, const char* name, int ndim, int64_t d0, int64_t d1, int64_t d2, int64_t d3) {
+  if (t.ptr == nullptr) return fail(G4B_ERR_BAD_ARG, "%s: null pointer", name);
+  if (t.ndim != ndim) return fail(G4B_ERR_BAD_ARG, "%s: expected rank %d, got %d", name, ndim, t.ndim);
+  const int64_t want[4] = {d0, d1, d2, d3};
+  for (int i = 0; i < ndim; ++i)
+    if (want[i] >= 0 && t.shape[i] != want[i])
+      return fail(G4B_ERR_BAD_ARG, "%s: extent %d is %lld, expected %lld", name, i, (long long)t.shape[i], (long long)want[i]);
+  return G4B_OK;
+}
+
+// A [.,.,.,D] row view the kernel can read or write 16 bytes at a time.
+int check_rows(const G4bTensor& t, const char* name) {
+  if (!is_float_dtype(t.dtype)) return fail(G4B_ERR_BAD_DTYPE, "%s must be f32, f16 or bf16", name);
+  if (t.shape[3] > 1 && t.stride[3] != 1) return fail(G4B_ERR_BAD_STRIDE, "%s: innermost stride must be 1", name);
+  if (((uintptr_t)t.ptr & 15) != 0) return fail(G4B_ERR_BAD_STRIDE, "%s: base must be 16-byte aligned", name);
+  for (int i = 0; i < 3; ++i)
+    if (t.shape[i] > 1 && (t.stride[i] % 4) != 0)
+      return fail(G4B_ERR_BAD_STRIDE, "%s: strides must be multiples of 4 elements", name);
+  return G4B_OK;
+}
+
+void copy3(int64_t* dst, const G4bTensor& t) { dst[0] = t.stride[0]; dst[1] = t.stride[1]; dst[2] = t.stride[2]; }
+
+}  // namespace
+
+int launch_rope_norm_append(const G4bRopeAppendArgs& a, cudaStream_t st) {
+  int rc;
+  if ((rc = check_view(a.q, "q", 4, -1, -1, -1, -1))) return rc;
+  const int64_t B = a.q.shape[0], H = a.q.shape[1], Tq = a.q.shape[2], D = a.q.shape[3];
+  if ((rc = check_view(a.k, "k", 4, B, -1, Tq, D))) return rc;
+  const int64_t G = a.k.shape[1];
+  if ((rc = check_rows(a.q, "q")) || (rc = check_rows(a.k, "k"))) return rc;
+  if (a.k.dtype != a.q.dtype) return fail(G4B_ERR_BAD_DTYPE, "q and k must have one dtype");
+  if (D % 8 != 0 || D < 8 || D > 512) return fail(G4B_ERR_UNSUPPORTED, "head dim must be a multiple of 8, at most 512");
+  const bool has_v = a.v.ptr != nullptr;
+  if (has_v) {
+    if ((rc = check_view(a.v, "v", 4, B, G, Tq, D)) || (rc = check_rows(a.v, "v"))) return rc;
+    if (a.v.dtype != a.q.dtype) return fail(G4B_ERR_BAD_DTYPE, "v must have the dtype of q and k");
+    if (a.v_cache.ptr == nullptr) return fail(G4B_ERR_BAD_ARG, "v needs v_cache");
+  } else if (a.v_cache.ptr != nullptr) {
+    return fail(G4B_ERR_BAD_ARG, "v_cache needs v");
+  }
+  if (a.q_out.ptr != nullptr && ((rc = check_view(a.q_out, "q_out", 4, B, H, Tq, D)) || (rc = check_rows(a.q_out, "q_out")))) return rc;
+  if (a.k_out.ptr != nullptr && ((rc = check_view(a.k_out, "k_out", 4, B, G, Tq, D)) || (rc = check_rows(a.k_out, "k_out")))) return rc;
+  if (a.rope_freqs.ptr != nullptr) {
+    if ((rc = check_view(a.rope_freqs, "rope_freqs", 1, D / 2, -1, -1, -1))) return rc;   // rope.py:147
+    if (a.rope_freqs.dtype != G4B_F32) return fail(G4B_ERR_BAD_DTYPE, "rope_freqs must be f32");
+  }
+  if ((rc = check_view(a.cache_offsets, "cache_offsets", 1, B, -1, -1, -1))) return rc;    // rope.py:148
+  if (a.cache_offsets.dtype != G4B_I32 && a.cache_offsets.dtype != G4B_I64)
+    return fail(G4B_ERR_BAD_DTYPE, "cache_offsets must be int32 or int64");
+  const G4bTensor* rsos[3] = {&a.q_rsos, &a.k_rsos, &a.v_rsos};
+  const char* rsos_name[3] = {"q_rsos", "k_rsos", "v_rsos"};
+  for (int i = 0; i < 3; ++i) {
+    if (rsos[i]->ptr == nullptr) continue;
+    if ((rc = check_view(*rsos[i], rsos_name[i], 3, B, i == 0 ? H : G, Tq, -1))) return rc;  // rope.py:152-157
+    if (rsos[i]->dtype != G4B_F32) return fail(G4B_ERR_BAD_DTYPE, "%s must be f32", rsos_name[i]);
+  }
+  const G4bTensor* w[2] = {&a.q_norm_w, &a.k_norm_w};
+  for (int i = 0; i < 2; ++i) {
+    if (w[i]->ptr == nullptr) continue;
+    if ((rc = check_view(*w[i], i == 0 ? "q_norm_w" : "k_norm_w", 1, D, -1, -1, -1))) return rc;  // rope.py:158-159
+    if (w[i]->dtype != G4B_F32) return fail(G4B_ERR_BAD_DTYPE, "norm weights must be f32");
+    if (((uintptr_t)w[i]->ptr & 15) != 0) return fail(G4B_ERR_BAD_STRIDE, "norm weights must be 16-byte aligned");
+  }
+  const bool paged = a.block_tables.ptr != nullptr;
+  const G4bTensor* caches[2] = {&a.k_cache, &a.v_cache};
+  for (int i = 0; i < 2; ++i) {
+    const G4bTensor& c = *caches[i];
+    if (c.ptr == nullptr) continue;
+    const char* nm = i == 0 ? "k_cache" : "v_cache";
+    if ((rc = check_view(c, nm, 4, -1, G, -1, D))) return rc;
+    if (!is_float_dtype(c.dtype)) return fail(G4B_ERR_BAD_DTYPE, "%s must be f32, f16 or bf16", nm);
+    if (!contiguous_from(c, 0)) return fail(G4B_ERR_BAD_STRIDE, "%s must be contiguous", nm);
+    if (((uintptr_t)c.ptr & 15) != 0) return fail(G4B_ERR_BAD_STRIDE, "%s must be 16-byte aligned", nm);
+    if (paged) {
+      if (c.shape[2] != a.page_size) return fail(G4B_ERR_BAD_ARG, "%s: pool dim 2 must equal page_size", nm);
+    } else {
+      if (c.shape[0] != B) return fail(G4B_ERR_BAD_ARG, "%s: ring cache must have B slots", nm);
+      if (Tq > c.shape[2]) return fail(G4B_ERR_BAD_ARG, "more new tokens than cache rows");   // add_kv_to_cache.py:123
+    }
+  }
+  if (a.k_cache.ptr != nullptr && a.v_cache.ptr != nullptr) {
+    if (a.k_cache.dtype != a.v_cache.dtype) return fail(G4B_ERR_BAD_DTYPE, "k_cache and v_cache must have one dtype");
+    for (int i = 0; i < 4; ++i)
+      if (a.k_cache.shape[i] != a.v_cache.shape[i]) return fail(G4B_ERR_BAD_ARG, "k_cache/v_cache shapes differ");
+  }
+  if (paged) {
+    if ((rc = check_view(a.block_tables, "block_tables", 2, B, -1, -1, -1))) return rc;
+    if (a.block_tables.dtype != G4B_I32) return fail(G4B_ERR_BAD_DTYPE, "block_tables must be int32");
+    if (a.page_size <= 0 || (a.page_size & (a.page_size - 1)) != 0) return fail(G4B_ERR_BAD_ARG, "page_size must be a power of two");
+    if (a.k_cache.ptr == nullptr) return fail(G4B_ERR_BAD_ARG, "block_tables without a cache");
+  }
+  if (a.user_phase.ptr != nullptr) {
+    if ((rc = check_view(a.user_phase, "user_phase", 1, B, -1, -1, -1))) return rc;
+    if (a.user_phase.dtype != G4B_U8) return fail(G4B_ERR_BAD_DTYPE, "user_phase must be uint8");
+  }
+
+  RopeParams p{};
+  p.q = a.q.ptr; p.k = a.k.ptr; p.v = a.v.ptr; p.q_out = a.q_out.ptr; p.k_out = a.k_out.ptr;
+  p.freqs = (const float*)a.rope_freqs.ptr; p.freq_stride = a.rope_freqs.stride[0];
+  p.cache_offsets = a.cache_offsets.ptr; p.off_stride = a.cache_offsets.stride[0];
+  p.offsets_are_i64 = a.cache_offsets.dtype == G4B_I64;
+  p.q_rsos = (const float*)a.q_rsos.ptr; p.k_rsos = (const float*)a.k_rsos.ptr; p.v_rsos = (const float*)a.v_rsos.ptr;
+  p.q_w = (const float*)a.q_norm_w.ptr; p.k_w = (const float*)a.k_norm_w.ptr;
+  p.qw_stride = a.q_norm_w.stride[0]; p.kw_stride = a.k_norm_w.stride[0];
+  p.k_cache = a.k_cache.ptr; p.v_cache = a.v_cache.ptr;
+  p.user_phase = (const uint8_t*)a.user_phase.ptr; p.phase_stride = a.user_phase.stride[0];
+  p.block_tables = (const int32_t*)a.block_tables.ptr;
+  p.bt_s0 = a.block_tables.stride[0]; p.bt_s1 = a.block_tables.stride[1];
+  copy3(p.qs, a.q); copy3(p.ks, a.k); copy3(p.vs, a.v); copy3(p.qos, a.q_out); copy3(p.kos, a.k_out);
+  copy3(p.qrs, a.q_rsos); copy3(p.krs, a.k_rsos); copy3(p.vrs, a.v_rsos);
+  p.in_dtype = a.q.dtype; p.q_out_dtype = a.q_out.dtype; p.k_out_dtype = a.k_out.dtype;
+  p.cache_dtype = a.k_cache.ptr != nullptr ? a.k_cache.dtype : a.v_cache.dtype;
+  p.B = (int)B; p.H = (int)H; p.G = (int)G; p.Tq = (int)Tq; p.D = (int)D;
+  p.n_heads = (int)(H + G + (has_v ? G : 0));
+  p.phase = a.phase; p.norm_qk = a.norm_qk; p.norm_v = a.norm_v; p.eps = a.rmsnorm_eps;
+  if (paged) {
+    p.page_size = a.page_size;
+    while ((1 << p.page_shift) < a.page_size) ++p.page_shift;
+    p.num_pages = (int)a.k_cache.shape[0];
+    p.max_pages = (int)a.block_tables.shape[1];
+  } else if (a.k_cache.ptr != nullptr || a.v_cache.ptr != nullptr) {
+    p.T = (int)(a.k_cache.ptr != nullptr ? a.k_cache.shape[2] : a.v_cache.shape[2]);
+  } else {
+    p.T = 1;
+  }
+  p.status = device_status_ptr();
+  if (p.status == nullptr) return G4B_ERR_CUDA;
+
+  const int64_t rows = B * Tq;
+  if (rows == 0 || p.n_heads == 0) return G4B_OK;
+  // Few rows (decode): one head per warp, for parallelism.  Many (prefill): a warp takes four
+  // heads of a token and computes the token's sines and cosines once for them.
+  p.heads_per_warp = rows * p.n_heads >= 16384 ? 4 : 1;
+  const int64_t n_slots = (p.n_heads + p.heads_per_warp - 1) / p.heads_per_warp;
+  const int64_t warps = rows * n_slots;
+  const int64_t blocks = (warps + 7) / 8;
+  if (blocks > 0x7fffffffLL) return fail(G4B_ERR_UNSUPPORTED, "rope_norm_append: too many rows");
+  rope_norm_append_kernel<<<(unsigned)blocks, 256, 0, st>>>(p);
+  G4B_CUDA_CHECK(cudaGetLastError());
+  return G4B_OK;
+}
+
+}  // namespace g4b
+
+extern "C" int g4b_rope_norm_append(const G4bRopeAppendArgs* args, void* cuda_stream) {
+  if (args == nullptr) return g4b::fail(G4B_ERR_BAD_ARG, "args is null");
+  return g4b::launch_rope_norm_append(*args, (cudaStream_t)cuda_stream);
+}

@@ -183,6 +183,53 @@ int g4b_advance_decode_state(const G4bAdvanceArgs* args, void* cuda_stream);
  */
 int g4b_attn_decode_static_scratch(const G4bAttnArgs* args, void* cuda_stream);
 
+/*
+ * One launch for the three the reference issues between the q/k/v projections and the
+ * attention call (g4b/models/gemma4e.py:564-592): apply_rope on q and k
+ * (g4b/kernels/rope.py:8-39,123-211: per-head RMS norm with weight, then rotation of the
+ * element pairs (i, i + D/2) by theta = (cache_offsets[b] + t) * rope_freqs[i], in fp32),
+ * add_kv_to_cache of the rotated k, and add_kv_to_cache of v with the weight-less V norm
+ * (g4b/kernels/add_kv_to_cache.py:148-159).
+ *
+ * Where the rows go:
+ *   q  -> q_out if given (any float dtype: this is how an f32 scratchpad becomes the 16-bit
+ *         Q that the prefill kernel reads), else back into q (what apply_rope does);
+ *   k  -> k_cache (ring or paged, only slots with user_phase[b] == phase) and/or k_out; with
+ *         neither, back into k (what apply_rope does);
+ *   v  -> v_cache (same gate); v and v_cache may be absent together.
+ * The rotation is not gated by phase (the reference's is not either).
+ *
+ * Norms: q and k are normalised iff norm_qk != 0, v iff norm_v != 0.  A row's sum of squares
+ * comes from *_rsos if given (the reference's matmul epilogue produces it), else the kernel
+ * computes it from the row.  q_norm_w / k_norm_w [D] are optional (absent = ones).
+ * rope_freqs absent = no rotation (norm and append only).
+ */
+typedef struct G4bRopeAppendArgs {
+  G4bTensor q;             /* [B, H, Tq, D] view, last stride 1; f32, f16 or bf16 */
+  G4bTensor k;             /* [B, G, Tq, D] view */
+  G4bTensor v;             /* optional [B, G, Tq, D] view */
+  G4bTensor q_out;         /* optional [B, H, Tq, D] view */
+  G4bTensor k_out;         /* optional [B, G, Tq, D] view */
+  G4bTensor rope_freqs;    /* optional f32 [D/2] */
+  G4bTensor cache_offsets; /* [B] int32 or int64: position of token 0 of each slot */
+  G4bTensor q_rsos;        /* optional f32 [B, H, Tq] view */
+  G4bTensor k_rsos;        /* optional f32 [B, G, Tq] view */
+  G4bTensor v_rsos;        /* optional f32 [B, G, Tq] view */
+  G4bTensor q_norm_w;      /* optional f32 [D] */
+  G4bTensor k_norm_w;      /* optional f32 [D] */
+  G4bTensor k_cache;       /* optional ring [B, G, T, D] or pool [num_pages, G, page_size, D] */
+  G4bTensor v_cache;       /* optional, same form as k_cache */
+  G4bTensor user_phase;    /* optional uint8 [B] */
+  G4bTensor block_tables;  /* optional int32 [B, max_pages]: caches are page pools */
+  float rmsnorm_eps;
+  int32_t phase;
+  int32_t page_size;
+  int32_t norm_qk;
+  int32_t norm_v;
+  int32_t reserved;
+} G4bRopeAppendArgs;
+int g4b_rope_norm_append(const G4bRopeAppendArgs* args, void* cuda_stream);
+
 /* Message of the last failing call on this thread ("" if none). No reference counterpart:
  * the reference raises Python exceptions from its wrappers (fa2.py:656-657). */
 const char* g4b_last_error_string(void);

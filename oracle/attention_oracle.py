@@ -17,6 +17,8 @@ What each function follows:
   gather_pages          new (paged layout): pool[block_table[j // page], :, j % page, :]
   flash_attention       g4b/kernels/fa2.py:256-480 semantics over the above
   add_kv_to_cache       g4b/kernels/add_kv_to_cache.py:148-158
+  rope_norm             g4b/kernels/rope.py:22-39,166-173; scripts/reference_impl.py:77-85,255-265
+  rope_norm_append      the sequence at g4b/models/gemma4e.py:564-592 over the two above
   advance_decode_state  g4b/kernels/advance_decode_state.py:52-63
   combine_partials      g4b/kernels/fa2.py:618-626
   select_kv_splits      g4b/kernels/fa2.py:201-212
@@ -155,6 +157,45 @@ def add_kv_to_cache(x, cache, cache_offsets, rmsnorm_eps, x_rsos=None, user_phas
                 page = int(block_tables[b, pos // page_size])
                 out[page, :, pos % page_size] = val[b, :, t]
     return out
+
+
+def rope_norm(x, positions, rope_freqs, *, rsos=None, weight=None, eps=1e-6, norm=True) -> torch.Tensor:
+    """x [B,heads,t,D] -> fp32 rows scaled by rsqrt(rsos/D + eps) * weight (rsos defaults to the
+    row's own sum of squares) and rotated: pairs (i, i + D/2) turn by theta =
+    positions[b,t] * rope_freqs[i], theta an fp32 product (rope.py:22-39,166-173;
+    reference_impl.py:259-265).  rope_freqs None = no rotation; norm False = no scaling."""
+    xf = x.detach().to(torch.float32)
+    D = xf.shape[-1]
+    if norm:
+        ss = xf.square().sum(-1) if rsos is None else rsos.detach().to(torch.float32)
+        inv = torch.rsqrt(ss / D + eps)[..., None]
+        xf = xf * (inv * weight.to(torch.float32) if weight is not None else inv)
+    if rope_freqs is None:
+        return xf
+    theta = positions.to(torch.float32)[:, None, :, None] * rope_freqs.to(torch.float32)[None, None, None, :]
+    sin, cos = theta.sin(), theta.cos()
+    x1, x2 = xf[..., : D // 2], xf[..., D // 2:]
+    return torch.cat([cos * x1 - sin * x2, cos * x2 + sin * x1], dim=-1)
+
+
+def rope_norm_append(q, k, v, rope_freqs, cache_offsets, k_cache, v_cache, rmsnorm_eps, *, q_rsos=None,
+                     k_rsos=None, v_rsos=None, q_rmsnorm_w=None, k_rmsnorm_w=None, norm_qk=True, norm_v=True,
+                     user_phase=None, phase=0, block_tables=None, page_size=16):
+    """Returns (q', k', k_cache', v_cache'): q and k normalised and rotated in fp32 (not phase
+    gated), and the caches after appending k' and the normalised v for the slots in phase
+    (g4b/models/gemma4e.py:564-592)."""
+    B, _, Tq, D = q.shape
+    pos = cache_offsets.to(torch.int64)[:, None] + torch.arange(Tq)[None, :]
+    q2 = rope_norm(q, pos, rope_freqs, rsos=q_rsos, weight=q_rmsnorm_w, eps=rmsnorm_eps, norm=norm_qk)
+    k2 = rope_norm(k, pos, rope_freqs, rsos=k_rsos, weight=k_rmsnorm_w, eps=rmsnorm_eps, norm=norm_qk)
+    kc = add_kv_to_cache(k2, k_cache, cache_offsets, rmsnorm_eps, None, user_phase, phase,
+                         block_tables=block_tables, page_size=page_size) if k_cache is not None else None
+    vc = None
+    if v is not None:
+        v2 = rope_norm(v, pos, None, rsos=v_rsos, eps=rmsnorm_eps, norm=norm_v)
+        vc = add_kv_to_cache(v2, v_cache, cache_offsets, rmsnorm_eps, None, user_phase, phase,
+                             block_tables=block_tables, page_size=page_size)
+    return q2, k2, kc, vc
 
 
 def advance_decode_state(input_token_ids, out_token_ids, cache_offsets, time_dim_sizes, user_phase):

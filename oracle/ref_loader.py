@@ -69,3 +69,23 @@ def make_layer_cache(*, heads: int, kv_heads: int, head_dim: int, context_length
         rope_dimension_count=head_dim, rope_dimension_count_swa=head_dim,
     )
     return ref.LayerKVCache(conf, 0)
+
+
+def make_rope_and_norms(*, head_dim: int, is_swa: bool, freq_base: float, eps: float, rope_freqs=None,
+                        q_weight=None, k_weight=None):
+    """The reference's RoPE (reference_impl.py:240-265) and its q / k / v RMSNorm modules
+    (reference_impl.py:77-85; the V norm has no weight) as Attention.forward uses them
+    (reference_impl.py:219-233)."""
+    ref = load_reference_impl()
+    conf = ref.Gemma4Config(
+        block_count=1, context_length=1, embedding_length=head_dim,
+        feed_forward_length=1, attention_head_count=1, attention_head_count_kv=1,
+        rope_freq_base=freq_base, rope_freq_base_swa=freq_base, attention_layer_norm_rms_epsilon=eps,
+        attention_key_length=head_dim, attention_value_length=head_dim, final_logit_softcapping=0.0,
+        attention_sliding_window=1, attention_shared_kv_layers=0,
+        embedding_length_per_layer_input=0, attention_sliding_window_pattern=[is_swa],
+        attention_key_length_swa=head_dim, attention_value_length_swa=head_dim,
+        rope_dimension_count=head_dim, rope_dimension_count_swa=head_dim,
+    )
+    rope = ref.RoPE(conf, None if is_swa else rope_freqs)
+    return rope, ref.RMSNorm(conf, q_weight), ref.RMSNorm(conf, k_weight), ref.RMSNorm(conf, None)

@@ -63,7 +63,45 @@ def run_case(name, *, heads, kv_heads, head_dim, context_length, sliding_window,
     print(name, tuple(out.shape), float(out.abs().mean()))
 
 
+def run_rope_case(name, *, heads, kv_heads, head_dim, n_tokens, base_time_offset, is_swa, freq_base, seed):
+    """q/k/v of one chunk through the reference's q_norm/k_norm/v_norm and RoPE, in the order
+    of Attention.forward (reference_impl.py:219-233).  A global layer divides its frequencies by
+    the model's rope_freqs factors (reference_impl.py:246-247)."""
+    gen = torch.Generator().manual_seed(seed)
+    eps = 1e-6
+    q_w = (1.0 + 0.25 * rnd(gen, head_dim)).to(torch.float16).to(torch.float32)
+    k_w = (1.0 + 0.25 * rnd(gen, head_dim)).to(torch.float16).to(torch.float32)
+    factors = None if is_swa else (1.0 + torch.rand(head_dim // 2, generator=gen) * 7.0)
+    rope, q_norm, k_norm, v_norm = ref_loader.make_rope_and_norms(
+        head_dim=head_dim, is_swa=is_swa, freq_base=freq_base, eps=eps, rope_freqs=factors,
+        q_weight=q_w, k_weight=k_w)
+    q = 4.0 * rnd(gen, 1, heads, n_tokens, head_dim)
+    k = 0.5 * rnd(gen, 1, kv_heads, n_tokens, head_dim)
+    v = 2.0 * rnd(gen, 1, kv_heads, n_tokens, head_dim)
+    (q_out,) = rope(q_norm(q), base_time_offset=base_time_offset)
+    (k_out,) = rope(k_norm(k), base_time_offset=base_time_offset)
+    v_out = v_norm(v)
+    np.savez(
+        OUT / f"{name}.npz",
+        q=q[0].numpy().astype(np.float16), k=k[0].numpy().astype(np.float16), v=v[0].numpy().astype(np.float16),
+        q_w=q_w.numpy().astype(np.float16), k_w=k_w.numpy().astype(np.float16),
+        freqs=rope.freqs.numpy().astype(np.float32),
+        q_out=q_out[0].numpy().astype(np.float32), k_out=k_out[0].numpy().astype(np.float32),
+        v_out=v_out[0].numpy().astype(np.float32),
+        base_time_offset=np.int32(base_time_offset), eps=np.float32(eps),
+    )
+    print(name, tuple(q_out.shape), float(q_out.abs().mean()))
+
+
 def main():
+    # norm + rotary embedding ahead of the append: a sliding-window layer (plain frequencies)
+    # and a global layer (frequencies divided by per-pair factors), at small and large positions
+    run_rope_case("rope_swa", heads=4, kv_heads=2, head_dim=256, n_tokens=9, base_time_offset=0,
+                  is_swa=True, freq_base=10000.0, seed=21)
+    run_rope_case("rope_global_far", heads=4, kv_heads=2, head_dim=256, n_tokens=5, base_time_offset=100000,
+                  is_swa=False, freq_base=1000000.0, seed=22)
+    run_rope_case("rope_d128", heads=2, kv_heads=1, head_dim=128, n_tokens=4, base_time_offset=37,
+                  is_swa=True, freq_base=10000.0, seed=23)
     common = dict(heads=4, kv_heads=2, head_dim=256)
     # fresh causal prefill, global layer, BASELINE scale 1/sqrt(256)
     run_case("prefill_causal", **common, context_length=64, sliding_window=16, is_swa=False,

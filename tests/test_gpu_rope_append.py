@@ -1,0 +1,179 @@
+"""Norm + rotary embedding + KV append in one launch, on the GPU through the C ABI, against
+the reference's own outputs (golden vectors) and the oracle.
+
+Tolerances: the arithmetic is fp32 on both sides, so fp32 outputs agree to a few ulp
+(2e-5 abs+rel: the multiplications are grouped differently and rsqrt / sincos are different
+implementations); 16-bit outputs to one ulp of that type.  Where the row is only moved
+(block-table and ring indexing) the comparison is on which rows changed, bit for bit."""
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+from g4b_b200.kernels.fa2 import flash_attention
+from g4b_b200.kernels.rope import apply_rope, rope_norm_append
+from helpers import assert_close, orc, randn
+
+pytestmark = pytest.mark.gpu
+GOLD = Path(__file__).resolve().parent / "golden"
+
+
+def load(name):
+    z = np.load(GOLD / f"{name}.npz")
+    return {k: (torch.from_numpy(z[k].astype(np.float32)) if z[k].ndim else z[k].item()) for k in z.files}
+
+
+def ulp_tol(dtype):
+    return {torch.float32: 2e-5, torch.float16: 1e-3, torch.bfloat16: 8e-3}[dtype]
+
+
+@pytest.mark.parametrize("name", ["rope_swa", "rope_global_far", "rope_d128"])
+def test_apply_rope_matches_reference_golden(cuda, name):
+    """The reference's signature, in place on fp32 q and k, sums of squares passed in."""
+    g = load(name)
+    q, k = g["q"][None].to(cuda), g["k"][None].to(cuda)
+    off = torch.tensor([int(g["base_time_offset"])], dtype=torch.int32, device=cuda)
+    apply_rope(q, k, g["freqs"].to(cuda), off, (q * q).sum(-1), (k * k).sum(-1), g["q_w"].to(cuda),
+               g["k_w"].to(cuda), float(g["eps"]))
+    assert torch.allclose(q[0].cpu(), g["q_out"], atol=2e-5, rtol=2e-5), (q[0].cpu() - g["q_out"]).abs().max()
+    assert torch.allclose(k[0].cpu(), g["k_out"], atol=2e-5, rtol=2e-5), (k[0].cpu() - g["k_out"]).abs().max()
+
+
+@pytest.mark.parametrize("name", ["rope_swa", "rope_global_far"])
+@pytest.mark.parametrize("cache_dtype", [torch.float16, torch.bfloat16, torch.float32])
+def test_fused_matches_reference_golden(cuda, name, cache_dtype):
+    """Fused form on the golden inputs: q to a separate 16-bit tensor, k and the normalised v
+    into a ring cache that wraps, sums of squares computed by the kernel."""
+    g = load(name)
+    H, n, D = g["q"].shape
+    G = g["k"].shape[0]
+    T = n + 2
+    base = int(g["base_time_offset"])
+    q, k, v = (g[x][None].to(cuda) for x in ("q", "k", "v"))
+    q_keep = q.clone()
+    q_out = torch.zeros(1, H, n, D, dtype=cache_dtype, device=cuda)
+    kc = torch.zeros(1, G, T, D, dtype=cache_dtype, device=cuda)
+    vc = torch.zeros(1, G, T, D, dtype=cache_dtype, device=cuda)
+    off = torch.tensor([base], dtype=torch.int64, device=cuda)
+    rope_norm_append(q, k, v, g["freqs"].to(cuda), off, kc, vc, float(g["eps"]), q_out=q_out,
+                     q_rmsnorm_w=g["q_w"].to(cuda), k_rmsnorm_w=g["k_w"].to(cuda))
+    tol = ulp_tol(cache_dtype)
+    assert torch.equal(q, q_keep), "q must stay untouched when q_out is given"
+    assert torch.allclose(q_out[0].float().cpu(), g["q_out"], atol=tol, rtol=tol)
+    rows = [(base + t) % T for t in range(n)]
+    assert torch.allclose(kc[0][:, rows].float().cpu(), g["k_out"], atol=tol, rtol=tol)
+    assert torch.allclose(vc[0][:, rows].float().cpu(), g["v_out"], atol=tol, rtol=tol)
+    untouched = [r for r in range(T) if r not in rows]
+    assert (kc[0][:, untouched] == 0).all() and (vc[0][:, untouched] == 0).all()
+
+
+@pytest.mark.parametrize("in_dtype", [torch.float32, torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B,Tq", [(3, 1), (2, 19), (4, 512)])
+def test_fused_ring_against_oracle(cuda, in_dtype, B, Tq):
+    """Engine layout (physical [B,t,heads,D] viewed as [B,heads,t,D]), rsos passed as strided
+    views, phase gate on the append but not on the rotation."""
+    gen = torch.Generator().manual_seed(100 + B + Tq)
+    H, G, D, T = 8, 2, 256, Tq + 40
+    q_phys = randn(gen, B, Tq, H, D, dtype=in_dtype)
+    k_phys = randn(gen, B, Tq, G, D, dtype=in_dtype)
+    v_phys = randn(gen, B, Tq, G, D, dtype=in_dtype)
+    q, k, v = (x.permute(0, 2, 1, 3) for x in (q_phys, k_phys, v_phys))
+    rs = [(x.float() ** 2).sum(-1).contiguous() for x in (q_phys, k_phys, v_phys)]      # [B,t,heads]
+    q_w, k_w = 1 + 0.1 * randn(gen, D), 1 + 0.1 * randn(gen, D)
+    freqs = 1.0 / (10000.0 ** (torch.arange(0, D, 2) / D))
+    off = torch.tensor([5, T - 3, 1000, 77][:B], dtype=torch.int32)
+    phase = torch.tensor([1, 1, 2, 1][:B], dtype=torch.uint8)
+    kc0, vc0 = randn(gen, B, G, T, D, dtype=torch.float16), randn(gen, B, G, T, D, dtype=torch.float16)
+    want_q, want_k, want_kc, want_vc = orc.rope_norm_append(
+        q, k, v, freqs, off, kc0, vc0, 1e-6, q_rsos=rs[0].permute(0, 2, 1), k_rsos=rs[1].permute(0, 2, 1),
+        v_rsos=rs[2].permute(0, 2, 1), q_rmsnorm_w=q_w, k_rmsnorm_w=k_w, user_phase=phase, phase=1)
+
+    qd, kd, vd = (x.to(cuda).permute(0, 2, 1, 3) for x in (q_phys, k_phys, v_phys))
+    rsd = [x.to(cuda).permute(0, 2, 1) for x in rs]
+    kc, vc = kc0.to(cuda), vc0.to(cuda)
+    k_out = torch.zeros(B, G, Tq, D, dtype=torch.float32, device=cuda)
+    rope_norm_append(qd, kd, vd, freqs.to(cuda), off.to(cuda), kc, vc, 1e-6, k_out=k_out, q_rsos=rsd[0],
+                     k_rsos=rsd[1], v_rsos=rsd[2], q_rmsnorm_w=q_w.to(cuda), k_rmsnorm_w=k_w.to(cuda),
+                     user_phase=phase.to(cuda), phase=1)
+    tol = ulp_tol(in_dtype)
+    assert torch.allclose(qd.float().cpu(), want_q, atol=tol, rtol=tol)        # in place, all slots
+    assert torch.allclose(k_out.cpu(), want_k, atol=2e-5, rtol=2e-5)
+    assert torch.allclose(kc.float().cpu(), want_kc.float(), atol=1e-3, rtol=1e-3)
+    assert torch.allclose(vc.float().cpu(), want_vc.float(), atol=1e-3, rtol=1e-3)
+    # rows of slots off phase, and rows that received no token, keep their bits
+    same = (want_kc == kc0).all(-1)
+    assert torch.equal(kc.cpu()[same], kc0[same]) and torch.equal(vc.cpu()[same], vc0[same])
+
+
+@pytest.mark.parametrize("page_size", [16, 32])
+def test_fused_paged_then_attention(cuda, page_size):
+    """Paged caches: append a chunk through the fused kernel, then run attention on what it
+    wrote and compare with the oracle end to end (bf16, the prefill kernel's input type)."""
+    gen = torch.Generator().manual_seed(9)
+    B, H, G, D, Tq = 2, 4, 2, 256, 150
+    before = [0, 45]
+    pages_per = [(b + Tq + page_size - 1) // page_size for b in before]
+    num_pages = sum(pages_per) + 3
+    perm = torch.randperm(num_pages, generator=gen).to(torch.int32)
+    bt = torch.full((B, max(pages_per)), -1, dtype=torch.int32)
+    at = 0
+    for b, n in enumerate(pages_per):
+        bt[b, :n] = perm[at:at + n]
+        at += n
+    q, k, v = randn(gen, B, H, Tq, D), randn(gen, B, G, Tq, D), randn(gen, B, G, Tq, D)
+    k_pool0 = randn(gen, num_pages, G, page_size, D, dtype=torch.bfloat16)
+    v_pool0 = randn(gen, num_pages, G, page_size, D, dtype=torch.bfloat16)
+    freqs = 1.0 / (10000.0 ** (torch.arange(0, D, 2) / D))
+    off = torch.tensor(before, dtype=torch.int32)
+    time = off + Tq
+    cw = bt.shape[1] * page_size
+    want_q, _, want_kp, want_vp = orc.rope_norm_append(q, k, v, freqs, off, k_pool0, v_pool0, 1e-6,
+                                                       block_tables=bt, page_size=page_size)
+    o = torch.zeros(B, H, Tq, D)
+    want_o = orc.flash_attention(want_q.to(torch.bfloat16), want_kp, want_vp, o, time, None, cw, 1, scale=1 / 16,
+                                 block_tables=bt, page_size=page_size)
+
+    kp, vp = k_pool0.to(cuda), v_pool0.to(cuda)
+    q16 = torch.zeros(B, H, Tq, D, dtype=torch.bfloat16, device=cuda)
+    rope_norm_append(q.to(cuda), k.to(cuda), v.to(cuda), freqs.to(cuda), off.to(cuda), kp, vp, 1e-6, q_out=q16,
+                     block_tables=bt.to(cuda), page_size=page_size)
+    assert torch.allclose(kp.float().cpu(), want_kp.float(), atol=8e-3, rtol=8e-3)
+    assert torch.allclose(vp.float().cpu(), want_vp.float(), atol=8e-3, rtol=8e-3)
+    same = (want_kp == k_pool0).all(-1)
+    assert torch.equal(kp.cpu()[same], k_pool0[same]), "pages outside the block tables were written"
+    od = torch.zeros(B, H, Tq, D, dtype=torch.bfloat16, device=cuda)
+    flash_attention(q16, kp, vp, od, time.to(cuda), None, cw, 1, scale=1 / 16, block_tables=bt.to(cuda),
+                    page_size=page_size)
+    # K, V and q each carry one bf16 rounding that may fall differently on the two sides
+    assert_close(od, want_o, "attention over the fused append", abs_tol=8e-3, rel_tol=2e-2)
+
+
+def test_no_rotation_and_no_norm_moves_bits(cuda):
+    """rope_freqs absent and norms off: the call degenerates to a cast-and-append, bit-exact."""
+    gen = torch.Generator().manual_seed(5)
+    B, H, G, D, Tq, T = 2, 2, 2, 128, 5, 9
+    q, k, v = (randn(gen, B, h, Tq, D, dtype=torch.float16) for h in (H, G, G))
+    kc0, vc0 = randn(gen, B, G, T, D, dtype=torch.float16), randn(gen, B, G, T, D, dtype=torch.float16)
+    off = torch.tensor([7, 2], dtype=torch.int32)
+    want_k = orc.add_kv_to_cache(k, kc0, off, 0.0)
+    want_v = orc.add_kv_to_cache(v, vc0, off, 0.0)
+    qd, kc, vc = q.to(cuda), kc0.to(cuda), vc0.to(cuda)
+    rope_norm_append(qd, k.to(cuda), v.to(cuda), None, off.to(cuda), kc, vc, 0.0, norm_qk=False, norm_v=False)
+    assert torch.equal(kc.cpu(), want_k) and torch.equal(vc.cpu(), want_v) and torch.equal(qd.cpu(), q)
+
+
+def test_bad_arguments_raise(cuda):
+    D = 256
+    q = torch.zeros(1, 4, 2, D, device=cuda)
+    k = torch.zeros(1, 2, 2, D, device=cuda)
+    off = torch.zeros(1, dtype=torch.int32, device=cuda)
+    freqs = torch.zeros(D // 2, device=cuda)
+    with pytest.raises(ValueError):       # frequencies must cover D/2 pairs (rope.py:147)
+        apply_rope(q, k, freqs[:64], off, None, None, None, None, 1e-6)
+    with pytest.raises(ValueError):       # k must share batch, tokens and head dim with q
+        apply_rope(q, k[:, :, :1], freqs, off, None, None, None, None, 1e-6)
+    with pytest.raises(ValueError):       # v without a cache to put it in
+        rope_norm_append(q, k, k.clone(), freqs, off, None, None, 1e-6)
+    with pytest.raises(ValueError):
+        apply_rope(q.half(), k, freqs, off, None, None, None, None, 1e-6)

@@ -176,3 +176,52 @@ def test_oracle_advance_and_policy():
     assert [orc.select_kv_splits(w, 16, 2, 1) for w in (1024, 4096, 4097, 8192, 32767, 32768)] == [1, 1, 4, 8, 8, 16]
     assert orc.select_kv_splits(65536, 4, 2, 1) == 4
     assert orc.select_kv_splits(65536, 16, 1, 1) == 1 and orc.select_kv_splits(65536, 16, 2, 2) == 1
+
+
+ROPE_CASES = ["rope_swa", "rope_global_far", "rope_d128"]
+
+
+@pytest.mark.parametrize("name", ROPE_CASES)
+def test_oracle_rope_norm_matches_reference_golden(name):
+    """q_norm/k_norm/v_norm + RoPE of the reference (reference_impl.py:219-233) against the
+    oracle's restatement of the kernel's formulation (g4b/kernels/rope.py:22-39)."""
+    g = load(name)
+    n = g["q"].shape[1]
+    pos = (int(g["base_time_offset"]) + torch.arange(n))[None]
+    eps = float(g["eps"])
+    q = orc.rope_norm(g["q"][None], pos, g["freqs"], weight=g["q_w"], eps=eps)[0]
+    k = orc.rope_norm(g["k"][None], pos, g["freqs"], weight=g["k_w"], eps=eps)[0]
+    v = orc.rope_norm(g["v"][None], pos, None, eps=eps)[0]
+    # fp32 throughout on both sides; the orders of the multiplications differ
+    assert torch.allclose(q, g["q_out"], atol=2e-5, rtol=2e-5), (q - g["q_out"]).abs().max()
+    assert torch.allclose(k, g["k_out"], atol=2e-5, rtol=2e-5), (k - g["k_out"]).abs().max()
+    assert torch.allclose(v, g["v_out"], atol=2e-5, rtol=2e-5), (v - g["v_out"]).abs().max()
+
+
+@pytest.mark.skipif(not ref_loader.available(), reason="reference checkout not mounted")
+def test_oracle_rope_norm_append_live_against_reference():
+    """Fresh inputs through the reference's norms, RoPE and LayerKVCache.add, against the
+    oracle's fused restatement writing a ring cache."""
+    gen = torch.Generator().manual_seed(77)
+    G, H, D, n = 2, 4, 256, 12
+    q_w = 1 + 0.1 * torch.randn(D, generator=gen)
+    k_w = 1 + 0.1 * torch.randn(D, generator=gen)
+    rope, q_norm, k_norm, v_norm = ref_loader.make_rope_and_norms(head_dim=D, is_swa=True, freq_base=10000.0,
+                                                                  eps=1e-6, q_weight=q_w, k_weight=k_w)
+    cache = ref_loader.make_layer_cache(heads=H, kv_heads=G, head_dim=D, context_length=64, sliding_window=16,
+                                        is_swa=False)
+    q, k, v = (torch.randn(1, h, n, D, generator=gen) for h in (H, G, G))
+    cache.set_prefill()
+    base = cache.base_time_offset
+    (k_ref,) = rope(k_norm(k), base_time_offset=base)
+    (q_ref,) = rope(q_norm(q), base_time_offset=base)
+    cache.add(k_ref, v_norm(v))
+    out_ref = cache.retrieve(q_ref / 16)
+    kc, vc = torch.zeros(1, G, 32, D), torch.zeros(1, G, 32, D)
+    q2, k2, kc, vc = orc.rope_norm_append(q, k, v, rope.freqs, torch.tensor([base]), kc, vc, 1e-6,
+                                          q_rmsnorm_w=q_w, k_rmsnorm_w=k_w)
+    assert torch.allclose(q2, q_ref, atol=2e-5, rtol=2e-5)
+    assert torch.allclose(kc[0, :, :n], k_ref[0], atol=2e-5, rtol=2e-5)
+    o = torch.zeros(1, H, n, D)
+    out = orc.flash_attention(q2, kc, vc, o, torch.tensor([n], dtype=torch.int32), None, 32, 1, scale=1 / 16)
+    assert torch.allclose(out, out_ref, atol=1e-5, rtol=1e-4)
