@@ -111,6 +111,18 @@ __device__ long long g_item_trace[128][16];
 // absolute position: all `time` keys are addressable (so 128-key tiles start on page
 // boundaries) and the exposed window is just another lower bound.  Items are ordered with
 // the latest (heaviest) query tiles first; in a CTA pair the two CTAs take heads 2u and 2u+1.
+// The slot's length and phase (geo_time, geo_active) come from G4B_ITEM_LOOP_HEAD, which reads
+// them one item ahead: fetched at the item switch itself, their two dependent global loads
+// held up the MMA issuer and the softmax warps for thousands of cycles per item.
+#define G4B_ITEM_LOOP_PROLOGUE()                                                                     \
+  int time_nx_ = 0;                                                                                   \
+  bool act_nx_ = false;                                                                               \
+  fetch_item(item_of_round(0), time_nx_, act_nx_)
+#define G4B_ITEM_LOOP_HEAD(round)                                                                    \
+  const int item = item_of_round(round);                                                              \
+  const int geo_time = time_nx_;                                                                      \
+  const bool geo_active = act_nx_;                                                                    \
+  fetch_item(((round) + 1) * n_workers < n_items ? item_of_round((round) + 1) : -1, time_nx_, act_nx_)
 #define G4B_ITEM_GEOMETRY(item)                                                                      \
   const int unit_ = (item) % units_per_level;                                                         \
   const int q_tile = p.n_q_tiles - 1 - (item) / units_per_level;                                      \
@@ -118,9 +130,9 @@ __device__ long long g_item_trace[128][16];
   const int b = bh / p.H, h = bh % p.H;                                                               \
   const int g = h / (p.H / p.G);                                                                      \
   const int m0 = q_tile * kBM;                                                                        \
-  const bool active = p.user_phase == nullptr || p.user_phase[b * p.phase_stride] == (uint8_t)p.phase; \
+  const bool active = geo_active;                                                                     \
   const bool paged = p.block_tables != nullptr;                                                       \
-  const int time = p.time_dim_sizes[b * p.time_stride];                                               \
+  const int time = geo_time;                                                                          \
   const int window = paged ? time : min(time, p.ctx_window);                                          \
   const int win_lo = paged ? max(0, time - p.ctx_window) : 0;                                         \
   const int ring_start = paged ? 0 : max(time - p.ctx_window, 0) % p.T;                               \
@@ -251,6 +263,13 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     const int item = round * n_workers + pos;
     return item < n_items ? item : -1;
   };
+  auto fetch_item = [&](int item, int& time_o, bool& act_o) {
+    if (item < 0) { time_o = 0; act_o = false; return; }
+    const int unit_ = item % units_per_level;
+    const int b_ = (kPair ? 2 * unit_ + (int)rank : unit_) / p.H;
+    act_o = p.user_phase == nullptr || p.user_phase[b_ * p.phase_stride] == (uint8_t)p.phase;
+    time_o = p.time_dim_sizes[b_ * p.time_stride];
+  };
   uint8_t* smem = smem_raw;
   uint8_t* sQ = smem;
   uint8_t* sRing = smem + kQBytes;
@@ -331,8 +350,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     uint32_t cc = 0;   // chunk counter over the ring (runs on across work items)
     int n_done = 0;    // work items this worker has gone through
     bool ok = true;
+    G4B_ITEM_LOOP_PROLOGUE();
     for (int round = 0; round * n_workers < n_items && ok; ++round) {
-    const int item = item_of_round(round);
+    G4B_ITEM_LOOP_HEAD(round);
     if (item < 0) continue;
     G4B_ITEM_GEOMETRY(item);
     if (n_tiles <= 0) continue;
@@ -604,8 +624,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         uint32_t cc = 0;
         int tg = 0;       // tiles issued so far: S buffer and barrier phases run on across items
         int n_done = 0;
+        G4B_ITEM_LOOP_PROLOGUE();
         for (int round = 0; round * n_workers < n_items && ok; ++round) {
-        const int item = item_of_round(round);
+        G4B_ITEM_LOOP_HEAD(round);
         if (item < 0) continue;
         G4B_ITEM_GEOMETRY(item);
         if (n_tiles <= 0) continue;
@@ -714,8 +735,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     uint32_t cc = 0;
     int tg = 0;       // tiles issued so far: S buffer and barrier phases run on across items
     int n_done = 0;
+    G4B_ITEM_LOOP_PROLOGUE();
     for (int round = 0; round * n_workers < n_items && ok; ++round) {
-    const int item = item_of_round(round);
+    G4B_ITEM_LOOP_HEAD(round);
     if (item < 0) continue;
     G4B_ITEM_GEOMETRY(item);
     if (n_tiles <= 0) continue;
@@ -840,8 +862,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     bool ok = true;
     int tg = 0;       // tiles seen so far: S buffer and barrier phases run on across items
     int n_done = 0;
+    G4B_ITEM_LOOP_PROLOGUE();
     for (int round = 0; round * n_workers < n_items && ok; ++round) {
-    const int item = item_of_round(round);
+    G4B_ITEM_LOOP_HEAD(round);
     if (item < 0) continue;
     G4B_ITEM_GEOMETRY(item);
     if (n_tiles <= 0) {
