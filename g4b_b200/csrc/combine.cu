@@ -17,20 +17,57 @@ struct CombineParams {
   int64_t po_s[5], pl_s[4], pm_s[4], o_s[4];
   int64_t phase_stride;
   int S, B, H, Tq, D, phase;
+  int groups;          // split groups per block (power of two, 1..32); the block covers 1024 / groups elements
 };
 
 constexpr int kCombineThreads = 256;
 constexpr int kCombineMaxSplits = 1024;   // weights of one row live in shared memory
 
-// One block per (b, h, t) row.  Phase 1: the threads share out the splits, find the row
-// maximum and turn every split's (m, l) into a weight 2^(m_s - m) and the row sum.  Phase 2:
-// the block is (split group) x (pair of head-dim elements); each thread accumulates its
-// splits with independent loads, and the groups are summed through shared memory.
+
+// 4 consecutive elements of a partial row.  vmode 2: one 16-byte (f32) or 8-byte (16-bit)
+// load; 1: two 8-byte loads (f32 rows that start on odd multiples of 8 bytes, as in a packed
+// [.., D + 2] buffer); 0: element by element, n_valid of them.
+template <typename TP>
+__device__ __forceinline__ float4 load4_partial(const TP* src, int vmode, int n_valid) {
+  float4 r = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (vmode == 2) {
+    if constexpr (sizeof(TP) == 4) {
+      r = *reinterpret_cast<const float4*>(src);
+    } else {
+      const uint2 raw = *reinterpret_cast<const uint2*>(src);
+      const TP* e = reinterpret_cast<const TP*>(&raw);
+      r = make_float4(ElemTraits<TP>::to_float(e[0]), ElemTraits<TP>::to_float(e[1]),
+                      ElemTraits<TP>::to_float(e[2]), ElemTraits<TP>::to_float(e[3]));
+    }
+  } else if (vmode == 1) {
+    if constexpr (sizeof(TP) == 4) {
+      const float2 a = *reinterpret_cast<const float2*>(src);
+      const float2 b = *reinterpret_cast<const float2*>(src + 2);
+      r = make_float4(a.x, a.y, b.x, b.y);
+    }
+  } else {
+    if (n_valid > 0) r.x = ElemTraits<TP>::to_float(src[0]);
+    if (n_valid > 1) r.y = ElemTraits<TP>::to_float(src[1]);
+    if (n_valid > 2) r.z = ElemTraits<TP>::to_float(src[2]);
+    if (n_valid > 3) r.w = ElemTraits<TP>::to_float(src[3]);
+  }
+  return r;
+}
+
+// One block per ((b, h, t) row, slice of the head dim).  Phase 1 (every block of the row
+// repeats it: 2 S floats): the threads share out the splits, find the row maximum and turn
+// every split's (m, l) into a weight 2^(m_s - m) and the row sum.  Phase 2: the block is
+// `groups` split groups x (256 / groups) lanes of 4 elements; a thread adds up its
+// S / groups splits with independent 16-byte loads, and the groups are summed through shared
+// memory.  The launcher takes as many groups as there are splits (up to 32), so that with few
+// rows and many splits (one long sequence: 8 rows, 128 or more splits) the grid still has 8
+// blocks per row and no thread walks more than a handful of splits, and with many rows and
+// 16 splits no thread is idle.
 template <typename TP, typename TO>
 __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams p) {
   __shared__ float s_w[kCombineMaxSplits];
   __shared__ float s_red[kCombineThreads / 32];
-  __shared__ float s_acc[kCombineThreads][2];
+  __shared__ float4 s_acc[kCombineThreads];
   int64_t row = blockIdx.x;
   const int t = (int)(row % p.Tq); row /= p.Tq;
   const int h = (int)(row % p.H);
@@ -70,36 +107,37 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams 
   // ---- phase 2 ----
   const TP* po = (const TP*)p.po + b * p.po_s[1] + h * p.po_s[2] + t * p.po_s[3];
   TO* o = (TO*)p.o + b * p.o_s[0] + h * p.o_s[1] + t * p.o_s[2];
-  const int pairs = (p.D + 1) / 2;
-  // as many split groups as fit: pairs * groups <= threads (groups >= 1)
-  int groups = kCombineThreads / pairs;
-  if (groups < 1) groups = 1;
-  if (groups > p.S) groups = p.S;
-  for (int d0 = 0; d0 < pairs; d0 += kCombineThreads / groups) {
-    const int per = kCombineThreads / groups;          // pairs handled per pass
-    const int grp = tid / per, pi = d0 + tid % per;
-    float a0 = 0.f, a1 = 0.f;
-    if (grp < groups && pi < pairs) {
-      const int d = 2 * pi;
-      const bool two = d + 1 < p.D;
+  const int lanes = kCombineThreads / p.groups;               // threads per split group
+  const int grp = tid / lanes;
+  const int cols = lanes * 4;                                 // head-dim elements per block
+  const int d = blockIdx.y * cols + (tid % lanes) * 4;        // this thread's 4 elements
+  const int n_valid = p.D - d;                                // <= 0: past the head dim
+  // vector loads need every split's row to start aligned like the first one
+  int vmode = 0;
+  if (n_valid >= 4) {
+    const uintptr_t a0 = (uintptr_t)(po + d);
+    if (a0 % (4 * sizeof(TP)) == 0 && p.po_s[0] % 4 == 0) vmode = 2;
+    else if (sizeof(TP) == 4 && a0 % 8 == 0 && p.po_s[0] % 2 == 0) vmode = 1;
+  }
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  if (n_valid > 0) {
 #pragma unroll 4
-      for (int s = grp; s < p.S; s += groups) {
-        const float w = s_w[s];
-        if (w == 0.f) continue;
-        const TP* src = po + s * p.po_s[0] + d;
-        a0 += ElemTraits<TP>::to_float(src[0]) * w;
-        if (two) a1 += ElemTraits<TP>::to_float(src[1]) * w;
-      }
+    for (int s = grp; s < p.S; s += p.groups) {
+      const float w = s_w[s];
+      if (w == 0.f) continue;
+      const float4 x = load4_partial<TP>(po + s * p.po_s[0] + d, vmode, n_valid);
+      acc.x += x.x * w; acc.y += x.y * w; acc.z += x.z * w; acc.w += x.w * w;
     }
-    __syncthreads();
-    s_acc[tid][0] = a0; s_acc[tid][1] = a1;
-    __syncthreads();
-    if (grp == 0 && pi < pairs) {
-      for (int g2 = 1; g2 < groups; ++g2) { a0 += s_acc[g2 * per + tid][0]; a1 += s_acc[g2 * per + tid][1]; }
-      const int d = 2 * pi;
-      o[d] = ElemTraits<TO>::from_float(a0 * inv_l);
-      if (d + 1 < p.D) o[d + 1] = ElemTraits<TO>::from_float(a1 * inv_l);
-    }
+  }
+  s_acc[tid] = acc;
+  __syncthreads();
+  for (int c = tid; c < cols; c += kCombineThreads) {
+    // element c of the block's slice, summed over the groups
+    const int c4 = c >> 2, ci = c & 3;
+    float sum = 0.f;
+    for (int g2 = 0; g2 < p.groups; ++g2) sum += reinterpret_cast<const float*>(&s_acc[g2 * lanes + c4])[ci];
+    const int dd = blockIdx.y * cols + c;
+    if (dd < p.D) o[dd] = ElemTraits<TO>::from_float(sum * inv_l);
   }
 }
 
@@ -117,10 +155,14 @@ int launch_combine(const G4bCombineArgs& a, cudaStream_t st) {
   if (rows == 0) return G4B_OK;
   if (rows > 0x7fffffffLL) return fail(G4B_ERR_UNSUPPORTED, "combine: too many rows");
   if (p.S > kCombineMaxSplits) return fail(G4B_ERR_TOO_LARGE, "combine: at most %d splits", kCombineMaxSplits);
+  p.groups = 1;
+  while (p.groups < 32 && p.groups < p.S) p.groups *= 2;
+  const int cols = kCombineThreads / p.groups * 4;
+  const dim3 grid((unsigned)rows, (unsigned)((p.D + cols - 1) / cols), 1);
   bool launched = false;
   G4B_DISPATCH_FLOAT(a.partial_o.dtype, TP,
     G4B_DISPATCH_FLOAT(a.o.dtype, TO,
-      combine_kernel<TP, TO><<<(unsigned)rows, kCombineThreads, 0, st>>>(p); launched = true));
+      combine_kernel<TP, TO><<<grid, kCombineThreads, 0, st>>>(p); launched = true));
   if (!launched) return fail(G4B_ERR_BAD_DTYPE, "combine: partial_o/o dtypes must be f32, f16 or bf16");
   G4B_CUDA_CHECK(cudaGetLastError());
   return G4B_OK;
