@@ -301,9 +301,9 @@ class DecodeWorkload:
 
     def __init__(self, name, dev, seed, rank=0, world=1, sequences=256):
         from g4b_b200.kernels import fa2
-        from g4b_b200.kernels.add_kv_to_cache import add_kv_to_cache
+        from g4b_b200.kernels.rope import rope_norm_append
 
-        self.fa2, self.append = fa2, add_kv_to_cache
+        self.fa2, self.append = fa2, rope_norm_append
         self.name, self.dev, self.rank, self.world = name, dev, rank, world
         gen = torch.Generator(device="cpu").manual_seed(seed)
         if name == "decode_paged":
@@ -365,7 +365,7 @@ class DecodeWorkload:
         # algorithmic K/V bytes and traffic grows with the token count (profiles/)
         self.traffic = kv_bytes * 1.0006 + 5.4e6 * (B / 32.0) if name == "decode_paged" else None
         self.metric, self.unit, self.bound = "decode_attn_hbm_gbs", "GB/s", "hbm"
-        self.launches_per_step = 4                               # 2 appends + decode + combine
+        self.launches_per_step = 3                               # append (K and V) + decode + combine
         self.h2d = (self.h_q.numel() + self.h_kn.numel() + self.h_vn.numel()) * 2
         self.d2h = self.h_o.numel() * 2
         self.config = {"workload": name, "sequences": B, "ctx_sum": int(lens.sum()), "ctx_min": int(lens.min()),
@@ -395,8 +395,9 @@ class DecodeWorkload:
         self.k_pool, self.v_pool = self.pools[i % len(self.pools)]
         last = (not self.long_split) or self.rank == self.world - 1
         if last:   # the new token's row lives on the rank that owns the tail of the sequence
-            self.append(self.kn, self.k_pool, self.off, 1e-6, block_tables=self.bt, page_size=PAGE)
-            self.append(self.vn, self.v_pool, self.off, 1e-6, block_tables=self.bt, page_size=PAGE)
+            # K and V rows in one launch (no rotation, no norm: a plain append of both)
+            self.append(self.q, self.kn, self.vn, None, self.off, self.k_pool, self.v_pool, 1e-6,
+                        norm_qk=False, norm_v=False, block_tables=self.bt, page_size=PAGE)
         if not self.long_split:
             self.fa2.flash_attention(self.q, self.k_pool, self.v_pool, self.o, self.time, None, self.max_len,
                                      self.fa2.PHASE_DECODE, self.po, self.pl, self.pm, scale=SCALE,

@@ -38,6 +38,7 @@ struct RopeParams {
   int T;                        // ring length
   int page_size, page_shift, num_pages, max_pages;
   int offsets_are_i64, phase, norm_qk, norm_v;
+  int q_untouched;              // no norm, no rotation, no q_out: q rows are left alone
   float eps;
   int32_t* status;
 };
@@ -153,7 +154,7 @@ __global__ void __launch_bounds__(256) rope_norm_append_kernel(RopeParams p) {
     int out_dtype = p.in_dtype;
     if (kind == 0) {
       if (p.q_out != nullptr) { out = p.q_out; out_dtype = p.q_out_dtype; out_off = b * p.qos[0] + h * p.qos[1] + t * p.qos[2]; }
-      else { out = const_cast<void*>(p.q); out_off = src_off; }
+      else if (!p.q_untouched) { out = const_cast<void*>(p.q); out_off = src_off; }
     } else if (kind == 1) {
       if (p.k_out != nullptr) { out = p.k_out; out_dtype = p.k_out_dtype; out_off = b * p.kos[0] + h * p.kos[1] + t * p.kos[2]; }
       else if (p.k_cache == nullptr) { out = const_cast<void*>(p.k); out_off = src_off; }
@@ -347,6 +348,7 @@ int launch_rope_norm_append(const G4bRopeAppendArgs& a, cudaStream_t st) {
   p.B = (int)B; p.H = (int)H; p.G = (int)G; p.Tq = (int)Tq; p.D = (int)D;
   p.n_heads = (int)(H + G + (has_v ? G : 0));
   p.phase = a.phase; p.norm_qk = a.norm_qk; p.norm_v = a.norm_v; p.eps = a.rmsnorm_eps;
+  p.q_untouched = a.norm_qk == 0 && a.rope_freqs.ptr == nullptr && a.q_out.ptr == nullptr;
   if (paged) {
     p.page_size = a.page_size;
     while ((1 << p.page_shift) < a.page_size) ++p.page_shift;
