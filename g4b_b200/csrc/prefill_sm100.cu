@@ -51,7 +51,7 @@ constexpr uint32_t kColO = 0, kColS0 = 256, kColS1 = 384;
 
 enum : int32_t {
   kErrQFull = 0x301, kErrKvEmpty = 0x302, kErrKvFull = 0x303, kErrSFull = 0x304,
-  kErrPFull = 0x305, kErrPvDone = 0x306, kErrSmemAlign = 0x307, kErrPair = 0x308, kErrBadPage = 0x309, kErrQEmpty = 0x30a, kErrOFree = 0x30b,
+  kErrPFull = 0x305, kErrPvDone = 0x306, kErrSmemAlign = 0x307, kErrPair = 0x308, kErrBadPage = 0x309, kErrQEmpty = 0x30a, kErrOFree = 0x30b, kErrStageFree = 0x30c,
 };
 
 struct PrefillParams {
@@ -80,6 +80,7 @@ struct Barriers {
   uint64_t pv_done;
   uint64_t q_empty;        // last Q.K^T of a work item done: the Q buffer may be refilled
   uint64_t o_free;         // the softmax warps have read O out of tensor memory
+  uint64_t stage_free;     // the softmax warps are done with the ring slot they borrowed for the output
   uint64_t pair[4];        // one per softmax warp pair (64 arrivals): shared-memory exchanges
   uint32_t tmem_base;
   int32_t abort_flag;
@@ -243,10 +244,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
                const __grid_constant__ CUtensorMap v_map, PrefillParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  // Ring slots in use.  Short work items (sliding windows: ~5 tiles) gain more from coalesced
-  // output stores than from look-ahead: that variant uses 4 slots and the fifth becomes the
-  // staging buffer of the epilogue.
-  constexpr int kSt = kStageOut ? kStages - 1 : kStages;
+  // kStageOut: the epilogue turns the output block through shared memory to store whole
+  // 128-byte row segments.  It borrows the ring slot of the item's last V chunk: that slot is
+  // the last one the item frees and the one the producer refills last (with a chunk the next
+  // item needs only for its second P.V product), so the producer just waits for stage_free
+  // before that one refill and the ring keeps all five slots in the steady state.
+  constexpr int kSt = kStages;
   const uint32_t rank = kPair ? ptx::cluster_ctarank() : 0u;   // 0 = the CTA that issues the MMAs
   const bool leader = rank == 0;
 
@@ -293,6 +296,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     ptx::mbar_init(bar_pv, 1);
     ptx::mbar_init(ptx::smem_u32(&bars->q_empty), 1);
     ptx::mbar_init(ptx::smem_u32(&bars->o_free), 8 * kN);
+    ptx::mbar_init(ptx::smem_u32(&bars->stage_free), 8);     // this CTA's softmax warps
     for (int s = 0; s < 4; ++s) ptx::mbar_init(ptx::smem_u32(&bars->pair[s]), 2);   // one arrival per warp of the pair
     ptx::fence_barrier_init();
     ptx::prefetch_tensormap(&q_map);
@@ -364,6 +368,20 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     vsrc = ksrc;
     vsrc.base = paged ? (const T*)p.v : (const T*)p.v + ((int64_t)b * p.G + g) * p.T * kHD;
     const int bg = b * p.G + g;
+    // The previous item's epilogue borrows the slot of its last V chunk (chunk cc - 1), which
+    // chunk cc + 4 refills.  stage_free completes once per item, so it must also be waited for
+    // before this item can complete it again: at the latest before this item's last chunk.
+    bool stage_pending = kStageOut && n_done > 0;
+    const uint32_t stage_cc = cc + (uint32_t)min(4, 2 * n_tiles - 1);
+    auto wait_stage = [&]() -> bool {
+      if (!stage_pending || cc != stage_cc) return true;
+      stage_pending = false;
+      int w = 1;
+      if (lane == 0) w = ptx::mbar_wait(ptx::smem_u32(&bars->stage_free), (n_done - 1) & 1) ? 1 : 0;
+      w = __shfl_sync(0xffffffffu, w, 0);
+      if (!w) { if (lane == 0) record(p.status, kErrStageFree); ok = false; }
+      return w != 0;
+    };
     G4B_ITEM_AT(0);   // producer reaches the item
     {
       // the Q buffer is free once the last Q.K^T of the previous item has run
@@ -515,7 +533,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       const int st = cc % kSt;
       const uint32_t full = issuer_bar(&bars->kv_full[st]);
       G4B_TRACE_AT(j, 7);
-      if (!wait_empty(st, cc)) return;
+      if (!wait_empty(st, cc) || !wait_stage()) return;
       G4B_TRACE_AT(j, 5);   // K(j) slot free, loads go out
       uint8_t* dst = sRing + st * kChunkBytes;
       if (!manual) {
@@ -555,7 +573,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       const int st = cc % kSt;
       const uint32_t full = issuer_bar(&bars->kv_full[st]);
       G4B_TRACE_AT(j, 6);
-      if (!wait_empty(st, cc)) return;
+      if (!wait_empty(st, cc) || !wait_stage()) return;
       G4B_TRACE_AT(j, 4);   // V(j) slot free, loads go out
       uint8_t* dst = sRing + st * kChunkBytes;
       if (!manual) {
@@ -1106,7 +1124,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           // 16-byte store touches its own line.  Instead the warp turns its [32 rows x 64
           // columns] block through shared memory (4 KB per warp, 16-byte chunks XOR-swizzled by
           // row so neither side has bank conflicts) and stores whole 128-byte row segments.
-          uint8_t* stage = sRing + (kStages - 1) * kChunkBytes + (warp - 2) * 4096;
+          // (2 chunks per tile in the pair form: the item's last V chunk is chunk 2 (tg + n_tiles) - 1)
+          const int stage_slot = (2 * (tg + n_tiles) - 1) % kStages;
+          uint8_t* stage = sRing + stage_slot * kChunkBytes + (warp - 2) * 4096;
           const int64_t row_base = b * p.o_s0 + h * p.o_s1 + (int64_t)(m0 + lane_base) * p.o_s2 + half * 128;
 #pragma unroll
           for (int cp = 0; cp < 2; ++cp) {
@@ -1125,6 +1145,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
             }
             __syncwarp();
           }
+          // the slot goes back to the producer, whose TMA writes must come after these accesses
+          ptx::fence_proxy_async_smem();
+          __syncwarp();
+          if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->stage_free));
         } else if (row_ok) {
 #pragma unroll
           for (int c4 = 0; c4 < 4; ++c4) {
@@ -1297,11 +1321,9 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   p.time_stride = a.time_dim_sizes.stride[0]; p.phase_stride = a.user_phase.stride[0];
   p.B = (int)B; p.H = (int)H; p.G = (int)G; p.Tq = (int)Tq; p.T = paged ? 1 : (int)T;
   p.n_q_tiles = (int)n_q_tiles;
-  // tiles per work item, from what the host knows (context lengths live on the device)
-  const int64_t est_tiles = a.sliding_window > 0 ? (a.sliding_window + 127) / 128 + 1 : (int64_t)a.ctx_window_size / 256 + 1;
-  // G4B_PREFILL_STAGE_OUT=0/1 overrides the choice (for tests that cover both forms at one size)
-  static const int force_stage = []() { const char* e = getenv("G4B_PREFILL_STAGE_OUT"); return e ? (e[0] == '1' ? 1 : 0) : -1; }();
-  const bool stage_out = pair && a.o.dtype != G4B_F32 && (force_stage >= 0 ? force_stage == 1 : est_tiles <= 12);
+  // G4B_PREFILL_STAGE_OUT=0 forces direct output stores (for tests that cover both forms)
+  static const bool no_stage = []() { const char* e = getenv("G4B_PREFILL_STAGE_OUT"); return e && e[0] == '0'; }();
+  const bool stage_out = pair && a.o.dtype != G4B_F32 && !no_stage;
   if (paged) {
     p.block_tables = (const int32_t*)a.block_tables.ptr;
     p.bt_s0 = a.block_tables.stride[0]; p.bt_s1 = a.block_tables.stride[1];
