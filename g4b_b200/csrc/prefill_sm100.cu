@@ -54,6 +54,24 @@ enum : int32_t {
   kErrPFull = 0x305, kErrPvDone = 0x306, kErrSmemAlign = 0x307, kErrPair = 0x308, kErrBadPage = 0x309, kErrQEmpty = 0x30a, kErrOFree = 0x30b, kErrStageFree = 0x30c,
 };
 
+// Division of a non-negative 31-bit value by a launch constant as multiply-high + shift: the
+// item geometry holds half a dozen divisions, each a ~100-cycle dependent chain in a warp
+// that nothing overlaps with, paid by every role at every item switch.
+struct FastDiv {
+  uint32_t mul, shift, d;
+  __host__ void set(uint32_t div) {
+    d = div < 1 ? 1 : div;
+    if (d == 1) { mul = 0; shift = 0; return; }
+    uint32_t lg = 0;
+    while ((1ull << lg) < d) ++lg;
+    const uint32_t pw = 31 + lg;
+    mul = (uint32_t)(((1ull << pw) + d - 1) / d);
+    shift = pw - 32;
+  }
+  __device__ __forceinline__ int div(int x) const { return d == 1 ? x : (int)(__umulhi((uint32_t)x, mul) >> shift); }
+  __device__ __forceinline__ int mod(int x) const { return x - div(x) * (int)d; }
+};
+
 struct PrefillParams {
   void* o;
   const void* k; const void* v;              // raw cache pointers (manual fallback loads)
@@ -64,6 +82,7 @@ struct PrefillParams {
   int page_shift, num_pages, max_pages;      // paged mode
   int B, H, G, Tq, T;
   int n_q_tiles;                             // ceil(Tq / 128)
+  FastDiv by_units, by_H, by_HperG, by_T;    // units per query tile, H, H / G, ring length
   int ctx_window, sliding_window, phase, causal;
   int o_dtype;
   float scale_log2;
@@ -125,18 +144,19 @@ __device__ long long g_item_trace[128][16];
   const bool geo_active = act_nx_;                                                                    \
   fetch_item(((round) + 1) * n_workers < n_items ? item_of_round((round) + 1) : -1, time_nx_, act_nx_)
 #define G4B_ITEM_GEOMETRY(item)                                                                      \
-  const int unit_ = (item) % units_per_level;                                                         \
-  const int q_tile = p.n_q_tiles - 1 - (item) / units_per_level;                                      \
+  const int level_ = p.by_units.div(item);                                                            \
+  const int unit_ = (item) - level_ * units_per_level;                                                \
+  const int q_tile = p.n_q_tiles - 1 - level_;                                                        \
   const int bh = kPair ? 2 * unit_ + (int)rank : unit_;                                               \
-  const int b = bh / p.H, h = bh % p.H;                                                               \
-  const int g = h / (p.H / p.G);                                                                      \
+  const int b = p.by_H.div(bh), h = bh - b * p.H;                                                     \
+  const int g = p.by_HperG.div(h);                                                                    \
   const int m0 = q_tile * kBM;                                                                        \
   const bool active = geo_active;                                                                     \
   const bool paged = p.block_tables != nullptr;                                                       \
   const int time = geo_time;                                                                          \
   const int window = paged ? time : min(time, p.ctx_window);                                          \
   const int win_lo = paged ? max(0, time - p.ctx_window) : 0;                                         \
-  const int ring_start = paged ? 0 : max(time - p.ctx_window, 0) % p.T;                               \
+  const int ring_start = paged ? 0 : p.by_T.mod(max(time - p.ctx_window, 0));                         \
   const int q_t_base = window - p.Tq; /* logical position of query row 0 */                           \
   const int rows_valid = min(kBM, p.Tq - m0);                                                         \
   const int qpos_min = q_t_base + m0;                                                                 \
@@ -268,8 +288,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
   };
   auto fetch_item = [&](int item, int& time_o, bool& act_o) {
     if (item < 0) { time_o = 0; act_o = false; return; }
-    const int unit_ = item % units_per_level;
-    const int b_ = (kPair ? 2 * unit_ + (int)rank : unit_) / p.H;
+    const int unit_ = p.by_units.mod(item);
+    const int b_ = p.by_H.div(kPair ? 2 * unit_ + (int)rank : unit_);
     act_o = p.user_phase == nullptr || p.user_phase[b_ * p.phase_stride] == (uint8_t)p.phase;
     time_o = p.time_dim_sizes[b_ * p.time_stride];
   };
@@ -1321,6 +1341,10 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   p.time_stride = a.time_dim_sizes.stride[0]; p.phase_stride = a.user_phase.stride[0];
   p.B = (int)B; p.H = (int)H; p.G = (int)G; p.Tq = (int)Tq; p.T = paged ? 1 : (int)T;
   p.n_q_tiles = (int)n_q_tiles;
+  p.by_units.set((uint32_t)(pair ? B * H / 2 : B * H));
+  p.by_H.set((uint32_t)H);
+  p.by_HperG.set((uint32_t)(H / G));
+  p.by_T.set((uint32_t)(paged ? 1 : T));
   // G4B_PREFILL_STAGE_OUT=0 forces direct output stores (for tests that cover both forms)
   static const bool no_stage = []() { const char* e = getenv("G4B_PREFILL_STAGE_OUT"); return e && e[0] == '0'; }();
   const bool stage_out = pair && a.o.dtype != G4B_F32 && !no_stage;
