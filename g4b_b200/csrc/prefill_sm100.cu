@@ -258,7 +258,7 @@ template <> struct PackT<__half> {
 //   each CTA stages only half of every tile (K: half the keys, V: half the head dim), so the
 //   ring covers twice the time and Q.K^T reads 96 instead of 128 bytes of shared memory per
 //   cycle -- the two things that starve the single-CTA form.
-template <typename T, bool kPair, bool kStageOut>
+template <typename T, bool kPair, bool kStageOut, bool kShortItems>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                const __grid_constant__ CUtensorMap v_map, PrefillParams p) {
@@ -1025,9 +1025,66 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         continue;
       }
 
-      // ---- general path: new reference maximum, few-keys rows, first tile ----
-      // Lazy rescale: keep the old reference maximum unless the new one is more than 2^8
-      // above it (p stays <= 256, exact enough in f32 sums and representable in f16/bf16).
+      if (kShortItems && !few_keys) {
+        // Variant for short work items (sliding windows), where the first tile is a fifth of
+        // the item; with long items the extra code only disturbs the steady state (-2 %).
+        // The reference maximum moves (first tile of an item, or a jump of more than 2^8: lazy
+        // rescale -- p stays <= 256, exact enough in f32 sums and representable in f16/bf16).
+        // Same two-part hand-over as above, after O and l have been rescaled.
+        float alpha = 1.f;
+        bool rescale = false;
+        if (exceed) {
+          rescale = (m_used != -INFINITY);
+          alpha = rescale ? ptx::ex2_approx(m_used - m_blk) : 1.f;
+          m_used = m_blk;
+        }
+        l_run *= alpha;
+        const float neg_m = (m_used == -INFINITY) ? 0.f : -m_used;
+        sum4[0] = sum4[1] = sum4[2] = sum4[3] = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = ptx::ex2_approx(fmaf(__uint_as_float(sraw[0][i]), p.scale_log2, neg_m));
+          const float p1 = ptx::ex2_approx(fmaf(__uint_as_float(sraw[0][i + 1]), p.scale_log2, neg_m));
+          sum4[(i >> 1) & 3] += p0 + p1;
+          pk[i >> 1] = PackT<T>::pack(p0, p1);
+        }
+        // O may only be touched once PV(j-1) has drained, and must be rescaled before P.V(j)
+        // adds to it, i.e. before any part of P is published
+        if (j > 0) {
+          if (!__all_sync(0xffffffffu, ptx::mbar_wait(bar_pv, (t - 1) & 1))) { record(p.status, kErrPvDone); ok = false; break; }
+          ptx::tc_fence_after();
+          if (__any_sync(0xffffffffu, rescale)) {
+#pragma unroll 1
+            for (int c4 = 0; c4 < 4; ++c4) {
+              uint32_t ov[32];
+              ptx::tmem_ld32(trow + kColO + half * 128 + c4 * 32, ov);
+              ptx::tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 32; ++i) ov[i] = __float_as_uint(__uint_as_float(ov[i]) * alpha);
+              ptx::tmem_st32(trow + kColO + half * 128 + c4 * 32, ov);
+            }
+          }
+        }
+        ptx::tmem_st16(trow + s_col + half * 32, pk);
+        ptx::tc_wait_st();
+        ptx::tc_fence_before();
+        arrive_issuer(bar_pa);
+#pragma unroll
+        for (int i = 0; i < 32; i += 2) {
+          const float p0 = ptx::ex2_approx(fmaf(__uint_as_float(sraw[1][i]), p.scale_log2, neg_m));
+          const float p1 = ptx::ex2_approx(fmaf(__uint_as_float(sraw[1][i + 1]), p.scale_log2, neg_m));
+          sum4[(i >> 1) & 3] += p0 + p1;
+          pk[16 + (i >> 1)] = PackT<T>::pack(p0, p1);
+        }
+        ptx::tmem_st16(trow + s_col + half * 32 + 16, pk + 16);
+        l_run += (sum4[0] + sum4[1]) + (sum4[2] + sum4[3]);
+        ptx::tc_wait_st();
+        ptx::tc_fence_before();
+        arrive_issuer(bar_pb);
+        continue;
+      }
+
+      // ---- precise path: items in which some row sees fewer than 64 keys ----
       float alpha = 1.f;
       bool rescale = false;
       if (exceed) {
@@ -1236,14 +1293,14 @@ static int encode_map(CUtensorMap* map, int dtype, int rank, void* base, const u
   return G4B_OK;
 }
 
-template <typename T, bool kPair, bool kStageOut>
+template <typename T, bool kPair, bool kStageOut, bool kShortItems>
 static int launch_variant(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const PrefillParams& p,
                           dim3 grid, cudaStream_t st) {
   static bool attr_set[64] = {false};
   int dev = 0;
   G4B_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    G4B_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<T, kPair, kStageOut>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    G4B_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<T, kPair, kStageOut, kShortItems>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -1258,16 +1315,17 @@ static int launch_variant(const CUtensorMap& qm, const CUtensorMap& km, const CU
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  G4B_CUDA_CHECK(cudaLaunchKernelEx(&cfg, prefill_kernel<T, kPair, kStageOut>, qm, km, vm, p));
+  G4B_CUDA_CHECK(cudaLaunchKernelEx(&cfg, prefill_kernel<T, kPair, kStageOut, kShortItems>, qm, km, vm, p));
   return G4B_OK;
 }
 
 template <typename T>
 static int launch_typed(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const PrefillParams& p,
-                        dim3 grid, bool pair, bool stage_out, cudaStream_t st) {
-  if (pair && stage_out) return launch_variant<T, true, true>(qm, km, vm, p, grid, st);
-  if (pair) return launch_variant<T, true, false>(qm, km, vm, p, grid, st);
-  return launch_variant<T, false, false>(qm, km, vm, p, grid, st);
+                        dim3 grid, bool pair, bool stage_out, bool short_items, cudaStream_t st) {
+  if (pair && stage_out && short_items) return launch_variant<T, true, true, true>(qm, km, vm, p, grid, st);
+  if (pair && stage_out) return launch_variant<T, true, true, false>(qm, km, vm, p, grid, st);
+  if (pair) return launch_variant<T, true, false, false>(qm, km, vm, p, grid, st);
+  return launch_variant<T, false, false, false>(qm, km, vm, p, grid, st);
 }
 
 }  // namespace
@@ -1348,6 +1406,9 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   // G4B_PREFILL_STAGE_OUT=0 forces direct output stores (for tests that cover both forms)
   static const bool no_stage = []() { const char* e = getenv("G4B_PREFILL_STAGE_OUT"); return e && e[0] == '0'; }();
   const bool stage_out = pair && a.o.dtype != G4B_F32 && !no_stage;
+  // tiles per work item, from what the host knows (context lengths live on the device)
+  const int64_t est_tiles = a.sliding_window > 0 ? (a.sliding_window + 127) / 128 + 1 : (int64_t)a.ctx_window_size / 256 + 1;
+  const bool short_items = est_tiles <= 12;
   if (paged) {
     p.block_tables = (const int32_t*)a.block_tables.ptr;
     p.bt_s0 = a.block_tables.stride[0]; p.bt_s1 = a.block_tables.stride[1];
@@ -1374,8 +1435,8 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   if (workers < 1) workers = 1;
   if (workers > n_items) workers = n_items;
   dim3 grid((unsigned)(pair ? 2 * workers : workers), 1, 1);
-  if (a.q.dtype == G4B_BF16) return launch_typed<__nv_bfloat16>(qm, km, vm, p, grid, pair, stage_out, st);
-  return launch_typed<__half>(qm, km, vm, p, grid, pair, stage_out, st);
+  if (a.q.dtype == G4B_BF16) return launch_typed<__nv_bfloat16>(qm, km, vm, p, grid, pair, stage_out, short_items, st);
+  return launch_typed<__half>(qm, km, vm, p, grid, pair, stage_out, short_items, st);
 }
 
 }  // namespace g4b
