@@ -59,10 +59,9 @@ __device__ __forceinline__ float4 load4_partial(const TP* src, int vmode, int n_
 // every split's (m, l) into a weight 2^(m_s - m) and the row sum.  Phase 2: the block is
 // `groups` split groups x (256 / groups) lanes of 4 elements; a thread adds up its
 // S / groups splits with independent 16-byte loads, and the groups are summed through shared
-// memory.  The launcher takes as many groups as there are splits (up to 32), so that with few
-// rows and many splits (one long sequence: 8 rows, 128 or more splits) the grid still has 8
-// blocks per row and no thread walks more than a handful of splits, and with many rows and
-// 16 splits no thread is idle.
+// memory.  The launcher takes few groups (whole rows per block) when there are many rows, and
+// up to 32 when there are few (one long sequence: 8 rows, 128 or more splits), so that the
+// grid still has 8 blocks per row and no thread walks more than a handful of splits.
 template <typename TP, typename TO>
 __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams p) {
   __shared__ float s_w[kCombineMaxSplits];
@@ -155,8 +154,15 @@ int launch_combine(const G4bCombineArgs& a, cudaStream_t st) {
   if (rows == 0) return G4B_OK;
   if (rows > 0x7fffffffLL) return fail(G4B_ERR_UNSUPPORTED, "combine: too many rows");
   if (p.S > kCombineMaxSplits) return fail(G4B_ERR_TOO_LARGE, "combine: at most %d splits", kCombineMaxSplits);
-  p.groups = 1;
-  while (p.groups < 32 && p.groups < p.S) p.groups *= 2;
+  // Split groups per block: at least enough that the block's lanes do not reach past the head
+  // dim, then more (narrower blocks, more of them) only while the grid is short of a few
+  // waves -- every block repeats phase 1 and pays two block-wide reductions.
+  int g_min = 1;
+  while (g_min < 32 && kCombineThreads / g_min * 4 > p.D) g_min *= 2;
+  p.groups = g_min;
+  while (p.groups < 32 && p.groups < p.S &&
+         rows * ((p.D + kCombineThreads / p.groups * 4 - 1) / (kCombineThreads / p.groups * 4)) < 592)
+    p.groups *= 2;
   const int cols = kCombineThreads / p.groups * 4;
   const dim3 grid((unsigned)rows, (unsigned)((p.D + cols - 1) / cols), 1);
   bool launched = false;
