@@ -217,7 +217,7 @@ class PrefillWorkload:
         self.h2d = (self.h_q.numel() + self.h_k.numel() + self.h_v.numel()) * 2
         self.d2h = self.h_o.numel() * 2
         # DRAM bytes of one launch from the committed ncu capture (profiles/): read + write
-        self.traffic = 421.1e6 if name == "prefill_causal" else None
+        self.traffic = 398.6e6 if name == "prefill_causal" else None
         self.config = {"workload": name, "batch_per_gpu": B, "seq_len": S, "q_heads": H, "kv_heads": G,
                        "head_dim": D, "window": self.window, "scale": SCALE,
                        "l2": "inputs (%d MB) larger than L2" % ((self.h2d + self.d2h) >> 20)}
