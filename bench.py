@@ -299,7 +299,7 @@ class DecodeWorkload:
     """Configs 4 and 5: paged KV with shuffled block tables; a step appends the new token's
     K and V rows and runs decode attention (split-KV + combine)."""
 
-    def __init__(self, name, dev, seed, rank=0, world=1, sequences=256):
+    def __init__(self, name, dev, seed, rank=0, world=1, sequences=256, nccl_gather=False, kv_splits=0):
         from g4b_b200.kernels import fa2
         from g4b_b200.kernels.rope import rope_norm_append
 
@@ -313,7 +313,7 @@ class DecodeWorkload:
         else:
             self.dtype = torch.bfloat16
             self.lens = torch.tensor([131072], dtype=torch.int64)
-            self.splits = 128
+            self.splits = 148          # x 2 kv heads = two CTAs on every SM
         self.long_split = name == "decode_long" and world > 1
         lens = self.lens
         B = len(lens)
@@ -326,9 +326,11 @@ class DecodeWorkload:
             rng = gdist.split_pages(int(pages_per[0]), world, rank)
             local_pages = torch.tensor([len(rng)])
             self.local_lens = torch.tensor([min(int(lens[0]), rng.stop * PAGE) - rng.start * PAGE])
-            self.splits = max(8, 128 // world)
+            self.splits = 128
         else:
             local_pages, self.local_lens = pages_per, lens
+        if kv_splits > 0:
+            self.splits = kv_splits
         num_pages = int(local_pages.sum())
         gdev = torch.Generator(device=dev).manual_seed(seed + 1 + rank)
         self.k_pool = torch.randn(num_pages, G, PAGE, D, generator=gdev, device=dev, dtype=torch.float32).to(self.dtype) \
@@ -358,7 +360,12 @@ class DecodeWorkload:
         self.packed = torch.empty(S, B, H, 1, D + 2, device=dev, dtype=torch.float32)
         self.po, self.pl, self.pm = self.packed[..., :D], self.packed[..., D], self.packed[..., D + 1]
         if self.long_split:
+            from g4b_b200 import dist as gdist
+
             self.gathered = torch.empty(world * S, B, H, 1, D + 2, device=dev, dtype=torch.float32)
+            self.nccl_gather = nccl_gather
+            if not nccl_gather:
+                self.exchange = gdist.PartialExchange(B * H, D, device=dev)
         kv_bytes = float(self.local_lens.sum()) * G * D * 2 * 2
         self.units = kv_bytes                                    # K/V bytes per step (this rank)
         # DRAM bytes per launch: the ncu capture of a 32-sequence case read 1.0006x its
@@ -408,9 +415,14 @@ class DecodeWorkload:
         self.fa2.attention_decode_partials(self.q, self.k_pool, self.v_pool, self.o, self.time, None, self.max_len,
                                            self.fa2.PHASE_DECODE, self.po, self.pl, self.pm, self.splits, scale=SCALE,
                                            block_tables=self.bt, page_size=PAGE)
-        gdist.gather_packed(self.packed, out=self.gathered)
-        go, gl, gm = gdist.unpack_gathered(self.gathered)
-        self.fa2.combine_partials(go, gl, gm, self.o, self.world * self.splits)
+        if self.nccl_gather:
+            # the library-collective form: all-gather every split's partial, one merge
+            gdist.gather_packed(self.packed, out=self.gathered)
+            go, gl, gm = gdist.unpack_gathered(self.gathered)
+            self.fa2.combine_partials(go, gl, gm, self.o, self.world * self.splits)
+        else:
+            # one kernel: local merge, exchange through peer memory, final merge
+            self.exchange.combine(self.po, self.pl, self.pm, self.o, self.splits)
 
     def e2e_step(self, i=0):
         self.q.copy_(self.h_q, non_blocking=True)
@@ -443,12 +455,12 @@ class DecodeWorkload:
         return touched / dt / 1e9, f"{n} of {self.B} sequences ({touched >> 20} MB of K/V), page gather + fp32 attention"
 
 
-def make_workload(name, dev, rank, world, sequences=256):
+def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_splits=0):
     seeds = {"prefill_causal": 1, "prefill_swa": 2, "decode_paged": 3, "decode_long": 4}
     if name.startswith("prefill"):
         return PrefillWorkload(name, dev, seeds[name] + 100 * rank)
     return DecodeWorkload(name, dev, seeds[name] + (0 if name == "decode_long" else 100 * rank), rank, world,
-                          sequences)
+                          sequences, nccl_gather, kv_splits)
 
 
 # ------------------------------------------------------------------------------------------
@@ -471,14 +483,25 @@ def run_ours(args):
     from g4b_b200 import _cabi
 
     peaks = measured_peaks()
-    wl = make_workload(args.workload, dev, rank, world, args.sequences)
+    wl = make_workload(args.workload, dev, rank, world, args.sequences, args.nccl_gather, args.kv_splits)
     sampler = ClockSampler(local) if rank == 0 else None
     for i in range(3):          # first calls set kernel attributes etc.: keep them out of capture
         wl.step(i)
     torch.cuda.synchronize()
     # a step that contains an NCCL collective is launched directly: replaying captured
-    # collectives from several graphs stalled here, and the step is not launch-bound enough to need it
-    use_graph = not args.no_graph and not getattr(wl, "long_split", False)
+    # collectives from several graphs stalled here
+    use_graph = not args.no_graph and not (getattr(wl, "long_split", False) and args.nccl_gather)
+    if getattr(wl, "long_split", False) and not args.nccl_gather:
+        # the two forms of the cross-GPU merge must agree before anything is timed
+        wl.step(0)
+        mine = wl.o.float().clone()
+        wl.nccl_gather = True
+        wl.step(0)
+        wl.nccl_gather = False
+        torch.cuda.synchronize()
+        err = (mine - wl.o.float()).abs().max().item()
+        if err > 2e-2:
+            raise SystemExit(f"rank {rank}: peer-memory merge and all-gather merge differ by {err}")
     run_step = GraphRunner(wl.step, wl.variants, use_graph)
     wl.config["launch"] = run_step.mode
     ms = timed_region(run_step, args.steps, args.warmup, world, dev, sampler)
@@ -614,6 +637,10 @@ def main():
     ap.add_argument("--sequences", type=int, default=256,
                     help="decode_paged only: number of sequences (256 = the benchmark configuration; "
                          "smaller values are for profiler captures)")
+    ap.add_argument("--kv-splits", type=int, default=0, help="decode workloads: split count (0 = the workload's default)")
+    ap.add_argument("--nccl-gather", action="store_true",
+                    help="decode_long on N > 1 GPUs: all-gather the partials with NCCL and merge in a second launch "
+                         "instead of the one-kernel exchange over peer memory")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of replaying CUDA graphs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
     ap.add_argument("--no-decode", action="store_true", help="skip the decode half of the default line")

@@ -230,6 +230,43 @@ typedef struct G4bRopeAppendArgs {
 } G4bRopeAppendArgs;
 int g4b_rope_norm_append(const G4bRopeAppendArgs* args, void* cuda_stream);
 
+/*
+ * Split-KV merge across GPUs in one launch, for one sequence whose KV range is split over
+ * `world` GPUs (one process per GPU).  No counterpart in the reference, which is single-GPU;
+ * the arithmetic is the reference's merge (g4b/kernels/fa2.py:618-626) applied twice: the
+ * `num_splits` local partials are merged into one, the merged partials of all ranks are
+ * exchanged through peer-mapped memory (every rank stores its piece into every rank's
+ * exchange buffer and raises a flag there), and merged again into `o`.  Every rank must make
+ * the same sequence of calls with the same shapes, and a slot must be in `phase` on all
+ * ranks or on none.
+ *
+ * xbuf[r] / flags[r]: address, in this process, of rank r's exchange buffer / flag array
+ * (own entries: ordinary local memory; others: peer mappings).  Sizes per rank from
+ * g4b_exchange_buffer_bytes(); both must start zeroed and be used for nothing else.  state:
+ * two zero-initialised uint32 in local memory.  A peer that does not show up within about a
+ * second leaves code 0x401 in the device status word.
+ */
+typedef struct G4bExchangeArgs {
+  G4bTensor partial_o;     /* local [S, B, H, Tq, D] f32/f16/bf16 */
+  G4bTensor partial_l;     /* local [S, B, H, Tq] f32 */
+  G4bTensor partial_m;     /* local [S, B, H, Tq] f32, log2 units */
+  G4bTensor o;             /* [B, H, Tq, D] */
+  G4bTensor user_phase;    /* optional uint8 [B] */
+  void* xbuf[8];
+  void* flags[8];
+  void* state;
+  int64_t xbuf_bytes;      /* size of every rank's exchange buffer */
+  int64_t flags_bytes;     /* size of every rank's flag array */
+  int32_t num_splits;
+  int32_t phase;
+  int32_t world;
+  int32_t rank;
+} G4bExchangeArgs;
+int g4b_attn_combine_exchange(const G4bExchangeArgs* args, void* cuda_stream);
+/* Bytes of one rank's exchange buffer (return value) and flag array (*flags_bytes) for
+ * `rows` = B * H * Tq rows of `head_dim` elements. */
+int64_t g4b_exchange_buffer_bytes(int world, int64_t rows, int head_dim, int64_t* flags_bytes);
+
 /* Message of the last failing call on this thread ("" if none). No reference counterpart:
  * the reference raises Python exceptions from its wrappers (fa2.py:656-657). */
 const char* g4b_last_error_string(void);
