@@ -3,11 +3,12 @@
 The reference is single-GPU (one ``Device(0)``, g4b/__main__.py:46); everything here is new.
 Three of the four sharded workloads need no communication at all (requests, kv heads and
 sequences are independent).  Only single-sequence long-context decode exchanges data: every
-rank attends to its contiguous share of the KV pages and the per-rank (acc, l, m) partials --
-the reference's split-KV format (g4b/kernels/fa2.py:438-472) -- are all-gathered (NCCL over
-NVLink) and merged by the same combine kernel that merges intra-GPU splits
-(fa2.py:546-631).  The gathered partials are ordinary local memory when the kernel reads
-them.
+rank attends to its contiguous share of the KV pages, and the per-rank (acc, l, m) partials --
+the reference's split-KV format (g4b/kernels/fa2.py:438-472) -- are merged across ranks
+(fa2.py:546-631 arithmetic).  Two forms: ``PartialExchange`` does it in one kernel over
+peer-mapped memory; ``gather_packed`` + ``fa2.combine_partials`` all-gathers the partials with
+the process group's backend (NCCL on GPUs, gloo on CPU tensors) and merges them with the same
+kernel that merges intra-GPU splits.
 """
 from __future__ import annotations
 

@@ -92,3 +92,33 @@ def test_bad_arguments_raise(cuda):
     peers = [(torch.zeros(16, device=cuda), torch.zeros(16, dtype=torch.int32, device=cuda))]
     with pytest.raises(ValueError):
         PartialExchange(8, 256, peers=peers, rank=0)        # buffers too small
+
+
+def test_absent_peer_ends_in_a_status_code_not_a_hang(cuda):
+    """A peer that never delivers: the bounded wait (about a second) runs out, the kernel
+    returns, the status word names the wait, o is left alone and the context stays usable."""
+    from g4b_b200 import _cabi
+
+    gen = torch.Generator().manual_seed(3)
+    S, B, H, D, world = 4, 1, 2, 256, 2
+    rows, slices = B * H, D // COLS
+    po, pl, pm = make_partials(gen, S, B, H, D)
+    peers = [(torch.zeros(2 * world * rows * slices * (COLS + 2), device=cuda),
+              torch.zeros(2 * world * rows * slices, dtype=torch.int32, device=cuda)) for _ in range(world)]
+    ex = PartialExchange(rows, D, peers=peers, rank=0)
+    o = torch.full((B, H, 1, D), 5.0, device=cuda)
+    ex.combine(po.to(cuda), pl.to(cuda), pm.to(cuda), o, S)     # nothing ever sets rank 1's flags
+    assert _cabi.device_status() == 0x401                      # synchronises, reads and clears
+    assert (o == 5.0).all()
+    assert ex.state.tolist() == [1, 0]                          # the launch still completed its bookkeeping
+    # the same object works again once the peer's pieces are there
+    xb = peers[0][0].view(2, world, rows, slices, COLS + 2)
+    acc, l, m = merged_partial(po, pl, pm)
+    xb[0, 1, :, :, :COLS] = acc.reshape(rows, slices, COLS).to(cuda)
+    xb[0, 1, :, :, COLS] = l.reshape(rows, 1).to(cuda)
+    xb[0, 1, :, :, COLS + 1] = m.reshape(rows, 1).to(cuda)
+    peers[0][1].view(2, world, rows * slices)[0, 1] = 2
+    ex.combine(po.to(cuda), pl.to(cuda), pm.to(cuda), o, S)
+    want = orc.combine_partials(torch.cat([po, po]), torch.cat([pl, pl]), torch.cat([pm, pm]), 2 * S)
+    assert torch.allclose(o.cpu(), want, atol=1e-5, rtol=1e-5)
+    assert _cabi.device_status() == 0
