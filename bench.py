@@ -8,7 +8,8 @@ Prints ONE JSON line.  Workloads (shapes of the five benchmark configurations):
     decode_paged    256 sequences, ctx ~ U[1024,32768], fp16 KV in shuffled 16-token pages,
                     one step = append the new token's K/V + attention
     decode_long     1 sequence of 131072 tokens, bf16 paged KV; with N > 1 the KV range is
-                    split across GPUs and the (acc, l, m) partials are all-gathered by NCCL
+                    split across GPUs and the (acc, l, m) partials are merged across them
+    rope_append     the launch before attention: norm + rotary embedding + KV append, GB/s
 A step is one pass of the hot path over one batch.  ``value`` has inputs resident in HBM;
 ``e2e`` goes through the public Python operators with pinned host buffers, host<->device
 copies inside the timed region.  With N > 1 every rank runs the same per-GPU batch (weak
@@ -295,6 +296,71 @@ class PrefillWorkload:
         return flops / dt / 1e12, f"{done} of {self.B} batch items, first {S} tokens, fp32, 1024-query blocks"
 
 
+class RopeAppendWorkload:
+    """The launch right before attention on a prefill chunk: per-head RMS norm + rotary
+    embedding of q and k, V norm, append of k and v to the ring caches, q out in bf16.  fp32
+    inputs in the engine's [B,t,heads,D] layout (B4 t8192 H8 G2 D256), bf16 caches.  HBM-bound:
+    algorithmic bytes = fp32 reads of q, k, v + bf16 writes of q, k, v."""
+
+    variants = 1
+
+    def __init__(self, name, dev, seed):
+        from g4b_b200.kernels.rope import rope_norm_append
+
+        self.fn = rope_norm_append
+        self.name, self.dtype = name, torch.bfloat16
+        B, S = 4, 8192
+        self.B, self.S = B, S
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        self.h_q = torch.randn(B, S, H, D, generator=gen).pin_memory()
+        self.h_k = torch.randn(B, S, G, D, generator=gen).pin_memory()
+        self.h_v = torch.randn(B, S, G, D, generator=gen).pin_memory()
+        self.q, self.k, self.v = self.h_q.to(dev), self.h_k.to(dev), self.h_v.to(dev)
+        self.q16 = torch.empty(B, S, H, D, dtype=self.dtype, device=dev)
+        self.h_q16 = torch.empty(B, S, H, D, dtype=self.dtype).pin_memory()
+        self.kc = torch.zeros(B, G, S, D, dtype=self.dtype, device=dev)
+        self.vc = torch.zeros(B, G, S, D, dtype=self.dtype, device=dev)
+        self.qw = (1 + 0.1 * torch.randn(D, generator=gen)).to(dev)
+        self.kw = (1 + 0.1 * torch.randn(D, generator=gen)).to(dev)
+        self.freqs = (1.0 / (10000.0 ** (torch.arange(0, D, 2) / D))).to(dev)
+        self.off = torch.zeros(B, dtype=torch.int32, device=dev)
+        rows = B * S
+        self.units = float(rows * (H + 2 * G) * D * (4 + 2))
+        self.metric, self.unit, self.bound = "rope_append_hbm_gbs", "GB/s", "hbm"
+        self.launches_per_step = 1
+        self.traffic = None
+        self.h2d = (self.h_q.numel() + self.h_k.numel() + self.h_v.numel()) * 4
+        self.d2h = self.h_q16.numel() * 2
+        self.config = {"workload": name, "batch_per_gpu": B, "tokens": S, "q_heads": H, "kv_heads": G, "head_dim": D,
+                       "in_dtype": "f32", "out_dtype": "bf16", "l2": "inputs (%d MB) larger than L2" % (self.h2d >> 20)}
+
+    def step(self, i=0):
+        self.fn(self.q.permute(0, 2, 1, 3), self.k.permute(0, 2, 1, 3), self.v.permute(0, 2, 1, 3), self.freqs, self.off,
+                self.kc, self.vc, 1e-6, q_out=self.q16.permute(0, 2, 1, 3), q_rmsnorm_w=self.qw, k_rmsnorm_w=self.kw)
+
+    def e2e_step(self, i=0):
+        self.q.copy_(self.h_q, non_blocking=True)
+        self.k.copy_(self.h_k, non_blocking=True)
+        self.v.copy_(self.h_v, non_blocking=True)
+        self.step(i)
+        self.h_q16.copy_(self.q16, non_blocking=True)
+
+    def value_from(self, ms_per_step, world):
+        return self.units * world / (ms_per_step * 1e-3) / 1e9
+
+    def cpu_sample(self, budget_s=15.0):
+        from oracle import attention_oracle as orc
+
+        n = 1024
+        q, k, v = (x[:1, :n].permute(0, 2, 1, 3) for x in (self.h_q, self.h_k, self.h_v))
+        kc, vc = torch.zeros(1, G, n, D, dtype=self.dtype), torch.zeros(1, G, n, D, dtype=self.dtype)
+        t0 = time.perf_counter()
+        orc.rope_norm_append(q, k, v, self.freqs.cpu(), torch.zeros(1, dtype=torch.int32), kc, vc, 1e-6,
+                             q_rmsnorm_w=self.qw.cpu(), k_rmsnorm_w=self.kw.cpu())
+        dt = time.perf_counter() - t0
+        return n * (H + 2 * G) * D * 6 / dt / 1e9, f"{n} tokens of 1 batch item, torch fp32"
+
+
 class DecodeWorkload:
     """Configs 4 and 5: paged KV with shuffled block tables; a step appends the new token's
     K and V rows and runs decode attention (split-KV + combine)."""
@@ -456,7 +522,9 @@ class DecodeWorkload:
 
 
 def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_splits=0):
-    seeds = {"prefill_causal": 1, "prefill_swa": 2, "decode_paged": 3, "decode_long": 4}
+    seeds = {"prefill_causal": 1, "prefill_swa": 2, "decode_paged": 3, "decode_long": 4, "rope_append": 5}
+    if name == "rope_append":
+        return RopeAppendWorkload(name, dev, seeds[name] + 100 * rank)
     if name.startswith("prefill"):
         return PrefillWorkload(name, dev, seeds[name] + 100 * rank)
     return DecodeWorkload(name, dev, seeds[name] + (0 if name == "decode_long" else 100 * rank), rank, world,
@@ -633,7 +701,7 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="prefill_causal",
-                    choices=["prefill_causal", "prefill_swa", "decode_paged", "decode_long"])
+                    choices=["prefill_causal", "prefill_swa", "decode_paged", "decode_long", "rope_append"])
     ap.add_argument("--sequences", type=int, default=256,
                     help="decode_paged only: number of sequences (256 = the benchmark configuration; "
                          "smaller values are for profiler captures)")

@@ -16,7 +16,6 @@
 namespace g4b {
 namespace {
 
-constexpr int kMaxIter = 2;   // D/2 <= 256 elements: two passes of 32 lanes x 4
 
 struct RopeParams {
   const void* q; const void* k; const void* v;
@@ -101,7 +100,136 @@ __device__ __forceinline__ int64_t cache_row(const RopeParams& p, int b, int g, 
   return ((int64_t)b * p.G + g) * p.T + r;
 }
 
-__global__ void __launch_bounds__(256) rope_norm_append_kernel(RopeParams p) {
+// One tensor's heads of one token (KIND 0 q, 1 k, 2 v, a compile-time constant so that the
+// source / destination choices cost nothing at run time), four rows at a time: the loads of
+// all four rows go out before anything is computed, so that a lane has eight 16-byte loads
+// in flight (one row at a time left HBM at a quarter of its bandwidth).
+template <int KIND, int ITERS>
+__device__ __forceinline__ void rows_of_kind(const RopeParams& p, int h_begin, int h_end, int b, int t, int64_t pos,
+                                             bool in_phase, int lane, const float4 (&sn)[ITERS],
+                                             const float4 (&cs)[ITERS]) {
+  constexpr int kBatch = 4;
+  const int half = p.D >> 1;
+  const void* src = KIND == 0 ? p.q : (KIND == 1 ? p.k : p.v);
+  const int64_t* ss = KIND == 0 ? p.qs : (KIND == 1 ? p.ks : p.vs);
+  const int64_t src_row = b * ss[0] + t * ss[2];
+  const int64_t src_hs = ss[1];
+  // destinations
+  void* cache = KIND == 1 ? p.k_cache : (KIND == 2 ? p.v_cache : nullptr);
+  const bool to_cache = cache != nullptr && in_phase;
+  void* out = nullptr;
+  int64_t out_row = 0, out_hs = 0;
+  int out_dtype = p.in_dtype;
+  if (KIND == 0) {
+    if (p.q_out != nullptr) { out = p.q_out; out_dtype = p.q_out_dtype; out_row = b * p.qos[0] + t * p.qos[2]; out_hs = p.qos[1]; }
+    else if (!p.q_untouched) { out = const_cast<void*>(p.q); out_row = src_row; out_hs = src_hs; }
+  } else if (KIND == 1) {
+    if (p.k_out != nullptr) { out = p.k_out; out_dtype = p.k_out_dtype; out_row = b * p.kos[0] + t * p.kos[2]; out_hs = p.kos[1]; }
+    else if (p.k_cache == nullptr) { out = const_cast<void*>(p.k); out_row = src_row; out_hs = src_hs; }
+  }
+  if (out == nullptr && !to_cache) return;     // nothing to write (warp-uniform)
+  const bool norm = KIND == 2 ? p.norm_v != 0 : p.norm_qk != 0;
+  const float* rsos = KIND == 0 ? p.q_rsos : (KIND == 1 ? p.k_rsos : p.v_rsos);
+  const int64_t* rs = KIND == 0 ? p.qrs : (KIND == 1 ? p.krs : p.vrs);
+  const float* w = KIND == 0 ? p.q_w : (KIND == 1 ? p.k_w : nullptr);
+  const int64_t ws = KIND == 0 ? p.qw_stride : p.kw_stride;
+  // norm weights of this lane's elements (the same for every head of the tensor)
+  float4 w1[ITERS], w2[ITERS];
+  if (norm && w != nullptr) {
+#pragma unroll
+    for (int it = 0; it < ITERS; ++it) {
+      const int d1 = it * 128 + lane * 4;
+      if (d1 < half) {
+        if (ws == 1) {
+          w1[it] = *reinterpret_cast<const float4*>(w + d1);
+          w2[it] = *reinterpret_cast<const float4*>(w + d1 + half);
+        } else {
+          w1[it] = make_float4(w[d1 * ws], w[(d1 + 1) * ws], w[(d1 + 2) * ws], w[(d1 + 3) * ws]);
+          w2[it] = make_float4(w[(d1 + half) * ws], w[(d1 + half + 1) * ws], w[(d1 + half + 2) * ws], w[(d1 + half + 3) * ws]);
+        }
+      }
+    }
+  }
+  const bool rotate = KIND != 2 && p.freqs != nullptr;
+
+  for (int h0 = h_begin; h0 < h_end; h0 += kBatch) {
+    float4 x1[kBatch][ITERS], x2[kBatch][ITERS];
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      if (h0 + i < h_end) {
+        const int64_t so = src_row + (h0 + i) * src_hs;
+#pragma unroll
+        for (int it = 0; it < ITERS; ++it) {
+          const int d1 = it * 128 + lane * 4;
+          if (d1 < half) {
+            x1[i][it] = load4(src, p.in_dtype, so + d1);
+            x2[i][it] = load4(src, p.in_dtype, so + d1 + half);
+          }
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < kBatch; ++i) {
+      const int h = h0 + i;
+      if (h >= h_end) continue;
+      const int64_t crow = to_cache ? cache_row(p, b, h, pos, lane) : -1;
+      if (norm) {
+        float sumsq = 0.f;
+        if (rsos != nullptr) {
+          sumsq = rsos[b * rs[0] + h * rs[1] + t * rs[2]];
+        } else {
+#pragma unroll
+          for (int it = 0; it < ITERS; ++it)
+            if (it * 128 + lane * 4 < half) sumsq += dot4(x1[i][it]) + dot4(x2[i][it]);
+#pragma unroll
+          for (int o = 16; o > 0; o >>= 1) sumsq += __shfl_xor_sync(0xffffffffu, sumsq, o);
+        }
+        const float inv = rsqrtf(sumsq / (float)p.D + p.eps);
+#pragma unroll
+        for (int it = 0; it < ITERS; ++it) {
+          if (it * 128 + lane * 4 < half) {
+            if (w != nullptr) {
+              // x * (inv * w): the reference's grouping (rope.py:33-34)
+              x1[i][it] = mul4(x1[i][it], scale4(w1[it], inv));
+              x2[i][it] = mul4(x2[i][it], scale4(w2[it], inv));
+            } else {
+              x1[i][it] = scale4(x1[i][it], inv);
+              x2[i][it] = scale4(x2[i][it], inv);
+            }
+          }
+        }
+      }
+#pragma unroll
+      for (int it = 0; it < ITERS; ++it) {
+        const int d1 = it * 128 + lane * 4;
+        if (d1 < half) {
+          float4 y1 = x1[i][it], y2 = x2[i][it];
+          if (rotate) {
+            const float4 a = x1[i][it], c = x2[i][it], s = sn[it], co = cs[it];
+            y1 = make_float4(co.x * a.x - s.x * c.x, co.y * a.y - s.y * c.y, co.z * a.z - s.z * c.z, co.w * a.w - s.w * c.w);
+            y2 = make_float4(co.x * c.x + s.x * a.x, co.y * c.y + s.y * a.y, co.z * c.z + s.z * a.z, co.w * c.w + s.w * a.w);
+          }
+          if (out != nullptr) {
+            const int64_t oo = out_row + h * out_hs + d1;
+            store4(out, out_dtype, oo, y1);
+            store4(out, out_dtype, oo + half, y2);
+          }
+          if (crow >= 0) {
+            store4(cache, p.cache_dtype, crow * p.D + d1, y1);
+            store4(cache, p.cache_dtype, crow * p.D + d1 + half, y2);
+          }
+        }
+      }
+    }
+  }
+}
+
+// ITERS: passes of 32 lanes x 4 pairs over half the head dim (1 up to D = 256, 2 up to 512).
+// A warp takes heads [h_begin, h_end) of one token out of the token's H + 2G (q heads, then k,
+// then v): all of them at prefill sizes, so that the token's sines and cosines are computed
+// once; one at decode sizes, for parallelism.
+template <int ITERS>
+__global__ void __launch_bounds__(256, ITERS == 1 ? 3 : 2) rope_norm_append_kernel(RopeParams p) {
   const int lane = threadIdx.x & 31;
   const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int n_slots = (p.n_heads + p.heads_per_warp - 1) / p.heads_per_warp;
@@ -121,14 +249,13 @@ __global__ void __launch_bounds__(256) rope_norm_append_kernel(RopeParams p) {
   const int h_end = min(h_begin + p.heads_per_warp, p.n_heads);
 
   // sines and cosines of this token, for the pairs this lane owns
-  float4 sn[kMaxIter], cs[kMaxIter];
-  const bool rotate = p.freqs != nullptr && h_begin < p.H + p.G;
+  float4 sn[ITERS], cs[ITERS];
 #pragma unroll
-  for (int it = 0; it < kMaxIter; ++it) {
+  for (int it = 0; it < ITERS; ++it) {
     const int d1 = it * 128 + lane * 4;
     sn[it] = make_float4(0.f, 0.f, 0.f, 0.f);
     cs[it] = make_float4(1.f, 1.f, 1.f, 1.f);
-    if (rotate && d1 < half) {
+    if (p.freqs != nullptr && h_begin < p.H + p.G && d1 < half) {
       const float fp = (float)pos;
       // theta is the fp32 product, as in the reference (rope.py:171) and its torch oracle
       sincosf(fp * p.freqs[(d1 + 0) * p.freq_stride], &sn[it].x, &cs[it].x);
@@ -137,98 +264,13 @@ __global__ void __launch_bounds__(256) rope_norm_append_kernel(RopeParams p) {
       sincosf(fp * p.freqs[(d1 + 3) * p.freq_stride], &sn[it].w, &cs[it].w);
     }
   }
-
-  for (int hh = h_begin; hh < h_end; ++hh) {
-    // which tensor this head index belongs to: 0 q, 1 k, 2 v
-    const int kind = hh < p.H ? 0 : (hh < p.H + p.G ? 1 : 2);
-    const int h = kind == 0 ? hh : (kind == 1 ? hh - p.H : hh - p.H - p.G);
-    const void* src_base = kind == 0 ? p.q : (kind == 1 ? p.k : p.v);
-    const int64_t* ss = kind == 0 ? p.qs : (kind == 1 ? p.ks : p.vs);
-    const int64_t src_off = b * ss[0] + h * ss[1] + t * ss[2];
-
-    int64_t crow = -1;
-    void* cache = kind == 1 ? p.k_cache : (kind == 2 ? p.v_cache : nullptr);
-    if (cache != nullptr && in_phase) crow = cache_row(p, b, h, pos, lane);
-    void* out = nullptr;
-    int64_t out_off = 0;
-    int out_dtype = p.in_dtype;
-    if (kind == 0) {
-      if (p.q_out != nullptr) { out = p.q_out; out_dtype = p.q_out_dtype; out_off = b * p.qos[0] + h * p.qos[1] + t * p.qos[2]; }
-      else if (!p.q_untouched) { out = const_cast<void*>(p.q); out_off = src_off; }
-    } else if (kind == 1) {
-      if (p.k_out != nullptr) { out = p.k_out; out_dtype = p.k_out_dtype; out_off = b * p.kos[0] + h * p.kos[1] + t * p.kos[2]; }
-      else if (p.k_cache == nullptr) { out = const_cast<void*>(p.k); out_off = src_off; }
-    }
-    if (out == nullptr && crow < 0) continue;    // nothing to write (warp-uniform)
-
-    float4 x1[kMaxIter], x2[kMaxIter];
-    float sumsq = 0.f;
-#pragma unroll
-    for (int it = 0; it < kMaxIter; ++it) {
-      const int d1 = it * 128 + lane * 4;
-      if (d1 < half) {
-        x1[it] = load4(src_base, p.in_dtype, src_off + d1);
-        x2[it] = load4(src_base, p.in_dtype, src_off + d1 + half);
-        sumsq += dot4(x1[it]) + dot4(x2[it]);
-      }
-    }
-    const bool norm = kind == 2 ? p.norm_v != 0 : p.norm_qk != 0;
-    if (norm) {
-      const float* rsos = kind == 0 ? p.q_rsos : (kind == 1 ? p.k_rsos : p.v_rsos);
-      const int64_t* rs = kind == 0 ? p.qrs : (kind == 1 ? p.krs : p.vrs);
-      if (rsos != nullptr) {
-        sumsq = rsos[b * rs[0] + h * rs[1] + t * rs[2]];
-      } else {
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sumsq += __shfl_xor_sync(0xffffffffu, sumsq, o);
-      }
-      const float inv = rsqrtf(sumsq / (float)p.D + p.eps);
-      const float* w = kind == 0 ? p.q_w : (kind == 1 ? p.k_w : nullptr);
-      const int64_t ws = kind == 0 ? p.qw_stride : p.kw_stride;
-#pragma unroll
-      for (int it = 0; it < kMaxIter; ++it) {
-        const int d1 = it * 128 + lane * 4;
-        if (d1 < half) {
-          if (w != nullptr) {
-            float4 w1, w2;
-            if (ws == 1) {
-              w1 = *reinterpret_cast<const float4*>(w + d1);
-              w2 = *reinterpret_cast<const float4*>(w + d1 + half);
-            } else {
-              w1 = make_float4(w[d1 * ws], w[(d1 + 1) * ws], w[(d1 + 2) * ws], w[(d1 + 3) * ws]);
-              w2 = make_float4(w[(d1 + half) * ws], w[(d1 + half + 1) * ws], w[(d1 + half + 2) * ws], w[(d1 + half + 3) * ws]);
-            }
-            // x * (inv * w): the reference's grouping (rope.py:33-34)
-            x1[it] = mul4(x1[it], scale4(w1, inv));
-            x2[it] = mul4(x2[it], scale4(w2, inv));
-          } else {
-            x1[it] = scale4(x1[it], inv);
-            x2[it] = scale4(x2[it], inv);
-          }
-        }
-      }
-    }
-#pragma unroll
-    for (int it = 0; it < kMaxIter; ++it) {
-      const int d1 = it * 128 + lane * 4;
-      if (d1 < half) {
-        float4 y1 = x1[it], y2 = x2[it];
-        if (kind != 2 && p.freqs != nullptr) {
-          const float4 a = x1[it], c = x2[it], s = sn[it], co = cs[it];
-          y1 = make_float4(co.x * a.x - s.x * c.x, co.y * a.y - s.y * c.y, co.z * a.z - s.z * c.z, co.w * a.w - s.w * c.w);
-          y2 = make_float4(co.x * c.x + s.x * a.x, co.y * c.y + s.y * a.y, co.z * c.z + s.z * a.z, co.w * c.w + s.w * a.w);
-        }
-        if (out != nullptr) {
-          store4(out, out_dtype, out_off + d1, y1);
-          store4(out, out_dtype, out_off + d1 + half, y2);
-        }
-        if (crow >= 0) {
-          store4(cache, p.cache_dtype, crow * p.D + d1, y1);
-          store4(cache, p.cache_dtype, crow * p.D + d1 + half, y2);
-        }
-      }
-    }
-  }
+  // the warp's head range, cut into its q, k and v parts
+  const int q0 = min(h_begin, p.H), q1 = min(h_end, p.H);
+  const int k0 = min(max(h_begin, p.H), p.H + p.G) - p.H, k1 = min(max(h_end, p.H), p.H + p.G) - p.H;
+  const int v0 = max(h_begin, p.H + p.G) - p.H - p.G, v1 = max(h_end, p.H + p.G) - p.H - p.G;
+  if (q1 > q0) rows_of_kind<0, ITERS>(p, q0, q1, b, t, pos, in_phase, lane, sn, cs);
+  if (k1 > k0) rows_of_kind<1, ITERS>(p, k0, k1, b, t, pos, in_phase, lane, sn, cs);
+  if (v1 > v0) rows_of_kind<2, ITERS>(p, v0, v1, b, t, pos, in_phase, lane, sn, cs);
 }
 
 int check_view(const G4bTensor& t, const char* name, int ndim, int64_t d0, int64_t d1, int64_t d2, int64_t d3) {
@@ -364,14 +406,15 @@ int launch_rope_norm_append(const G4bRopeAppendArgs& a, cudaStream_t st) {
 
   const int64_t rows = B * Tq;
   if (rows == 0 || p.n_heads == 0) return G4B_OK;
-  // Few rows (decode): one head per warp, for parallelism.  Many (prefill): a warp takes four
-  // heads of a token and computes the token's sines and cosines once for them.
-  p.heads_per_warp = rows * p.n_heads >= 16384 ? 4 : 1;
+  // Few rows (decode): one head per warp, for parallelism.  Many (prefill): a warp takes all
+  // heads of a token, four at a time, and computes the token's sines and cosines once.
+  p.heads_per_warp = rows * p.n_heads >= 16384 ? p.n_heads : 1;
   const int64_t n_slots = (p.n_heads + p.heads_per_warp - 1) / p.heads_per_warp;
   const int64_t warps = rows * n_slots;
   const int64_t blocks = (warps + 7) / 8;
   if (blocks > 0x7fffffffLL) return fail(G4B_ERR_UNSUPPORTED, "rope_norm_append: too many rows");
-  rope_norm_append_kernel<<<(unsigned)blocks, 256, 0, st>>>(p);
+  if (D <= 256) rope_norm_append_kernel<1><<<(unsigned)blocks, 256, 0, st>>>(p);
+  else rope_norm_append_kernel<2><<<(unsigned)blocks, 256, 0, st>>>(p);
   G4B_CUDA_CHECK(cudaGetLastError());
   return G4B_OK;
 }
