@@ -183,3 +183,23 @@ def test_decode_full_size_property(cuda):
         k = orc.gather_pages(case["k_pool"], case["block_tables"][b], lens[b], 16)
         v = orc.gather_pages(case["v_pool"], case["block_tables"][b], lens[b], 16)
         assert_close(a[b], orc.attention_core(case["q"][b], k, v, scale=1 / 16), f"seq {b}")
+
+
+def test_decode_one_long_sequence_full_size(cuda):
+    """One sequence of 131072 tokens (bf16, 16-token pages, shuffled table): the whole answer
+    against the oracle, for the split counts the benchmark uses and for the merge kernels."""
+    from g4b_b200.dist import PartialExchange
+
+    case = make_paged_case(36, lens=[131072], H=8, G=2, dtype=torch.bfloat16, extra_pages=5)
+    k = orc.gather_pages(case["k_pool"], case["block_tables"][0], 131072, 16)
+    v = orc.gather_pages(case["v_pool"], case["block_tables"][0], 131072, 16)
+    want = orc.attention_core(case["q"][0], k, v, scale=1 / 16)
+    for splits in (16, 148):
+        got, (po, pl, pm) = run_paged(case, cuda, splits=splits, max_splits=splits)
+        assert_close(got[0], want, f"{splits} splits")
+    # the same partials through the one-kernel cross-GPU merge (a world of one)
+    peers = [(torch.zeros(2 * 8 * 8 * 34, device=cuda), torch.zeros(2 * 8 * 8, dtype=torch.int32, device=cuda))]
+    ex = PartialExchange(8, 256, peers=peers, rank=0)
+    o = torch.zeros(1, 8, 1, 256, dtype=torch.bfloat16, device=cuda)
+    ex.combine(po, pl, pm, o, 148)
+    assert_close(o[0].cpu(), want, "exchange merge of 148 splits")
