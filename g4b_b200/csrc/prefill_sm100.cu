@@ -423,7 +423,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           ptx::tma_load_4d_hint(ptx::smem_u32(sQ + s * 16384), &q_map, bar_q, s * 64, m0, h, b, pol_q);
       }
     }
-    // lane 0 waits for the stage to drain; the verdict is shared so the warp stays converged
+    // lane 0 waits for the stage to drain; the outcome is shared so the warp stays converged
     auto wait_empty = [&](int st, uint32_t c) -> bool {
       int w = 1;
       if (lane == 0) w = ptx::mbar_wait(ptx::smem_u32(&bars->kv_empty[st]), ((c / kSt) & 1) ^ 1) ? 1 : 0;
@@ -995,7 +995,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       mx = fmaxf(mx, xm[(half ^ 1) * kBM + r]);
       const float m_blk = mx * p.scale_log2;
       const bool exceed = m_blk > m_used + 8.f;
-      if (fast && __any_sync(0xffffffffu, exceed)) fast = false;   // same verdict in the partner warp
+      if (fast && __any_sync(0xffffffffu, exceed)) fast = false;   // same outcome in the partner warp
 
       if (fast) {
         // first 32 keys of this half are final: let the P.V product start on them
