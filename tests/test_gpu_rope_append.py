@@ -177,3 +177,29 @@ def test_bad_arguments_raise(cuda):
         rope_norm_append(q, k, k.clone(), freqs, off, None, None, 1e-6)
     with pytest.raises(ValueError):
         apply_rope(q.half(), k, freqs, off, None, None, None, None, 1e-6)
+
+
+@pytest.mark.parametrize("D,H,G,B,Tq", [(512, 2, 1, 2, 7), (64, 4, 4, 1, 33), (128, 5, 1, 1, 2400), (512, 3, 1, 1, 3300)])
+def test_other_head_dims_and_head_counts(cuda, D, H, G, B, Tq):
+    """Head dims 64 / 128 / 512 (the two-pass form of the kernel), head counts that do not fill
+    the four-row batches, and both work splits (one head per warp; all heads of a token per
+    warp above 16384 rows)."""
+    gen = torch.Generator().manual_seed(D + H + Tq)
+    T = Tq + 5
+    q, k, v = randn(gen, B, H, Tq, D), randn(gen, B, G, Tq, D), randn(gen, B, G, Tq, D)
+    q_w, k_w = 1 + 0.1 * randn(gen, D), 1 + 0.1 * randn(gen, D)
+    freqs = 1.0 / (10000.0 ** (torch.arange(0, D, 2) / D))
+    off = torch.tensor([3, T - 2][:B], dtype=torch.int32)
+    kc0, vc0 = randn(gen, B, G, T, D, dtype=torch.bfloat16), randn(gen, B, G, T, D, dtype=torch.bfloat16)
+    want_q, want_k, want_kc, want_vc = orc.rope_norm_append(q, k, v, freqs, off, kc0, vc0, 1e-6, q_rmsnorm_w=q_w,
+                                                            k_rmsnorm_w=k_w)
+    qd, kd = q.to(cuda), k.to(cuda)
+    kc, vc = kc0.to(cuda), vc0.to(cuda)
+    k_out = torch.zeros(B, G, Tq, D, device=cuda)
+    rope_norm_append(qd, kd, v.to(cuda), freqs.to(cuda), off.to(cuda), kc, vc, 1e-6, k_out=k_out,
+                     q_rmsnorm_w=q_w.to(cuda), k_rmsnorm_w=k_w.to(cuda))
+    assert torch.allclose(qd.cpu(), want_q, atol=2e-5, rtol=2e-5)             # in place, fp32
+    assert torch.allclose(k_out.cpu(), want_k, atol=2e-5, rtol=2e-5)
+    assert torch.equal(kd.cpu(), k)                                           # k itself is left alone when it has a destination
+    assert torch.allclose(kc.float().cpu(), want_kc.float(), atol=8e-3, rtol=8e-3)
+    assert torch.allclose(vc.float().cpu(), want_vc.float(), atol=8e-3, rtol=8e-3)
