@@ -250,3 +250,14 @@ def test_prefill_paged_equals_ring(cuda):
     v = torch.stack([orc.gather_pages(case["v_pool"], case["block_tables"][b], 512, 16) for b in range(2)])
     ring = dict(q_phys=case["q_phys"], q=case["q"], k=k.contiguous(), v=v.contiguous(), time=case["time"], ctx_window=512)
     assert torch.equal(run(ring, cuda), paged)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_prefill_long_contexts_use_the_long_item_kernel(cuda, dtype):
+    """Contexts of several thousand keys select the long-item variant of the pair kernel (the
+    small cases above all run the short-item one): chunked prefill at the end of paged
+    contexts, and of a ring cache that wraps."""
+    case = make_paged_prefill_case(64, times=[4500, 3333], Tq=256, H=8, G=2, dtype=dtype, poison=True)
+    assert_close(run_paged_prefill(case, cuda), oracle_paged_prefill(case), "paged, long contexts")
+    ring = make_ring_case(65, B=2, H=8, G=2, Tq=384, T=4100, dtype=dtype, times=[4100 + 777, 3000])
+    assert_close(run(ring, cuda), oracle(ring), "ring, long contexts")
