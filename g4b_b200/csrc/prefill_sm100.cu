@@ -7,8 +7,11 @@
 // and full stages (fa2.py:354-435), per-slot phase skip (fa2.py:333-335); adds the softmax
 // scale and the per-query sliding window of scripts/reference_impl.py:437-443.
 //
-// One CTA = 128 query rows of one query head.  Ten warps:
-//   warp 0      producer: TMA loads of Q (once) and of K / V chunks into a 5-stage ring
+// A work item = 128 query rows of one query head.  The grid is persistent: one CTA (or, when
+// the head counts allow it, one cluster of two CTAs that take two heads of one kv head and
+// share every K / V tile through cta_group::2 MMAs) per SM walks a static list of items,
+// heaviest first.  Ten warps:
+//   warp 0      producer: TMA loads of Q (once per item) and of K / V chunks into a 5-slot ring
 //   warp 1      one thread issues every tcgen05.mma; the warp owns the TMEM allocation
 //   warps 2..9  softmax, two warpgroups: a thread owns query row r (TMEM lane r) for one
 //               half of a tile's 128 keys, so row max / row sum need no shuffles, only one
@@ -25,8 +28,9 @@
 // QK(j+1) / PV(j-1) while the softmax warps turn S(j) into P(j).
 //
 // Shared memory: Q 64 KB (4 slabs of [128 rows x 64 d], 128-byte swizzle) + 5 x 32 KB ring.
-// A K chunk is half the head dim of a tile ([128 keys x 128 d], 2 slabs); a V chunk is
-// half the keys of a tile ([64 keys x 256 d], 4 slabs).
+// One-CTA form: a K chunk is half the head dim of a tile ([128 keys x 128 d], 2 slabs), a V
+// chunk half the keys ([64 keys x 256 d], 4 slabs).  Pair form: each CTA stages half of every
+// tile, K as its 64 keys x 256 d, V as 128 keys x its 128 head-dim columns.
 #include "common.cuh"
 #include "sm100_ptx.cuh"
 
