@@ -85,6 +85,8 @@ struct PrefillParams {
   int64_t time_stride, phase_stride, bt_s0, bt_s1;
   int page_shift, num_pages, max_pages;      // paged mode
   int B, H, G, Tq, T;
+  const float* q_f32;                        // q given as f32 (the engine's scratchpad type): converted on load
+  int64_t q_s0, q_s1, q_s2;                  // its strides for b, h, t (elements)
   int n_q_tiles;                             // ceil(Tq / 128)
   FastDiv by_units, by_H, by_HperG, by_T;    // units per query tile, H, H / G, ring length
   int ctx_window, sliding_window, phase, causal;
@@ -415,7 +417,29 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       if (!w) { if (lane == 0) record(p.status, kErrQEmpty); ok = false; break; }
     }
     G4B_ITEM_AT(1);   // Q buffer free, Q load goes out
-    if (lane == 0) {
+    if (p.q_f32 != nullptr) {
+      // f32 q: the warp reads one row (1 KB) per pass, rounds it to the cache type and writes
+      // the four 128-byte-swizzled slabs the TMA load would have produced; rows past Tq are
+      // zero like the out-of-bounds fill
+      const float* q0 = p.q_f32 + b * p.q_s0 + h * p.q_s1;
+      const int slab = lane >> 3, c16 = lane & 7;
+#pragma unroll 4
+      for (int r = 0; r < kBM; ++r) {
+        uint4 w = make_uint4(0u, 0u, 0u, 0u);
+        if (m0 + r < p.Tq) {
+          const float4* src = reinterpret_cast<const float4*>(q0 + (int64_t)(m0 + r) * p.q_s2 + lane * 8);
+          const float4 a = src[0], c = src[1];
+          w = make_uint4(PackT<T>::pack(a.x, a.y), PackT<T>::pack(a.z, a.w), PackT<T>::pack(c.x, c.y), PackT<T>::pack(c.z, c.w));
+        }
+        *reinterpret_cast<uint4*>(sQ + slab * 16384 + r * 128 + ((c16 ^ (r & 7)) << 4)) = w;
+      }
+      ptx::fence_proxy_async_smem();
+      __syncwarp();
+      if (lane == 0) {
+        if constexpr (kPair) ptx::mbar_arrive_cluster(issuer_bar(&bars->q_full));
+        else ptx::mbar_arrive(bar_q);
+      }
+    } else if (lane == 0) {
       if constexpr (kPair) {
         const uint32_t qb = issuer_bar(&bars->q_full);
         ptx::mbar_arrive_expect_tx_cluster(qb, kQBytes);
@@ -1346,16 +1370,17 @@ extern "C" int g4b_debug_read_trace(long long* out) {
 
 int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   const bool paged = a.block_tables.ptr != nullptr;
-  if (a.q.dtype != a.k_cache.dtype)
-    return fail(G4B_ERR_BAD_DTYPE, "prefill: q must have the cache dtype (f16 or bf16)");
-  if (a.o.dtype != a.q.dtype && a.o.dtype != G4B_F32)
-    return fail(G4B_ERR_BAD_DTYPE, "prefill: o must have the q dtype or be f32");
+  const bool q_f32 = a.q.dtype == G4B_F32;
+  if (!q_f32 && a.q.dtype != a.k_cache.dtype)
+    return fail(G4B_ERR_BAD_DTYPE, "prefill: q must have the cache dtype (f16 or bf16) or be f32");
+  if (a.o.dtype != a.k_cache.dtype && a.o.dtype != G4B_F32)
+    return fail(G4B_ERR_BAD_DTYPE, "prefill: o must have the cache dtype or be f32");
   const int64_t B = a.q.shape[0], H = a.q.shape[1], Tq = a.q.shape[2], D = a.q.shape[3];
   const int64_t G = a.k_cache.shape[1], T = a.k_cache.shape[2];
   if (B == 0 || Tq == 0) return G4B_OK;
   const int esz = 2;
   for (int i = 0; i < 3; ++i) {
-    if ((a.q.stride[i] * esz) % 16 != 0) return fail(G4B_ERR_BAD_STRIDE, "prefill: q strides must be multiples of 16 bytes");
+    if ((a.q.stride[i] * (q_f32 ? 4 : esz)) % 16 != 0) return fail(G4B_ERR_BAD_STRIDE, "prefill: q strides must be multiples of 16 bytes");
   }
   if (((uintptr_t)a.q.ptr) & 15) return fail(G4B_ERR_BAD_STRIDE, "prefill: q must be 16-byte aligned");
   const int osz = dtype_size(a.o.dtype);
@@ -1375,7 +1400,7 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
     const uint64_t dims[4] = {(uint64_t)D, (uint64_t)Tq, (uint64_t)H, (uint64_t)B};
     const uint64_t strides[3] = {(uint64_t)a.q.stride[2] * esz, (uint64_t)a.q.stride[1] * esz, (uint64_t)a.q.stride[0] * esz};
     const uint32_t box[4] = {64, (uint32_t)kBM, 1, 1};
-    if ((rc = encode_map(&qm, a.q.dtype, 4, a.q.ptr, dims, strides, box, "q"))) return rc;
+    if (!q_f32 && (rc = encode_map(&qm, a.q.dtype, 4, a.q.ptr, dims, strides, box, "q"))) return rc;
   }
   if (!paged) {
     const uint64_t dims[3] = {(uint64_t)D, (uint64_t)T, (uint64_t)(B * G)};
@@ -1439,7 +1464,12 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   if (workers < 1) workers = 1;
   if (workers > n_items) workers = n_items;
   dim3 grid((unsigned)(pair ? 2 * workers : workers), 1, 1);
-  if (a.q.dtype == G4B_BF16) return launch_typed<__nv_bfloat16>(qm, km, vm, p, grid, pair, stage_out, short_items, st);
+  if (q_f32) {
+    qm = km;   // never used by the kernel: q is converted on load
+    p.q_f32 = (const float*)a.q.ptr;
+    p.q_s0 = a.q.stride[0]; p.q_s1 = a.q.stride[1]; p.q_s2 = a.q.stride[2];
+  }
+  if (a.k_cache.dtype == G4B_BF16) return launch_typed<__nv_bfloat16>(qm, km, vm, p, grid, pair, stage_out, short_items, st);
   return launch_typed<__half>(qm, km, vm, p, grid, pair, stage_out, short_items, st);
 }
 

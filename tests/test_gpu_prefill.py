@@ -261,3 +261,20 @@ def test_prefill_long_contexts_use_the_long_item_kernel(cuda, dtype):
     assert_close(run_paged_prefill(case, cuda), oracle_paged_prefill(case), "paged, long contexts")
     ring = make_ring_case(65, B=2, H=8, G=2, Tq=384, T=4100, dtype=dtype, times=[4100 + 777, 3000])
     assert_close(run(ring, cuda), oracle(ring), "ring, long contexts")
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B,H,G,Tq,T", [(2, 8, 2, 200, 333), (1, 3, 3, 129, 129), (2, 8, 2, 384, 4200)])
+def test_prefill_accepts_f32_q_and_o(cuda, dtype, B, H, G, Tq, T):
+    """The engine's scratchpad types (g4b/models/gemma4e.py:30-32): q and o fp32, caches 16-bit.
+    q is rounded to the cache type on load; pair and one-CTA forms, short- and long-item kernels."""
+    case = make_ring_case(70 + Tq, B=B, H=H, G=G, Tq=Tq, T=T, dtype=dtype)
+    gen = torch.Generator().manual_seed(71)
+    q32 = randn(gen, B, Tq, H, 256)                                   # not representable in 16 bits
+    case32 = dict(case, q_phys=q32, q=q32.permute(0, 2, 1, 3))
+    want = oracle(dict(case, q=q32.to(dtype).float().permute(0, 2, 1, 3)))
+    got = run(case32, cuda, o_dtype=torch.float32)
+    assert got.dtype == torch.float32
+    assert_close(got, want, "f32 q, f32 o")
+    got16 = run(case32, cuda, o_dtype=dtype)
+    assert_close(got16, want, "f32 q, 16-bit o")
