@@ -203,3 +203,27 @@ def test_other_head_dims_and_head_counts(cuda, D, H, G, B, Tq):
     assert torch.equal(kd.cpu(), k)                                           # k itself is left alone when it has a destination
     assert torch.allclose(kc.float().cpu(), want_kc.float(), atol=8e-3, rtol=8e-3)
     assert torch.allclose(vc.float().cpu(), want_vc.float(), atol=8e-3, rtol=8e-3)
+
+
+def test_reference_rope_script_case(cuda):
+    """The case of the reference's rope comparison script (tests/compare_scripts/test_rope.py:
+    B, h, T, k = 1, 48, 1, 512; q and k of the same shape; position 1000; frequency base 1e5;
+    frequency scales of 1 for the first half of the pairs and -inf for the rest, i.e. those
+    pairs are not rotated), through apply_rope and against the oracle."""
+    gen = torch.Generator().manual_seed(48)
+    B, h, T, k = 1, 48, 1, 512
+    q, kk = randn(gen, B, h, T, k), randn(gen, B, h, T, k)
+    q_w, k_w = randn(gen, k), randn(gen, k)
+    scales = torch.cat([torch.ones(k // 4), torch.full((k // 4,), float("-inf"))])
+    freqs = 1.0 / (100000.0 ** (torch.arange(0, k, 2) / k)) / scales
+    off = torch.tensor([1000], dtype=torch.int64)
+    pos = off[:, None] + torch.arange(T)[None]
+    want_q = orc.rope_norm(q, pos, freqs, rsos=(q * q).sum(-1), weight=q_w, eps=1e-6)
+    want_k = orc.rope_norm(kk, pos, freqs, rsos=(kk * kk).sum(-1), weight=k_w, eps=1e-6)
+    qd, kd = q.to(cuda), kk.to(cuda)
+    apply_rope(qd, kd, freqs.to(cuda), off.to(cuda), (qd * qd).sum(-1), (kd * kd).sum(-1), q_w.to(cuda), k_w.to(cuda), 1e-6)
+    assert torch.allclose(qd.cpu(), want_q, atol=5e-5, rtol=5e-5), (qd.cpu() - want_q).abs().max()
+    assert torch.allclose(kd.cpu(), want_k, atol=5e-5, rtol=5e-5), (kd.cpu() - want_k).abs().max()
+    # the unrotated pairs are exactly the normalised inputs
+    inv = torch.rsqrt((q * q).sum(-1) / k + 1e-6)[..., None]
+    assert torch.allclose(qd.cpu()[..., k // 4: k // 2], (q * (inv * q_w))[..., k // 4: k // 2], atol=1e-6, rtol=1e-6)
