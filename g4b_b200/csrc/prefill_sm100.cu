@@ -85,6 +85,12 @@ struct PrefillParams {
   int64_t time_stride, phase_stride, bt_s0, bt_s1;
   int page_shift, num_pages, max_pages;      // paged mode
   int B, H, G, Tq, T;
+  // split-KV for chunks that would leave most SMs idle: work items are (item, key range),
+  // un-normalised (acc, l, m) go to the caller's partial buffers and a merge launch follows
+  float* po; float* pl; float* pm;
+  int64_t po_s[4], pl_s[4], pm_s[4];         // strides of s, b, h, t (elements; d stride 1)
+  int n_splits;
+  FastDiv by_splits;
   const float* q_f32;                        // q given as f32 (the engine's scratchpad type): converted on load
   int64_t q_s0, q_s1, q_s2;                  // its strides for b, h, t (elements)
   int n_q_tiles;                             // ceil(Tq / 128)
@@ -150,8 +156,10 @@ __device__ long long g_item_trace[128][16];
   const bool geo_active = act_nx_;                                                                    \
   fetch_item(((round) + 1) * n_workers < n_items ? item_of_round((round) + 1) : -1, time_nx_, act_nx_)
 #define G4B_ITEM_GEOMETRY(item)                                                                      \
-  const int level_ = p.by_units.div(item);                                                            \
-  const int unit_ = (item) - level_ * units_per_level;                                                \
+  const int item_ = kSplit ? p.by_splits.div(item) : (item);                                          \
+  const int split_ = kSplit ? (item) - item_ * p.n_splits : 0;                                        \
+  const int level_ = p.by_units.div(item_);                                                           \
+  const int unit_ = item_ - level_ * units_per_level;                                                 \
   const int q_tile = p.n_q_tiles - 1 - level_;                                                        \
   const int bh = kPair ? 2 * unit_ + (int)rank : unit_;                                               \
   const int b = p.by_H.div(bh), h = bh - b * p.H;                                                     \
@@ -172,9 +180,13 @@ __device__ long long g_item_trace[128][16];
   /* uniform over the item: some row may see fewer than 64 keys in all */                             \
   const bool few_keys = qpos_min - win_lo < 64 || (p.sliding_window > 0 && p.sliding_window < 64);    \
   const bool precise = PackT<T>::kSplitP && few_keys;                                                 \
-  const int tile_lo = key_lo / kBN;                                                                   \
-  const int n_tiles = (active && key_hi > key_lo) ? (key_hi + kBN - 1) / kBN - tile_lo : 0;           \
-  (void)ring_start; (void)precise; (void)few_keys; (void)g; (void)h; (void)tile_lo; (void)qpos_max
+  const int tile_lo_all_ = key_lo / kBN;                                                              \
+  const int n_tiles_all_ = (active && key_hi > key_lo) ? (key_hi + kBN - 1) / kBN - tile_lo_all_ : 0; \
+  /* this split's share of the item's key tiles */                                                    \
+  const int tps_ = kSplit ? p.by_splits.div(n_tiles_all_ + p.n_splits - 1) : n_tiles_all_;            \
+  const int tile_lo = tile_lo_all_ + split_ * tps_;                                                   \
+  const int n_tiles = max(0, min(tps_, n_tiles_all_ - split_ * tps_));                                \
+  (void)ring_start; (void)precise; (void)few_keys; (void)g; (void)h; (void)tile_lo; (void)qpos_max; (void)split_
 
 // Where logical key `key` of this (slot, kv head) lives, or null if it is outside the
 // context (ring buffer or page pool).
@@ -264,7 +276,7 @@ template <> struct PackT<__half> {
 //   each CTA stages only half of every tile (K: half the keys, V: half the head dim), so the
 //   ring covers twice the time and Q.K^T reads 96 instead of 128 bytes of shared memory per
 //   cycle -- the two things that starve the single-CTA form.
-template <typename T, bool kPair, bool kStageOut, bool kShortItems>
+template <typename T, bool kPair, bool kStageOut, bool kShortItems, bool kSplit>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                const __grid_constant__ CUtensorMap v_map, PrefillParams p) {
@@ -284,7 +296,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
   // runs ahead into the next item while the current one drains.  Round r hands item
   // r * workers + w to worker w, alternating the direction so heavy and light items pair up.
   const int units_per_level = kPair ? (p.B * p.H) / 2 : p.B * p.H;   // (slot, head[s]) units per query tile
-  const int n_items = p.n_q_tiles * units_per_level;
+  const int n_items = p.n_q_tiles * units_per_level * (kSplit ? p.n_splits : 1);
   const int n_workers = kPair ? (int)gridDim.x / 2 : (int)gridDim.x;
   const int worker = kPair ? (int)blockIdx.x / 2 : (int)blockIdx.x;
   auto item_of_round = [&](int round) -> int {
@@ -294,7 +306,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
   };
   auto fetch_item = [&](int item, int& time_o, bool& act_o) {
     if (item < 0) { time_o = 0; act_o = false; return; }
-    const int unit_ = p.by_units.mod(item);
+    const int item_ = kSplit ? p.by_splits.div(item) : item;
+    const int unit_ = p.by_units.mod(item_);
     const int b_ = p.by_H.div(kPair ? 2 * unit_ + (int)rank : unit_);
     act_o = p.user_phase == nullptr || p.user_phase[b_ * p.phase_stride] == (uint8_t)p.phase;
     time_o = p.time_dim_sizes[b_ * p.time_stride];
@@ -934,6 +947,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     if (item < 0) continue;
     G4B_ITEM_GEOMETRY(item);
     if (n_tiles <= 0) {
+      if constexpr (kSplit) {
+        // an empty key range: the merge skips a partial with m = -inf, l = 0 (fa2.py:466-472)
+        if (active && half == 0 && r < rows_valid) {
+          p.pl[split_ * p.pl_s[0] + b * p.pl_s[1] + h * p.pl_s[2] + (int64_t)(m0 + r) * p.pl_s[3]] = 0.f;
+          p.pm[split_ * p.pm_s[0] + b * p.pm_s[1] + h * p.pm_s[2] + (int64_t)(m0 + r) * p.pm_s[3]] = -INFINITY;
+        }
+        continue;
+      }
       // no visible key for any row of this tile: the output rows are defined as zero
       if (active && half == 0 && r < rows_valid) {
         const int64_t off = b * p.o_s0 + h * p.o_s1 + (int64_t)(m0 + r) * p.o_s2;
@@ -1190,7 +1211,29 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       const bool row_ok = r < rows_valid;
       const uint64_t pol_o = ptx::policy_evict_first();   // the output is not read again here
       const int64_t off = b * p.o_s0 + h * p.o_s1 + (int64_t)(m0 + r) * p.o_s2 + half * 128;
-      if (p.o_dtype == G4B_F32) {
+      if constexpr (kSplit) {
+        // split-KV: the un-normalised accumulator, the row sum and the reference maximum (log2
+        // units) in the reference's partial format (fa2.py:438-472)
+        float* dst_row = p.po + split_ * p.po_s[0] + b * p.po_s[1] + h * p.po_s[2] + (int64_t)(m0 + r) * p.po_s[3] + half * 128;
+#pragma unroll 1
+        for (int c4 = 0; c4 < 4; ++c4) {
+          uint32_t ov[32];
+          ptx::tmem_ld32(trow + kColO + half * 128 + c4 * 32, ov);
+          ptx::tc_wait_ld();
+          if (row_ok) {
+            float4* dst = reinterpret_cast<float4*>(dst_row + c4 * 32);
+#pragma unroll
+            for (int i = 0; i < 8; ++i) dst[i] = make_float4(__uint_as_float(ov[4 * i]), __uint_as_float(ov[4 * i + 1]),
+                                                             __uint_as_float(ov[4 * i + 2]), __uint_as_float(ov[4 * i + 3]));
+          }
+        }
+        ptx::tc_fence_before();
+        arrive_issuer(issuer_bar(&bars->o_free));
+        if (row_ok && half == 0) {
+          p.pl[split_ * p.pl_s[0] + b * p.pl_s[1] + h * p.pl_s[2] + (int64_t)(m0 + r) * p.pl_s[3]] = l_run;
+          p.pm[split_ * p.pm_s[0] + b * p.pm_s[1] + h * p.pm_s[2] + (int64_t)(m0 + r) * p.pm_s[3]] = m_used;
+        }
+      } else if (p.o_dtype == G4B_F32) {
 #pragma unroll 1
         for (int c4 = 0; c4 < 4; ++c4) {
           uint32_t ov[32];
@@ -1321,14 +1364,14 @@ static int encode_map(CUtensorMap* map, int dtype, int rank, void* base, const u
   return G4B_OK;
 }
 
-template <typename T, bool kPair, bool kStageOut, bool kShortItems>
+template <typename T, bool kPair, bool kStageOut, bool kShortItems, bool kSplit>
 static int launch_variant(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const PrefillParams& p,
                           dim3 grid, cudaStream_t st) {
   static bool attr_set[64] = {false};
   int dev = 0;
   G4B_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    G4B_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<T, kPair, kStageOut, kShortItems>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    G4B_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<T, kPair, kStageOut, kShortItems, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -1343,17 +1386,21 @@ static int launch_variant(const CUtensorMap& qm, const CUtensorMap& km, const CU
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  G4B_CUDA_CHECK(cudaLaunchKernelEx(&cfg, prefill_kernel<T, kPair, kStageOut, kShortItems>, qm, km, vm, p));
+  G4B_CUDA_CHECK(cudaLaunchKernelEx(&cfg, prefill_kernel<T, kPair, kStageOut, kShortItems, kSplit>, qm, km, vm, p));
   return G4B_OK;
 }
 
 template <typename T>
 static int launch_typed(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const PrefillParams& p,
-                        dim3 grid, bool pair, bool stage_out, bool short_items, cudaStream_t st) {
-  if (pair && stage_out && short_items) return launch_variant<T, true, true, true>(qm, km, vm, p, grid, st);
-  if (pair && stage_out) return launch_variant<T, true, true, false>(qm, km, vm, p, grid, st);
-  if (pair) return launch_variant<T, true, false, false>(qm, km, vm, p, grid, st);
-  return launch_variant<T, false, false, false>(qm, km, vm, p, grid, st);
+                        dim3 grid, bool pair, bool stage_out, bool short_items, bool split, cudaStream_t st) {
+  if (split) {
+    if (pair) return launch_variant<T, true, false, false, true>(qm, km, vm, p, grid, st);
+    return launch_variant<T, false, false, false, true>(qm, km, vm, p, grid, st);
+  }
+  if (pair && stage_out && short_items) return launch_variant<T, true, true, true, false>(qm, km, vm, p, grid, st);
+  if (pair && stage_out) return launch_variant<T, true, true, false, false>(qm, km, vm, p, grid, st);
+  if (pair) return launch_variant<T, true, false, false, false>(qm, km, vm, p, grid, st);
+  return launch_variant<T, false, false, false, false>(qm, km, vm, p, grid, st);
 }
 
 }  // namespace
@@ -1459,18 +1506,60 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   G4B_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= 64) return fail(G4B_ERR_CUDA, "device index out of range");
   if (sm_count[dev] == 0) G4B_CUDA_CHECK(cudaDeviceGetAttribute(&sm_count[dev], cudaDevAttrMultiProcessorCount, dev));
-  const int64_t n_items = n_q_tiles * (pair ? (B * H) / 2 : B * H);
+  const int64_t base_items = n_q_tiles * (pair ? (B * H) / 2 : B * H);
   int64_t workers = pair ? sm_count[dev] / 2 : sm_count[dev];
   if (workers < 1) workers = 1;
+  // Split-KV: a chunk of a few hundred query rows is a handful of work items however long the
+  // context is (B1 H16 Tq256 over 65536 keys: 16 CTA pairs busy for 512 tiles each, 58 idle).
+  // With the caller's partial buffers at hand the key range of every item is cut into as many
+  // pieces as it takes to occupy the workers, at least four tiles each; a merge launch follows.
+  p.n_splits = 1;
+  const bool have_partials = a.partial_o.ptr != nullptr && a.partial_l.ptr != nullptr && a.partial_m.ptr != nullptr;
+  if (have_partials) {
+    int64_t want = a.num_kv_splits > 0 ? a.num_kv_splits : (base_items * 2 <= workers ? workers / base_items : 1);
+    const int64_t keys_bound = a.sliding_window > 0 ? a.sliding_window + kBM : a.ctx_window_size;
+    const int64_t tiles_bound = (keys_bound + kBN - 1) / kBN;
+    if (a.num_kv_splits <= 0 && want > tiles_bound / 4) want = tiles_bound / 4;
+    if (want > a.partial_o.shape[0]) want = a.partial_o.shape[0];
+    if (want > a.partial_l.shape[0]) want = a.partial_l.shape[0];
+    if (want > a.partial_m.shape[0]) want = a.partial_m.shape[0];
+    if (want > 1024) want = 1024;
+    if (want > 1) {
+      if (a.partial_o.dtype != G4B_F32 || a.partial_l.dtype != G4B_F32 || a.partial_m.dtype != G4B_F32)
+        return fail(G4B_ERR_BAD_DTYPE, "prefill: split-KV partials must be f32");
+      if (a.partial_o.ndim != 5 || a.partial_l.ndim != 4 || a.partial_m.ndim != 4)
+        return fail(G4B_ERR_BAD_ARG, "prefill: partial_o must be [S,B,H,Tq,D], partial_l/m [S,B,H,Tq]");
+      for (int i = 0; i < 4; ++i) {
+        if (a.partial_o.shape[i + 1] != a.q.shape[i]) return fail(G4B_ERR_BAD_ARG, "prefill: partial_o shape must be [S,B,H,Tq,D]");
+        if (i < 3 && (a.partial_l.shape[i + 1] != a.q.shape[i] || a.partial_m.shape[i + 1] != a.q.shape[i]))
+          return fail(G4B_ERR_BAD_ARG, "prefill: partial_l/partial_m shape must be [S,B,H,Tq]");
+        if (a.partial_o.stride[i] % 4 != 0) return fail(G4B_ERR_BAD_STRIDE, "prefill: partial_o strides must be multiples of 16 bytes");
+      }
+      if (a.partial_o.stride[4] != 1 || (((uintptr_t)a.partial_o.ptr) & 15))
+        return fail(G4B_ERR_BAD_STRIDE, "prefill: partial_o rows must be contiguous and 16-byte aligned");
+      p.n_splits = (int)want;
+      p.by_splits.set((uint32_t)want);
+      p.po = (float*)a.partial_o.ptr; p.pl = (float*)a.partial_l.ptr; p.pm = (float*)a.partial_m.ptr;
+      for (int i = 0; i < 4; ++i) { p.po_s[i] = a.partial_o.stride[i]; p.pl_s[i] = a.partial_l.stride[i]; p.pm_s[i] = a.partial_m.stride[i]; }
+    }
+  }
+  const int64_t n_items = base_items * p.n_splits;
+  if (n_items > 0x7fffffffLL) return fail(G4B_ERR_UNSUPPORTED, "prefill: too many work items");
   if (workers > n_items) workers = n_items;
   dim3 grid((unsigned)(pair ? 2 * workers : workers), 1, 1);
+  const bool stage = stage_out && p.n_splits == 1;   // partials are stored directly
   if (q_f32) {
     qm = km;   // never used by the kernel: q is converted on load
     p.q_f32 = (const float*)a.q.ptr;
     p.q_s0 = a.q.stride[0]; p.q_s1 = a.q.stride[1]; p.q_s2 = a.q.stride[2];
   }
-  if (a.k_cache.dtype == G4B_BF16) return launch_typed<__nv_bfloat16>(qm, km, vm, p, grid, pair, stage_out, short_items, st);
-  return launch_typed<__half>(qm, km, vm, p, grid, pair, stage_out, short_items, st);
+  if (a.k_cache.dtype == G4B_BF16) rc = launch_typed<__nv_bfloat16>(qm, km, vm, p, grid, pair, stage, short_items, p.n_splits > 1, st);
+  else rc = launch_typed<__half>(qm, km, vm, p, grid, pair, stage, short_items, p.n_splits > 1, st);
+  if (rc != G4B_OK || p.n_splits == 1) return rc;
+  G4bCombineArgs c{};
+  c.partial_o = a.partial_o; c.partial_l = a.partial_l; c.partial_m = a.partial_m; c.o = a.o;
+  c.user_phase = a.user_phase; c.num_splits = p.n_splits; c.phase = a.phase;
+  return launch_combine(c, st);
 }
 
 }  // namespace g4b

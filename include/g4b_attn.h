@@ -106,7 +106,11 @@ typedef struct G4bAttnArgs {
 int g4b_flash_attention(const G4bAttnArgs* args, void* cuda_stream);
 
 /* replaces the launch of _attn_kernel for Tq > 1 (fa2.py:256-480, 672-690):
- * tcgen05 / TMEM / TMA flash-attention forward, head dim 256, f16 or bf16. */
+ * tcgen05 / TMEM / TMA flash-attention forward, head dim 256, f16 or bf16 caches, q and o in
+ * the cache dtype or f32.  If the partial triple is given (f32, [S,B,H,Tq,D] / [S,B,H,Tq]) and
+ * the chunk has too few (slot, head, 128-row tile) units to occupy the GPU, every unit's key
+ * range is split over up to S pieces (num_kv_splits forces a count) and merged by a second
+ * launch; the reference splits in the decode phase only (fa2.py:201-212). */
 int g4b_attn_prefill(const G4bAttnArgs* args, void* cuda_stream);
 
 /* replaces the launch of _attn_kernel for Tq == 1 (fa2.py:256-480 with

@@ -278,3 +278,60 @@ def test_prefill_accepts_f32_q_and_o(cuda, dtype, B, H, G, Tq, T):
     assert_close(got, want, "f32 q, f32 o")
     got16 = run(case32, cuda, o_dtype=dtype)
     assert_close(got16, want, "f32 q, 16-bit o")
+
+
+def run_split(case, cuda, *, splits, max_splits=8, sliding_window=None, stage=fa2.STAGE_CAUSAL, o_dtype=None):
+    q_phys, k, v, time = (case[n].to(cuda) for n in ("q_phys", "k", "v", "time"))
+    B, Tq, H, D = q_phys.shape
+    o_phys = torch.zeros(B, Tq, H, D, dtype=o_dtype or q_phys.dtype, device=cuda)
+    po = torch.full((max_splits, B, H, Tq, D), float("nan"), device=cuda)      # whatever is read must have been written
+    pl = torch.full((max_splits, B, H, Tq), float("nan"), device=cuda)
+    pm = torch.full((max_splits, B, H, Tq), float("nan"), device=cuda)
+    fa2.flash_attention(q_phys.permute(0, 2, 1, 3), k, v, o_phys.permute(0, 2, 1, 3), time, None, case["ctx_window"], 1,
+                        po, pl, pm, stage=stage, scale=1 / 16, sliding_window=sliding_window, num_kv_splits=splits)
+    return o_phys.permute(0, 2, 1, 3).cpu(), (po, pl, pm)
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("splits", [None, 2, 5, 8])
+def test_prefill_split_kv_chunk(cuda, dtype, splits):
+    """A chunk of 200 rows at the end of contexts of a few thousand keys, with the key range
+    of every work item cut into pieces (forced counts, and the count the launcher picks when it
+    is given partial buffers): same answer as the oracle, and as the unsplit kernel."""
+    case = make_ring_case(80, B=2, H=8, G=2, Tq=200, T=3000, dtype=dtype, times=[3000 + 40, 2222])
+    want = oracle(case)
+    got, (po, pl, pm) = run_split(case, cuda, splits=splits)
+    assert_close(got, want, f"split-KV prefill, {splits} splits")
+    assert_close(got, run(case, cuda).float(), "split vs unsplit")
+
+
+def test_prefill_split_kv_empty_ranges_windows_and_f32(cuda):
+    """More pieces than some items have tiles (early query tiles of a causal prefill see one or
+    two tiles: their later pieces are empty), a sliding window, STAGE_FULL, f32 output, and a
+    slot off phase whose rows must keep their content."""
+    case = make_ring_case(81, B=2, H=4, G=2, Tq=640, T=640, dtype=torch.bfloat16, times=[640, 640])
+    for kw in (dict(), dict(sliding_window=200), dict(stage=fa2.STAGE_FULL)):
+        got, _ = run_split(case, cuda, splits=4, o_dtype=torch.float32, **kw)
+        assert_close(got, oracle(case, **kw), f"split-KV {kw}")
+    q_phys, k, v, time = (case[n].to(cuda) for n in ("q_phys", "k", "v", "time"))
+    o = torch.full((2, 640, 4, 256), 3.0, dtype=torch.bfloat16, device=cuda)
+    ph = torch.tensor([1, 2], dtype=torch.uint8, device=cuda)
+    po = torch.zeros(4, 2, 4, 640, 256, device=cuda); pl = torch.zeros(4, 2, 4, 640, device=cuda); pm = torch.zeros(4, 2, 4, 640, device=cuda)
+    fa2.flash_attention(q_phys.permute(0, 2, 1, 3), k, v, o.permute(0, 2, 1, 3), time, ph, 640, 1, po, pl, pm, scale=1 / 16,
+                        num_kv_splits=4)
+    assert_close(o[0].permute(1, 0, 2).cpu(), oracle(case)[0], "slot in phase")
+    assert (o[1] == 3.0).all()
+
+
+def test_prefill_split_kv_paged_long_context(cuda):
+    """The shape split-KV is for: one request, 256 new rows, tens of thousands of keys in pages."""
+    case = make_paged_prefill_case(82, times=[20000], Tq=256, H=16, G=4, dtype=torch.float16)
+    q_phys = case["q_phys"].to(cuda)
+    o_phys = torch.zeros_like(q_phys)
+    S = 8
+    po = torch.empty(S, 1, 16, 256, 256, device=cuda); pl = torch.empty(S, 1, 16, 256, device=cuda); pm = torch.empty(S, 1, 16, 256, device=cuda)
+    fa2.flash_attention(q_phys.permute(0, 2, 1, 3), case["k_pool"].to(cuda), case["v_pool"].to(cuda), o_phys.permute(0, 2, 1, 3),
+                        case["time"].to(cuda), None, case["max_len"], 1, po, pl, pm, scale=1 / 16,
+                        block_tables=case["block_tables"].to(cuda), page_size=case["page_size"])
+    assert_close(o_phys.permute(0, 2, 1, 3), oracle_paged_prefill(case), "paged split-KV prefill")
+    assert torch.isfinite(pm[:4]).any()      # the launcher did split (16 pair items on 74 workers)
