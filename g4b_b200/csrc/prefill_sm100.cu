@@ -1524,9 +1524,12 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
     if (want > a.partial_l.shape[0]) want = a.partial_l.shape[0];
     if (want > a.partial_m.shape[0]) want = a.partial_m.shape[0];
     if (want > 1024) want = 1024;
+    // buffers of another type (the engine's decode workspace is f16) are simply not used,
+    // unless the caller asked for a split count
+    const bool f32_partials = a.partial_o.dtype == G4B_F32 && a.partial_l.dtype == G4B_F32 && a.partial_m.dtype == G4B_F32;
+    if (!f32_partials && a.num_kv_splits <= 0) want = 1;
     if (want > 1) {
-      if (a.partial_o.dtype != G4B_F32 || a.partial_l.dtype != G4B_F32 || a.partial_m.dtype != G4B_F32)
-        return fail(G4B_ERR_BAD_DTYPE, "prefill: split-KV partials must be f32");
+      if (!f32_partials) return fail(G4B_ERR_BAD_DTYPE, "prefill: split-KV partials must be f32");
       if (a.partial_o.ndim != 5 || a.partial_l.ndim != 4 || a.partial_m.ndim != 4)
         return fail(G4B_ERR_BAD_ARG, "prefill: partial_o must be [S,B,H,Tq,D], partial_l/m [S,B,H,Tq]");
       for (int i = 0; i < 4; ++i) {

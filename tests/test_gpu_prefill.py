@@ -335,3 +335,19 @@ def test_prefill_split_kv_paged_long_context(cuda):
                         block_tables=case["block_tables"].to(cuda), page_size=case["page_size"])
     assert_close(o_phys.permute(0, 2, 1, 3), oracle_paged_prefill(case), "paged split-KV prefill")
     assert torch.isfinite(pm[:4]).any()      # the launcher did split (16 pair items on 74 workers)
+
+
+def test_prefill_ignores_f16_partials(cuda):
+    """The engine's decode workspace is f16 (gemma4e.py:819): handed to a prefill call it is
+    left alone and the chunk runs unsplit; asking for a split count with it is an error."""
+    case = make_ring_case(83, B=1, H=8, G=2, Tq=128, T=2048, dtype=torch.float16)
+    q_phys, k, v, time = (case[n].to(cuda) for n in ("q_phys", "k", "v", "time"))
+    o = torch.zeros_like(q_phys)
+    po = torch.full((4, 1, 8, 128, 256), 9.0, dtype=torch.float16, device=cuda)
+    pl = torch.full((4, 1, 8, 128), 9.0, device=cuda); pm = torch.full((4, 1, 8, 128), 9.0, device=cuda)
+    fa2.flash_attention(q_phys.permute(0, 2, 1, 3), k, v, o.permute(0, 2, 1, 3), time, None, 2048, 1, po, pl, pm, scale=1 / 16)
+    assert_close(o.permute(0, 2, 1, 3), oracle(case), "unsplit with f16 partials present")
+    assert (po == 9.0).all() and (pl == 9.0).all()
+    with pytest.raises(ValueError):
+        fa2.flash_attention(q_phys.permute(0, 2, 1, 3), k, v, o.permute(0, 2, 1, 3), time, None, 2048, 1, po, pl, pm,
+                            scale=1 / 16, num_kv_splits=4)
