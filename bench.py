@@ -9,6 +9,8 @@ Prints ONE JSON line.  Workloads (shapes of the five benchmark configurations):
                     one step = append the new token's K/V + attention
     decode_long     1 sequence of 131072 tokens, bf16 paged KV; with N > 1 the KV range is
                     split across GPUs and the (acc, l, m) partials are merged across them
+    prefill_chunk   256 new rows of one request over 65536 cached keys (split-KV over the SMs;
+                    --kv-splits -1 runs it unsplit)
     rope_append     the launch before attention: norm + rotary embedding + KV append, GB/s
 A step is one pass of the hot path over one batch.  ``value`` has inputs resident in HBM;
 ``e2e`` goes through the public Python operators with pinned host buffers, host<->device
@@ -296,6 +298,66 @@ class PrefillWorkload:
         return flops / dt / 1e12, f"{done} of {self.B} batch items, first {S} tokens, fp32, 1024-query blocks"
 
 
+class PrefillChunkWorkload:
+    """One request's prefill chunk late in a long context: 256 new rows attend to 65536 cached
+    keys (B1 H16 G4 D256 bf16, ring cache, causal) -- the shape of the reference's own
+    prefill_t256_w65536 comparison case.  Only 32 (head, 128-row tile) units: the kernel splits
+    their key ranges over the SMs (partial buffers given) and merges."""
+
+    variants = 1
+
+    def __init__(self, name, dev, seed, split=True):
+        from g4b_b200.kernels import fa2
+
+        self.fa2, self.name, self.dtype = fa2, name, torch.bfloat16
+        B, Hc, Gc, t, T = 1, 16, 4, 256, 65536
+        self.B, self.t, self.T, self.Hc = B, t, T, Hc
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        self.h_q = torch.randn(B, t, Hc, D, generator=gen).to(self.dtype).pin_memory()
+        self.h_o = torch.empty(B, t, Hc, D, dtype=self.dtype).pin_memory()
+        gdev = torch.Generator(device=dev).manual_seed(seed + 1)
+        self.k = torch.randn(B, Gc, T, D, generator=gdev, device=dev, dtype=torch.float32).to(self.dtype)
+        self.v = torch.randn(B, Gc, T, D, generator=gdev, device=dev, dtype=torch.float32).to(self.dtype)
+        self.q = self.h_q.to(dev)
+        self.o = torch.empty_like(self.q)
+        self.time = torch.full((B,), T, dtype=torch.int32, device=dev)
+        S = 16 if split else 0
+        self.po = torch.empty(S, B, Hc, t, D, device=dev) if split else None
+        self.pl = torch.empty(S, B, Hc, t, device=dev) if split else None
+        self.pm = torch.empty(S, B, Hc, t, device=dev) if split else None
+        self.units = 4.0 * B * Hc * D * (t * (T - t) + t * (t + 1) / 2)
+        self.metric, self.unit, self.bound = "prefill_attn_tflops", "TFLOP/s", "tensor"
+        self.launches_per_step = 2 if split else 1
+        self.traffic = None
+        self.h2d, self.d2h = self.h_q.numel() * 2, self.h_o.numel() * 2
+        self.config = {"workload": name, "batch_per_gpu": B, "chunk_rows": t, "context": T, "q_heads": Hc, "kv_heads": Gc,
+                       "head_dim": D, "scale": SCALE, "split_kv": bool(split),
+                       "l2": "K/V (%d MB) larger than L2" % ((self.k.numel() + self.v.numel()) * 2 >> 20)}
+
+    def step(self, i=0):
+        self.fa2.flash_attention(self.q.permute(0, 2, 1, 3), self.k, self.v, self.o.permute(0, 2, 1, 3), self.time, None,
+                                 self.T, self.fa2.PHASE_PREFILL, self.po, self.pl, self.pm, scale=SCALE)
+
+    def e2e_step(self, i=0):
+        self.q.copy_(self.h_q, non_blocking=True)
+        self.step(i)
+        self.h_o.copy_(self.o, non_blocking=True)
+
+    def value_from(self, ms_per_step, world):
+        return self.units * world / (ms_per_step * 1e-3) / 1e12
+
+    def cpu_sample(self, budget_s=15.0):
+        from oracle import attention_oracle as orc
+
+        n = 32     # rows of the chunk
+        q = self.h_q[0, :n].float().permute(1, 0, 2)
+        k, v = self.k[0].float().cpu(), self.v[0].float().cpu()
+        t0 = time.perf_counter()
+        orc.attention_core(q, k[:, : self.T - self.t + n], v[:, : self.T - self.t + n], scale=SCALE, causal=True)
+        dt = time.perf_counter() - t0
+        return 4.0 * self.Hc * D * n * (self.T - self.t + n / 2) / dt / 1e12, f"{n} of {self.t} chunk rows, all heads, fp32"
+
+
 class RopeAppendWorkload:
     """The launch right before attention on a prefill chunk: per-head RMS norm + rotary
     embedding of q and k, V norm, append of k and v to the ring caches, q out in bf16.  fp32
@@ -525,6 +587,8 @@ def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_s
     seeds = {"prefill_causal": 1, "prefill_swa": 2, "decode_paged": 3, "decode_long": 4, "rope_append": 5}
     if name == "rope_append":
         return RopeAppendWorkload(name, dev, seeds[name] + 100 * rank)
+    if name == "prefill_chunk":
+        return PrefillChunkWorkload(name, dev, 6 + 100 * rank, split=kv_splits >= 0)
     if name.startswith("prefill"):
         return PrefillWorkload(name, dev, seeds[name] + 100 * rank)
     return DecodeWorkload(name, dev, seeds[name] + (0 if name == "decode_long" else 100 * rank), rank, world,
@@ -701,11 +765,11 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="prefill_causal",
-                    choices=["prefill_causal", "prefill_swa", "decode_paged", "decode_long", "rope_append"])
+                    choices=["prefill_causal", "prefill_swa", "prefill_chunk", "decode_paged", "decode_long", "rope_append"])
     ap.add_argument("--sequences", type=int, default=256,
                     help="decode_paged only: number of sequences (256 = the benchmark configuration; "
                          "smaller values are for profiler captures)")
-    ap.add_argument("--kv-splits", type=int, default=0, help="decode workloads: split count (0 = the workload's default)")
+    ap.add_argument("--kv-splits", type=int, default=0, help="decode workloads: split count (0 = the workload's default); prefill_chunk: -1 = no split-KV")
     ap.add_argument("--nccl-gather", action="store_true",
                     help="decode_long on N > 1 GPUs: all-gather the partials with NCCL and merge in a second launch "
                          "instead of the one-kernel exchange over peer memory")
