@@ -713,7 +713,7 @@ def run_reference(args):
     from oracle import attention_oracle as orc
 
     gen = torch.Generator().manual_seed(1)
-    if name.startswith("prefill"):
+    if name in ("prefill_causal", "prefill_swa"):
         # bounded sample: ~1 s of host work per step so K + W steps end within minutes
         S, window = (4096, None) if name == "prefill_causal" else (8192, 512)
         q = torch.randn(H, S, D, generator=gen).to(torch.bfloat16).float()
@@ -723,6 +723,33 @@ def run_reference(args):
         fn = lambda: orc.attention_core(q, k, v, scale=SCALE, causal=True, sliding_window=window)
         metric, unit, div = "prefill_attn_tflops", "TFLOP/s", 1e12
         sample = f"1 batch item, {S} tokens, all {H} heads per step, fp32, 1024-query blocks"
+        full_b, full_s = (4, 8192) if name == "prefill_causal" else (2, 32768)
+        config = {"workload": name, "batch_per_gpu": full_b, "seq_len": full_s, "q_heads": H, "kv_heads": G,
+                  "head_dim": D, "window": window, "scale": SCALE}
+    elif name == "prefill_chunk":
+        Hc, Gc, t, T, n = 16, 4, 256, 65536, 32
+        q = torch.randn(Hc, n, D, generator=gen).to(torch.bfloat16).float()
+        k = torch.randn(Gc, T - t + n, D, generator=gen).to(torch.bfloat16).float()
+        v = torch.randn(Gc, T - t + n, D, generator=gen).to(torch.bfloat16).float()
+        units = 4.0 * Hc * D * n * (T - t + n / 2)
+        fn = lambda: orc.attention_core(q, k, v, scale=SCALE, causal=True)
+        metric, unit, div = "prefill_attn_tflops", "TFLOP/s", 1e12
+        sample = f"{n} of {t} chunk rows over {T - t + n} keys, all {Hc} heads per step, fp32"
+        config = {"workload": name, "batch_per_gpu": 1, "chunk_rows": t, "context": T, "q_heads": Hc, "kv_heads": Gc,
+                  "head_dim": D, "scale": SCALE}
+    elif name == "rope_append":
+        n = 1024
+        q, k, v = (torch.randn(1, h, n, D, generator=gen) for h in (H, G, G))
+        qw, kw = 1 + 0.1 * torch.randn(D, generator=gen), 1 + 0.1 * torch.randn(D, generator=gen)
+        freqs = 1.0 / (10000.0 ** (torch.arange(0, D, 2) / D))
+        kc, vc = torch.zeros(1, G, n, D, dtype=torch.bfloat16), torch.zeros(1, G, n, D, dtype=torch.bfloat16)
+        off = torch.zeros(1, dtype=torch.int32)
+        units = float(n * (H + 2 * G) * D * 6)
+        fn = lambda: orc.rope_norm_append(q, k, v, freqs, off, kc, vc, 1e-6, q_rmsnorm_w=qw, k_rmsnorm_w=kw)
+        metric, unit, div = "rope_append_hbm_gbs", "GB/s", 1e9
+        sample = f"{n} tokens of 1 batch item per step, torch fp32"
+        config = {"workload": name, "batch_per_gpu": 4, "tokens": 8192, "q_heads": H, "kv_heads": G, "head_dim": D,
+                  "in_dtype": "f32", "out_dtype": "bf16"}
     else:
         L = 32768 if name == "decode_paged" else 131072
         n_pages = L // PAGE
@@ -739,6 +766,8 @@ def run_reference(args):
 
         metric, unit, div = "decode_attn_hbm_gbs", "GB/s", 1e9
         sample = f"1 sequence of {L} tokens per step, page gather + fp32 attention"
+        config = {"workload": name, "sequences": 256 if name == "decode_paged" else 1, "page_size": PAGE,
+                  "kv_dtype": "float16" if name == "decode_paged" else "bfloat16", "scale": SCALE}
     for _ in range(args.warmup):
         fn()
     t0 = time.perf_counter()
@@ -750,7 +779,7 @@ def run_reference(args):
         "impl": "reference", "metric": metric, "value": round(value, 5), "unit": unit, "n_gpus": args.gpus,
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded N(0,1))",
-        "config": {"workload": name},
+        "config": config,
         "cpu_baseline": {"value": round(value, 5), "unit": unit, "cores": torch.get_num_threads(), "kind": "port",
                          "sample": sample},
         "e2e": {"value": round(value, 5), "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
