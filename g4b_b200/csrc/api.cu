@@ -129,7 +129,23 @@ static int max_partial_splits(const G4bAttnArgs& a) {
 static int resolve_splits(const G4bAttnArgs& a) {
   const int max_splits = max_partial_splits(a);
   if (a.num_kv_splits > 0) return a.num_kv_splits < max_splits ? a.num_kv_splits : max_splits;
-  return g4b_select_kv_splits(a.ctx_window_size, max_splits, a.phase, (int)a.q.shape[2]);
+  int s = g4b_select_kv_splits(a.ctx_window_size, max_splits, a.phase, (int)a.q.shape[2]);
+  // The reference's table only looks at the context length (fa2.py:201-212).  A decode CTA is
+  // one (slot, kv head, split) and this GPU holds 2 x 148 of them: with few slots the table
+  // leaves most SMs idle (8 slots x 4 kv heads at 4096 keys: 32 CTAs).  Where the caller's
+  // workspace has room, split further, down to 256 keys per split.  Static in the shapes, like
+  // the reference's choice, so the launch geometry stays capturable.
+  if (a.q.shape[2] == 1 && s < max_splits && a.q.ndim == 4 && a.k_cache.ndim == 4) {
+    const int64_t units = a.q.shape[0] * a.k_cache.shape[1];
+    if (units > 0 && units * s < 296) {
+      int64_t want = (296 + units - 1) / units;
+      const int64_t by_len = a.ctx_window_size / 256;
+      if (want > by_len) want = by_len;
+      if (want > max_splits) want = max_splits;
+      if (want > s) s = (int)want;
+    }
+  }
+  return s;
 }
 
 }  // namespace g4b
