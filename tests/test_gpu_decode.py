@@ -203,3 +203,16 @@ def test_decode_one_long_sequence_full_size(cuda):
     o = torch.zeros(1, 8, 1, 256, dtype=torch.bfloat16, device=cuda)
     ex.combine(po, pl, pm, o, 148)
     assert_close(o[0].cpu(), want, "exchange merge of 148 splits")
+
+
+@pytest.mark.parametrize("H,G", [(16, 1), (12, 1), (9, 3)])
+def test_single_token_with_more_than_8_heads_per_kv_head(cuda, H, G):
+    """Groups wider than the decode kernel's 8 query heads per kv head (and head counts that
+    rule out the CTA-pair form) still answer at Tq = 1: the call takes the prefill kernel."""
+    case = make_ring_case(37 + H, B=3, H=H, G=G, Tq=1, T=700, dtype=torch.bfloat16, times=[700, 717, 5])
+    q, k, v, time = (case[n].to(cuda) for n in ("q", "k", "v", "time"))
+    o = torch.zeros_like(q)
+    fa2.flash_attention(q, k, v, o, time, None, 700, fa2.PHASE_DECODE, scale=1 / 16)
+    want = orc.flash_attention(case["q"], case["k"], case["v"], torch.zeros(3, H, 1, 256), case["time"], None, 700, 2,
+                               scale=1 / 16)
+    assert_close(o, want, f"H{H} G{G} at Tq 1")
