@@ -77,3 +77,93 @@ def test_random_decode_paged(cuda, seed):
                                cw, 2, scale=1 / 16, sliding_window=sw, block_tables=case["block_tables"], page_size=page)
     tol = dict(abs_tol=4e-3, rel_tol=2e-2) if po_dtype == torch.float16 and S > 1 else {}
     assert_close(o, want, f"seed {seed}: H{H} G{G} lens{lens} page{page} S{S} sw{sw} cw{cw}", **tol)
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_prefill_paged(cuda, seed):
+    from helpers import randn
+
+    rng = random.Random(5000 + seed)
+    H, G = rng.choice(HEADS)
+    B = rng.randint(1, 3)
+    page = rng.choice([16, 16, 32, 64])
+    Tq = rng.choice([2, 31, 128, 150, 256, 333])
+    times = [Tq + rng.choice([0, 1, page - 1, 77, 500, 1500]) for _ in range(B)]
+    dtype = rng.choice([torch.float16, torch.bfloat16])
+    case = make_paged_case(6000 + seed, lens=times, H=H, G=G, dtype=dtype, page_size=page)
+    gen = torch.Generator().manual_seed(seed)
+    q_phys = randn(gen, B, Tq, H, 256, dtype=dtype)
+    # rows of the last page past each context hold NaN: they must never be multiplied in
+    for b, n in enumerate(times):
+        if n % page:
+            last = int(case["block_tables"][b, (n - 1) // page])
+            case["k_pool"][last, :, n % page:] = float("nan")
+            case["v_pool"][last, :, n % page:] = float("nan")
+    sw = rng.choice([None, None, rng.randint(1, 600)])
+    cw = rng.choice([case["max_len"], case["max_len"], max(Tq, case["max_len"] // 2)])
+    stage = rng.choice([fa2.STAGE_CAUSAL, fa2.STAGE_CAUSAL, fa2.STAGE_FULL])
+    S = rng.choice([0, 0, 4])
+    parts = (torch.empty(S, B, H, Tq, 256, device=cuda), torch.empty(S, B, H, Tq, device=cuda),
+             torch.empty(S, B, H, Tq, device=cuda)) if S else (None, None, None)
+    o_phys = torch.zeros(B, Tq, H, 256, dtype=dtype, device=cuda)
+    fa2.flash_attention(q_phys.to(cuda).permute(0, 2, 1, 3), case["k_pool"].to(cuda), case["v_pool"].to(cuda),
+                        o_phys.permute(0, 2, 1, 3), case["time"].to(cuda), None, cw, 1, *parts, stage=stage, scale=1 / 16,
+                        sliding_window=sw, block_tables=case["block_tables"].to(cuda), page_size=page,
+                        num_kv_splits=(S or None))
+    kp = torch.nan_to_num(case["k_pool"].float(), nan=0.0)
+    vp = torch.nan_to_num(case["v_pool"].float(), nan=0.0)
+    want = orc.flash_attention(q_phys.permute(0, 2, 1, 3), kp, vp, torch.zeros(B, H, Tq, 256), case["time"], None, cw, 1,
+                               stage=stage, scale=1 / 16, sliding_window=sw, block_tables=case["block_tables"], page_size=page)
+    assert_close(o_phys.permute(0, 2, 1, 3), want, f"seed {seed}: H{H} G{G} times{times} Tq{Tq} page{page} sw{sw} cw{cw} S{S}")
+
+
+@pytest.mark.parametrize("seed", range(12))
+def test_random_rope_append(cuda, seed):
+    from g4b_b200.kernels.rope import rope_norm_append
+    from helpers import randn
+
+    rng = random.Random(7000 + seed)
+    H, G = rng.choice(HEADS)
+    D = rng.choice([64, 128, 256, 256, 512])
+    B, Tq = rng.randint(1, 3), rng.choice([1, 3, 40, 700])
+    in_dtype = rng.choice([torch.float32, torch.float32, torch.bfloat16, torch.float16])
+    c_dtype = rng.choice([torch.bfloat16, torch.float16, torch.float32])
+    paged = rng.random() < 0.5
+    gen = torch.Generator().manual_seed(seed)
+    q, k, v = (randn(gen, B, Tq, h, D, dtype=in_dtype).permute(0, 2, 1, 3) for h in (H, G, G))
+    qw, kw = 1 + 0.1 * randn(gen, D), 1 + 0.1 * randn(gen, D)
+    freqs = 1.0 / (10000.0 ** (torch.arange(0, D, 2) / D))
+    before = [rng.randint(0, 90) for _ in range(B)]
+    off = torch.tensor(before, dtype=rng.choice([torch.int32, torch.int64]))
+    ph = _phase_vec(rng, B, 1)
+    if paged:
+        page = rng.choice([16, 32])
+        pages_per = [(b + Tq + page - 1) // page for b in before]
+        n_pages = sum(pages_per) + 2
+        perm = torch.randperm(n_pages, generator=gen).to(torch.int32)
+        bt = torch.full((B, max(pages_per)), -1, dtype=torch.int32)
+        at = 0
+        for b, n in enumerate(pages_per):
+            bt[b, :n] = perm[at:at + n]
+            at += n
+        kc0, vc0 = randn(gen, n_pages, G, page, D, dtype=c_dtype), randn(gen, n_pages, G, page, D, dtype=c_dtype)
+        extra = dict(block_tables=bt, page_size=page)
+    else:
+        T = Tq + rng.randint(0, 50)
+        kc0, vc0 = randn(gen, B, G, T, D, dtype=c_dtype), randn(gen, B, G, T, D, dtype=c_dtype)
+        extra = {}
+    norm_qk, norm_v, rotate = rng.random() < 0.8, rng.random() < 0.7, rng.random() < 0.85
+    want_q, _, want_kc, want_vc = orc.rope_norm_append(q, k, v, freqs if rotate else None, off, kc0, vc0, 1e-6,
+                                                       q_rmsnorm_w=qw, k_rmsnorm_w=kw, norm_qk=norm_qk, norm_v=norm_v,
+                                                       user_phase=ph, phase=1, **extra)
+    kc, vc = kc0.to(cuda), vc0.to(cuda)
+    q_out = torch.zeros(B, H, Tq, D, dtype=c_dtype, device=cuda)
+    dev_extra = {key: (val.to(cuda) if torch.is_tensor(val) else val) for key, val in extra.items()}
+    rope_norm_append(q.to(cuda), k.to(cuda), v.to(cuda), freqs.to(cuda) if rotate else None, off.to(cuda), kc, vc, 1e-6,
+                     q_out=q_out, q_rmsnorm_w=qw.to(cuda), k_rmsnorm_w=kw.to(cuda), norm_qk=norm_qk, norm_v=norm_v,
+                     user_phase=ph.to(cuda), phase=1, **dev_extra)
+    tol = {torch.float32: 3e-5, torch.float16: 2e-3, torch.bfloat16: 1.6e-2}[c_dtype]
+    what = f"seed {seed}: H{H} G{G} D{D} B{B} Tq{Tq} {in_dtype}->{c_dtype} paged={paged}"
+    assert torch.allclose(q_out.float().cpu(), want_q, atol=tol, rtol=tol), what
+    assert torch.allclose(kc.float().cpu(), want_kc.float(), atol=tol, rtol=tol), what
+    assert torch.allclose(vc.float().cpu(), want_vc.float(), atol=tol, rtol=tol), what
