@@ -12,6 +12,15 @@ def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box with -m gpu)")
 
 
+@pytest.fixture(scope="session", autouse=True)
+def _library_built():
+    """The C-ABI library is built in-tree (seconds when the sources have not changed: the build
+    keeps a digest); the suite does not depend on someone having built it before."""
+    from g4b_b200 import build
+
+    build.build()
+
+
 @pytest.fixture(scope="session")
 def cuda():
     import torch
