@@ -34,11 +34,14 @@ struct RopeParams {
   int B, H, G, Tq, D;
   int n_heads;                  // H + G (+ G with v)
   int heads_per_warp;
+  uint32_t n_slots;             // warps per token = ceil(n_heads / heads_per_warp)
+  uint32_t rows;                // B * Tq
   int T;                        // ring length
   int page_size, page_shift, num_pages, max_pages;
   int offsets_are_i64, phase, norm_qk, norm_v;
   int q_untouched;              // no norm, no rotation, no q_out: q rows are left alone
   float eps;
+  float inv_d;                  // 1 / D when D is a power of two, else 0
   int32_t* status;
 };
 
@@ -80,35 +83,51 @@ __device__ __forceinline__ float4 mul4(float4 a, float4 b) { return make_float4(
 __device__ __forceinline__ float4 scale4(float4 a, float s) { return make_float4(a.x * s, a.y * s, a.z * s, a.w * s); }
 __device__ __forceinline__ float dot4(float4 a) { return a.x * a.x + a.y * a.y + a.z * a.z + a.w * a.w; }
 
-// Row of the cache that position `pos` of slot b, kv head g lands in; -1 after recording why not.
-__device__ __forceinline__ int64_t cache_row(const RopeParams& p, int b, int g, int64_t pos, int lane) {
+// Where position `pos` of slot b lands in the caches: row of kv head g = base + g * head_stride.
+// Worked out once per warp (the ring's modulo and the block-table look-up do not depend on the
+// head).  base < 0 after recording why not, or when the warp appends nothing.
+struct CachePos { int64_t base; int64_t head_stride; };
+
+__device__ __forceinline__ CachePos cache_pos(const RopeParams& p, int b, int64_t pos, int lane) {
+  CachePos c{-1, 0};
   if (p.block_tables != nullptr) {
     const int64_t pg = pos >> p.page_shift;
     if (pos < 0 || pg >= p.max_pages) {
       if (lane == 0) atomicCAS(p.status, 0, 0x100 | 1);
-      return -1;
+      return c;
     }
     const int32_t page = p.block_tables[b * p.bt_s0 + pg * p.bt_s1];
     if (page < 0 || page >= p.num_pages) {
       if (lane == 0) atomicCAS(p.status, 0, 0x100 | 2);
-      return -1;
+      return c;
     }
-    return ((int64_t)page * p.G + g) * p.page_size + (pos & (p.page_size - 1));
+    c.base = (int64_t)page * p.G * p.page_size + (pos & (p.page_size - 1));
+    c.head_stride = p.page_size;
+    return c;
   }
-  int64_t r = pos % p.T;
-  if (r < 0) r += p.T;
-  return ((int64_t)b * p.G + g) * p.T + r;
+  int64_t r;
+  if ((uint64_t)pos <= 0x7fffffffull) {
+    r = (uint32_t)pos % (uint32_t)p.T;          // the usual case, without a 64-bit division
+  } else {
+    r = pos % p.T;
+    if (r < 0) r += p.T;
+  }
+  c.base = (int64_t)b * p.G * p.T + r;
+  c.head_stride = p.T;
+  return c;
 }
 
 // One tensor's heads of one token (KIND 0 q, 1 k, 2 v, a compile-time constant so that the
 // source / destination choices cost nothing at run time), four rows at a time: the loads of
 // all four rows go out before anything is computed, so that a lane has eight 16-byte loads
 // in flight (one row at a time left HBM at a quarter of its bandwidth).
-template <int KIND, int ITERS>
-__device__ __forceinline__ void rows_of_kind(const RopeParams& p, int h_begin, int h_end, int b, int t, int64_t pos,
-                                             bool in_phase, int lane, const float4 (&sn)[ITERS],
-                                             const float4 (&cs)[ITERS]) {
+template <int KIND, int ITERS, bool kExact, int kOut>
+__device__ __forceinline__ void rows_of_kind(const RopeParams& p, int h_begin, int h_end, int b, int t, CachePos cpos,
+                                             int lane, const float4 (&sn)[ITERS], const float4 (&cs)[ITERS]) {
   constexpr int kBatch = 4;
+  // kOut != 0 is the engine's own configuration (see the kernel): which options are on is
+  // then known at compile time, and the per-row tests of them disappear.
+  constexpr bool kEngine = kOut != 0;
   const int half = p.D >> 1;
   const void* src = KIND == 0 ? p.q : (KIND == 1 ? p.k : p.v);
   const int64_t* ss = KIND == 0 ? p.qs : (KIND == 1 ? p.ks : p.vs);
@@ -116,30 +135,36 @@ __device__ __forceinline__ void rows_of_kind(const RopeParams& p, int h_begin, i
   const int64_t src_hs = ss[1];
   // destinations
   void* cache = KIND == 1 ? p.k_cache : (KIND == 2 ? p.v_cache : nullptr);
-  const bool to_cache = cache != nullptr && in_phase;
+  const bool to_cache = (kEngine ? KIND != 0 : cache != nullptr) && cpos.base >= 0;
   void* out = nullptr;
   int64_t out_row = 0, out_hs = 0;
-  int out_dtype = p.in_dtype;
-  if (KIND == 0) {
+  const int in_dtype = kOut != 0 ? (int)G4B_F32 : p.in_dtype;
+  const int cache_dtype = kOut != 0 ? kOut : p.cache_dtype;
+  int out_dtype = in_dtype;
+  if (kEngine) {
+    if (KIND == 0) { out = p.q_out; out_row = b * p.qos[0] + t * p.qos[2]; out_hs = p.qos[1]; }
+  } else if (KIND == 0) {
     if (p.q_out != nullptr) { out = p.q_out; out_dtype = p.q_out_dtype; out_row = b * p.qos[0] + t * p.qos[2]; out_hs = p.qos[1]; }
     else if (!p.q_untouched) { out = const_cast<void*>(p.q); out_row = src_row; out_hs = src_hs; }
   } else if (KIND == 1) {
     if (p.k_out != nullptr) { out = p.k_out; out_dtype = p.k_out_dtype; out_row = b * p.kos[0] + t * p.kos[2]; out_hs = p.kos[1]; }
     else if (p.k_cache == nullptr) { out = const_cast<void*>(p.k); out_row = src_row; out_hs = src_hs; }
   }
-  if (out == nullptr && !to_cache) return;     // nothing to write (warp-uniform)
-  const bool norm = KIND == 2 ? p.norm_v != 0 : p.norm_qk != 0;
-  const float* rsos = KIND == 0 ? p.q_rsos : (KIND == 1 ? p.k_rsos : p.v_rsos);
+  const bool has_out = kEngine ? KIND == 0 : out != nullptr;
+  if (!has_out && !to_cache) return;     // nothing to write (warp-uniform)
+  const bool norm = KIND == 2 ? p.norm_v != 0 : (kEngine || p.norm_qk != 0);
+  const float* rsos = kEngine ? nullptr : (KIND == 0 ? p.q_rsos : (KIND == 1 ? p.k_rsos : p.v_rsos));
   const int64_t* rs = KIND == 0 ? p.qrs : (KIND == 1 ? p.krs : p.vrs);
   const float* w = KIND == 0 ? p.q_w : (KIND == 1 ? p.k_w : nullptr);
-  const int64_t ws = KIND == 0 ? p.qw_stride : p.kw_stride;
+  const int64_t ws = kEngine ? 1 : (KIND == 0 ? p.qw_stride : p.kw_stride);
+  const bool has_w = kEngine ? KIND != 2 : w != nullptr;
   // norm weights of this lane's elements (the same for every head of the tensor)
   float4 w1[ITERS], w2[ITERS];
-  if (norm && w != nullptr) {
+  if (norm && has_w) {
 #pragma unroll
     for (int it = 0; it < ITERS; ++it) {
       const int d1 = it * 128 + lane * 4;
-      if (d1 < half) {
+      if (kExact || d1 < half) {
         if (ws == 1) {
           w1[it] = *reinterpret_cast<const float4*>(w + d1);
           w2[it] = *reinterpret_cast<const float4*>(w + d1 + half);
@@ -150,7 +175,7 @@ __device__ __forceinline__ void rows_of_kind(const RopeParams& p, int h_begin, i
       }
     }
   }
-  const bool rotate = KIND != 2 && p.freqs != nullptr;
+  const bool rotate = KIND != 2 && (kEngine || p.freqs != nullptr);
 
   for (int h0 = h_begin; h0 < h_end; h0 += kBatch) {
     float4 x1[kBatch][ITERS], x2[kBatch][ITERS];
@@ -161,9 +186,9 @@ __device__ __forceinline__ void rows_of_kind(const RopeParams& p, int h_begin, i
 #pragma unroll
         for (int it = 0; it < ITERS; ++it) {
           const int d1 = it * 128 + lane * 4;
-          if (d1 < half) {
-            x1[i][it] = load4(src, p.in_dtype, so + d1);
-            x2[i][it] = load4(src, p.in_dtype, so + d1 + half);
+          if (kExact || d1 < half) {
+            x1[i][it] = load4(src, in_dtype, so + d1);
+            x2[i][it] = load4(src, in_dtype, so + d1 + half);
           }
         }
       }
@@ -172,23 +197,24 @@ __device__ __forceinline__ void rows_of_kind(const RopeParams& p, int h_begin, i
     for (int i = 0; i < kBatch; ++i) {
       const int h = h0 + i;
       if (h >= h_end) continue;
-      const int64_t crow = to_cache ? cache_row(p, b, h, pos, lane) : -1;
+      const int64_t crow = to_cache ? cpos.base + h * cpos.head_stride : -1;
       if (norm) {
         float sumsq = 0.f;
-        if (rsos != nullptr) {
+        if (!kEngine && rsos != nullptr) {
           sumsq = rsos[b * rs[0] + h * rs[1] + t * rs[2]];
         } else {
 #pragma unroll
           for (int it = 0; it < ITERS; ++it)
-            if (it * 128 + lane * 4 < half) sumsq += dot4(x1[i][it]) + dot4(x2[i][it]);
+            if (kExact || it * 128 + lane * 4 < half) sumsq += dot4(x1[i][it]) + dot4(x2[i][it]);
 #pragma unroll
           for (int o = 16; o > 0; o >>= 1) sumsq += __shfl_xor_sync(0xffffffffu, sumsq, o);
         }
-        const float inv = rsqrtf(sumsq / (float)p.D + p.eps);
+        // a power-of-two D makes the product the same number as the quotient
+        const float inv = rsqrtf((p.inv_d != 0.f ? sumsq * p.inv_d : sumsq / (float)p.D) + p.eps);
 #pragma unroll
         for (int it = 0; it < ITERS; ++it) {
-          if (it * 128 + lane * 4 < half) {
-            if (w != nullptr) {
+          if (kExact || it * 128 + lane * 4 < half) {
+            if (has_w) {
               // x * (inv * w): the reference's grouping (rope.py:33-34)
               x1[i][it] = mul4(x1[i][it], scale4(w1[it], inv));
               x2[i][it] = mul4(x2[i][it], scale4(w2[it], inv));
@@ -202,21 +228,21 @@ __device__ __forceinline__ void rows_of_kind(const RopeParams& p, int h_begin, i
 #pragma unroll
       for (int it = 0; it < ITERS; ++it) {
         const int d1 = it * 128 + lane * 4;
-        if (d1 < half) {
+        if (kExact || d1 < half) {
           float4 y1 = x1[i][it], y2 = x2[i][it];
           if (rotate) {
             const float4 a = x1[i][it], c = x2[i][it], s = sn[it], co = cs[it];
             y1 = make_float4(co.x * a.x - s.x * c.x, co.y * a.y - s.y * c.y, co.z * a.z - s.z * c.z, co.w * a.w - s.w * c.w);
             y2 = make_float4(co.x * c.x + s.x * a.x, co.y * c.y + s.y * a.y, co.z * c.z + s.z * a.z, co.w * c.w + s.w * a.w);
           }
-          if (out != nullptr) {
+          if (has_out) {
             const int64_t oo = out_row + h * out_hs + d1;
-            store4(out, out_dtype, oo, y1);
-            store4(out, out_dtype, oo + half, y2);
+            store4(out, kOut != 0 ? kOut : out_dtype, oo, y1);
+            store4(out, kOut != 0 ? kOut : out_dtype, oo + half, y2);
           }
           if (crow >= 0) {
-            store4(cache, p.cache_dtype, crow * p.D + d1, y1);
-            store4(cache, p.cache_dtype, crow * p.D + d1 + half, y2);
+            store4(cache, cache_dtype, crow * p.D + d1, y1);
+            store4(cache, cache_dtype, crow * p.D + d1 + half, y2);
           }
         }
       }
@@ -224,19 +250,27 @@ __device__ __forceinline__ void rows_of_kind(const RopeParams& p, int h_begin, i
   }
 }
 
-// ITERS: passes of 32 lanes x 4 pairs over half the head dim (1 up to D = 256, 2 up to 512).
+// ITERS: passes of 32 lanes x 4 pairs over half the head dim (1 up to D = 256, 2 up to 512);
+// kExact: D is exactly ITERS * 256, so no lane is ever past the row's end.
 // A warp takes heads [h_begin, h_end) of one token out of the token's H + 2G (q heads, then k,
 // then v): all of them at prefill sizes, so that the token's sines and cosines are computed
-// once; one at decode sizes, for parallelism.
-template <int ITERS>
-__global__ void __launch_bounds__(256, ITERS == 1 ? 3 : 2) rope_norm_append_kernel(RopeParams p) {
-  const int lane = threadIdx.x & 31;
-  const int64_t warp = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
-  const int n_slots = (p.n_heads + p.heads_per_warp - 1) / p.heads_per_warp;
-  const int64_t row = warp / n_slots;
-  if (row >= (int64_t)p.B * p.Tq) return;
-  const int slot = (int)(warp % n_slots);
-  const int b = (int)(row / p.Tq), t = (int)(row % p.Tq);
+// once; one at decode sizes, for parallelism.  Index arithmetic that runs once per warp is
+// 32-bit (the host bounds the warp count): 64-bit divisions cost a subroutine each.
+// kOut: 0, or the 16-bit type of q_out and of the caches in the engine's own configuration
+// (gemma4e.py:564-592: f32 q/k/v, q and k normed with weights and rotated, v normed without,
+// q to q_out, k and v to the caches only, no precomputed sums of squares), so that neither
+// loads and stores nor rows carry run-time switches.
+template <int ITERS, bool kExact, int kOut>
+__global__ void __launch_bounds__(32, ITERS == 1 ? (kOut != 0 ? 32 : 28) : 16) rope_norm_append_kernel(RopeParams p) {
+  // One warp per block: everything that depends on the warp alone then derives from blockIdx,
+  // which the compiler knows to be uniform (uniform registers and branches, no convergence
+  // barriers around the per-head conditions).
+  const int lane = threadIdx.x;
+  const uint32_t warp = blockIdx.x;
+  const uint32_t row = p.n_slots == 1 ? warp : warp / p.n_slots;
+  if (row >= p.rows) return;
+  const int slot = (int)(warp - row * p.n_slots);
+  const int b = (int)(row / (uint32_t)p.Tq), t = (int)(row - (uint32_t)b * (uint32_t)p.Tq);
   const int half = p.D >> 1;
 
   int64_t off;
@@ -255,7 +289,7 @@ __global__ void __launch_bounds__(256, ITERS == 1 ? 3 : 2) rope_norm_append_kern
     const int d1 = it * 128 + lane * 4;
     sn[it] = make_float4(0.f, 0.f, 0.f, 0.f);
     cs[it] = make_float4(1.f, 1.f, 1.f, 1.f);
-    if (p.freqs != nullptr && h_begin < p.H + p.G && d1 < half) {
+    if (p.freqs != nullptr && h_begin < p.H + p.G && (kExact || d1 < half)) {
       const float fp = (float)pos;
       // theta is the fp32 product, as in the reference (rope.py:171) and its torch oracle
       sincosf(fp * p.freqs[(d1 + 0) * p.freq_stride], &sn[it].x, &cs[it].x);
@@ -268,9 +302,11 @@ __global__ void __launch_bounds__(256, ITERS == 1 ? 3 : 2) rope_norm_append_kern
   const int q0 = min(h_begin, p.H), q1 = min(h_end, p.H);
   const int k0 = min(max(h_begin, p.H), p.H + p.G) - p.H, k1 = min(max(h_end, p.H), p.H + p.G) - p.H;
   const int v0 = max(h_begin, p.H + p.G) - p.H - p.G, v1 = max(h_end, p.H + p.G) - p.H - p.G;
-  if (q1 > q0) rows_of_kind<0, ITERS>(p, q0, q1, b, t, pos, in_phase, lane, sn, cs);
-  if (k1 > k0) rows_of_kind<1, ITERS>(p, k0, k1, b, t, pos, in_phase, lane, sn, cs);
-  if (v1 > v0) rows_of_kind<2, ITERS>(p, v0, v1, b, t, pos, in_phase, lane, sn, cs);
+  CachePos cpos{-1, 0};
+  if (in_phase && h_end > p.H && (p.k_cache != nullptr || p.v_cache != nullptr)) cpos = cache_pos(p, b, pos, lane);
+  if (q1 > q0) rows_of_kind<0, ITERS, kExact, kOut>(p, q0, q1, b, t, cpos, lane, sn, cs);
+  if (k1 > k0) rows_of_kind<1, ITERS, kExact, kOut>(p, k0, k1, b, t, cpos, lane, sn, cs);
+  if (v1 > v0) rows_of_kind<2, ITERS, kExact, kOut>(p, v0, v1, b, t, cpos, lane, sn, cs);
 }
 
 int check_view(const G4bTensor& t, const char* name, int ndim, int64_t d0, int64_t d1, int64_t d2, int64_t d3) {
@@ -411,10 +447,32 @@ int launch_rope_norm_append(const G4bRopeAppendArgs& a, cudaStream_t st) {
   p.heads_per_warp = rows * p.n_heads >= 16384 ? p.n_heads : 1;
   const int64_t n_slots = (p.n_heads + p.heads_per_warp - 1) / p.heads_per_warp;
   const int64_t warps = rows * n_slots;
-  const int64_t blocks = (warps + 7) / 8;
-  if (blocks > 0x7fffffffLL) return fail(G4B_ERR_UNSUPPORTED, "rope_norm_append: too many rows");
-  if (D <= 256) rope_norm_append_kernel<1><<<(unsigned)blocks, 256, 0, st>>>(p);
-  else rope_norm_append_kernel<2><<<(unsigned)blocks, 256, 0, st>>>(p);
+  const int64_t blocks = warps;
+  if (warps > 0x7fffffffLL) return fail(G4B_ERR_UNSUPPORTED, "rope_norm_append: too many rows");
+  p.inv_d = (D & (D - 1)) == 0 ? 1.f / (float)D : 0.f;
+  p.n_slots = (uint32_t)n_slots;
+  p.rows = (uint32_t)rows;
+  const bool exact = D == 256 || D == 512;
+  // the engine's own configuration gets the variants with everything decided at compile time
+  int out16 = 0;
+  if (a.q.dtype == G4B_F32 && a.q_out.ptr != nullptr && a.k_out.ptr == nullptr && a.k_cache.ptr != nullptr &&
+      (a.q_out.dtype == G4B_F16 || a.q_out.dtype == G4B_BF16) && a.q_out.dtype == p.cache_dtype &&
+      a.rope_freqs.ptr != nullptr && a.norm_qk != 0 && a.q_norm_w.ptr != nullptr && a.k_norm_w.ptr != nullptr &&
+      p.qw_stride == 1 && p.kw_stride == 1 && a.q_rsos.ptr == nullptr && a.k_rsos.ptr == nullptr &&
+      a.v_rsos.ptr == nullptr)
+    out16 = a.q_out.dtype;
+#define G4B_ROPE_LAUNCH(ITERS_, EXACT_)                                                                   \
+  do {                                                                                                    \
+    if (out16 == G4B_F16) rope_norm_append_kernel<ITERS_, EXACT_, G4B_F16><<<(unsigned)blocks, 32, 0, st>>>(p);        \
+    else if (out16 == G4B_BF16) rope_norm_append_kernel<ITERS_, EXACT_, G4B_BF16><<<(unsigned)blocks, 32, 0, st>>>(p); \
+    else rope_norm_append_kernel<ITERS_, EXACT_, 0><<<(unsigned)blocks, 32, 0, st>>>(p);                 \
+  } while (0)
+  if (D <= 256) {
+    if (exact) G4B_ROPE_LAUNCH(1, true); else G4B_ROPE_LAUNCH(1, false);
+  } else {
+    if (exact) G4B_ROPE_LAUNCH(2, true); else G4B_ROPE_LAUNCH(2, false);
+  }
+#undef G4B_ROPE_LAUNCH
   G4B_CUDA_CHECK(cudaGetLastError());
   return G4B_OK;
 }
