@@ -6,7 +6,7 @@
 // not have.
 //
 // Both kernels are launch-bound at decode sizes (512 rows of 512 B) and pure streaming at
-// prefill sizes: one warp per (slot, kv head, token) row, 16-byte vector accesses.
+// prefill sizes: one warp per four consecutive tokens of a (slot, kv head), 16-byte accesses.
 #include "common.cuh"
 #include <type_traits>
 
@@ -37,107 +37,147 @@ template <typename T> __device__ __forceinline__ float ld_f(const T* p) {
   return ElemTraits<T>::to_float(*p);
 }
 
-// One warp per row.  VEC = elements per lane per iteration (8).
+constexpr int kAppendRows = 4;   // consecutive tokens of one (slot, kv head) per warp
+
+// One warp per block, kAppendRows consecutive tokens of one (slot, kv head) per warp: what
+// depends on the warp alone derives from blockIdx (uniform registers, 32-bit arithmetic; the
+// host bounds the grid), the ring's modulo is taken once, and the loads of all the rows go out
+// before any is converted, so that a lane has up to eight 16-byte loads in flight.
 template <typename TX, typename TC, bool kSameBits>
-__global__ void __launch_bounds__(256) kv_append_kernel(AppendParams p) {
-  const int warps_per_block = blockDim.x >> 5;
-  const int64_t row = (int64_t)blockIdx.x * warps_per_block + (threadIdx.x >> 5);
-  const int lane = threadIdx.x & 31;
-  const int64_t rows = (int64_t)p.B * p.G * p.Tq;
-  if (row >= rows) return;
-  const int t = (int)(row % p.Tq);
-  const int g = (int)((row / p.Tq) % p.G);
-  const int b = (int)(row / ((int64_t)p.Tq * p.G));
+__global__ void __launch_bounds__(32) kv_append_kernel(AppendParams p) {
+  const int lane = threadIdx.x;
+  const uint32_t groups = (uint32_t)(p.Tq + kAppendRows - 1) / kAppendRows;   // row groups per (slot, head)
+  const uint32_t bg = blockIdx.x / groups;
+  const int t0 = (int)(blockIdx.x - bg * groups) * kAppendRows;
+  const int b = (int)(bg / (uint32_t)p.G), g = (int)(bg - (uint32_t)b * (uint32_t)p.G);
+  const int n = min(kAppendRows, p.Tq - t0);
 
   if (p.user_phase != nullptr && p.user_phase[b * p.phase_stride] != (uint8_t)p.phase) return;
 
   int64_t off;
   if (p.offsets_are_i64) off = ((const int64_t*)p.cache_offsets)[b * p.off_stride];
   else off = ((const int32_t*)p.cache_offsets)[b * p.off_stride];
+  const int64_t pos0 = off + t0;
 
-  TC* dst;
+  // destination rows; nullptr after recording why not
+  TC* dst[kAppendRows];
   if (p.block_tables != nullptr) {
-    const int64_t pos = off + t;
-    const int64_t pg = pos >> p.page_shift;
-    if (pos < 0 || pg >= p.max_pages) {  // refuse to write outside the block table
-      if (lane == 0) atomicCAS(p.status, 0, 0x100 | 1);
-      return;
+#pragma unroll
+    for (int i = 0; i < kAppendRows; ++i) {
+      dst[i] = nullptr;
+      if (i >= n) continue;
+      const int64_t pos = pos0 + i;
+      const int64_t pg = pos >> p.page_shift;
+      if (pos < 0 || pg >= p.max_pages) {  // refuse to write outside the block table
+        if (lane == 0) atomicCAS(p.status, 0, 0x100 | 1);
+        continue;
+      }
+      const int32_t page = p.block_tables[b * p.bt_stride0 + pg * p.bt_stride1];
+      if (page < 0 || page >= p.num_pages) {
+        if (lane == 0) atomicCAS(p.status, 0, 0x100 | 2);
+        continue;
+      }
+      const int r = (int)(pos & (p.page_size - 1));
+      dst[i] = (TC*)p.cache + (((int64_t)page * p.G + g) * p.page_size + r) * p.D;
     }
-    const int32_t page = p.block_tables[b * p.bt_stride0 + pg * p.bt_stride1];
-    if (page < 0 || page >= p.num_pages) {
-      if (lane == 0) atomicCAS(p.status, 0, 0x100 | 2);
-      return;
-    }
-    const int r = (int)(pos & (p.page_size - 1));
-    dst = (TC*)p.cache + (((int64_t)page * p.G + g) * p.page_size + r) * p.D;
   } else {
-    int64_t r = (off + t) % p.T;
-    if (r < 0) r += p.T;
-    dst = (TC*)p.cache + (((int64_t)b * p.G + g) * p.T + r) * p.D;
+    int64_t r;
+    if ((uint64_t)pos0 <= 0x7fffffffull) {
+      r = (uint32_t)pos0 % (uint32_t)p.T;        // the usual case, without a 64-bit division
+    } else {
+      r = pos0 % p.T;
+      if (r < 0) r += p.T;
+    }
+    TC* const slot = (TC*)p.cache + ((int64_t)b * p.G + g) * p.T * p.D;
+#pragma unroll
+    for (int i = 0; i < kAppendRows; ++i) {
+      int64_t ri = r + i;
+      if (ri >= p.T) ri -= p.T;                  // Tq <= T, so one wrap at most
+      dst[i] = i < n ? slot + ri * p.D : nullptr;
+    }
   }
-  const TX* src = (const TX*)p.x + b * p.xs0 + g * p.xs1 + t * p.xs2;
+  const TX* const src0 = (const TX*)p.x + b * p.xs0 + g * p.xs1 + (int64_t)t0 * p.xs2;
+  const bool norm = p.x_rsos != nullptr;
 
   if constexpr (kSameBits) {
     // same element type, no norm: move bits untouched
-    if (p.x_rsos == nullptr) {
+    if (!norm) {
       constexpr int V = 16 / sizeof(TX);
-      const bool aligned = ((((uintptr_t)src) | ((uintptr_t)dst)) & 15) == 0 && (p.D % V) == 0;
+      bool aligned = (p.D % V) == 0 && ((uintptr_t)src0 & 15) == 0 && (p.xs2 % V) == 0;
+#pragma unroll
+      for (int i = 0; i < kAppendRows; ++i) aligned = aligned && ((uintptr_t)dst[i] & 15) == 0;
       if (aligned) {
-        for (int d = lane * V; d < p.D; d += 32 * V)
-          *(uint4*)(dst + d) = *(const uint4*)(src + d);
+        for (int d = lane * V; d < p.D; d += 32 * V) {
+          uint4 v[kAppendRows];
+#pragma unroll
+          for (int i = 0; i < kAppendRows; ++i)
+            if (i < n) v[i] = *(const uint4*)(src0 + i * p.xs2 + d);
+#pragma unroll
+          for (int i = 0; i < kAppendRows; ++i)
+            if (dst[i] != nullptr) *(uint4*)(dst[i] + d) = v[i];
+        }
       } else {
-        for (int d = lane; d < p.D; d += 32) dst[d] = (TC)src[d];
+        for (int i = 0; i < n; ++i)
+          if (dst[i] != nullptr)
+            for (int d = lane; d < p.D; d += 32) dst[i][d] = (TC)src0[i * p.xs2 + d];
       }
       return;
     }
   }
-  float r = 1.0f;
-  const bool norm = p.x_rsos != nullptr;
-  if (norm) r = rsqrtf(p.x_rsos[b * p.rs0 + g * p.rs1 + t * p.rs2] / (float)p.D + p.eps);
-  const bool vec_ok = (p.D % 8) == 0 && (((uintptr_t)src) & (8 * sizeof(TX) - 1)) == 0 &&
-                      (((uintptr_t)dst) & (8 * sizeof(TC) - 1)) == 0;
+  float scale[kAppendRows];
+#pragma unroll
+  for (int i = 0; i < kAppendRows; ++i) {
+    scale[i] = 1.0f;
+    if (norm && i < n) scale[i] = rsqrtf(p.x_rsos[b * p.rs0 + g * p.rs1 + (t0 + i) * p.rs2] / (float)p.D + p.eps);
+  }
+  bool vec_ok = (p.D % 8) == 0 && ((uintptr_t)src0 & (8 * sizeof(TX) - 1)) == 0 && (p.xs2 % 8) == 0;
+#pragma unroll
+  for (int i = 0; i < kAppendRows; ++i) vec_ok = vec_ok && ((uintptr_t)dst[i] & (8 * sizeof(TC) - 1)) == 0;
   if (vec_ok) {
     // 8 elements per lane per pass: 16- or 32-byte loads, 16- or 32-byte stores
     for (int d = lane * 8; d < p.D; d += 256) {
-      alignas(32) TX in[8];
-      alignas(32) TC out[8];
-      if constexpr (sizeof(TX) == 4) {
-        *(uint4*)&in[0] = *(const uint4*)(src + d);
-        *(uint4*)&in[4] = *(const uint4*)(src + d + 4);
-      } else {
-        *(uint4*)&in[0] = *(const uint4*)(src + d);
+      alignas(32) TX in[kAppendRows][8];
+#pragma unroll
+      for (int i = 0; i < kAppendRows; ++i) {
+        if (i >= n) continue;
+        const TX* src = src0 + i * p.xs2 + d;
+        *(uint4*)&in[i][0] = *(const uint4*)src;
+        if constexpr (sizeof(TX) == 4) *(uint4*)&in[i][4] = *(const uint4*)(src + 4);
       }
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        float v = ElemTraits<TX>::to_float(in[i]);
-        if (norm) v *= r;
-        out[i] = ElemTraits<TC>::from_float(v);
-      }
-      if constexpr (sizeof(TC) == 4) {
-        *(uint4*)(dst + d) = *(const uint4*)&out[0];
-        *(uint4*)(dst + d + 4) = *(const uint4*)&out[4];
-      } else {
-        *(uint4*)(dst + d) = *(const uint4*)&out[0];
+      for (int i = 0; i < kAppendRows; ++i) {
+        if (dst[i] == nullptr) continue;
+        alignas(32) TC out[8];
+#pragma unroll
+        for (int e = 0; e < 8; ++e) {
+          float v = ElemTraits<TX>::to_float(in[i][e]);
+          if (norm) v *= scale[i];
+          out[e] = ElemTraits<TC>::from_float(v);
+        }
+        *(uint4*)(dst[i] + d) = *(const uint4*)&out[0];
+        if constexpr (sizeof(TC) == 4) *(uint4*)(dst[i] + d + 4) = *(const uint4*)&out[4];
       }
     }
     return;
   }
-  for (int d = lane; d < p.D; d += 32) {
-    float v = ld_f(src + d);
-    if (norm) v *= r;
-    dst[d] = ElemTraits<TC>::from_float(v);
+  for (int i = 0; i < n; ++i) {
+    if (dst[i] == nullptr) continue;
+    for (int d = lane; d < p.D; d += 32) {
+      float v = ld_f(src0 + i * p.xs2 + d);
+      if (norm) v *= scale[i];
+      dst[i][d] = ElemTraits<TC>::from_float(v);
+    }
   }
 }
 
 template <typename TX, typename TC>
 static int launch_typed(const AppendParams& p, cudaStream_t st) {
-  const int64_t rows = (int64_t)p.B * p.G * p.Tq;
-  if (rows == 0) return G4B_OK;
-  const int wpb = 8;
-  const int64_t blocks = (rows + wpb - 1) / wpb;
+  const int64_t groups = (p.Tq + kAppendRows - 1) / kAppendRows;
+  const int64_t blocks = (int64_t)p.B * p.G * groups;
+  if (blocks == 0) return G4B_OK;
   if (blocks > 0x7fffffffLL) return fail(G4B_ERR_UNSUPPORTED, "kv_append: too many rows");
   constexpr bool same = std::is_same<TX, TC>::value;
-  kv_append_kernel<TX, TC, same><<<(unsigned)blocks, wpb * 32, 0, st>>>(p);
+  kv_append_kernel<TX, TC, same><<<(unsigned)blocks, 32, 0, st>>>(p);
   G4B_CUDA_CHECK(cudaGetLastError());
   return G4B_OK;
 }
