@@ -12,6 +12,7 @@ Prints ONE JSON line.  Workloads (shapes of the five benchmark configurations):
     prefill_chunk   256 new rows of one request over 65536 cached keys (split-KV over the SMs;
                     --kv-splits -1 runs it unsplit)
     rope_append     the launch before attention: norm + rotary embedding + KV append, GB/s
+    kv_append       add_kv_to_cache alone on a prefill chunk (V norm, f32 -> f16), GB/s
 A step is one pass of the hot path over one batch.  ``value`` has inputs resident in HBM;
 ``e2e`` goes through the public Python operators with pinned host buffers, host<->device
 copies inside the timed region.  With N > 1 every rank runs the same per-GPU batch (weak
@@ -423,6 +424,60 @@ class RopeAppendWorkload:
         return n * (H + 2 * G) * D * 6 / dt / 1e9, f"{n} tokens of 1 batch item, torch fp32"
 
 
+class KVAppendWorkload:
+    """add_kv_to_cache on its own at prefill-chunk sizes: V rows [B,G,t,D] in fp32 with their
+    precomputed sums of squares, normalised and cast into an f16 ring cache (B8 G4 t32768
+    D256).  HBM-bound: algorithmic bytes = fp32 reads + f16 writes of the rows."""
+
+    variants = 1
+
+    def __init__(self, name, dev, seed):
+        from g4b_b200.kernels.add_kv_to_cache import add_kv_to_cache
+
+        self.fn, self.name, self.dtype = add_kv_to_cache, name, torch.float16
+        B, S, Gk = 8, 32768, 4
+        gen = torch.Generator(device="cpu").manual_seed(seed)
+        self.h_x = torch.randn(B, S, Gk, D, generator=gen).pin_memory()       # the engine's [B,t,heads,D] layout
+        self.x = self.h_x.to(dev)
+        self.rsos = (self.x.permute(0, 2, 1, 3) ** 2).sum(-1)
+        self.cache = torch.zeros(B, Gk, S, D, dtype=self.dtype, device=dev)
+        self.h_probe = torch.empty(B, Gk, 16, D, dtype=self.dtype).pin_memory()
+        self.d_probe = torch.empty(B, Gk, 16, D, dtype=self.dtype, device=dev)
+        self.off = torch.zeros(B, dtype=torch.int32, device=dev)
+        self.units = float(B * S * Gk * D * (4 + 2))
+        self.metric, self.unit, self.bound = "kv_append_hbm_gbs", "GB/s", "hbm"
+        self.launches_per_step = 1
+        self.traffic = None
+        self.h2d = self.h_x.numel() * 4
+        self.d2h = self.h_probe.numel() * 2
+        self.config = {"workload": name, "batch_per_gpu": B, "tokens": S, "kv_heads": Gk, "head_dim": D,
+                       "in_dtype": "f32", "cache_dtype": "f16", "norm": True,
+                       "l2": "inputs (%d MB) larger than L2" % (self.h2d >> 20)}
+
+    def step(self, i=0):
+        self.fn(self.x.permute(0, 2, 1, 3), self.cache, self.off, 1e-6, self.rsos)
+
+    def e2e_step(self, i=0):
+        self.x.copy_(self.h_x, non_blocking=True)
+        self.step(i)
+        self.d_probe.copy_(self.cache[:, :, :16])                         # the rows a caller would check
+        self.h_probe.copy_(self.d_probe, non_blocking=True)
+
+    def value_from(self, ms_per_step, world):
+        return self.units * world / (ms_per_step * 1e-3) / 1e9
+
+    def cpu_sample(self, budget_s=15.0):
+        from oracle import attention_oracle as orc
+
+        n = 2048
+        x = self.h_x[:1, :n].permute(0, 2, 1, 3)
+        cache = torch.zeros(1, x.shape[1], n, D, dtype=self.dtype)
+        t0 = time.perf_counter()
+        orc.add_kv_to_cache(x, cache, torch.zeros(1, dtype=torch.int32), 1e-6, (x ** 2).sum(-1))
+        dt = time.perf_counter() - t0
+        return n * x.shape[1] * D * 6 / dt / 1e9, f"{n} tokens of 1 batch item, torch fp32"
+
+
 class DecodeWorkload:
     """Configs 4 and 5: paged KV with shuffled block tables; a step appends the new token's
     K and V rows and runs decode attention (split-KV + combine)."""
@@ -584,7 +639,10 @@ class DecodeWorkload:
 
 
 def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_splits=0):
-    seeds = {"prefill_causal": 1, "prefill_swa": 2, "decode_paged": 3, "decode_long": 4, "rope_append": 5}
+    seeds = {"prefill_causal": 1, "prefill_swa": 2, "decode_paged": 3, "decode_long": 4, "rope_append": 5,
+             "kv_append": 7}
+    if name == "kv_append":
+        return KVAppendWorkload(name, dev, seeds[name] + 100 * rank)
     if name == "rope_append":
         return RopeAppendWorkload(name, dev, seeds[name] + 100 * rank)
     if name == "prefill_chunk":
@@ -750,6 +808,17 @@ def run_reference(args):
         sample = f"{n} tokens of 1 batch item per step, torch fp32"
         config = {"workload": name, "batch_per_gpu": 4, "tokens": 8192, "q_heads": H, "kv_heads": G, "head_dim": D,
                   "in_dtype": "f32", "out_dtype": "bf16"}
+    elif name == "kv_append":
+        n, Gk = 2048, 4
+        x = torch.randn(1, Gk, n, D, generator=gen)
+        cache = torch.zeros(1, Gk, n, D, dtype=torch.float16)
+        off = torch.zeros(1, dtype=torch.int32)
+        units = float(n * Gk * D * 6)
+        fn = lambda: orc.add_kv_to_cache(x, cache, off, 1e-6, (x ** 2).sum(-1))
+        metric, unit, div = "kv_append_hbm_gbs", "GB/s", 1e9
+        sample = f"{n} tokens of 1 batch item per step, torch fp32"
+        config = {"workload": name, "batch_per_gpu": 8, "tokens": 32768, "kv_heads": Gk, "head_dim": D,
+                  "in_dtype": "f32", "cache_dtype": "f16", "norm": True}
     else:
         L = 32768 if name == "decode_paged" else 131072
         n_pages = L // PAGE
@@ -794,7 +863,8 @@ def main():
     ap.add_argument("--warmup", type=int, default=5)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="prefill_causal",
-                    choices=["prefill_causal", "prefill_swa", "prefill_chunk", "decode_paged", "decode_long", "rope_append"])
+                    choices=["prefill_causal", "prefill_swa", "prefill_chunk", "decode_paged", "decode_long", "rope_append",
+                             "kv_append"])
     ap.add_argument("--sequences", type=int, default=256,
                     help="decode_paged only: number of sequences (256 = the benchmark configuration; "
                          "smaller values are for profiler captures)")
