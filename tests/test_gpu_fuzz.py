@@ -167,3 +167,53 @@ def test_random_rope_append(cuda, seed):
     assert torch.allclose(q_out.float().cpu(), want_q, atol=tol, rtol=tol), what
     assert torch.allclose(kc.float().cpu(), want_kc.float(), atol=tol, rtol=tol), what
     assert torch.allclose(vc.float().cpu(), want_vc.float(), atol=tol, rtol=tol), what
+
+
+@pytest.mark.parametrize("seed", range(16))
+def test_random_kv_append(cuda, seed):
+    """add_kv_to_cache over head dims off the 8-element grid, rows that start off a 16-byte
+    boundary (the element-wise path), token counts off the four-row grouping, rings written
+    completely (Tq = T) and wrapped, pages, slots off phase, both offset types."""
+    from g4b_b200.kernels.add_kv_to_cache import add_kv_to_cache
+    from helpers import randn
+
+    rng = random.Random(9000 + seed)
+    B, G = rng.randint(1, 4), rng.choice([1, 2, 4, 5])
+    D = rng.choice([256, 256, 64, 40, 36, 30, 512, 264])
+    Tq = rng.choice([1, 2, 3, 4, 5, 7, 8, 31, 64, 130])
+    x_dtype = rng.choice([torch.float32, torch.float16, torch.bfloat16])
+    c_dtype = rng.choice([x_dtype, torch.float16, torch.bfloat16, torch.float32])
+    norm = rng.random() < 0.5
+    paged = rng.random() < 0.4
+    shift = rng.choice([0, 0, 1, 3])               # elements the rows start past an aligned address
+    gen = torch.Generator().manual_seed(seed)
+    x_phys = randn(gen, B, Tq, G, D + shift, dtype=x_dtype)
+    x = x_phys[..., shift:].permute(0, 2, 1, 3)
+    rsos = (x.float() ** 2).sum(-1) if norm else None
+    phase = _phase_vec(rng, B, 1) if rng.random() < 0.5 else None
+    off_dtype = rng.choice([torch.int32, torch.int64])
+    if paged:
+        page = rng.choice([16, 32])
+        per_seq = (Tq + 50 + page - 1) // page + 1
+        n_pages = B * per_seq + 3
+        cache = randn(gen, n_pages, G, page, D, dtype=c_dtype)
+        bt = torch.randperm(n_pages, generator=gen)[: B * per_seq].to(torch.int32).view(B, per_seq)
+        off = torch.tensor([rng.randint(0, 50) for _ in range(B)], dtype=off_dtype)
+        kw = dict(block_tables=bt, page_size=page)
+        kw_d = dict(block_tables=bt.to(cuda), page_size=page)
+    else:
+        T = Tq + rng.choice([0, 0, 1, 9, 100])
+        cache = randn(gen, B, G, T, D, dtype=c_dtype)
+        off = torch.tensor([rng.randint(0, 3 * T) for _ in range(B)], dtype=off_dtype)
+        kw, kw_d = {}, {}
+    want = orc.add_kv_to_cache(x, cache, off, 1e-6, rsos, phase, 1, **kw)
+    cache_d = cache.to(cuda)
+    xd = x_phys.to(cuda)[..., shift:].permute(0, 2, 1, 3)
+    add_kv_to_cache(xd, cache_d, off.to(cuda), 1e-6, None if rsos is None else rsos.to(cuda),
+                    None if phase is None else phase.to(cuda), 1, **kw_d)
+    what = f"seed {seed}: B{B} G{G} D{D} Tq{Tq} {x_dtype}->{c_dtype} norm{norm} paged{paged} shift{shift}"
+    if norm:
+        tol = {torch.float32: 2e-6, torch.float16: 1e-3, torch.bfloat16: 8e-3}[c_dtype]
+        assert torch.allclose(cache_d.cpu().float(), want.float(), rtol=tol, atol=tol), what
+    else:
+        assert torch.equal(cache_d.cpu().view(torch.uint8), want.view(torch.uint8)), what
