@@ -67,10 +67,11 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams 
   __shared__ float s_w[kCombineMaxSplits];
   __shared__ float s_red[kCombineThreads / 32];
   __shared__ float4 s_acc[kCombineThreads];
-  int64_t row = blockIdx.x;
-  const int t = (int)(row % p.Tq); row /= p.Tq;
-  const int h = (int)(row % p.H);
-  const int b = (int)(row / p.H);
+  // 32-bit index arithmetic: the row count is a grid extent
+  const uint32_t row = blockIdx.x, bh = row / (uint32_t)p.Tq;
+  const int t = (int)(row - bh * (uint32_t)p.Tq);
+  const int b = (int)(bh / (uint32_t)p.H);
+  const int h = (int)(bh - (uint32_t)b * (uint32_t)p.H);
   if (p.user_phase != nullptr && p.user_phase[b * p.phase_stride] != (uint8_t)p.phase) return;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   const int64_t ml_off = b * p.pm_s[1] + h * p.pm_s[2] + t * p.pm_s[3];
