@@ -81,8 +81,8 @@ class G4bExchangeArgs(ctypes.Structure):
     _fields_ = [
         ("partial_o", G4bTensor), ("partial_l", G4bTensor), ("partial_m", G4bTensor), ("o", G4bTensor),
         ("user_phase", G4bTensor),
-        ("xbuf", ctypes.c_void_p * 8), ("flags", ctypes.c_void_p * 8), ("state", ctypes.c_void_p),
-        ("xbuf_bytes", ctypes.c_int64), ("flags_bytes", ctypes.c_int64),
+        ("xbuf", ctypes.c_void_p * 8), ("state", ctypes.c_void_p),
+        ("xbuf_bytes", ctypes.c_int64),
         ("num_splits", ctypes.c_int32), ("phase", ctypes.c_int32), ("world", ctypes.c_int32), ("rank", ctypes.c_int32),
     ]
 
@@ -102,7 +102,7 @@ EXPORTS = {
     "g4b_attn_decode_static_scratch": (ctypes.c_int, [ctypes.POINTER(G4bAttnArgs), ctypes.c_void_p]),
     "g4b_attn_combine": (ctypes.c_int, [ctypes.POINTER(G4bCombineArgs), ctypes.c_void_p]),
     "g4b_attn_combine_exchange": (ctypes.c_int, [ctypes.POINTER(G4bExchangeArgs), ctypes.c_void_p]),
-    "g4b_exchange_buffer_bytes": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int64, ctypes.c_int, ctypes.POINTER(ctypes.c_int64)]),
+    "g4b_exchange_buffer_bytes": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int64, ctypes.c_int]),
     "g4b_select_kv_splits": (ctypes.c_int, [ctypes.c_int] * 4),
     "g4b_kv_append": (ctypes.c_int, [ctypes.POINTER(G4bAppendArgs), ctypes.c_void_p]),
     "g4b_rope_norm_append": (ctypes.c_int, [ctypes.POINTER(G4bRopeAppendArgs), ctypes.c_void_p]),

@@ -7,15 +7,23 @@
 // (fa2.py:618-626), so each GPU first merges its own S partials into one, then the W merged
 // partials are exchanged and merged again.  The exchange is not a library collective: each
 // block stores its piece of the merged partial straight into every peer's exchange buffer
-// (plain stores to peer-mapped memory travel over NVLink), raises a flag there, waits for
-// the same flag from every peer in its own memory, and finishes the merge.  8 KB per GPU pair
-// cross the links; there is no second launch and no host round trip.
+// (plain stores to peer-mapped memory travel over NVLink), waits for the same piece from every
+// peer in its own memory, and finishes the merge.  16 KB per GPU pair cross the links; there
+// is no second launch and no host round trip.
+//
+// Every value travels as one 8-byte word {value, launch count}: an aligned 8-byte store is
+// seen whole or not at all, so the word is its own arrival flag.  The receiver polls the words
+// themselves until they carry this launch's count.  No fence and no separate flag write sit
+// between the data and its announcement, which is what the latency of so small an exchange is
+// made of (data, system fence, flag, each a trip over the link: 20 us per launch with a flag
+// per piece against 5 us for the same merge without peers).
 //
 // Blocks wait only for blocks of OTHER GPUs (same index there), never for blocks of their own
 // grid, so nothing depends on co-residency of the grid.  Every wait is bounded; on a timeout
 // the block records a code in the device status word and gives up.  Buffers are double
 // buffered by launch parity: a peer can be at most one launch ahead, because its next launch
-// cannot finish without this GPU's next contribution.
+// cannot finish without this GPU's next contribution; a word of the same parity therefore
+// still holds the count of two launches ago, never this one's.
 #include "common.cuh"
 
 namespace g4b {
@@ -34,29 +42,25 @@ struct ExchangeParams {
   const uint8_t* user_phase;
   int64_t po_s[5], pl_s[4], pm_s[4], o_s[4];
   int64_t phase_stride;
-  float* xbuf[kXMaxWorld];        // exchange buffer of every rank (own entry: local memory)
-  uint32_t* flags[kXMaxWorld];    // flag array of every rank
+  unsigned long long* xbuf[kXMaxWorld];   // exchange buffer of every rank (own entry: local memory)
   uint32_t* state;                // local: {launches completed, blocks done in this launch}
   int32_t* status;
   int S, B, H, Tq, D, phase, world, rank;
   int rows, slices;
 };
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-  asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_word_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-  uint32_t v;
-  asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ unsigned long long ld_word_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
   return v;
 }
 
-// Element offsets inside one rank's exchange buffer / flag array.
+// Word offset inside one rank's exchange buffer.
 __device__ __forceinline__ int64_t xbuf_off(const ExchangeParams& p, int par, int src, int row, int slice) {
   return ((((int64_t)par * p.world + src) * p.rows + row) * p.slices + slice) * (kXCols + 2);
-}
-__device__ __forceinline__ int64_t flag_off(const ExchangeParams& p, int par, int src, int blk) {
-  return ((int64_t)par * p.world + src) * ((int64_t)p.rows * p.slices) + blk;
 }
 
 template <typename TP, typename TO>
@@ -129,27 +133,24 @@ __global__ void __launch_bounds__(kXThreads) combine_exchange_kernel(ExchangePar
       }
       // ---- push this rank's merged piece to every rank (own copy included) ----
       const int64_t off = xbuf_off(p, par, p.rank, row, slice) + tid;
-      for (int r = 0; r < p.world; ++r) p.xbuf[r][off] = v;
-      __threadfence_system();
+      const unsigned long long word = ((unsigned long long)epoch << 32) | __float_as_uint(v);
+      for (int r = 0; r < p.world; ++r) st_word_sys(p.xbuf[r] + off, word);
     }
-    __syncthreads();
-    if (tid < p.world) {
-      st_release_sys(p.flags[tid] + flag_off(p, par, p.rank, blk), epoch);
-      // ---- wait for the same piece from rank `tid` ----
-      const uint32_t* mine = p.flags[p.rank] + flag_off(p, par, tid, blk);
-      const long long t0 = clock64();
-      while (ld_acquire_sys(mine) != epoch) {
-        if (clock64() - t0 > kXWaitLimit) { atomicCAS(p.status, 0, kErrPeerWait); s_fail = 1; break; }
+    // ---- wait for every rank's piece: a word has arrived once it carries this launch's count ----
+    const long long t0 = clock64();
+    for (int i = tid; i < p.world * (kXCols + 2); i += kXThreads) {
+      const int r = i / (kXCols + 2), e = i % (kXCols + 2);
+      const unsigned long long* src = p.xbuf[p.rank] + xbuf_off(p, par, r, row, slice) + e;
+      unsigned long long w = ld_word_sys(src);
+      while ((uint32_t)(w >> 32) != epoch) {
+        if (s_fail || clock64() - t0 > kXWaitLimit) { atomicCAS(p.status, 0, kErrPeerWait); s_fail = 1; break; }
+        w = ld_word_sys(src);
       }
+      s_part[r][e] = __uint_as_float((uint32_t)w);
     }
     __syncthreads();
     if (!s_fail) {
-      // ---- final merge of the W pieces (read around L1: a peer wrote them) ----
-      for (int i = tid; i < p.world * (kXCols + 2); i += kXThreads) {
-        const int r = i / (kXCols + 2), e = i % (kXCols + 2);
-        s_part[r][e] = __ldcg(p.xbuf[p.rank] + xbuf_off(p, par, r, row, slice) + e);
-      }
-      __syncthreads();
+      // ---- final merge of the W pieces ----
       if (tid < kXCols && d < p.D) {
         float mm = -INFINITY;
         for (int r = 0; r < p.world; ++r) mm = fmaxf(mm, s_part[r][kXCols + 1]);
@@ -196,9 +197,9 @@ int launch_combine_exchange(const G4bExchangeArgs& a, cudaStream_t st) {
   if (a.state == nullptr) return fail(G4B_ERR_BAD_ARG, "exchange: state is null");
   ExchangeParams p{};
   for (int r = 0; r < a.world; ++r) {
-    if (a.xbuf[r] == nullptr || a.flags[r] == nullptr) return fail(G4B_ERR_BAD_ARG, "exchange: buffer of rank %d missing", r);
-    p.xbuf[r] = (float*)a.xbuf[r];
-    p.flags[r] = (uint32_t*)a.flags[r];
+    if (a.xbuf[r] == nullptr) return fail(G4B_ERR_BAD_ARG, "exchange: buffer of rank %d missing", r);
+    if (((uintptr_t)a.xbuf[r] & 7) != 0) return fail(G4B_ERR_BAD_STRIDE, "exchange: buffers must be 8-byte aligned");
+    p.xbuf[r] = (unsigned long long*)a.xbuf[r];
   }
   p.po = a.partial_o.ptr; p.pl = (const float*)a.partial_l.ptr; p.pm = (const float*)a.partial_m.ptr; p.o = a.o.ptr;
   p.user_phase = (const uint8_t*)a.user_phase.ptr; p.phase_stride = a.user_phase.stride[0];
@@ -211,10 +212,9 @@ int launch_combine_exchange(const G4bExchangeArgs& a, cudaStream_t st) {
   if (rows == 0) return G4B_OK;
   p.rows = (int)rows; p.slices = (p.D + kXCols - 1) / kXCols;
   if (rows > 65535 || p.slices > 65535) return fail(G4B_ERR_TOO_LARGE, "exchange: too many rows");
-  const int64_t need_x = 2ll * a.world * rows * p.slices * (kXCols + 2) * 4;
-  const int64_t need_f = 2ll * a.world * rows * p.slices * 4;
-  if (a.xbuf_bytes < need_x || a.flags_bytes < need_f)
-    return fail(G4B_ERR_BAD_ARG, "exchange: buffers too small (need %lld and %lld bytes per rank)", (long long)need_x, (long long)need_f);
+  const int64_t need_x = 2ll * a.world * rows * p.slices * (kXCols + 2) * 8;
+  if (a.xbuf_bytes < need_x)
+    return fail(G4B_ERR_BAD_ARG, "exchange: buffers too small (need %lld bytes per rank)", (long long)need_x);
   p.status = device_status_ptr();
   if (p.status == nullptr) return G4B_ERR_CUDA;
   const dim3 grid((unsigned)rows, (unsigned)p.slices, 1);
@@ -234,8 +234,7 @@ extern "C" int g4b_attn_combine_exchange(const G4bExchangeArgs* args, void* cuda
   return g4b::launch_combine_exchange(*args, (cudaStream_t)cuda_stream);
 }
 
-extern "C" int64_t g4b_exchange_buffer_bytes(int world, int64_t rows, int head_dim, int64_t* flags_bytes) {
+extern "C" int64_t g4b_exchange_buffer_bytes(int world, int64_t rows, int head_dim) {
   const int64_t slices = (head_dim + g4b::kXCols - 1) / g4b::kXCols;
-  if (flags_bytes != nullptr) *flags_bytes = 2ll * world * rows * slices * 4;
-  return 2ll * world * rows * slices * (g4b::kXCols + 2) * 4;
+  return 2ll * world * rows * slices * (g4b::kXCols + 2) * 8;
 }

@@ -101,17 +101,16 @@ def unpack_gathered(gathered):
 class PartialExchange:
     """Cross-GPU split-KV merge in one launch (``g4b_attn_combine_exchange``): the local
     partials are merged, the merged partials travel between the GPUs by plain stores into
-    peer-mapped buffers with a flag per piece, and every rank finishes the merge -- no
-    collective call, no second launch.
+    peer-mapped buffers as 8-byte words that carry the launch count beside the value (a word
+    announces itself: no fence, no flag), and every rank finishes the merge -- no collective
+    call, no second launch.
 
     ``PartialExchange(rows, head_dim)`` inside an initialised NCCL process group allocates the
-    exchange buffer and the flag array in symmetric memory (``torch.distributed._symmetric_memory``)
-    and maps every peer's.  ``peers=[(xbuf, flags), ...]`` instead takes ready-made local
-    tensors, one pair per rank (a world of one, or a test that plays the other ranks' part)."""
+    exchange buffer in symmetric memory (``torch.distributed._symmetric_memory``) and maps
+    every peer's.  ``peers=[xbuf, ...]`` instead takes ready-made zeroed local tensors, one per
+    rank (a world of one, or a test that plays the other ranks' part)."""
 
     def __init__(self, rows: int, head_dim: int, *, device=None, group=None, peers=None, rank=None):
-        import ctypes
-
         import torch
 
         from g4b_b200 import _cabi
@@ -123,33 +122,27 @@ class PartialExchange:
             import torch.distributed as dist
 
             self.world, self.rank = dist.get_world_size(group), dist.get_rank(group)
-        fb = ctypes.c_int64(0)
-        self.xbuf_bytes = int(_cabi.load().g4b_exchange_buffer_bytes(self.world, rows, head_dim, ctypes.byref(fb)))
-        self.flags_bytes = int(fb.value)
+        self.xbuf_bytes = int(_cabi.load().g4b_exchange_buffer_bytes(self.world, rows, head_dim))
         if peers is not None:
-            self.xbuf_ptrs = [int(x.data_ptr()) for x, _ in peers]
-            self.flag_ptrs = [int(f.data_ptr()) for _, f in peers]
-            for x, f in peers:
-                if x.numel() * x.element_size() < self.xbuf_bytes or f.numel() * f.element_size() < self.flags_bytes:
-                    raise ValueError(f"exchange buffers need {self.xbuf_bytes} and {self.flags_bytes} bytes per rank")
+            self.xbuf_ptrs = [int(x.data_ptr()) for x in peers]
+            for x in peers:
+                if x.numel() * x.element_size() < self.xbuf_bytes:
+                    raise ValueError(f"exchange buffers need {self.xbuf_bytes} bytes per rank")
             self._keep += list(peers)
-            device = peers[self.rank][0].device
+            device = peers[self.rank].device
         else:
             import torch.distributed as dist
             import torch.distributed._symmetric_memory as symm
 
             device = torch.device(device if device is not None else f"cuda:{torch.cuda.current_device()}")
             name = (group or dist.group.WORLD).group_name
-            xbuf = symm.empty(self.xbuf_bytes // 4, dtype=torch.float32, device=device)
-            flags = symm.empty(self.flags_bytes // 4, dtype=torch.int32, device=device)
+            xbuf = symm.empty(self.xbuf_bytes // 8, dtype=torch.int64, device=device)
             xbuf.zero_()
-            flags.zero_()
-            hx, hf = symm.rendezvous(xbuf, name), symm.rendezvous(flags, name)
+            hx = symm.rendezvous(xbuf, name)
             self.xbuf_ptrs = [int(p) for p in hx.buffer_ptrs]
-            self.flag_ptrs = [int(p) for p in hf.buffer_ptrs]
-            self._keep += [xbuf, flags, hx, hf]
+            self._keep += [xbuf, hx]
             torch.cuda.synchronize(device)
-            dist.barrier(group)      # nobody pushes before every rank's flags are zero
+            dist.barrier(group)      # nobody pushes before every rank's buffer is zero
         self.state = torch.zeros(2, dtype=torch.int32, device=device)
 
     def combine(self, partial_o, partial_l, partial_m, o, num_splits: int, *, user_phase=None, phase: int = 2, stream=None):
@@ -167,9 +160,8 @@ class PartialExchange:
         a.user_phase = _cabi.as_tensor(user_phase)
         for r in range(self.world):
             a.xbuf[r] = self.xbuf_ptrs[r]
-            a.flags[r] = self.flag_ptrs[r]
         a.state = self.state.data_ptr()
-        a.xbuf_bytes, a.flags_bytes = self.xbuf_bytes, self.flags_bytes
+        a.xbuf_bytes = self.xbuf_bytes
         a.num_splits, a.phase, a.world, a.rank = int(num_splits), int(phase), self.world, self.rank
         _cabi.check(_cabi.load().g4b_attn_combine_exchange(ctypes.byref(a), ctypes.c_void_p(_cabi.current_stream(stream))))
         return None

@@ -240,13 +240,13 @@ int g4b_rope_norm_append(const G4bRopeAppendArgs* args, void* cuda_stream);
  * the arithmetic is the reference's merge (g4b/kernels/fa2.py:618-626) applied twice: the
  * `num_splits` local partials are merged into one, the merged partials of all ranks are
  * exchanged through peer-mapped memory (every rank stores its piece into every rank's
- * exchange buffer and raises a flag there), and merged again into `o`.  Every rank must make
- * the same sequence of calls with the same shapes, and a slot must be in `phase` on all
- * ranks or on none.
+ * exchange buffer as 8-byte words {value, launch count}, so a word announces itself), and
+ * merged again into `o`.  Every rank must make the same sequence of calls with the same
+ * shapes, and a slot must be in `phase` on all ranks or on none.
  *
- * xbuf[r] / flags[r]: address, in this process, of rank r's exchange buffer / flag array
- * (own entries: ordinary local memory; others: peer mappings).  Sizes per rank from
- * g4b_exchange_buffer_bytes(); both must start zeroed and be used for nothing else.  state:
+ * xbuf[r]: address, in this process, of rank r's exchange buffer (own entry: ordinary local
+ * memory; others: peer mappings), 8-byte aligned.  Size per rank from
+ * g4b_exchange_buffer_bytes(); it must start zeroed and be used for nothing else.  state:
  * two zero-initialised uint32 in local memory.  A peer that does not show up within about a
  * second leaves code 0x401 in the device status word.
  */
@@ -257,19 +257,16 @@ typedef struct G4bExchangeArgs {
   G4bTensor o;             /* [B, H, Tq, D] */
   G4bTensor user_phase;    /* optional uint8 [B] */
   void* xbuf[8];
-  void* flags[8];
   void* state;
   int64_t xbuf_bytes;      /* size of every rank's exchange buffer */
-  int64_t flags_bytes;     /* size of every rank's flag array */
   int32_t num_splits;
   int32_t phase;
   int32_t world;
   int32_t rank;
 } G4bExchangeArgs;
 int g4b_attn_combine_exchange(const G4bExchangeArgs* args, void* cuda_stream);
-/* Bytes of one rank's exchange buffer (return value) and flag array (*flags_bytes) for
- * `rows` = B * H * Tq rows of `head_dim` elements. */
-int64_t g4b_exchange_buffer_bytes(int world, int64_t rows, int head_dim, int64_t* flags_bytes);
+/* Bytes of one rank's exchange buffer for `rows` = B * H * Tq rows of `head_dim` elements. */
+int64_t g4b_exchange_buffer_bytes(int world, int64_t rows, int head_dim);
 
 /* Message of the last failing call on this thread ("" if none). No reference counterpart:
  * the reference raises Python exceptions from its wrappers (fa2.py:656-657). */

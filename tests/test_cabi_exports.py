@@ -131,14 +131,7 @@ def test_tensor_like_duck_typing():
 
 def test_exchange_buffer_sizes_host_only():
     """g4b_exchange_buffer_bytes is pure host arithmetic: 2 parities x world x rows x 32-element
-    slices x (32 + l + m) floats, and one flag word per (parity, rank, row, slice)."""
-    import ctypes
-
-    from g4b_b200 import _cabi
-
+    slices x (32 + l + m) words of 8 bytes (value, launch count)."""
     lib = _cabi.load()
-    fb = ctypes.c_int64(0)
-    xb = lib.g4b_exchange_buffer_bytes(8, 8, 256, ctypes.byref(fb))
-    assert xb == 2 * 8 * 8 * 8 * 34 * 4 and fb.value == 2 * 8 * 8 * 8 * 4
-    xb = lib.g4b_exchange_buffer_bytes(2, 3, 40, ctypes.byref(fb))      # head dim rounds up to 2 slices
-    assert xb == 2 * 2 * 3 * 2 * 34 * 4 and fb.value == 2 * 2 * 3 * 2 * 4
+    assert lib.g4b_exchange_buffer_bytes(8, 8, 256) == 2 * 8 * 8 * 8 * 34 * 8
+    assert lib.g4b_exchange_buffer_bytes(2, 3, 40) == 2 * 2 * 3 * 2 * 34 * 8      # head dim rounds up to 2 slices

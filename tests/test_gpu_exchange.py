@@ -1,7 +1,8 @@
 """Cross-GPU split-KV merge kernel on ONE GPU: the other ranks' part is played by the test,
-which writes their merged partials and flags into this rank's exchange buffer BEFORE the
-launch (so the kernel never waits for another kernel), gives the kernel local tensors in
-place of the peers' memory, and checks both what the kernel merged and what it pushed."""
+which writes their merged partials (8-byte words: value, launch count) into this rank's
+exchange buffer BEFORE the launch (so the kernel never waits for another kernel), gives the
+kernel local tensors in place of the peers' memory, and checks both what the kernel merged
+and what it pushed."""
 import pytest
 import torch
 
@@ -17,6 +18,26 @@ def merged_partial(po, pl, pm):
     m = pm.max(0).values
     w = torch.where(torch.isinf(pm), torch.zeros_like(pm), torch.exp2(pm - m))
     return (po * w[..., None]).sum(0), (pl * w).sum(0), m
+
+
+def new_buffers(cuda, world, rows, slices):
+    """One zeroed exchange buffer per rank: [parity, source rank, row, slice, 34 words] of int64."""
+    return [torch.zeros(2 * world * rows * slices * (COLS + 2), dtype=torch.int64, device=cuda) for _ in range(world)]
+
+
+def words(buf, world, rows, slices):
+    """The buffer as int32 [2, world, rows, slices, 34, 2]: [..., 0] the value's bits, [..., 1] the count."""
+    return buf.view(torch.int32).view(2, world, rows, slices, COLS + 2, 2)
+
+
+def deliver(buf, world, rows, slices, par, r, merged, epoch, cuda):
+    """Writes rank r's merged partial into a buffer the way rank r's kernel would."""
+    acc, l, m = merged
+    w = words(buf, world, rows, slices)
+    piece = torch.cat([acc.reshape(rows, slices, COLS), l.reshape(rows, 1, 1).expand(rows, slices, 1),
+                       m.reshape(rows, 1, 1).expand(rows, slices, 1)], -1).contiguous()
+    w[par, r, :, :, :, 0] = piece.view(torch.int32).to(cuda)
+    w[par, r, :, :, :, 1] = epoch
 
 
 def make_partials(gen, S, B, H, D, empty_splits=()):
@@ -38,35 +59,28 @@ def test_merge_with_peers_played_by_the_test(cuda, world, rank, o_dtype):
     want = orc.combine_partials(torch.cat([p[0] for p in parts]), torch.cat([p[1] for p in parts]),
                                 torch.cat([p[2] for p in parts]), world * S)
 
-    peers = [(torch.zeros(2 * world * rows * slices * (COLS + 2), device=cuda),
-              torch.zeros(2 * world * rows * slices, dtype=torch.int32, device=cuda)) for _ in range(world)]
+    peers = new_buffers(cuda, world, rows, slices)
     ex = PartialExchange(rows, D, peers=peers, rank=rank)
     # two launches: the launch count and the buffer parity advance on the device
     for epoch in (1, 2):
         par = epoch & 1
-        xb = peers[rank][0].view(2, world, rows, slices, COLS + 2)
-        fl = peers[rank][1].view(2, world, rows * slices)
         for r in range(world):
-            if r == rank:
-                continue
-            acc, l, m = merged[r]
-            xb[par, r, :, :, :COLS] = acc.reshape(rows, slices, COLS).to(cuda)
-            xb[par, r, :, :, COLS] = l.reshape(rows, 1).to(cuda)
-            xb[par, r, :, :, COLS + 1] = m.reshape(rows, 1).to(cuda)
-            fl[par, r] = epoch
+            if r != rank:
+                deliver(peers[rank], world, rows, slices, par, r, merged[r], epoch, cuda)
         o = torch.zeros(B, H, 1, D, dtype=o_dtype, device=cuda)
         po, pl, pm = (x.to(cuda) for x in parts[rank])
         ex.combine(po, pl, pm, o, S)
         tol = 1e-5 if o_dtype == torch.float32 else 8e-3
         assert torch.allclose(o.float().cpu(), want, atol=tol, rtol=tol), (o.float().cpu() - want).abs().max()
-        # what this rank pushed to every rank: its merged partial, and the flag
+        # what this rank pushed to every rank: its merged partial, every word with the count
         acc, l, m = merged[rank]
         for r in range(world):
-            got = peers[r][0].view(2, world, rows, slices, COLS + 2)[par, rank].cpu()
+            w = words(peers[r], world, rows, slices)[par, rank].cpu()
+            got = w[..., 0].contiguous().view(torch.float32)
             assert torch.allclose(got[..., :COLS].reshape(rows, D), acc.reshape(rows, D), atol=1e-5, rtol=1e-5)
             assert torch.allclose(got[..., COLS], l.reshape(rows, 1).expand(rows, slices), atol=1e-5, rtol=1e-5)
             assert torch.equal(got[..., COLS + 1], m.reshape(rows, 1).expand(rows, slices))
-            assert (peers[r][1].view(2, world, rows * slices)[par, rank] == epoch).all()
+            assert (w[..., 1] == epoch).all()
         assert ex.state.tolist() == [epoch, 0]
 
 
@@ -79,8 +93,7 @@ def test_strided_packed_partials_and_phase_skip(cuda):
     packed = torch.cat([po, pl[..., None], pm[..., None]], -1).to(cuda)
     want = orc.combine_partials(po, pl, pm, S)
     rows, slices = B * H, D // COLS
-    peers = [(torch.zeros(2 * rows * slices * (COLS + 2), device=cuda), torch.zeros(2 * rows * slices, dtype=torch.int32, device=cuda))]
-    ex = PartialExchange(rows, D, peers=peers, rank=0)
+    ex = PartialExchange(rows, D, peers=new_buffers(cuda, 1, rows, slices), rank=0)
     o = torch.full((B, H, 1, D), 7.0, device=cuda)
     phase = torch.tensor([2, 1], dtype=torch.uint8, device=cuda)
     ex.combine(packed[..., :D], packed[..., D], packed[..., D + 1], o, S, user_phase=phase, phase=2)
@@ -89,7 +102,7 @@ def test_strided_packed_partials_and_phase_skip(cuda):
 
 
 def test_bad_arguments_raise(cuda):
-    peers = [(torch.zeros(16, device=cuda), torch.zeros(16, dtype=torch.int32, device=cuda))]
+    peers = [torch.zeros(16, dtype=torch.int64, device=cuda)]
     with pytest.raises(ValueError):
         PartialExchange(8, 256, peers=peers, rank=0)        # buffers too small
 
@@ -103,21 +116,15 @@ def test_absent_peer_ends_in_a_status_code_not_a_hang(cuda):
     S, B, H, D, world = 4, 1, 2, 256, 2
     rows, slices = B * H, D // COLS
     po, pl, pm = make_partials(gen, S, B, H, D)
-    peers = [(torch.zeros(2 * world * rows * slices * (COLS + 2), device=cuda),
-              torch.zeros(2 * world * rows * slices, dtype=torch.int32, device=cuda)) for _ in range(world)]
+    peers = new_buffers(cuda, world, rows, slices)
     ex = PartialExchange(rows, D, peers=peers, rank=0)
     o = torch.full((B, H, 1, D), 5.0, device=cuda)
-    ex.combine(po.to(cuda), pl.to(cuda), pm.to(cuda), o, S)     # nothing ever sets rank 1's flags
+    ex.combine(po.to(cuda), pl.to(cuda), pm.to(cuda), o, S)     # nothing ever writes rank 1's words
     assert _cabi.device_status() == 0x401                      # synchronises, reads and clears
     assert (o == 5.0).all()
     assert ex.state.tolist() == [1, 0]                          # the launch still completed its bookkeeping
     # the same object works again once the peer's pieces are there
-    xb = peers[0][0].view(2, world, rows, slices, COLS + 2)
-    acc, l, m = merged_partial(po, pl, pm)
-    xb[0, 1, :, :, :COLS] = acc.reshape(rows, slices, COLS).to(cuda)
-    xb[0, 1, :, :, COLS] = l.reshape(rows, 1).to(cuda)
-    xb[0, 1, :, :, COLS + 1] = m.reshape(rows, 1).to(cuda)
-    peers[0][1].view(2, world, rows * slices)[0, 1] = 2
+    deliver(peers[0], world, rows, slices, 0, 1, merged_partial(po, pl, pm), 2, cuda)
     ex.combine(po.to(cuda), pl.to(cuda), pm.to(cuda), o, S)
     want = orc.combine_partials(torch.cat([po, po]), torch.cat([pl, pl]), torch.cat([pm, pm]), 2 * S)
     assert torch.allclose(o.cpu(), want, atol=1e-5, rtol=1e-5)
