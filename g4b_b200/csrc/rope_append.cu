@@ -8,9 +8,11 @@
 // here the row goes from registers to the cache, and q can leave in the 16-bit type the
 // prefill kernel wants.
 //
-// Pure streaming: one warp per (slot, token, head) row or per few heads of one token (the
-// sines and cosines of a token are shared by its heads), 16-byte accesses.  A lane holds the
-// elements [4l, 4l+4) and [D/2 + 4l, D/2 + 4l + 4) of the row, i.e. complete rotation pairs.
+// Pure streaming: a one-warp block per (slot, token, head) row at decode sizes, per token with
+// all its heads at prefill sizes (the sines and cosines of a token are shared by its heads),
+// 16-byte accesses.  A lane holds the elements [4l, 4l+4) and [D/2 + 4l, D/2 + 4l + 4) of the
+// row, i.e. complete rotation pairs.  The kernel is bound by instruction issue before HBM, so
+// the per-row instruction count is what the structure below is about.
 #include "common.cuh"
 
 namespace g4b {
