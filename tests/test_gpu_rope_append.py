@@ -227,3 +227,56 @@ def test_reference_rope_script_case(cuda):
     # the unrotated pairs are exactly the normalised inputs
     inv = torch.rsqrt((q * q).sum(-1) / k + 1e-6)[..., None]
     assert torch.allclose(qd.cpu()[..., k // 4: k // 2], (q * (inv * q_w))[..., k // 4: k // 2], atol=1e-6, rtol=1e-6)
+
+
+@pytest.mark.parametrize("D", [64, 200, 256, 512])
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B,Tq,paged", [(5, 1, True), (3, 6, False), (2, 2100, True), (1, 1500, False)])
+def test_engine_configuration_variants(cuda, D, dtype, B, Tq, paged):
+    """The configuration the engine runs (gemma4e.py:564-592): f32 q/k/v, q and k normed with
+    weights and rotated, v normed, q into a 16-bit q_out, k and v into 16-bit caches only.  The
+    kernel has compile-time variants for exactly this; here they run at head dims on and off
+    their full-width case, one row per warp (few rows) and a token per warp (many), ring and
+    pages, with and without V norm, far positions, and a slot off phase."""
+    gen = torch.Generator().manual_seed(D + Tq)
+    H, G = 8, 2
+    q, k, v = (randn(gen, B, Tq, h, D).permute(0, 2, 1, 3) for h in (H, G, G))
+    q_w, k_w = 1 + 0.1 * randn(gen, D), 1 + 0.1 * randn(gen, D)
+    freqs = 1.0 / (10000.0 ** (torch.arange(0, D, 2) / D))
+    before = [0, 100000, 17, 3, 50000][:B]
+    off = torch.tensor(before, dtype=torch.int32)
+    phase = torch.tensor([1, 1, 2, 1, 1][:B], dtype=torch.uint8)
+    norm_v = Tq != 6
+    if paged:
+        page = 16
+        pages_per = [(b + Tq + page - 1) // page for b in before]
+        n_pages = sum(p - b // page for p, b in zip(pages_per, before)) + 2      # only the pages the new rows touch
+        perm = torch.randperm(n_pages, generator=gen).to(torch.int32)
+        bt = torch.full((B, max(pages_per)), -1, dtype=torch.int32)
+        at = 0
+        for b, (n, first) in enumerate(zip(pages_per, before)):
+            lo = first // page
+            bt[b, lo:n] = perm[at:at + n - lo]
+            at += n - lo
+        kc0, vc0 = randn(gen, n_pages, G, page, D, dtype=dtype), randn(gen, n_pages, G, page, D, dtype=dtype)
+        extra = dict(block_tables=bt, page_size=page)
+    else:
+        T = Tq + 9
+        kc0, vc0 = randn(gen, B, G, T, D, dtype=dtype), randn(gen, B, G, T, D, dtype=dtype)
+        extra = {}
+    want_q, _, want_kc, want_vc = orc.rope_norm_append(q, k, v, freqs, off, kc0, vc0, 1e-6, q_rmsnorm_w=q_w,
+                                                       k_rmsnorm_w=k_w, norm_v=norm_v, user_phase=phase, phase=1, **extra)
+    kc, vc = kc0.to(cuda), vc0.to(cuda)
+    q_out = torch.zeros(B, H, Tq, D, dtype=dtype, device=cuda)
+    qd = q.to(cuda)
+    dev_extra = {key: (val.to(cuda) if torch.is_tensor(val) else val) for key, val in extra.items()}
+    rope_norm_append(qd, k.to(cuda), v.to(cuda), freqs.to(cuda), off.to(cuda), kc, vc, 1e-6, q_out=q_out,
+                     q_rmsnorm_w=q_w.to(cuda), k_rmsnorm_w=k_w.to(cuda), norm_v=norm_v, user_phase=phase.to(cuda),
+                     phase=1, **dev_extra)
+    tol = ulp_tol(dtype)
+    assert torch.equal(qd.cpu(), q), "q must stay untouched when q_out is given"
+    assert torch.allclose(q_out.float().cpu(), want_q, atol=tol, rtol=tol)
+    assert torch.allclose(kc.float().cpu(), want_kc.float(), atol=tol, rtol=tol)
+    assert torch.allclose(vc.float().cpu(), want_vc.float(), atol=tol, rtol=tol)
+    same = (want_kc == kc0).all(-1)
+    assert torch.equal(kc.cpu()[same], kc0[same]) and torch.equal(vc.cpu()[same], vc0[same])
