@@ -110,6 +110,7 @@ EXPORTS = {
     "g4b_last_error_string": (ctypes.c_char_p, []),
     "g4b_abi_version": (ctypes.c_int, []),
     "g4b_device_status": (ctypes.c_int, [ctypes.c_void_p, ctypes.POINTER(ctypes.c_int32)]),
+    "g4b_set_validate_only": (None, [ctypes.c_int]),
 }
 
 _lib = None
@@ -154,6 +155,45 @@ def _strides(t) -> list[int]:
     raise RuntimeError("Failed to normalize tensor stride into list[int]")
 
 
+_validate_only_depth = 0
+
+
+class validate_only:
+    """``with _cabi.validate_only():`` -- the library checks arguments and launches nothing
+    (g4b_set_validate_only), and the wrappers accept host tensors.  For tests of the argument
+    checks on machines without a GPU; a call that passes every check returns normally."""
+
+    def __enter__(self):
+        global _validate_only_depth
+        _validate_only_depth += 1
+        load().g4b_set_validate_only(1)
+        return self
+
+    def __exit__(self, *exc):
+        global _validate_only_depth
+        _validate_only_depth -= 1
+        if _validate_only_depth == 0:
+            load().g4b_set_validate_only(0)
+        return False
+
+
+def _check_device(t) -> None:
+    """A kernel given a host pointer, or a pointer into another GPU's memory that is not
+    mapped here, faults.  Torch tensors say where they live, so refuse them here; other
+    tensor-likes (the reference's own Tensor class) carry no device and pass."""
+    is_cuda = getattr(t, "is_cuda", None)
+    if is_cuda is None or _validate_only_depth > 0:
+        return
+    if not is_cuda:
+        raise ValueError("expected a CUDA tensor, got one in host memory")
+    import torch
+
+    cur = torch.cuda.current_device()
+    if t.device.index is not None and t.device.index != cur:
+        raise ValueError(f"tensor lives on cuda:{t.device.index} but the current device is cuda:{cur}; "
+                         "make its device current (torch.cuda.device) before the call")
+
+
 def as_tensor(t) -> G4bTensor:
     """Packs a tensor-like (or None) into the C view; strides are in elements."""
     out = G4bTensor()
@@ -163,6 +203,7 @@ def as_tensor(t) -> G4bTensor:
         return out
     if not (hasattr(t, "shape") and hasattr(t, "stride") and hasattr(t, "dtype") and hasattr(t, "data_ptr")):
         raise TypeError(f"expected a tensor-like with shape/stride/dtype/data_ptr, got {type(t).__name__}")
+    _check_device(t)
     shape = list(t.shape)
     if len(shape) > 5:
         raise ValueError("tensors of rank > 5 are not supported")
@@ -195,7 +236,7 @@ _VALUE_ERRORS = {-1, -2, -3, -4, -7}
 
 def check(rc: int) -> None:
     """Maps a G4B_ERR_* code to ValueError (bad arguments) or RuntimeError (CUDA / device)."""
-    if rc == 0:
+    if rc == 0 or rc == 1:      # 1 = G4B_VALIDATED (validate-only mode)
         return
     msg = load().g4b_last_error_string().decode("utf-8", "replace")
     if rc in _VALUE_ERRORS:
@@ -206,5 +247,7 @@ def check(rc: int) -> None:
 def device_status(stream=None) -> int:
     """Synchronises the stream and returns (and clears) the device status word."""
     out = ctypes.c_int32(0)
-    check(load().g4b_device_status(ctypes.c_void_p(current_stream(stream)), ctypes.byref(out)))
+    rc = load().g4b_device_status(ctypes.c_void_p(current_stream(stream)), ctypes.byref(out))
+    if rc != -6:                # G4B_ERR_DEVICE_WAIT only says that the word was not zero
+        check(rc)
     return int(out.value)

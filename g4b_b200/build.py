@@ -43,7 +43,6 @@ def _digest() -> str:
         h.update(f.name.encode())
         h.update(f.read_bytes())
     h.update(" ".join(NVCC_FLAGS).encode())
-    h.update(os.environ.get("G4B_NVCC_EXTRA", "").encode())
     return h.hexdigest()
 
 
@@ -58,7 +57,6 @@ def build(force: bool = False, verbose: bool = False) -> Path:
         return LIB
     nvcc = _nvcc()
     extra = ["-Xptxas", "-v"] if verbose else []
-    extra += os.environ.get("G4B_NVCC_EXTRA", "").split()   # e.g. -DG4B_TRACE for a developer build
 
     def compile_one(src: str) -> Path:
         obj = objdir / (Path(src).stem + ".o")

@@ -12,15 +12,27 @@ namespace g4b {
 static thread_local char tls_error[512] = {0};
 char* last_error_buffer() { return tls_error; }
 
+// Validate-only mode of the calling thread (g4b_set_validate_only): launchers stop after
+// their argument checks, before the first CUDA call, and return G4B_VALIDATED.
+static thread_local bool tls_validate_only = false;
+bool validate_only_mode() { return tls_validate_only; }
+
 // One status word per device, in static device memory (nothing is allocated).
 __device__ int32_t g_device_status = 0;
 
 int32_t* device_status_ptr() {
   constexpr int kMaxDev = 64;
+  // Filled without a lock: two threads that race on an entry both store the same address, and
+  // an aligned pointer store is not torn.
   static int32_t* cache[kMaxDev] = {nullptr};
   int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDev) {
-    fail(G4B_ERR_CUDA, "cudaGetDevice failed");
+  const cudaError_t ge = cudaGetDevice(&dev);
+  if (ge != cudaSuccess) {
+    fail(G4B_ERR_CUDA, "cudaGetDevice failed: %s", cudaGetErrorString(ge));
+    return nullptr;
+  }
+  if (dev < 0 || dev >= kMaxDev) {
+    fail(G4B_ERR_CUDA, "device index %d outside 0..%d", dev, kMaxDev - 1);
     return nullptr;
   }
   if (cache[dev] == nullptr) {
@@ -155,6 +167,8 @@ using namespace g4b;
 extern "C" {
 
 int g4b_abi_version(void) { return G4B_ABI_VERSION; }
+
+void g4b_set_validate_only(int on) { tls_validate_only = on != 0; }
 
 const char* g4b_last_error_string(void) { return last_error_buffer(); }
 
@@ -303,11 +317,13 @@ int g4b_device_status(void* cuda_stream, int32_t* status_out) {
   G4B_CUDA_CHECK(cudaStreamSynchronize(st));
   G4B_CUDA_CHECK(cudaMemcpyAsync(&v, dptr, sizeof(v), cudaMemcpyDeviceToHost, st));
   G4B_CUDA_CHECK(cudaStreamSynchronize(st));
+  if (status_out != nullptr) *status_out = v;
   if (v != 0) {
     G4B_CUDA_CHECK(cudaMemcpyAsync(dptr, &zero, sizeof(zero), cudaMemcpyHostToDevice, st));
     G4B_CUDA_CHECK(cudaStreamSynchronize(st));
+    return fail(G4B_ERR_DEVICE_WAIT, "a kernel recorded status 0x%x (0x1xx / 0x2xx: bad block-table entry in an append / "
+                "decode launch, 0x3xx: a bounded wait of the prefill kernel ran out, 0x4xx: a peer did not show up)", v);
   }
-  if (status_out != nullptr) *status_out = v;
   return G4B_OK;
 }
 

@@ -155,6 +155,7 @@ int launch_combine(const G4bCombineArgs& a, cudaStream_t st) {
   if (rows == 0) return G4B_OK;
   if (rows > 0x7fffffffLL) return fail(G4B_ERR_UNSUPPORTED, "combine: too many rows");
   if (p.S > kCombineMaxSplits) return fail(G4B_ERR_TOO_LARGE, "combine: at most %d splits", kCombineMaxSplits);
+  G4B_STOP_IF_VALIDATE_ONLY();
   // Split groups per block: at least enough that the block's lanes do not reach past the head
   // dim, then more (narrower blocks, more of them) only while the grid is short of a few
   // waves -- every block repeats phase 1 and pays two block-wide reductions.

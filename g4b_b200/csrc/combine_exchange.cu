@@ -215,6 +215,7 @@ int launch_combine_exchange(const G4bExchangeArgs& a, cudaStream_t st) {
   const int64_t need_x = 2ll * a.world * rows * p.slices * (kXCols + 2) * 8;
   if (a.xbuf_bytes < need_x)
     return fail(G4B_ERR_BAD_ARG, "exchange: buffers too small (need %lld bytes per rank)", (long long)need_x);
+  G4B_STOP_IF_VALIDATE_ONLY();
   p.status = device_status_ptr();
   if (p.status == nullptr) return G4B_ERR_CUDA;
   const dim3 grid((unsigned)rows, (unsigned)p.slices, 1);

@@ -54,6 +54,11 @@ inline bool contiguous_from(const G4bTensor& t, int from) {
   return true;
 }
 
+// True while the calling thread is in validate-only mode: a launcher that has finished its
+// argument checks returns G4B_VALIDATED instead of touching the CUDA runtime.
+bool validate_only_mode();  // api.cu
+#define G4B_STOP_IF_VALIDATE_ONLY() do { if (::g4b::validate_only_mode()) return G4B_VALIDATED; } while (0)
+
 // Device status word: 0, or the code of the first bounded wait that gave up.
 int32_t* device_status_ptr();  // address of the __device__ word on the current device (api.cu)
 

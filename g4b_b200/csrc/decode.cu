@@ -399,6 +399,7 @@ int launch_decode(const G4bAttnArgs& a, int num_splits, cudaStream_t st) {
   p.num_splits = num_splits;
   p.q_dtype = a.q.dtype; p.o_dtype = a.o.dtype; p.po_dtype = a.partial_o.dtype;
   p.scale_log2 = a.scale * 1.4426950408889634f;
+  G4B_STOP_IF_VALIDATE_ONLY();
   p.status = device_status_ptr();
   if (p.status == nullptr) return G4B_ERR_CUDA;
   if (p.B == 0) return G4B_OK;

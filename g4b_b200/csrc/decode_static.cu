@@ -26,11 +26,17 @@ static __device__ __align__(256) float g_decode_scratch[(size_t)kStaticRows * kS
 // with that device current.
 static float* decode_scratch_on_current_device() {
   constexpr int kMaxDev = 64;
+  // Filled without a lock: threads that race on an entry all store the same address, and an
+  // aligned pointer store is not torn.
   static float* cache[kMaxDev] = {nullptr};
   int dev = 0;
   cudaError_t e = cudaGetDevice(&dev);
-  if (e != cudaSuccess || dev < 0 || dev >= kMaxDev) {
+  if (e != cudaSuccess) {
     fail(G4B_ERR_CUDA, "cudaGetDevice failed: %s", cudaGetErrorString(e));
+    return nullptr;
+  }
+  if (dev < 0 || dev >= kMaxDev) {
+    fail(G4B_ERR_CUDA, "device index %d outside 0..%d", dev, kMaxDev - 1);
     return nullptr;
   }
   if (cache[dev] == nullptr) {
@@ -58,18 +64,25 @@ extern "C" int g4b_attn_decode_static_scratch(const G4bAttnArgs* args, void* cud
     return fail(G4B_ERR_UNSUPPORTED, "g4b_attn_decode_static_scratch needs q of shape [B,H,1,D]");
   if (a.q.shape[3] != kStaticHeadDim)
     return fail(G4B_ERR_UNSUPPORTED, "g4b_attn_decode_static_scratch is built for head dim %d", kStaticHeadDim);
-  int splits = a.num_kv_splits > 0 ? a.num_kv_splits
-                                   : g4b_select_kv_splits(a.ctx_window_size, kStaticMaxSplits, a.phase, 1);
-  if (splits < 1) splits = 1;
   const int64_t B = a.q.shape[0], H = a.q.shape[1];
+  int splits = a.num_kv_splits;
+  if (splits <= 0) {
+    // no count asked for: the reference's table, cut down to what the array holds (one split
+    // needs no workspace at all), so that large batches are served rather than refused
+    splits = g4b_select_kv_splits(a.ctx_window_size, kStaticMaxSplits, a.phase, 1);
+    const int64_t fit = B * H > 0 ? kStaticRows / (B * H) : kStaticMaxSplits;
+    if (splits > fit) splits = (int)fit;
+    if (splits < 1) splits = 1;
+  }
   const int64_t rows = (int64_t)splits * B * H;
-  if (splits > kStaticMaxSplits || rows > kStaticRows)
+  if (splits > kStaticMaxSplits || (splits > 1 && rows > kStaticRows))
     return fail(G4B_ERR_TOO_LARGE,
                 "static decode workspace too small: %d splits x %lld slots x %lld heads = %lld rows, the fixed "
                 "maximum is %d splits and %d rows; pass your own partial buffers to g4b_flash_attention instead",
                 splits, (long long)B, (long long)H, (long long)rows, kStaticMaxSplits, kStaticRows);
   a.num_kv_splits = splits;
   if (splits == 1) return g4b_attn_decode(&a, cuda_stream);   // no workspace needed at all
+  G4B_STOP_IF_VALIDATE_ONLY();
 
   float* scratch = decode_scratch_on_current_device();
   if (scratch == nullptr) return G4B_ERR_CUDA;

@@ -196,6 +196,7 @@ int launch_kv_append(const G4bAppendArgs& a, cudaStream_t st) {
   p.B = (int)a.x.shape[0]; p.G = (int)a.x.shape[1]; p.Tq = (int)a.x.shape[2]; p.D = (int)a.x.shape[3];
   p.offsets_are_i64 = a.cache_offsets.dtype == G4B_I64;
   p.phase = a.phase; p.eps = a.rmsnorm_eps;
+  G4B_STOP_IF_VALIDATE_ONLY();
   p.status = device_status_ptr();
   if (p.status == nullptr) return G4B_ERR_CUDA;
   if (p.block_tables != nullptr) {
@@ -233,6 +234,7 @@ __global__ void advance_kernel(int32_t* in_tok, const int32_t* out_tok, int32_t*
 int launch_advance(const G4bAdvanceArgs& a, cudaStream_t st) {
   const int B = (int)a.input_token_ids.shape[1];
   if (B == 0) return G4B_OK;
+  G4B_STOP_IF_VALIDATE_ONLY();
   advance_kernel<<<(B + 255) / 256, 256, 0, st>>>(
       (int32_t*)a.input_token_ids.ptr, (const int32_t*)a.out_token_ids.ptr,
       (int32_t*)a.cache_offsets.ptr, (int32_t*)a.time_dim_sizes.ptr,

@@ -35,7 +35,6 @@
 #include "sm100_ptx.cuh"
 
 #include <cudaTypedefs.h>
-#include <stdlib.h>
 
 namespace g4b {
 
@@ -118,25 +117,6 @@ struct Barriers {
 };
 
 __device__ __forceinline__ void record(int32_t* status, int32_t code) { atomicCAS(status, 0, code); }
-
-// Optional timeline of one CTA (developer builds with -DG4B_TRACE only): SM cycle counter at
-// the main hand-over points of every tile, read back with g4b_debug_read_trace().
-#ifdef G4B_TRACE
-__device__ long long g_trace[128][16];
-__device__ long long g_item_trace[128][16];
-#define G4B_TRACE_AT(tile, slot)                                                         \
-  do {                                                                                   \
-    if (blockIdx.x == 0 && n_done == 0 && lane == 0 && (tile) < 128) g_trace[(tile)][(slot)] = clock64(); \
-  } while (0)
-// per work item (row = item count of worker 0)
-#define G4B_ITEM_AT(slot)                                                                \
-  do {                                                                                   \
-    if (blockIdx.x == 0 && lane == 0 && n_done < 128) g_item_trace[n_done][(slot)] = clock64(); \
-  } while (0)
-#else
-#define G4B_TRACE_AT(tile, slot) do {} while (0)
-#define G4B_ITEM_AT(slot) do {} while (0)
-#endif
 
 // Geometry of one work item = 128 query rows of one head (fa2.py:52-64).  Ring mode counts
 // keys from the oldest one the cache exposes (fa2.py:52-56).  A paged cache is addressed by
@@ -346,6 +326,10 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     // boundary: refuse to run otherwise.
     if (leader) {
       int32_t a = *reinterpret_cast<volatile int32_t*>(p.status);
+      // only a wait of this kernel that ran out (0x3xx) drains it: a bad block-table entry that
+      // an append, decode or earlier prefill launch reported must not turn later launches into
+      // no-ops
+      if ((a & 0xf00) != 0x300 || a == kErrBadPage) a = 0;
       if (a == 0 && (ptx::smem_u32(smem_raw) & 1023u) != 0) { record(p.status, kErrSmemAlign); a = kErrSmemAlign; }
       bars->abort_flag = a;
       if constexpr (kPair) ptx::st_cluster_u32(ptx::map_to_cta(ptx::smem_u32(&bars->abort_flag), 1), (uint32_t)a);
@@ -421,7 +405,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       if (!w) { if (lane == 0) record(p.status, kErrStageFree); ok = false; }
       return w != 0;
     };
-    G4B_ITEM_AT(0);   // producer reaches the item
     {
       // the Q buffer is free once the last Q.K^T of the previous item has run
       int w = 1;
@@ -429,7 +412,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       w = __shfl_sync(0xffffffffu, w, 0);
       if (!w) { if (lane == 0) record(p.status, kErrQEmpty); ok = false; break; }
     }
-    G4B_ITEM_AT(1);   // Q buffer free, Q load goes out
     if (p.q_f32 != nullptr) {
       // f32 q: the warp reads one row (1 KB) per pass, rounds it to the cache type and writes
       // the four 128-byte-swizzled slabs the TMA load would have produced; rows past Tq are
@@ -593,9 +575,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       }
       const int st = cc % kSt;
       const uint32_t full = issuer_bar(&bars->kv_full[st]);
-      G4B_TRACE_AT(j, 7);
       if (!wait_empty(st, cc) || !wait_stage()) return;
-      G4B_TRACE_AT(j, 5);   // K(j) slot free, loads go out
       uint8_t* dst = sRing + st * kChunkBytes;
       if (!manual) {
         if (lane == 0) ptx::mbar_arrive_expect_tx_cluster(full, kChunkBytes);
@@ -633,9 +613,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       }
       const int st = cc % kSt;
       const uint32_t full = issuer_bar(&bars->kv_full[st]);
-      G4B_TRACE_AT(j, 6);
       if (!wait_empty(st, cc) || !wait_stage()) return;
-      G4B_TRACE_AT(j, 4);   // V(j) slot free, loads go out
       uint8_t* dst = sRing + st * kChunkBytes;
       if (!manual) {
         if (lane == 0) ptx::mbar_arrive_expect_tx_cluster(full, kChunkBytes);
@@ -709,11 +687,9 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         if (item < 0) continue;
         G4B_ITEM_GEOMETRY(item);
         if (n_tiles <= 0) continue;
-        G4B_ITEM_AT(2);   // issuer reaches the item
         ok = wait_all(bar_q, n_done & 1);
         if (!ok) { if (lane == 0) record(p.status, kErrQFull); break; }
         ptx::tc_fence_after();
-        G4B_ITEM_AT(3);   // Q seen by the issuer
         auto issue_qk = [&](int j) {
           const int t = tg + j;
           const uint32_t d_tmem = tmem + ((t & 1) ? kColS1 : kColS0);
@@ -737,7 +713,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
             if (j == n_tiles - 1) commit_both(&bars->q_empty);   // last use of this item's Q
           }
           __syncwarp();
-          G4B_TRACE_AT(j, 0);   // QK(j) issued
           ++cc;
         };
         auto issue_pv = [&](int j) {
@@ -749,7 +724,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           const int t = tg + j;
           const uint32_t v_lo = (ring_lo + st * (kChunkBytes >> 4)) | kLoVMajor;
           const uint32_t p_tmem = tmem + ((t & 1) ? kColS1 : kColS0);
-          G4B_TRACE_AT(j, 3);   // V chunk of tile j seen by the issuer
           if (j == 0 && n_done > 0) {
             // the first product of an item overwrites O: the previous item's O must have been read
             if (!wait_all(ptx::smem_u32(&bars->o_free), (n_done - 1) & 1)) {
@@ -765,7 +739,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
               ok = false; return;
             }
             ptx::tc_fence_after();
-            G4B_TRACE_AT(j, 1 + part);   // P part A / B seen by the issuer
             if (ptx::elect_one()) {
 #pragma unroll
               for (int i = 0; i < 4; ++i) {
@@ -790,7 +763,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           issue_pv(j);
           if (ok && j + 2 < n_tiles) issue_qk(j + 2);
         }
-        G4B_ITEM_AT(4);   // last P.V of the item issued
         tg += n_tiles;
         ++n_done;
         }   // work items
@@ -851,7 +823,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         if (j == n_tiles - 1) ptx::tc_commit(ptx::smem_u32(&bars->q_empty));   // last use of this item's Q
       }
       __syncwarp();
-      G4B_TRACE_AT(j, 0);   // QK(j) issued
     };
     auto issue_pv = [&](int j) {
       // both V chunks first (they landed long ago), then P in the order the softmax warps
@@ -868,7 +839,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       }
       const int t = tg + j;
       const uint32_t p_tmem = tmem + ((t & 1) ? kColS1 : kColS0);
-      G4B_TRACE_AT(j, 3);   // V chunks of tile j seen by the issuer
       if (j == 0 && n_done > 0) {
         // the first product of an item overwrites O: the previous item's O must have been read
         if (!wait_all(ptx::smem_u32(&bars->o_free), (n_done - 1) & 1)) {
@@ -884,7 +854,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
           ok = false; return;
         }
         ptx::tc_fence_after();
-        G4B_TRACE_AT(j, 1 + part);   // P part A / B seen by the issuer
         if (ptx::elect_one()) {
 #pragma unroll
           for (int vc = 0; vc < 2; ++vc) {
@@ -978,8 +947,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         record(p.status, kErrSFull); ok = false; break;
       }
       ptx::tc_fence_after();
-      if (warp == 2) G4B_TRACE_AT(j, 8);   // S(j) seen by the softmax warp
-      if (warp == 2 && j == 0) G4B_ITEM_AT(5);
       const int kbase = (tile_lo + j) * kBN;
       // warp-uniform: does any row of this CTA need element masks in this tile?
       const bool need_mask = (p.causal && kbase + kBN - 1 > qpos_min) || (kbase + kBN > window) ||
@@ -989,7 +956,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       ptx::tmem_ld32(trow + s_col + half * 64, sraw[0]);
       ptx::tmem_ld32(trow + s_col + half * 64 + 32, sraw[1]);
       ptx::tc_wait_ld();
-      if (warp == 2) G4B_TRACE_AT(j, 9);   // S(j) in registers
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
         const int nlo = lo_r - kbase - half * 64, nhi = hi_r - kbase - half * 64;
@@ -1040,7 +1006,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         record(p.status, kErrPair); ok = false; break;
       }
       ++pair_phase;
-      if (warp == 2) G4B_TRACE_AT(j, 10);  // partner's maximum received
       mx = fmaxf(mx, xm[(half ^ 1) * kBM + r]);
       const float m_blk = mx * p.scale_log2;
       const bool exceed = m_blk > m_used + 8.f;
@@ -1052,7 +1017,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         ptx::tc_wait_st();
         ptx::tc_fence_before();
         arrive_issuer(bar_pa);
-        if (warp == 2) G4B_TRACE_AT(j, 11);  // P part A published
         const float neg_m = -m_used;
 #pragma unroll
         for (int i = 0; i < 32; i += 2) {
@@ -1066,7 +1030,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         ptx::tc_wait_st();
         ptx::tc_fence_before();
         arrive_issuer(bar_pb);
-        if (warp == 2) G4B_TRACE_AT(j, 12);  // P part B published
         // keep the PV-done phase bookkeeping in step (no stall: PV(j-1) ended long ago)
         if (j > 0 && !__all_sync(0xffffffffu, ptx::mbar_wait(bar_pv, (t - 1) & 1))) {
           record(p.status, kErrPvDone); ok = false;
@@ -1194,7 +1157,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     }
 
     // ---- epilogue: O / l -> global ----
-    if (warp == 2) G4B_ITEM_AT(6);   // all P of the item published
     if (ok) {
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(bar_pv, (tg + n_tiles - 1) & 1))) { record(p.status, kErrPvDone); ok = false; }
       ptx::tc_fence_after();
@@ -1266,7 +1228,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         }
         ptx::tc_fence_before();
         arrive_issuer(issuer_bar(&bars->o_free));
-        if (warp == 2) G4B_ITEM_AT(7);   // O read out
         if constexpr (kStageOut) {
           // A lane owns a row, and rows are kilobytes apart in memory: stored directly, every
           // 16-byte store touches its own line.  Instead the warp turns its [32 rows x 64
@@ -1309,7 +1270,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         }
       }
     }
-    if (warp == 2) G4B_ITEM_AT(8);   // item stored
     tg += n_tiles;
     ++n_done;
     }   // work items
@@ -1405,16 +1365,6 @@ static int launch_typed(const CUtensorMap& qm, const CUtensorMap& km, const CUte
 
 }  // namespace
 
-#ifdef G4B_TRACE
-extern "C" int g4b_debug_read_item_trace(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_item_trace, sizeof(long long) * 128 * 16);
-}
-extern "C" int g4b_debug_read_trace(long long* out) {
-  return (int)cudaMemcpyFromSymbol(out, g_trace, sizeof(long long) * 128 * 16);
-}
-
-#endif
-
 int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   const bool paged = a.block_tables.ptr != nullptr;
   const bool q_f32 = a.q.dtype == G4B_F32;
@@ -1437,10 +1387,9 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   const int64_t n_q_tiles = (Tq + kBM - 1) / kBM;
   if (B * H * n_q_tiles > 0x7fffffffLL) return fail(G4B_ERR_UNSUPPORTED, "prefill: too many work items");
 
-  // Two heads of one kv head per CTA pair when the head counts allow it; G4B_PREFILL_SINGLE_CTA=1
-  // forces the one-CTA form (for comparisons).
-  static const bool force_single = []() { const char* e = getenv("G4B_PREFILL_SINGLE_CTA"); return e && e[0] == '1'; }();
-  const bool pair = !force_single && (H % 2 == 0) && ((H / G) % 2 == 0);
+  // Two heads of one kv head per CTA pair when the head counts allow it.
+  const bool pair = (H % 2 == 0) && ((H / G) % 2 == 0);
+  G4B_STOP_IF_VALIDATE_ONLY();
   CUtensorMap qm, km, vm;
   int rc;
   {
@@ -1479,9 +1428,7 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   p.by_H.set((uint32_t)H);
   p.by_HperG.set((uint32_t)(H / G));
   p.by_T.set((uint32_t)(paged ? 1 : T));
-  // G4B_PREFILL_STAGE_OUT=0 forces direct output stores (for tests that cover both forms)
-  static const bool no_stage = []() { const char* e = getenv("G4B_PREFILL_STAGE_OUT"); return e && e[0] == '0'; }();
-  const bool stage_out = pair && a.o.dtype != G4B_F32 && !no_stage;
+  const bool stage_out = pair && a.o.dtype != G4B_F32;
   // tiles per work item, from what the host knows (context lengths live on the device)
   const int64_t est_tiles = a.sliding_window > 0 ? (a.sliding_window + 127) / 128 + 1 : (int64_t)a.ctx_window_size / 256 + 1;
   const bool short_items = est_tiles <= 12;

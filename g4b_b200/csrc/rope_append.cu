@@ -439,6 +439,7 @@ int launch_rope_norm_append(const G4bRopeAppendArgs& a, cudaStream_t st) {
   } else {
     p.T = 1;
   }
+  G4B_STOP_IF_VALIDATE_ONLY();
   p.status = device_status_ptr();
   if (p.status == nullptr) return G4B_ERR_CUDA;
 

@@ -19,7 +19,7 @@
 extern "C" {
 #endif
 
-#define G4B_ABI_VERSION 1
+#define G4B_ABI_VERSION 2
 
 /* element types (g4b/tensor.py dtypes that reach this path) */
 enum G4bDtype {
@@ -39,12 +39,13 @@ enum G4bStage { G4B_STAGE_FULL = 1, G4B_STAGE_CAUSAL = 3 };
 
 enum G4bStatus {
   G4B_OK = 0,
+  G4B_VALIDATED = 1,         /* validate-only mode: every argument check passed, nothing launched */
   G4B_ERR_BAD_ARG = -1,      /* null pointer, bad rank, inconsistent shapes            */
   G4B_ERR_BAD_DTYPE = -2,    /* dtype combination no kernel is built for               */
   G4B_ERR_BAD_STRIDE = -3,   /* innermost stride != 1, non-contiguous cache, alignment */
   G4B_ERR_UNSUPPORTED = -4,  /* shape outside what the kernels cover (e.g. head dim)   */
   G4B_ERR_CUDA = -5,         /* a CUDA runtime / driver call failed                    */
-  G4B_ERR_DEVICE_WAIT = -6,  /* a bounded in-kernel wait ran out (see g4b_device_status) */
+  G4B_ERR_DEVICE_WAIT = -6,  /* g4b_device_status found a code that a kernel recorded      */
   G4B_ERR_TOO_LARGE = -7     /* size beyond a stated fixed maximum                     */
 };
 
@@ -178,7 +179,9 @@ int g4b_advance_decode_state(const G4bAdvanceArgs* args, void* cuda_stream);
  * except that partial_o / partial_l / partial_m must be absent: the split-KV workspace is a
  * fixed array inside the library (8192 rows of 258 floats, 8.06 MiB per GPU, held until the
  * process exits).  Limits: head dim 256, at most 16 splits, splits * B * H <= 8192; anything
- * larger returns G4B_ERR_TOO_LARGE.  Allocates nothing.  The first call on each device looks
+ * larger returns G4B_ERR_TOO_LARGE when the split count was asked for (num_kv_splits > 0); with
+ * num_kv_splits == 0 the count of g4b_select_kv_splits is cut down to what the array holds.
+ * Allocates nothing.  The first call on each device looks
  * up the array's device address (cudaGetSymbolAddress) and should therefore be made once
  * before any stream capture on that device.  All calls share the one array, which keeps the
  * previous call's contents: nothing needs clearing (every entry the merge reads is written
@@ -277,11 +280,24 @@ int g4b_abi_version(void);
 
 /*
  * Reads (and clears) the device-side status word of the current device after
- * synchronising the given stream: 0, or a code naming the bounded wait that gave up
- * inside a kernel.  Kernels never trap; a wait that runs out makes the kernel return
- * early and record its position here.  No reference counterpart.
+ * synchronising the given stream.  Kernels never trap: one that meets a block-table entry
+ * outside the pool skips it and records 0x1xx (append) / 0x2xx (decode) / 0x309 (prefill); a
+ * bounded wait that runs out makes the kernel return early and record 0x3xx (prefill) or
+ * 0x4xx (a peer GPU that did not show up).  The word keeps the FIRST code until this call
+ * clears it.  While it holds a 0x3xx wait code every later prefill launch returns at once
+ * without computing (the tensor pipe may be in an unknown state); codes of other kernels do
+ * not stop any launch.  Returns G4B_OK with *status_out = 0, or G4B_ERR_DEVICE_WAIT with the
+ * code in *status_out.  No reference counterpart.
  */
 int g4b_device_status(void* cuda_stream, int32_t* status_out);
+
+/*
+ * Validate-only mode for the calling thread (0 = off, the default).  While it is on, every
+ * entry point above runs its argument checks and returns G4B_VALIDATED (or the error) without
+ * making a CUDA call or launching anything; pointers are never dereferenced.  For tests of
+ * the argument checks on machines without a GPU.  No reference counterpart.
+ */
+void g4b_set_validate_only(int on);
 
 #ifdef __cplusplus
 }

@@ -10,6 +10,7 @@ if str(ROOT) not in sys.path:
 
 def pytest_configure(config):
     config.addinivalue_line("markers", "gpu: needs a CUDA device (run on the B200 box with -m gpu)")
+    config.addinivalue_line("markers", "launches_allowed: a CPU test that runs outside validate-only mode")
 
 
 @pytest.fixture(scope="session", autouse=True)
@@ -28,6 +29,19 @@ def cuda():
     if not torch.cuda.is_available():
         pytest.skip("no CUDA device")
     return torch.device("cuda:0")
+
+
+@pytest.fixture(autouse=True)
+def _cpu_tests_never_launch(request):
+    """Every test that is not a GPU test runs with the library in validate-only mode: argument
+    checks run, nothing is launched, so no CPU test can hand a host pointer to a kernel."""
+    if request.node.get_closest_marker("gpu") is not None or request.node.get_closest_marker("launches_allowed") is not None:
+        yield
+        return
+    from g4b_b200 import _cabi
+
+    with _cabi.validate_only():
+        yield
 
 
 @pytest.fixture(autouse=True)

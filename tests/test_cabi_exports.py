@@ -33,7 +33,7 @@ def test_header_symbols_are_exported():
 
 def test_abi_version_and_split_policy():
     lib = _cabi.load()
-    assert lib.g4b_abi_version() == 1
+    assert lib.g4b_abi_version() == 2
     for w in (1, 1024, 4096, 4097, 8191, 8192, 32767, 32768, 131072):
         for cap in (1, 2, 4, 8, 16, 64):
             for phase, tq in ((2, 1), (1, 1), (2, 2)):
@@ -135,3 +135,27 @@ def test_exchange_buffer_sizes_host_only():
     lib = _cabi.load()
     assert lib.g4b_exchange_buffer_bytes(8, 8, 256) == 2 * 8 * 8 * 8 * 34 * 8
     assert lib.g4b_exchange_buffer_bytes(2, 3, 40) == 2 * 2 * 3 * 2 * 34 * 8      # head dim rounds up to 2 slices
+
+
+def test_valid_arguments_pass_validation_without_a_launch():
+    """In validate-only mode a call whose arguments pass every check returns normally and
+    launches nothing (there is no GPU here to launch on)."""
+    q, k, v, o, time, phase = _attn_inputs()
+    fa2.flash_attention(q, k, v, o, time, phase, 64, 2, stream=0)
+    po, pl = torch.zeros(4, 2, 8, 1, 256), torch.zeros(4, 2, 8, 1)
+    fa2.flash_attention(q, k, v, o, time, phase, 64, 2, po, pl, pl.clone(), num_kv_splits=4, stream=0)
+    akv.add_kv_to_cache(torch.zeros(2, 2, 3, 256), torch.zeros(2, 2, 17, 256, dtype=torch.float16),
+                        torch.zeros(2, dtype=torch.int32), 1e-6, stream=0)
+    assert o.abs().sum() == 0
+
+
+@pytest.mark.launches_allowed
+def test_host_and_foreign_device_tensors_are_refused():
+    """Outside validate-only mode the wrappers refuse torch tensors that are not on the
+    current CUDA device before anything reaches the library."""
+    q, k, v, o, time, phase = _attn_inputs()
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        fa2.flash_attention(q, k, v, o, time, phase, 64, 2, stream=0)
+    with pytest.raises(ValueError, match="CUDA tensor"):
+        akv.add_kv_to_cache(torch.zeros(2, 2, 3, 256), torch.zeros(2, 2, 17, 256, dtype=torch.float16),
+                            torch.zeros(2, dtype=torch.int32), 1e-6, stream=0)
