@@ -3,7 +3,7 @@
     python bench.py [--gpus N] [--steps K] [--warmup W] [--workload NAME] [--impl reference]
 
 Prints ONE JSON line.  Workloads (shapes of the five benchmark configurations):
-    prefill_causal  B4 S8192 H8 G2 D256 bf16, causal, scale 1/16          (default)
+    prefill_causal  B4 S8192 H8 G2 D256 bf16, causal, scale 1/16          (default, headline)
     prefill_swa     B2 S32768 W512, per-query sliding window
     decode_paged    256 sequences, ctx ~ U[1024,32768], fp16 KV in shuffled 16-token pages,
                     one step = append the new token's K/V + attention
@@ -15,10 +15,27 @@ Prints ONE JSON line.  Workloads (shapes of the five benchmark configurations):
     kv_append       add_kv_to_cache alone on a prefill chunk (V norm, f32 -> f16), GB/s
 A step is one pass of the hot path over one batch.  ``value`` has inputs resident in HBM;
 ``e2e`` goes through the public Python operators with pinned host buffers, host<->device
-copies inside the timed region.  With N > 1 every rank runs the same per-GPU batch (weak
-scaling; requests, heads and sequences are independent) except decode_long, which splits one
-sequence (strong scaling).  ``--impl reference`` times the CPU oracle (a port of the
-reference's torch attention) on the host cores on a bounded sample of the same workload.
+copies inside the timed region.
+
+The default line is the headline (prefill_causal, the same per-GPU batch on every rank: weak
+scaling) plus one block per other configuration, each with its own time, roofline and a
+parity check against the CPU oracle made in this run:
+    swa          configuration 3; on N > 1 GPUs its (request, kv head) units, and at 8 GPUs
+                 halves of their query range with a window-sized key halo, are dealt over the
+                 ranks (strong scaling, no communication)
+    decode       configuration 4; on N > 1 GPUs ONE set of 256 sequences dealt over the ranks
+                 longest-first (strong scaling, no communication)
+    decode_long  configuration 5; on N > 1 GPUs the KV range of the one sequence is split over
+                 the ranks and the partials are merged through peer memory (strong scaling, the
+                 one exchange step of the path); every rank checks its output against the oracle
+    prefill_strong (N > 1 only) configuration 2's ONE batch of 4 requests dealt over the ranks
+                 by request and kv head
+plus ``sustained`` (the headline replayed for two seconds with the clocks sampled),
+``copy_ceiling`` (what the same pinned buffers reach with copies alone), ``cpu_config1`` (the
+reference's CPU case, configuration 1, timed in full) and ``triton_reference`` (the
+reference's own Triton kernel on the same GPU, when its sources were copied beside the repo).
+``--impl reference`` times the reference's CPU attention on the host cores over the whole
+per-GPU batch of the workload.
 """
 from __future__ import annotations
 
@@ -53,11 +70,22 @@ def measured_peaks():
     return dict(hbm=6650.0, tensor=1590.0, tensor_sustained=1400.0, source="fallback")
 
 
+def captured_traffic(workload: str):
+    """DRAM bytes (read + write) that the profiler counted for one launch of the workload's
+    dominant kernel, from the record kept beside the profile summaries: {"bytes_per_unit",
+    "fixed_bytes", "units"}; traffic of a launch = bytes_per_unit * units + fixed_bytes.  None
+    where no capture exists."""
+    p = ROOT / "profiles" / "traffic.json"
+    if not p.exists():
+        return None
+    return json.loads(p.read_text()).get(workload)
+
+
 class ClockSampler:
-    """Polls SM clock and throttle reasons through NVML while the timed region runs."""
+    """Polls SM clock, power and throttle reasons through NVML while the timed region runs."""
 
     def __init__(self, index: int):
-        self.samples, self.reasons, self.max_mhz = [], set(), None
+        self.samples, self.power, self.reasons, self.max_mhz = [], [], set(), None
         self._stop = threading.Event()
         self._thread = None
         try:
@@ -88,6 +116,7 @@ class ClockSampler:
                 for k, bit in names.items():
                     if mask & bit:
                         self.reasons.add(k)
+                self.power.append(nv.nvmlDeviceGetPowerUsage(self._h) / 1000.0)
             except Exception:
                 pass
             time.sleep(0.004)
@@ -101,9 +130,10 @@ class ClockSampler:
         self._stop.set()
         if self._thread is not None:
             self._thread.join()
-        s = sorted(self.samples)
+        s, w = sorted(self.samples), sorted(self.power)
         return {"sm_mhz": (s[len(s) // 2] if s else None), "sm_max_mhz": self.max_mhz,
-                "reasons": sorted(self.reasons), "samples": len(s)}
+                "reasons": sorted(self.reasons), "samples": len(s),
+                "power_w": (round(w[len(w) // 2], 1) if w else None)}
 
 
 def dist_env():
@@ -125,6 +155,14 @@ def max_over_ranks(ms: float, world: int, dev) -> float:
     t = torch.tensor([ms], dtype=torch.float64, device=dev)
     torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MAX)
     return float(t.item())
+
+
+def all_ranks_ok(ok: bool, world: int, dev) -> bool:
+    if world == 1:
+        return ok
+    t = torch.tensor([1 if ok else 0], dtype=torch.int32, device=dev)
+    torch.distributed.all_reduce(t, op=torch.distributed.ReduceOp.MIN)
+    return bool(t.item())
 
 
 def timed_region(step_fn, steps, warmup, world, dev, sampler=None, begin=None, end=None):
@@ -184,53 +222,109 @@ class GraphRunner:
             self.step_fn(i)
 
 
+def within_tolerance(got, want):
+    """The tolerance of the parity tests: |a - b| <= 2e-3 + 1e-2 |b|.  Returns (ok, worst excess)."""
+    got, want = got.detach().float().cpu(), want.detach().float().cpu()
+    if not bool(torch.isfinite(got).all()):
+        return False, float("inf")
+    excess = float(((got - want).abs() - (2e-3 + 1e-2 * want.abs())).max())
+    return excess <= 0, excess
+
+
 # ------------------------------------------------------------------------------------------
 # workloads
 # ------------------------------------------------------------------------------------------
-def prefill_flops(B, S, window=None):
+def unit_pairs(q_lo, q_hi, window=None):
+    """(query, visible key) pairs of the query positions [q_lo, q_hi): position p sees p + 1 keys,
+    or the last ``window`` of them."""
+    tri = lambda n: n * (n + 1) // 2
+    if window is None:
+        return tri(q_hi) - tri(q_lo)
+    ramp_hi = min(q_hi, window)
+    ramp = tri(ramp_hi) - tri(q_lo) if q_lo < ramp_hi else 0
+    return ramp + (q_hi - max(q_lo, window)) * window if q_hi > window else ramp
+
+
+def prefill_flops(B, S, window=None, heads=H):
     if window is None:
         pairs = S * (S + 1) // 2
     else:
         pairs = window * (window + 1) // 2 + (S - window) * window
-    return 4.0 * B * H * D * pairs
+    return 4.0 * B * heads * D * pairs
 
 
 class PrefillWorkload:
-    """Configs 2 and 3: q [B,S,H,D] physical (passed as the [B,H,S,D] view), caches [B,G,S,D]."""
+    """Configs 2 and 3: q [B,S,H,D] physical (passed as the [B,H,S,D] view), caches [B,G,S,D].
 
-    def __init__(self, name, dev, seed):
+    ``units`` (strong scaling over N > 1 GPUs) replaces the whole batch by this rank's share of
+    it: a list of (request, kv head, q_lo, q_hi, k_lo) from dist.shard_prefill_units.  Every unit
+    becomes one batch item with H/G query heads and one kv head, its queries the last
+    q_hi - q_lo positions of the q_hi - k_lo keys it holds."""
+
+    def __init__(self, name, dev, seed, units=None, full_batch=None):
         from g4b_b200.kernels import fa2
 
         self.fa2 = fa2
         self.name = name
-        self.B, self.S, self.window = (4, 8192, None) if name == "prefill_causal" else (2, 32768, 512)
+        self.B, self.S, self.window = (4, 8192, None) if name.startswith("prefill_causal") else (2, 32768, 512)
+        if full_batch is not None:
+            self.B = full_batch
         self.dtype = torch.bfloat16
         gen = torch.Generator(device="cpu").manual_seed(seed)
-        B, S = self.B, self.S
+        self.total_units = prefill_flops(self.B, self.S, self.window)      # whole job, FLOPs per step
+        self.scaling = "weak"
+        if units is None:
+            B, Hh, Gg, Tq, Tk = self.B, H, G, self.S, self.S
+            self.units = self.total_units
+        else:
+            assert len({(u[3] - u[2], u[3] - u[4]) for u in units}) == 1, "units of one rank must have one shape"
+            B, Hh, Gg = len(units), H // G, 1
+            Tq, Tk = units[0][3] - units[0][2], units[0][3] - units[0][4]
+            self.units = sum(4.0 * Hh * D * unit_pairs(u[2], u[3], self.window) for u in units)
+            self.scaling = "strong"
+        self.Bl, self.Hl, self.Gl, self.Tq, self.Tk = B, Hh, Gg, Tq, Tk
         # pinned host copies: source of the e2e leg's per-step uploads
-        self.h_q = torch.randn(B, S, H, D, generator=gen).to(self.dtype).pin_memory()
-        self.h_k = torch.randn(B, G, S, D, generator=gen).to(self.dtype).pin_memory()
-        self.h_v = torch.randn(B, G, S, D, generator=gen).to(self.dtype).pin_memory()
-        self.h_o = torch.empty(B, S, H, D, dtype=self.dtype).pin_memory()
+        self.h_q = torch.randn(B, Tq, Hh, D, generator=gen).to(self.dtype).pin_memory()
+        self.h_k = torch.randn(B, Gg, Tk, D, generator=gen).to(self.dtype).pin_memory()
+        self.h_v = torch.randn(B, Gg, Tk, D, generator=gen).to(self.dtype).pin_memory()
+        self.h_o = torch.empty(B, Tq, Hh, D, dtype=self.dtype).pin_memory()
         self.q, self.k, self.v = self.h_q.to(dev), self.h_k.to(dev), self.h_v.to(dev)
         self.o = torch.empty_like(self.q)
-        self.time = torch.full((B,), S, dtype=torch.int32, device=dev)
-        self.units = prefill_flops(B, S, self.window)          # FLOPs per step
-        self.metric, self.unit, self.bound = "prefill_attn_tflops", "TFLOP/s", "tensor"
+        self.time = torch.full((B,), Tk, dtype=torch.int32, device=dev)
+        self.metric, self.unit, self.bound, self.div = "prefill_attn_tflops", "TFLOP/s", "tensor", 1e12
         self.launches_per_step = 1
         self.h2d = (self.h_q.numel() + self.h_k.numel() + self.h_v.numel()) * 2
         self.d2h = self.h_o.numel() * 2
-        # DRAM bytes of one launch from the committed ncu capture (profiles/): read + write
-        self.traffic = 398.6e6 if name == "prefill_causal" else None
-        self.config = {"workload": name, "batch_per_gpu": B, "seq_len": S, "q_heads": H, "kv_heads": G,
+        self.config = {"workload": name, "batch_per_gpu": self.B, "seq_len": self.S, "q_heads": H, "kv_heads": G,
                        "head_dim": D, "window": self.window, "scale": SCALE,
                        "l2": "inputs (%d MB) larger than L2" % ((self.h2d + self.d2h) >> 20)}
+        if units is not None:
+            del self.config["batch_per_gpu"]
+            self.config.update({"batch": self.B, "units_this_rank": [list(u) for u in units],
+                                "unit_shape": {"q_heads": Hh, "kv_heads": Gg, "q_rows": Tq, "keys": Tk}})
 
     variants = 1
 
     def step(self, i=0):
         self.fa2.flash_attention(self.q.permute(0, 2, 1, 3), self.k, self.v, self.o.permute(0, 2, 1, 3), self.time,
-                                 None, self.S, self.fa2.PHASE_PREFILL, scale=SCALE, sliding_window=self.window)
+                                 None, self.Tk, self.fa2.PHASE_PREFILL, scale=SCALE, sliding_window=self.window)
+
+    def parity(self):
+        """Sampled query rows of the first and the last batch item against the oracle."""
+        from oracle import attention_oracle as orc
+
+        self.step(0)
+        torch.cuda.synchronize()
+        ok, worst = True, -1.0
+        for b in sorted({0, self.Bl - 1}):
+            k, v = self.h_k[b].float(), self.h_v[b].float()
+            for r in sorted({0, 1, self.Tq // 2 + 77, self.Tq - 1}):
+                pos = self.Tk - self.Tq + r
+                want = orc.attention_core(self.h_q[b, r:r + 1].float().permute(1, 0, 2), k[:, :pos + 1], v[:, :pos + 1],
+                                          scale=SCALE, causal=True, sliding_window=self.window)
+                good, ex = within_tolerance(self.o[b, r:r + 1].permute(1, 0, 2), want)
+                ok, worst = ok and good, max(worst, ex)
+        return ok, worst
 
     # End-to-end leg: a three-stage pipeline over two device buffer sets -- upload of step
     # i+1 (copy stream), attention of step i (launching stream) and download of step i-1
@@ -264,7 +358,7 @@ class PrefillWorkload:
         cur.wait_event(self.ev_up[b])
         if self.used[b]:
             cur.wait_event(self.ev_down[b])                 # o of this set has been downloaded
-        self.fa2.flash_attention(q.permute(0, 2, 1, 3), k, v, o.permute(0, 2, 1, 3), self.time, None, self.S,
+        self.fa2.flash_attention(q.permute(0, 2, 1, 3), k, v, o.permute(0, 2, 1, 3), self.time, None, self.Tk,
                                  self.fa2.PHASE_PREFILL, scale=SCALE, sliding_window=self.window)
         self.ev_done[b].record(cur)
         with torch.cuda.stream(self.s_down):
@@ -278,25 +372,39 @@ class PrefillWorkload:
         cur.wait_stream(self.s_down)
         cur.wait_stream(self.s_up)
 
-    def value_from(self, ms_per_step, world):
-        return self.units * world / (ms_per_step * 1e-3) / 1e12
+    def copy_ceiling(self, world, dev, reps=4):
+        """What the e2e leg's own pinned buffers reach with copies alone, all ranks at once:
+        uploads only, downloads only (GB/s per rank, from the slowest rank's time).  The e2e leg
+        overlaps the two directions, so its floor per step is the slower of the two."""
+        out = {}
+        for key, pairs, nbytes in (("h2d", [(self.q, self.h_q), (self.k, self.h_k), (self.v, self.h_v)], self.h2d),
+                                   ("d2h", [(self.h_o, self.o)], self.d2h)):
+            def once(_i=0):
+                for dst, src in pairs:
+                    dst.copy_(src, non_blocking=True)
+            ms = timed_region(once, reps, 2, world, dev) / reps
+            out[key + "_gbs_per_rank"] = round(nbytes / (ms * 1e-3) / 1e9, 2)
+            out[key + "_ms_per_step"] = round(ms, 4)
+        out["e2e_floor_ms_per_step"] = max(out["h2d_ms_per_step"], out["d2h_ms_per_step"])
+        out["ranks_copying_at_once"] = world
+        return out
 
     def cpu_sample(self, budget_s=15.0):
-        """Oracle on host cores: batch item 0, all heads, in 1024-query blocks; more items
-        while the budget lasts.  Returns (TFLOP/s, description)."""
+        """Oracle on host cores: whole batch items, all heads, in 1024-query blocks, while the
+        budget lasts.  Returns (TFLOP/s, description)."""
         from oracle import attention_oracle as orc
 
         q = self.h_q.float().permute(0, 2, 1, 3)
         k, v = self.h_k.float(), self.h_v.float()
-        S = self.S if self.window is None else 8192     # bounded sample of the long SWA sequence
+        S = self.Tk if self.window is None else min(self.Tk, 8192)     # bounded sample of the long SWA sequence
         done, t0 = 0, time.perf_counter()
-        while done < self.B and (done == 0 or time.perf_counter() - t0 < budget_s / 2):
+        while done < self.Bl and (done == 0 or time.perf_counter() - t0 < budget_s / 2):
             orc.attention_core(q[done][:, :S], k[done][:, :S], v[done][:, :S], scale=SCALE, causal=True,
                                sliding_window=self.window)
             done += 1
         dt = time.perf_counter() - t0
-        flops = prefill_flops(done, S, self.window)
-        return flops / dt / 1e12, f"{done} of {self.B} batch items, first {S} tokens, fp32, 1024-query blocks"
+        flops = prefill_flops(done, S, self.window, heads=self.Hl)
+        return flops / dt / 1e12, f"{done} of {self.Bl} batch items, first {S} tokens, fp32, 1024-query blocks"
 
 
 class PrefillChunkWorkload:
@@ -306,6 +414,7 @@ class PrefillChunkWorkload:
     their key ranges over the SMs (partial buffers given) and merges."""
 
     variants = 1
+    scaling = "weak"
 
     def __init__(self, name, dev, seed, split=True):
         from g4b_b200.kernels import fa2
@@ -327,9 +436,9 @@ class PrefillChunkWorkload:
         self.pl = torch.empty(S, B, Hc, t, device=dev) if split else None
         self.pm = torch.empty(S, B, Hc, t, device=dev) if split else None
         self.units = 4.0 * B * Hc * D * (t * (T - t) + t * (t + 1) / 2)
-        self.metric, self.unit, self.bound = "prefill_attn_tflops", "TFLOP/s", "tensor"
+        self.total_units = None
+        self.metric, self.unit, self.bound, self.div = "prefill_attn_tflops", "TFLOP/s", "tensor", 1e12
         self.launches_per_step = 2 if split else 1
-        self.traffic = None
         self.h2d, self.d2h = self.h_q.numel() * 2, self.h_o.numel() * 2
         self.config = {"workload": name, "batch_per_gpu": B, "chunk_rows": t, "context": T, "q_heads": Hc, "kv_heads": Gc,
                        "head_dim": D, "scale": SCALE, "split_kv": bool(split),
@@ -343,9 +452,6 @@ class PrefillChunkWorkload:
         self.q.copy_(self.h_q, non_blocking=True)
         self.step(i)
         self.h_o.copy_(self.o, non_blocking=True)
-
-    def value_from(self, ms_per_step, world):
-        return self.units * world / (ms_per_step * 1e-3) / 1e12
 
     def cpu_sample(self, budget_s=15.0):
         from oracle import attention_oracle as orc
@@ -366,6 +472,7 @@ class RopeAppendWorkload:
     algorithmic bytes = fp32 reads of q, k, v + bf16 writes of q, k, v."""
 
     variants = 1
+    scaling = "weak"
 
     def __init__(self, name, dev, seed):
         from g4b_b200.kernels.rope import rope_norm_append
@@ -389,9 +496,9 @@ class RopeAppendWorkload:
         self.off = torch.zeros(B, dtype=torch.int32, device=dev)
         rows = B * S
         self.units = float(rows * (H + 2 * G) * D * (4 + 2))
-        self.metric, self.unit, self.bound = "rope_append_hbm_gbs", "GB/s", "hbm"
+        self.total_units = None
+        self.metric, self.unit, self.bound, self.div = "rope_append_hbm_gbs", "GB/s", "hbm", 1e9
         self.launches_per_step = 1
-        self.traffic = None
         self.h2d = (self.h_q.numel() + self.h_k.numel() + self.h_v.numel()) * 4
         self.d2h = self.h_q16.numel() * 2
         self.config = {"workload": name, "batch_per_gpu": B, "tokens": S, "q_heads": H, "kv_heads": G, "head_dim": D,
@@ -407,9 +514,6 @@ class RopeAppendWorkload:
         self.v.copy_(self.h_v, non_blocking=True)
         self.step(i)
         self.h_q16.copy_(self.q16, non_blocking=True)
-
-    def value_from(self, ms_per_step, world):
-        return self.units * world / (ms_per_step * 1e-3) / 1e9
 
     def cpu_sample(self, budget_s=15.0):
         from oracle import attention_oracle as orc
@@ -430,6 +534,7 @@ class KVAppendWorkload:
     D256).  HBM-bound: algorithmic bytes = fp32 reads + f16 writes of the rows."""
 
     variants = 1
+    scaling = "weak"
 
     def __init__(self, name, dev, seed):
         from g4b_b200.kernels.add_kv_to_cache import add_kv_to_cache
@@ -445,9 +550,9 @@ class KVAppendWorkload:
         self.d_probe = torch.empty(B, Gk, 16, D, dtype=self.dtype, device=dev)
         self.off = torch.zeros(B, dtype=torch.int32, device=dev)
         self.units = float(B * S * Gk * D * (4 + 2))
-        self.metric, self.unit, self.bound = "kv_append_hbm_gbs", "GB/s", "hbm"
+        self.total_units = None
+        self.metric, self.unit, self.bound, self.div = "kv_append_hbm_gbs", "GB/s", "hbm", 1e9
         self.launches_per_step = 1
-        self.traffic = None
         self.h2d = self.h_x.numel() * 4
         self.d2h = self.h_probe.numel() * 2
         self.config = {"workload": name, "batch_per_gpu": B, "tokens": S, "kv_heads": Gk, "head_dim": D,
@@ -463,9 +568,6 @@ class KVAppendWorkload:
         self.d_probe.copy_(self.cache[:, :, :16])                         # the rows a caller would check
         self.h_probe.copy_(self.d_probe, non_blocking=True)
 
-    def value_from(self, ms_per_step, world):
-        return self.units * world / (ms_per_step * 1e-3) / 1e9
-
     def cpu_sample(self, budget_s=15.0):
         from oracle import attention_oracle as orc
 
@@ -480,22 +582,35 @@ class KVAppendWorkload:
 
 class DecodeWorkload:
     """Configs 4 and 5: paged KV with shuffled block tables; a step appends the new token's
-    K and V rows and runs decode attention (split-KV + combine)."""
+    K and V rows and runs decode attention (split-KV + combine).
 
-    def __init__(self, name, dev, seed, rank=0, world=1, sequences=256, nccl_gather=False, kv_splits=0):
+    decode_paged with ``shard`` on N > 1 GPUs: ONE set of sequences, dealt over the ranks
+    longest-first (dist.balance_sequences); a rank holds only its sequences' pages.
+    decode_long on N > 1 GPUs: the one sequence's pages are split contiguously over the ranks
+    (dist.split_pages); its K/V values come from one seed, so that every rank's share belongs
+    to the same sequence and the merged output can be checked against the oracle."""
+
+    def __init__(self, name, dev, seed, rank=0, world=1, sequences=256, nccl_gather=False, kv_splits=0, shard=False):
+        from g4b_b200 import dist as gdist
         from g4b_b200.kernels import fa2
         from g4b_b200.kernels.rope import rope_norm_append
 
         self.fa2, self.append = fa2, rope_norm_append
         self.name, self.dev, self.rank, self.world = name, dev, rank, world
         gen = torch.Generator(device="cpu").manual_seed(seed)
+        self.scaling = "weak"
         if name == "decode_paged":
             self.dtype = torch.float16
-            self.lens = torch.randint(1024, 32769, (sequences,), generator=gen, dtype=torch.int64)
+            self.all_lens = torch.randint(1024, 32769, (sequences,), generator=gen, dtype=torch.int64)
+            self.lens = self.all_lens
             self.splits = 16
+            if shard and world > 1:
+                mine = gdist.balance_sequences(self.all_lens.tolist(), world)[rank]
+                self.lens = self.all_lens[mine]
+                self.scaling = "strong"
         else:
             self.dtype = torch.bfloat16
-            self.lens = torch.tensor([131072], dtype=torch.int64)
+            self.all_lens = self.lens = torch.tensor([131072], dtype=torch.int64)
             self.splits = 148          # x 2 kv heads = two CTAs on every SM
         self.long_split = name == "decode_long" and world > 1
         lens = self.lens
@@ -504,23 +619,38 @@ class DecodeWorkload:
         pages_per = (lens + PAGE - 1) // PAGE
         if self.long_split:
             # this rank holds (and is handed block-table entries for) only its page range
-            from g4b_b200 import dist as gdist
-
-            rng = gdist.split_pages(int(pages_per[0]), world, rank)
-            local_pages = torch.tensor([len(rng)])
-            self.local_lens = torch.tensor([min(int(lens[0]), rng.stop * PAGE) - rng.start * PAGE])
+            self.page_range = gdist.split_pages(int(pages_per[0]), world, rank)
+            local_pages = torch.tensor([len(self.page_range)])
+            self.local_lens = torch.tensor([min(int(lens[0]), self.page_range.stop * PAGE) - self.page_range.start * PAGE])
             self.splits = 128
+            self.scaling = "strong"
         else:
+            self.page_range = range(0, int(pages_per[0])) if name == "decode_long" else None
             local_pages, self.local_lens = pages_per, lens
         if kv_splits > 0:
             self.splits = kv_splits
         num_pages = int(local_pages.sum())
-        gdev = torch.Generator(device=dev).manual_seed(seed + 1 + rank)
-        self.k_pool = torch.randn(num_pages, G, PAGE, D, generator=gdev, device=dev, dtype=torch.float32).to(self.dtype) \
-            if num_pages * G * PAGE * D < (1 << 28) else self._big_randn(num_pages, gdev)
-        self.v_pool = torch.randn(num_pages, G, PAGE, D, generator=gdev, device=dev, dtype=torch.float32).to(self.dtype) \
-            if num_pages * G * PAGE * D < (1 << 28) else self._big_randn(num_pages, gdev)
-        perm = torch.randperm(num_pages, generator=gen).to(torch.int32)
+        perm = torch.randperm(num_pages, generator=torch.Generator().manual_seed(seed + 7 + rank)).to(torch.int32)
+        if name == "decode_long":
+            # the whole sequence from one seed on every rank; a rank keeps its page range, page i
+            # of the range stored at pool position perm[i]
+            gseq = torch.Generator(device=dev).manual_seed(seed + 1)
+            L = int(lens[0])
+            self.seq_k = self._big_randn((G, L, D), gseq)          # [G, L, D]
+            self.seq_v = self._big_randn((G, L, D), gseq)
+            lo, n = self.page_range.start * PAGE, len(self.page_range)
+            def to_pool(seq):
+                pages = seq[:, lo:lo + n * PAGE].reshape(G, n, PAGE, D).permute(1, 0, 2, 3)
+                pool = torch.empty(n, G, PAGE, D, device=dev, dtype=self.dtype)
+                pool[perm.to(dev).long()] = pages
+                return pool
+            self.k_pool, self.v_pool = to_pool(self.seq_k), to_pool(self.seq_v)
+            if rank != 0:
+                self.seq_k = self.seq_v = None                     # only rank 0 computes the oracle
+        else:
+            gdev = torch.Generator(device=dev).manual_seed(seed + 1 + rank)
+            self.k_pool = self._big_randn((num_pages, G, PAGE, D), gdev)
+            self.v_pool = self._big_randn((num_pages, G, PAGE, D), gdev)
         max_pages = int(local_pages.max())
         bt = torch.zeros(B, max_pages, dtype=torch.int32)
         at = 0
@@ -533,35 +663,36 @@ class DecodeWorkload:
         self.max_len = max_pages * PAGE
         self.time = self.local_lens.to(torch.int32).to(dev)
         self.off = (self.local_lens - 1).to(torch.int32).to(dev)
-        self.h_q = torch.randn(B, H, 1, D, generator=gen).to(self.dtype).pin_memory()
-        self.h_kn = torch.randn(B, G, 1, D, generator=gen).to(self.dtype).pin_memory()
-        self.h_vn = torch.randn(B, G, 1, D, generator=gen).to(self.dtype).pin_memory()
+        gq = torch.Generator().manual_seed(seed + 3 + (0 if name == "decode_long" else rank))
+        self.h_q = torch.randn(B, H, 1, D, generator=gq).to(self.dtype).pin_memory()
+        self.h_kn = torch.randn(B, G, 1, D, generator=gq).to(self.dtype).pin_memory()
+        self.h_vn = torch.randn(B, G, 1, D, generator=gq).to(self.dtype).pin_memory()
         self.h_o = torch.empty(B, H, 1, D, dtype=self.dtype).pin_memory()
         self.q, self.kn, self.vn = self.h_q.to(dev), self.h_kn.to(dev), self.h_vn.to(dev)
         self.o = torch.empty_like(self.q)
         S = self.splits
         self.packed = torch.empty(S, B, H, 1, D + 2, device=dev, dtype=torch.float32)
         self.po, self.pl, self.pm = self.packed[..., :D], self.packed[..., D], self.packed[..., D + 1]
+        self.nccl_gather = nccl_gather
         if self.long_split:
-            from g4b_b200 import dist as gdist
-
             self.gathered = torch.empty(world * S, B, H, 1, D + 2, device=dev, dtype=torch.float32)
-            self.nccl_gather = nccl_gather
-            if not nccl_gather:
-                self.exchange = gdist.PartialExchange(B * H, D, device=dev)
+            self.exchange = gdist.PartialExchange(B * H, D, device=dev)
         kv_bytes = float(self.local_lens.sum()) * G * D * 2 * 2
         self.units = kv_bytes                                    # K/V bytes per step (this rank)
-        # DRAM bytes per launch: the ncu capture of a 32-sequence case read 1.0006x its
-        # algorithmic K/V bytes and traffic grows with the token count (profiles/)
-        self.traffic = kv_bytes * 1.0006 + 5.4e6 * (B / 32.0) if name == "decode_paged" else None
-        self.metric, self.unit, self.bound = "decode_attn_hbm_gbs", "GB/s", "hbm"
+        self.total_units = float(self.all_lens.sum()) * G * D * 2 * 2 if self.scaling == "strong" else None
+        self.metric, self.unit, self.bound, self.div = "decode_attn_hbm_gbs", "GB/s", "hbm", 1e9
         self.launches_per_step = 3                               # append (K and V) + decode + combine
         self.h2d = (self.h_q.numel() + self.h_kn.numel() + self.h_vn.numel()) * 2
         self.d2h = self.h_o.numel() * 2
-        self.config = {"workload": name, "sequences": B, "ctx_sum": int(lens.sum()), "ctx_min": int(lens.min()),
-                       "ctx_max": int(lens.max()), "page_size": PAGE, "kv_dtype": str(self.dtype).replace("torch.", ""),
-                       "kv_splits": self.splits, "scale": SCALE,
+        self.config = {"workload": name, "sequences": len(self.all_lens), "ctx_sum": int(self.all_lens.sum()),
+                       "ctx_min": int(self.all_lens.min()), "ctx_max": int(self.all_lens.max()), "page_size": PAGE,
+                       "kv_dtype": str(self.dtype).replace("torch.", ""), "kv_splits": self.splits, "scale": SCALE,
                        "l2": "K/V (%d MB per GPU) larger than L2" % (int(kv_bytes) >> 20)}
+        if self.scaling == "strong":
+            self.config.update({"sequences_this_rank": B, "ctx_sum_this_rank": int(self.local_lens.sum())})
+        if self.long_split:
+            self.config["merge"] = "all-gather + second merge launch (NCCL)" if nccl_gather else \
+                "one kernel: local merge, exchange through peer memory, final merge"
         # a K/V set that is not several times the 126 MB L2 would be served from cache on the
         # next step: rotate over copies (same block table, distinct memory) totalling >= 1 GB
         self.pools = [(self.k_pool, self.v_pool)]
@@ -573,12 +704,14 @@ class DecodeWorkload:
                 int(kv_bytes) >> 20, len(self.pools))
         self.variants = len(self.pools)
 
-    def _big_randn(self, num_pages, gdev):
-        out = torch.empty(num_pages, G, PAGE, D, device=self.dev, dtype=self.dtype)
-        chunk = 1 << 14
-        for s in range(0, num_pages, chunk):
-            e = min(num_pages, s + chunk)
-            out[s:e] = torch.randn(e - s, G, PAGE, D, generator=gdev, device=self.dev, dtype=torch.float32).to(self.dtype)
+    def _big_randn(self, shape, gdev):
+        """N(0,1) values of the cache dtype, generated in chunks so that the fp32 temporary stays small."""
+        out = torch.empty(shape, device=self.dev, dtype=self.dtype)
+        flat = out.view(-1)
+        chunk = 1 << 26
+        for s in range(0, flat.numel(), chunk):
+            e = min(flat.numel(), s + chunk)
+            flat[s:e] = torch.randn(e - s, generator=gdev, device=self.dev, dtype=torch.float32).to(self.dtype)
         return out
 
     def step(self, i=0):
@@ -607,18 +740,54 @@ class DecodeWorkload:
             # one kernel: local merge, exchange through peer memory, final merge
             self.exchange.combine(self.po, self.pl, self.pm, self.o, self.splits)
 
+    def parity(self):
+        """decode_long: the merged output of every rank against the oracle's attention over the
+        whole sequence (rank 0 computes it and broadcasts), for the peer-memory merge and, on
+        N > 1 GPUs, for the all-gather merge too.  decode_paged: the first and the last local
+        sequence against the oracle."""
+        from oracle import attention_oracle as orc
+
+        ok, worst = True, -1.0
+        if self.name == "decode_long":
+            want = torch.empty(1, H, 1, D, device=self.dev)
+            if self.rank == 0:
+                L = int(self.all_lens[0])
+                k, v = self.seq_k.float().cpu(), self.seq_v.float().cpu()
+                k[:, L - 1], v[:, L - 1] = self.h_kn[0, :, 0].float(), self.h_vn[0, :, 0].float()   # the appended row
+                want.copy_(orc.attention_core(self.h_q[0].float(), k, v, scale=SCALE)[None])
+                self.seq_k = self.seq_v = None
+            if self.world > 1:
+                torch.distributed.broadcast(want, 0)
+            forms = [False, True] if self.long_split else [False]
+            keep = self.nccl_gather
+            for form in forms:
+                self.nccl_gather = form
+                self.o.zero_()
+                self.step(0)
+                torch.cuda.synchronize()
+                good, ex = within_tolerance(self.o, want)
+                ok, worst = ok and good, max(worst, ex)
+            self.nccl_gather = keep
+            return ok, worst
+        self.step(0)
+        torch.cuda.synchronize()
+        kp, vp = self.pools[0]
+        for b in sorted({0, self.B - 1}):
+            L = int(self.local_lens[b])
+            pages = self.h_bt[b, : (L + PAGE - 1) // PAGE].long()
+            k = kp[pages.to(self.dev)].float().cpu().permute(1, 0, 2, 3).reshape(G, -1, D)[:, :L]
+            v = vp[pages.to(self.dev)].float().cpu().permute(1, 0, 2, 3).reshape(G, -1, D)[:, :L]
+            want = orc.attention_core(self.h_q[b].float(), k, v, scale=SCALE)
+            good, ex = within_tolerance(self.o[b], want)
+            ok, worst = ok and good, max(worst, ex)
+        return ok, worst
+
     def e2e_step(self, i=0):
         self.q.copy_(self.h_q, non_blocking=True)
         self.kn.copy_(self.h_kn, non_blocking=True)
         self.vn.copy_(self.h_vn, non_blocking=True)
         self.step(i)
         self.h_o.copy_(self.o, non_blocking=True)
-
-    def value_from(self, ms_per_step, world):
-        total = self.units * (1 if self.long_split else world)
-        if self.long_split:
-            total = float(self.lens.sum()) * G * D * 2 * 2
-        return total / (ms_per_step * 1e-3) / 1e9
 
     def cpu_sample(self, budget_s=15.0):
         from oracle import attention_oracle as orc
@@ -638,7 +807,11 @@ class DecodeWorkload:
         return touched / dt / 1e9, f"{n} of {self.B} sequences ({touched >> 20} MB of K/V), page gather + fp32 attention"
 
 
-def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_splits=0):
+def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_splits=0, strong=False):
+    """``strong``: the workload is ONE job dealt over the ranks (strong scaling) instead of the
+    same per-GPU batch on every rank."""
+    from g4b_b200 import dist as gdist
+
     seeds = {"prefill_causal": 1, "prefill_swa": 2, "decode_paged": 3, "decode_long": 4, "rope_append": 5,
              "kv_append": 7}
     if name == "kv_append":
@@ -648,20 +821,126 @@ def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_s
     if name == "prefill_chunk":
         return PrefillChunkWorkload(name, dev, 6 + 100 * rank, split=kv_splits >= 0)
     if name.startswith("prefill"):
-        return PrefillWorkload(name, dev, seeds[name] + 100 * rank)
+        units = None
+        if strong and world > 1:
+            nreq, S, W = (4, 8192, None) if name == "prefill_causal" else (2, 32768, 512)
+            units = gdist.shard_prefill_units(nreq, G, S, world, rank, W)
+        return PrefillWorkload(name, dev, seeds[name] + 100 * rank, units=units)
     return DecodeWorkload(name, dev, seeds[name] + (0 if name == "decode_long" else 100 * rank), rank, world,
-                          sequences, nccl_gather, kv_splits)
+                          sequences, nccl_gather, kv_splits, shard=strong)
 
 
 # ------------------------------------------------------------------------------------------
 # arms
 # ------------------------------------------------------------------------------------------
+def value_of(wl, ms_step, world):
+    """Whole-job throughput in the workload's unit: work of all ranks / time of the slowest."""
+    total = wl.total_units if wl.scaling == "strong" and wl.total_units is not None else wl.units * world
+    return total / (ms_step * 1e-3) / wl.div
+
+
+def roofline_of(wl, value, world, peaks, sustained=False):
+    peak = (peaks["tensor_sustained"] if sustained else peaks["tensor"]) if wl.bound == "tensor" else peaks["hbm"]
+    per_gpu = value / world
+    cap = captured_traffic(wl.name)
+    traffic = None
+    if cap is not None:     # per launch on one rank, scaled from the captured case by the units processed
+        traffic = cap["dram_bytes_per_algorithmic_unit"] * wl.units + cap.get("dram_bytes_per_batch_item", 0.0) * wl.B
+    kind = ("sustained" if sustained else "burst") if wl.bound == "tensor" else "copy"
+    return {"bound": wl.bound, "achieved": round(per_gpu, 3), "peak": peak, "unit": wl.unit,
+            "frac": round(per_gpu / peak, 4), "traffic": traffic, "peak_source": f"{peaks['source']} {kind}"}
+
+
+def measure(wl, steps, warmup, world, dev, use_graph, sampler=None):
+    """Returns (ms per step: max over ranks, launch mode, the runner)."""
+    for i in range(3):          # first calls set kernel attributes etc.: keep them out of capture
+        wl.step(i)
+    torch.cuda.synchronize()
+    run = GraphRunner(wl.step, wl.variants, use_graph)
+    ms = timed_region(run, steps, warmup, world, dev, sampler) / steps
+    return ms, run.mode, run
+
+
+def run_block(name, dev, rank, world, peaks, args, steps, warmup, *, strong, cpu=True):
+    """One extra block of the default line: build the workload, check it against the oracle,
+    time it, describe it."""
+    wl = make_workload(name, dev, rank, world, strong=strong)
+    good, excess = wl.parity()
+    good = all_ranks_ok(good, world, dev)
+    if not good:
+        raise SystemExit(f"rank {rank}: {name}: output differs from the oracle (tolerance exceeded by {excess:.3e})")
+    # a step that contains an NCCL collective is launched directly
+    use_graph = not args.no_graph and not (getattr(wl, "long_split", False) and wl.nccl_gather)
+    ms, mode, _ = measure(wl, steps, warmup, world, dev, use_graph)
+    value = value_of(wl, ms, world)
+    out = {"metric": wl.metric, "value": round(value, 2), "unit": wl.unit, "ms_per_step": round(ms, 5),
+           "scaling": wl.scaling if world > 1 else "single GPU", "n_gpus": world, "steps": steps,
+           "config": wl.config, "launch": mode, "roofline": roofline_of(wl, value, world, peaks),
+           "parity": "ok", "parity_tolerance": "|a-b| <= 2e-3 + 1e-2|b| against the CPU oracle, all ranks",
+           "gpu_launches": wl.launches_per_step * steps}
+    if getattr(wl, "long_split", False):
+        wl.nccl_gather = True
+        wl.config = dict(wl.config)
+        ms2, _, _ = measure(wl, steps, warmup, world, dev, False)
+        out["nccl_all_gather_form_ms_per_step"] = round(ms2, 5)
+    if cpu and rank == 0 and not args.no_cpu:
+        v, sample = wl.cpu_sample()
+        out["cpu_baseline"] = {"value": round(v, 5), "unit": wl.unit, "cores": torch.get_num_threads(),
+                               "kind": "port", "sample": sample}
+    return out
+
+
+def cpu_config1():
+    """Configuration 1, the reference's CPU case: B1 S512 H8 G2 D256 fp32 causal, scale 1/16,
+    through the oracle on the host cores, timed in full (median of 7 warm runs)."""
+    from oracle import attention_oracle as orc
+
+    gen = torch.Generator().manual_seed(0)
+    q, k, v = (torch.randn(h, 512, D, generator=gen) for h in (H, G, G))
+    orc.attention_core(q, k, v, scale=SCALE)
+    times = []
+    for _ in range(7):
+        t0 = time.perf_counter()
+        orc.attention_core(q, k, v, scale=SCALE)
+        times.append(time.perf_counter() - t0)
+    dt = sorted(times)[len(times) // 2]
+    flops = prefill_flops(1, 512)
+    return {"workload": "B1 S512 H8 G2 D256 fp32 causal", "ms": round(dt * 1e3, 3), "gflops_causal": round(flops / dt / 1e9, 2),
+            "gflops_as_executed_dense": round(2 * flops * 512 / 513 / dt / 1e9, 2), "cores": torch.get_num_threads(),
+            "kind": "port", "runs": len(times)}
+
+
+def bind_near_gpu(local):
+    """Keeps this rank's threads (and so its first-touch pinned pages) on the CPUs NVML lists
+    as near its GPU.  Changes only this process's affinity, no device setting."""
+    info = {"affinity_before": sorted(os.sched_getaffinity(0))}
+    try:
+        import pynvml
+
+        pynvml.nvmlInit()
+        h = pynvml.nvmlDeviceGetHandleByIndex(local)
+        words = pynvml.nvmlDeviceGetCpuAffinity(h, (os.cpu_count() + 63) // 64)
+        cpus = [64 * w + b for w, word in enumerate(words) for b in range(64) if (int(word) >> b) & 1]
+        allowed = sorted(set(cpus) & set(os.sched_getaffinity(0)))
+        if allowed:
+            os.sched_setaffinity(0, allowed)
+        info["cpus_near_gpu"] = len(allowed)
+    except Exception as exc:
+        info["cpus_near_gpu"] = f"unknown ({type(exc).__name__})"
+    try:
+        info["numa_nodes"] = len([d for d in os.listdir("/sys/devices/system/node") if d.startswith("node")])
+    except Exception:
+        info["numa_nodes"] = None
+    return info
+
+
 def run_ours(args):
     rank, world, local = dist_env()
     if args.gpus != world and world == 1 and args.gpus > 1:
         raise SystemExit("launch N > 1 with torchrun (one rank per GPU)")
     dev = torch.device(f"cuda:{local}")
     torch.cuda.set_device(dev)
+    host = bind_near_gpu(local)
     if world > 1:
         torch.distributed.init_process_group("nccl", device_id=dev)
     import __graft_entry__
@@ -673,31 +952,22 @@ def run_ours(args):
     from g4b_b200 import _cabi
 
     peaks = measured_peaks()
-    wl = make_workload(args.workload, dev, rank, world, args.sequences, args.nccl_gather, args.kv_splits)
+    headline = args.workload == "prefill_causal" and not args.no_extras
+    wl = make_workload(args.workload, dev, rank, world, args.sequences, args.nccl_gather, args.kv_splits,
+                       strong=args.strong)
+    parity = None
+    if hasattr(wl, "parity"):
+        good, excess = wl.parity()
+        if not all_ranks_ok(good, world, dev):
+            raise SystemExit(f"rank {rank}: {args.workload}: output differs from the oracle (tolerance exceeded by {excess:.3e})")
+        parity = "ok"
     sampler = ClockSampler(local) if rank == 0 else None
-    for i in range(3):          # first calls set kernel attributes etc.: keep them out of capture
-        wl.step(i)
-    torch.cuda.synchronize()
     # a step that contains an NCCL collective is launched directly: replaying captured
     # collectives from several graphs stalled here
     use_graph = not args.no_graph and not (getattr(wl, "long_split", False) and args.nccl_gather)
-    if getattr(wl, "long_split", False) and not args.nccl_gather:
-        # the two forms of the cross-GPU merge must agree before anything is timed
-        wl.step(0)
-        mine = wl.o.float().clone()
-        wl.nccl_gather = True
-        wl.step(0)
-        wl.nccl_gather = False
-        torch.cuda.synchronize()
-        err = (mine - wl.o.float()).abs().max().item()
-        if err > 2e-2:
-            raise SystemExit(f"rank {rank}: peer-memory merge and all-gather merge differ by {err}")
-    run_step = GraphRunner(wl.step, wl.variants, use_graph)
-    wl.config["launch"] = run_step.mode
-    ms = timed_region(run_step, args.steps, args.warmup, world, dev, sampler)
+    ms_step, mode, run_step = measure(wl, args.steps, args.warmup, world, dev, use_graph, sampler)
     clocks = sampler.stop() if sampler is not None else None
-    ms_step = ms / args.steps
-    value = wl.value_from(ms_step, world)
+    value = value_of(wl, ms_step, world)
 
     # end to end: pinned host inputs -> device -> operators -> pinned host result, every step
     if hasattr(wl, "e2e_begin"):      # multi-stream pipeline, launched from Python
@@ -706,61 +976,103 @@ def run_ours(args):
     else:
         run_e2e = GraphRunner(wl.e2e_step, wl.variants, use_graph)
         ms_e2e = timed_region(run_e2e, args.steps, args.warmup, world, dev) / args.steps
-    e2e_value = wl.value_from(ms_e2e, world)
+    e2e_value = value_of(wl, ms_e2e, world)
     status = _cabi.device_status()
     if status != 0:
         raise SystemExit(f"device status word {status:#x}: a kernel gave up on a bounded wait")
 
-    peak = peaks["tensor"] if wl.bound == "tensor" else peaks["hbm"]
-    per_gpu = value / (1 if getattr(wl, "long_split", False) else world)
     out = {
         "metric": wl.metric, "value": round(value, 3), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
         "warmup": args.warmup, "ms_per_step": round(ms_step, 5), "higher_is_better": True,
-        "scaling": "strong" if getattr(wl, "long_split", False) else "weak", "vs_baseline": None,
+        "scaling": wl.scaling, "vs_baseline": None,
         "dtype": "bf16" if wl.dtype == torch.bfloat16 else "f16", "data": "synthetic (seeded N(0,1))",
-        "config": wl.config,
+        "config": wl.config, "launch": mode,
         "e2e": {"value": round(e2e_value, 3), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d,
                 "d2h_bytes_per_step": wl.d2h, "ms_per_step": round(ms_e2e, 5)},
         "gpu_launches": wl.launches_per_step * args.steps,
-        "roofline": {"bound": wl.bound, "achieved": round(per_gpu, 3), "peak": peak, "unit": wl.unit,
-                     "frac": round(per_gpu / peak, 4), "traffic": wl.traffic,
-                     "peak_source": peaks["source"] + (" burst" if wl.bound == "tensor" else " copy")},
-        "clocks": clocks,
+        "roofline": roofline_of(wl, value, world, peaks),
+        "clocks": clocks, "host": host,
     }
-    if rank == 0 and world == 1 and not args.no_cpu:
+    if parity is not None:
+        out["parity"] = parity
+    if hasattr(wl, "copy_ceiling"):
+        out["e2e"]["copy_ceiling"] = wl.copy_ceiling(world, dev)
+    if headline or args.sustained:
+        # the same step replayed back to back for about two seconds: what the kernel holds once
+        # the power limit bites, beside the clock it ran at
+        n = max(args.steps, int(2200.0 / ms_step))
+        s2 = ClockSampler(local) if rank == 0 else None
+        ms_s = timed_region(run_step, n, 3, world, dev, s2) / n
+        c2 = s2.stop() if s2 is not None else None
+        v2 = value_of(wl, ms_s, world)
+        out["sustained"] = {"steps": n, "seconds": round(ms_s * n / 1e3, 2), "ms_per_step": round(ms_s, 5),
+                            "value": round(v2, 3), "unit": wl.unit, "clocks": c2,
+                            "ms_x_mhz": (round(ms_s * c2["sm_mhz"], 1) if c2 and c2["sm_mhz"] else None),
+                            "roofline": roofline_of(wl, v2, world, peaks, sustained=True)}
+    # the CPU legs get every core this process started with, not only those near the GPU
+    os.sched_setaffinity(0, host.pop("affinity_before"))
+    if rank == 0 and not args.no_cpu:
         v, sample = wl.cpu_sample()
         out["cpu_baseline"] = {"value": round(v, 5), "unit": wl.unit, "cores": torch.get_num_threads(),
                                "kind": "port", "sample": sample}
-    if rank == 0 and world == 1 and args.workload == "prefill_causal" and not args.no_decode:
-        # the metric has a decode half: report it in the same line
-        del wl
+    if headline:
+        # the other configurations of the metric, each with its own oracle check
+        del wl, run_step
         torch.cuda.empty_cache()
-        dw = make_workload("decode_paged", dev, rank, world)
-        for i in range(3):
-            dw.step(i)
-        torch.cuda.synchronize()
-        drun = GraphRunner(dw.step, dw.variants, not args.no_graph)
-        dw.config["launch"] = drun.mode
-        dms = timed_region(drun, max(5, args.steps // 2), max(3, args.warmup), world, dev) / max(5, args.steps // 2)
-        dv = dw.value_from(dms, world)
-        cv, csample = dw.cpu_sample() if not args.no_cpu else (None, None)
-        out["decode"] = {"metric": dw.metric, "value": round(dv, 2), "unit": dw.unit, "ms_per_step": round(dms, 5),
-                         "config": dw.config,
-                         "roofline": {"bound": "hbm", "achieved": round(dv, 2), "peak": peaks["hbm"], "unit": "GB/s",
-                                      "frac": round(dv / peaks["hbm"], 4), "traffic": dw.traffic,
-                                      "peak_source": peaks["source"] + " copy"},
-                         "cpu_baseline": None if cv is None else {"value": round(cv, 4), "unit": "GB/s",
-                                                                  "cores": torch.get_num_threads(), "kind": "port",
-                                                                  "sample": csample}}
+        k2, w2 = max(5, args.steps // 2), max(3, args.warmup)
+        if world > 1:
+            out["prefill_strong"] = run_block("prefill_causal", dev, rank, world, peaks, args, k2, w2, strong=True, cpu=False)
+            torch.cuda.empty_cache()
+        for key, name in (("swa", "prefill_swa"), ("decode", "decode_paged"), ("decode_long", "decode_long")):
+            out[key] = run_block(name, dev, rank, world, peaks, args, k2, w2, strong=True)
+            torch.cuda.empty_cache()
+        status = _cabi.device_status()
+        if status != 0:
+            raise SystemExit(f"device status word {status:#x} after the extra blocks")
+        if rank == 0 and not args.no_cpu:
+            out["cpu_config1"] = cpu_config1()
+        if rank == 0 and not args.no_triton:
+            try:
+                from baseline import triton_reference
+
+                out["triton_reference"] = triton_reference.run(["prefill_causal", "decode_ring"], tuned=False, reps=3)
+            except Exception as exc:       # informational block: never fail the line over it
+                out["triton_reference"] = {"unavailable": f"{type(exc).__name__}: {str(exc)[:200]}"}
+    if world > 1:
+        torch.distributed.barrier()
     if rank == 0:
         print(json.dumps(out))
     if world > 1:
         torch.distributed.destroy_process_group()
 
 
+def reference_prefill_fn(q, k, v, window):
+    """One pass over the batch with the reference's own LayerKVCache (scripts/reference_impl.py,
+    loaded unmodified from the copies oracle/make_ref.py leaves beside the oracle), or None when
+    they are not there.  q [B,H,S,D] fp32 pre-scaled, k / v [B,G,S,D] fp32."""
+    try:
+        from oracle import ref_loader
+
+        if not ref_loader.available() or window is not None:
+            return None          # the reference materialises [H,S,S] scores: 34 GB per item at S = 32768
+        Bq, Hh, S, _ = q.shape
+
+        def run():
+            for b in range(Bq):
+                cache = ref_loader.make_layer_cache(heads=Hh, kv_heads=k.shape[1], head_dim=D, context_length=S,
+                                                    sliding_window=S, is_swa=False)
+                cache.set_prefill()
+                cache.add(k[b:b + 1], v[b:b + 1])
+                cache.retrieve(q[b:b + 1])
+        return run
+    except Exception:
+        return None
+
+
 def run_reference(args):
-    """The reference's CPU attention (oracle port of scripts/reference_impl.py's LayerKVCache
-    math) on the host cores, bounded sample per step.  Rank 0 only."""
+    """The reference's CPU attention on the host cores over the whole per-GPU batch of the
+    workload: its own torch code where that can run (kind "reference"), else the oracle port of
+    the same arithmetic (kind "port").  Rank 0 only."""
     rank, world, _ = dist_env()
     if rank != 0:
         return
@@ -771,28 +1083,41 @@ def run_reference(args):
     from oracle import attention_oracle as orc
 
     gen = torch.Generator().manual_seed(1)
+    kind = "port"
     if name in ("prefill_causal", "prefill_swa"):
-        # bounded sample: ~1 s of host work per step so K + W steps end within minutes
-        S, window = (4096, None) if name == "prefill_causal" else (8192, 512)
-        q = torch.randn(H, S, D, generator=gen).to(torch.bfloat16).float()
-        k = torch.randn(G, S, D, generator=gen).to(torch.bfloat16).float()
-        v = torch.randn(G, S, D, generator=gen).to(torch.bfloat16).float()
-        units = prefill_flops(1, S, window)
-        fn = lambda: orc.attention_core(q, k, v, scale=SCALE, causal=True, sliding_window=window)
+        Bf, S, window = (4, 8192, None) if name == "prefill_causal" else (2, 32768, 512)
+        q = torch.randn(Bf, H, S, D, generator=gen).to(torch.bfloat16).float()
+        k = torch.randn(Bf, G, S, D, generator=gen).to(torch.bfloat16).float()
+        v = torch.randn(Bf, G, S, D, generator=gen).to(torch.bfloat16).float()
+        units = prefill_flops(Bf, S, window)
+
+        def port():
+            for b in range(Bf):
+                orc.attention_core(q[b], k[b], v[b], scale=SCALE, causal=True, sliding_window=window)
+
+        fn = port
+        sample = f"all {Bf} batch items x {S} tokens, all {H} heads per step, fp32, 1024-query blocks"
+        ref_fn = reference_prefill_fn(q * SCALE, k, v, window)
+        if ref_fn is not None and not args.port:
+            t0 = time.perf_counter()
+            ref_fn()
+            probe = time.perf_counter() - t0
+            if probe * (args.steps + args.warmup) < 420:       # keep the whole run within minutes
+                fn, kind = ref_fn, "reference"
+                sample = f"all {Bf} batch items x {S} tokens through the reference's LayerKVCache.add/.retrieve, fp32"
         metric, unit, div = "prefill_attn_tflops", "TFLOP/s", 1e12
-        sample = f"1 batch item, {S} tokens, all {H} heads per step, fp32, 1024-query blocks"
-        full_b, full_s = (4, 8192) if name == "prefill_causal" else (2, 32768)
-        config = {"workload": name, "batch_per_gpu": full_b, "seq_len": full_s, "q_heads": H, "kv_heads": G,
-                  "head_dim": D, "window": window, "scale": SCALE}
+        config = {"workload": name, "batch_per_gpu": Bf, "seq_len": S, "q_heads": H, "kv_heads": G,
+                  "head_dim": D, "window": window, "scale": SCALE,
+                  "l2": "inputs (%d MB) larger than L2" % ((2 * q.numel() + k.numel() + v.numel()) * 2 >> 20)}
     elif name == "prefill_chunk":
-        Hc, Gc, t, T, n = 16, 4, 256, 65536, 32
-        q = torch.randn(Hc, n, D, generator=gen).to(torch.bfloat16).float()
-        k = torch.randn(Gc, T - t + n, D, generator=gen).to(torch.bfloat16).float()
-        v = torch.randn(Gc, T - t + n, D, generator=gen).to(torch.bfloat16).float()
-        units = 4.0 * Hc * D * n * (T - t + n / 2)
-        fn = lambda: orc.attention_core(q, k, v, scale=SCALE, causal=True)
+        Hc, Gc, t, T = 16, 4, 256, 65536
+        q = torch.randn(Hc, t, D, generator=gen).to(torch.bfloat16).float()
+        k = torch.randn(Gc, T, D, generator=gen).to(torch.bfloat16).float()
+        v = torch.randn(Gc, T, D, generator=gen).to(torch.bfloat16).float()
+        units = 4.0 * Hc * D * (t * (T - t) + t * (t + 1) / 2)
+        fn = lambda: orc.attention_core(q, k, v, scale=SCALE, causal=True, q_block=32)
         metric, unit, div = "prefill_attn_tflops", "TFLOP/s", 1e12
-        sample = f"{n} of {t} chunk rows over {T - t + n} keys, all {Hc} heads per step, fp32"
+        sample = f"all {t} chunk rows over {T} keys, all {Hc} heads per step, fp32, 32-query blocks"
         config = {"workload": name, "batch_per_gpu": 1, "chunk_rows": t, "context": T, "q_heads": Hc, "kv_heads": Gc,
                   "head_dim": D, "scale": SCALE}
     elif name == "rope_append":
@@ -807,7 +1132,7 @@ def run_reference(args):
         metric, unit, div = "rope_append_hbm_gbs", "GB/s", 1e9
         sample = f"{n} tokens of 1 batch item per step, torch fp32"
         config = {"workload": name, "batch_per_gpu": 4, "tokens": 8192, "q_heads": H, "kv_heads": G, "head_dim": D,
-                  "in_dtype": "f32", "out_dtype": "bf16"}
+                  "in_dtype": "f32", "out_dtype": "bf16", "reference_sample": sample}
     elif name == "kv_append":
         n, Gk = 2048, 4
         x = torch.randn(1, Gk, n, D, generator=gen)
@@ -818,25 +1143,37 @@ def run_reference(args):
         metric, unit, div = "kv_append_hbm_gbs", "GB/s", 1e9
         sample = f"{n} tokens of 1 batch item per step, torch fp32"
         config = {"workload": name, "batch_per_gpu": 8, "tokens": 32768, "kv_heads": Gk, "head_dim": D,
-                  "in_dtype": "f32", "cache_dtype": "f16", "norm": True}
+                  "in_dtype": "f32", "cache_dtype": "f16", "norm": True, "reference_sample": sample}
     else:
-        L = 32768 if name == "decode_paged" else 131072
-        n_pages = L // PAGE
-        kp = torch.randn(n_pages, G, PAGE, D, generator=gen).to(torch.float16)
-        vp = torch.randn(n_pages, G, PAGE, D, generator=gen).to(torch.float16)
-        bt = torch.randperm(n_pages, generator=gen).to(torch.int32)
-        q = torch.randn(H, 1, D, generator=gen)
-        units = float(L) * G * D * 2 * 2
+        # decode_paged: the first 8 sequences of the benchmark's seeded set (what the GPU arm's
+        # cpu_baseline leg runs); decode_long: the one sequence
+        if name == "decode_paged":
+            lens = torch.randint(1024, 32769, (256,), generator=torch.Generator().manual_seed(3), dtype=torch.int64)[:8]
+            dt_kv = torch.float16
+        else:
+            lens, dt_kv = torch.tensor([131072]), torch.bfloat16
+        pages = [(int(L) + PAGE - 1) // PAGE for L in lens]
+        n_pages = sum(pages)
+        kp = torch.randn(n_pages, G, PAGE, D, generator=gen).to(dt_kv)
+        vp = torch.randn(n_pages, G, PAGE, D, generator=gen).to(dt_kv)
+        perm = torch.randperm(n_pages, generator=gen).to(torch.int32)
+        tables, at = [], 0
+        for n in pages:
+            tables.append(perm[at:at + n])
+            at += n
+        qs = torch.randn(len(lens), H, 1, D, generator=gen)
+        units = float(lens.sum()) * G * D * 2 * 2
 
         def fn():
-            kk = orc.gather_pages(kp, bt, L, PAGE)
-            vv = orc.gather_pages(vp, bt, L, PAGE)
-            return orc.attention_core(q, kk, vv, scale=SCALE)
+            for b, L in enumerate(lens):
+                kk = orc.gather_pages(kp, tables[b], int(L), PAGE)
+                vv = orc.gather_pages(vp, tables[b], int(L), PAGE)
+                orc.attention_core(qs[b], kk, vv, scale=SCALE)
 
         metric, unit, div = "decode_attn_hbm_gbs", "GB/s", 1e9
-        sample = f"1 sequence of {L} tokens per step, page gather + fp32 attention"
+        sample = f"{len(lens)} sequence(s), {int(lens.sum())} tokens per step, page gather + fp32 attention"
         config = {"workload": name, "sequences": 256 if name == "decode_paged" else 1, "page_size": PAGE,
-                  "kv_dtype": "float16" if name == "decode_paged" else "bfloat16", "scale": SCALE}
+                  "kv_dtype": str(dt_kv).replace("torch.", ""), "scale": SCALE, "reference_sample": sample}
     for _ in range(args.warmup):
         fn()
     t0 = time.perf_counter()
@@ -849,7 +1186,7 @@ def run_reference(args):
         "steps": args.steps, "warmup": args.warmup, "ms_per_step": round(dt * 1e3, 3), "higher_is_better": True,
         "scaling": "weak", "vs_baseline": None, "dtype": "f32", "data": "synthetic (seeded N(0,1))",
         "config": config,
-        "cpu_baseline": {"value": round(value, 5), "unit": unit, "cores": torch.get_num_threads(), "kind": "port",
+        "cpu_baseline": {"value": round(value, 5), "unit": unit, "cores": torch.get_num_threads(), "kind": kind,
                          "sample": sample},
         "e2e": {"value": round(value, 5), "unit": unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
@@ -872,9 +1209,14 @@ def main():
     ap.add_argument("--nccl-gather", action="store_true",
                     help="decode_long on N > 1 GPUs: all-gather the partials with NCCL and merge in a second launch "
                          "instead of the one-kernel exchange over peer memory")
+    ap.add_argument("--strong", action="store_true",
+                    help="N > 1: deal ONE job over the ranks (prefill units, decode sequences) instead of the same batch on every rank")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of replaying CUDA graphs")
-    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline leg")
-    ap.add_argument("--no-decode", action="store_true", help="skip the decode half of the default line")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
+    ap.add_argument("--no-extras", action="store_true", help="default workload: only the headline, none of the other configurations' blocks")
+    ap.add_argument("--no-triton", action="store_true", help="default line: skip the reference's Triton kernel")
+    ap.add_argument("--sustained", action="store_true", help="add the two-second replay to a single-workload line")
+    ap.add_argument("--port", action="store_true", help="--impl reference: time the oracle port even where the reference's own torch code is present")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

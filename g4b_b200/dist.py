@@ -29,6 +29,32 @@ def shard_request_heads(num_requests: int, kv_heads: int, world_size: int, rank:
     return [units[i] for i in shard_requests(len(units), world_size, rank)]
 
 
+def shard_prefill_units(num_requests: int, kv_heads: int, seq_len: int, world_size: int, rank: int,
+                        window: int | None = None) -> list[tuple[int, int, int, int, int]]:
+    """Units of a prefill batch for ``rank``: (request, kv head, q_lo, q_hi, k_lo).
+
+    A (request, kv head) pair is independent of every other (its query heads read only that kv
+    head).  With more GPUs than pairs and a sliding window, the query range of every pair is
+    also cut into equal parts: queries [q_lo, q_hi) then need the keys [k_lo, q_hi) with
+    k_lo = max(0, q_lo - (window - 1)), a halo of window - 1 keys before the part.  Without a
+    window a later part would need every earlier key and most of the work, so the query range
+    is only cut for windowed attention.
+    """
+    pairs = [(r, g) for r in range(num_requests) for g in range(kv_heads)]
+    parts = 1
+    if window is not None and world_size > len(pairs):
+        parts = world_size // len(pairs)
+        while parts > 1 and seq_len % parts != 0:
+            parts -= 1
+    step = seq_len // parts
+    units = []
+    for r, g in pairs:
+        for i in range(parts):
+            q_lo, q_hi = i * step, (i + 1) * step
+            units.append((r, g, q_lo, q_hi, max(0, q_lo - (window - 1)) if window is not None else 0))
+    return [units[i] for i in shard_requests(len(units), world_size, rank)]
+
+
 def balance_sequences(context_lens: Sequence[int], world_size: int) -> list[list[int]]:
     """Greedy longest-first assignment of sequences to GPUs so that KV bytes (proportional to
     context length) balance.  Returns the sequence indices of every rank."""

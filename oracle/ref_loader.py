@@ -20,7 +20,19 @@ import sys
 import types
 from pathlib import Path
 
-REFERENCE_ROOT = Path(os.environ.get("G4B_REFERENCE_ROOT", "/root/reference"))
+def _find_reference_root() -> Path:
+    """$G4B_REFERENCE_ROOT, else the byte copies that oracle/make_ref.py leaves under
+    oracle/_ref/ (they travel to a GPU box), else a checkout named ``reference`` beside the
+    repository."""
+    here = Path(__file__).resolve().parent
+    cands = [os.environ.get("G4B_REFERENCE_ROOT"), str(here / "_ref"), str(here.parents[1] / "reference")]
+    for c in cands:
+        if c and (Path(c) / "scripts" / "reference_impl.py").exists():
+            return Path(c)
+    return here / "_ref"
+
+
+REFERENCE_ROOT = _find_reference_root()
 
 
 def available() -> bool:

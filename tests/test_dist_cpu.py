@@ -27,6 +27,29 @@ def test_shard_request_heads_for_more_gpus_than_requests():
     assert sorted(sum(units, [])) == [(r, g) for r in range(4) for g in range(2)]
 
 
+def test_shard_prefill_units_cover_every_query_once():
+    # config 2 (4 requests, causal) and config 3 (2 requests, window 512) at 1, 2, 4 and 8 GPUs
+    for n_req, S, W in ((4, 8192, None), (2, 32768, 512)):
+        for w in (1, 2, 4, 8):
+            units = sum((gdist.shard_prefill_units(n_req, 2, S, w, r, W) for r in range(w)), [])
+            per_rank = [len(gdist.shard_prefill_units(n_req, 2, S, w, r, W)) for r in range(w)]
+            assert max(per_rank) - min(per_rank) <= (0 if len(units) % w == 0 else 1)
+            seen = {}
+            for r, g, q_lo, q_hi, k_lo in units:
+                assert 0 <= k_lo <= q_lo < q_hi <= S
+                assert k_lo == (max(0, q_lo - (W - 1)) if W else 0)
+                seen.setdefault((r, g), []).append((q_lo, q_hi))
+            assert sorted(seen) == [(r, g) for r in range(n_req) for g in range(2)]
+            for rngs in seen.values():
+                rngs.sort()
+                assert rngs[0][0] == 0 and rngs[-1][1] == S
+                assert all(a[1] == b[0] for a, b in zip(rngs, rngs[1:]))
+    # the query range is cut only when there are more GPUs than pairs and a window
+    assert len(gdist.shard_prefill_units(2, 2, 32768, 8, 0, 512)) == 1
+    assert gdist.shard_prefill_units(2, 2, 32768, 8, 1, 512)[0] == (0, 0, 16384, 32768, 16384 - 511)
+    assert len(gdist.shard_prefill_units(4, 2, 8192, 8, 3, None)) == 1
+
+
 def test_balance_sequences_longest_first():
     gen = torch.Generator().manual_seed(0)
     lens = torch.randint(1024, 32769, (256,), generator=gen).tolist()
