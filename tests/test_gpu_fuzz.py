@@ -75,7 +75,13 @@ def test_random_decode_paged(cuda, seed):
                         block_tables=bt, page_size=page, num_kv_splits=S)
     want = orc.flash_attention(case["q"], case["k_pool"], case["v_pool"], torch.full((B, H, 1, 256), 2.0), case["time"], ph,
                                cw, 2, scale=1 / 16, sliding_window=sw, block_tables=case["block_tables"], page_size=page)
-    tol = dict(abs_tol=4e-3, rel_tol=2e-2) if po_dtype == torch.float16 and S > 1 else {}
+    # f16 partial accumulators (what the reference engine allocates, gemma4e.py:819-821) round
+    # every split's un-normalised accumulator to 11 bits: relative 2^-11 per element, which after
+    # the merge is at most 2^-11 x the largest |v| the slot attends to.  That bound is added to
+    # the usual absolute term; the relative term stays.
+    tol = {}
+    if po_dtype == torch.float16 and S > 1:
+        tol = dict(abs_tol=2e-3 + 2.0 ** -11 * float(case["v_pool"].float().abs().max()))
     assert_close(o, want, f"seed {seed}: H{H} G{G} lens{lens} page{page} S{S} sw{sw} cw{cw}", **tol)
 
 

@@ -145,8 +145,14 @@ def test_fused_paged_then_attention(cuda, page_size):
     od = torch.zeros(B, H, Tq, D, dtype=torch.bfloat16, device=cuda)
     flash_attention(q16, kp, vp, od, time.to(cuda), None, cw, 1, scale=1 / 16, block_tables=bt.to(cuda),
                     page_size=page_size)
-    # K, V and q each carry one bf16 rounding that may fall differently on the two sides
-    assert_close(od, want_o, "attention over the fused append", abs_tol=8e-3, rel_tol=2e-2)
+    # K, V and q each carry one bf16 rounding that may fall differently on the two sides (checked
+    # row by row above), so the attention is compared with the oracle's over the rows the GPU
+    # holds, at the tolerance of every other parity test
+    want_gpu_rows = orc.flash_attention(q16.cpu(), kp.cpu(), vp.cpu(), o, time, None, cw, 1, scale=1 / 16,
+                                        block_tables=bt, page_size=page_size)
+    assert_close(od, want_gpu_rows, "attention over the fused append")
+    # and stays near the oracle's end-to-end answer (three independent bf16 roundings apart)
+    assert_close(od, want_o, "attention over the fused append, oracle rows", abs_tol=8e-3, rel_tol=2e-2)
 
 
 def test_no_rotation_and_no_norm_moves_bits(cuda):

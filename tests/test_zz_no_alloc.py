@@ -1,5 +1,6 @@
 """The allocation-free decode entry point (g4b_attn_decode_static_scratch), called through
-the C ABI, against the ordinary entry point that takes caller-provided partial buffers.
+the C ABI, against the ordinary entry point that takes caller-provided partial buffers and
+against the CPU oracle; the free device memory must be the same before and after a call.
 
 Collected last on purpose: a run that stops at the first failure has then already run every
 other test.  It passes on its own in a fresh process and after the other tests."""
@@ -7,7 +8,7 @@ import pytest
 import torch
 
 from g4b_b200.kernels import fa2
-from helpers import assert_close, make_paged_case, make_ring_case
+from helpers import assert_close, make_paged_case, make_ring_case, orc
 
 
 def _reference_call(case, cuda, splits, layout):
@@ -25,6 +26,15 @@ def _reference_call(case, cuda, splits, layout):
         fa2.flash_attention(q, case["k"].to(cuda), case["v"].to(cuda), o, case["time"].to(cuda), None,
                             case["ctx_window"], fa2.PHASE_DECODE, po, pl, pm, scale=1 / 16, num_kv_splits=splits)
     return o
+
+
+def _oracle(case, layout, user_phase=None, o_init=None):
+    q = case["q"]
+    o = torch.zeros(q.shape) if o_init is None else o_init
+    if layout == "paged":
+        return orc.flash_attention(q, case["k_pool"], case["v_pool"], o, case["time"], user_phase, case["max_len"], 2,
+                                   scale=1 / 16, block_tables=case["block_tables"], page_size=16)
+    return orc.flash_attention(q, case["k"], case["v"], o, case["time"], user_phase, case["ctx_window"], 2, scale=1 / 16)
 
 
 def _static_call(case, cuda, splits, layout):
@@ -51,9 +61,57 @@ def test_static_scratch_decode_matches_caller_buffers_twice(cuda):
         want = _reference_call(case, cuda, splits, layout)
         got = _static_call(case, cuda, splits, layout)
         assert_close(got, want.float(), f"static scratch, {layout}, {splits} splits")
+        assert_close(got, _oracle(case, layout), f"static scratch against the oracle, {layout}, {splits} splits")
     # and once more on the first inputs, now that the array holds the second call's partials
     assert_close(_static_call(first, cuda, 16, "paged"), _reference_call(first, cuda, 16, "paged").float(),
                  "static scratch, repeat")
+
+
+@pytest.mark.gpu
+def test_static_scratch_call_allocates_nothing(cuda):
+    """Free device memory as the driver reports it is the same before and after calls of the
+    entry point (inputs and outputs are made first, and the first call on the device, which
+    looks up the array's address, is made before the reading)."""
+    case = make_paged_case(73, lens=[2000, 900], H=8, G=2, dtype=torch.float16)
+    q, kp, vp, bt, time = (case[n].to(cuda) for n in ("q", "k_pool", "v_pool", "block_tables", "time"))
+    o = torch.zeros_like(q)
+    call = lambda: fa2.decode_attention_static_scratch(q, kp, vp, o, time, None, case["max_len"], fa2.PHASE_DECODE,
+                                                       scale=1 / 16, block_tables=bt, page_size=16, num_kv_splits=8)
+    call()
+    torch.cuda.synchronize()
+    free_before, _ = torch.cuda.mem_get_info()
+    torch_before = torch.cuda.memory_allocated()
+    for _ in range(3):
+        call()
+    torch.cuda.synchronize()
+    free_after, _ = torch.cuda.mem_get_info()
+    assert free_after == free_before, f"free device memory moved by {free_before - free_after} bytes"
+    assert torch.cuda.memory_allocated() == torch_before
+    assert_close(o, _oracle(case, "paged"), "static scratch")
+
+
+@pytest.mark.gpu
+def test_static_scratch_auto_split_count_and_off_phase_slot(cuda):
+    """No split count asked for, a window beyond 4096 and many slots: the reference's table
+    says 8 splits, 8 x 260 x 8 = 16640 rows do not fit the 8192-row array, so the entry point
+    drops to 3 and serves the batch.  One slot is off phase: its rows of the shared array keep
+    whatever an earlier call left there, and its row of o must stay as it was."""
+    B = 260
+    case = make_ring_case(74, B=B, H=8, G=2, Tq=1, T=64, dtype=torch.float16, times=[64] * B, ctx_window=64)
+    phase = torch.full((B,), 2, dtype=torch.uint8)
+    phase[7] = 1
+    q, k, v, time = (case[n].to(cuda) for n in ("q", "k", "v", "time"))
+    o = torch.full(q.shape, 3.0, dtype=q.dtype, device=cuda)
+    # ctx_window_size is the static bound the split policy looks at; the ring must be that long
+    T = 8192
+    kbig = torch.zeros(B, 2, T, 256, dtype=torch.float16, device=cuda)
+    vbig = torch.zeros_like(kbig)
+    kbig[:, :, :64], vbig[:, :, :64] = k, v
+    fa2.decode_attention_static_scratch(q, kbig, vbig, o, time, phase.to(cuda), T, fa2.PHASE_DECODE, scale=1 / 16)
+    want = orc.flash_attention(case["q"], case["k"], case["v"], torch.full(q.shape, 3.0), case["time"], phase, 64, 2,
+                               scale=1 / 16)
+    assert_close(o, want, "static scratch, auto split count")
+    assert bool((o[7] == 3.0).all()), "the off-phase slot's output was touched"
 
 
 def test_static_scratch_rejects_sizes_beyond_its_maximum():
