@@ -20,8 +20,9 @@ ring cache [B, G, T, D], so paged benchmark inputs are laid out as rings for it.
 
     python baseline/triton_reference.py [--tuned] [--case NAME ...]
 
-prints one JSON line per case: time per launch, TFLOP/s or GB/s, the block sizes the
-reference picked, and the parity of its output against the CPU oracle on sampled rows.
+prints one JSON line: per case the time per launch, TFLOP/s or GB/s, the block sizes the
+reference picked, the parity of its output against the CPU oracle on sampled rows, and the
+time of this library's flash_attention on the very same tensors.
 Without --tuned the reference's G4B_SKIP_TUNING=1 mode is used (its hand-picked production
 configurations, fa2.py:152-158); with --tuned its whole autotune space is searched first.
 """
@@ -156,6 +157,8 @@ def _sampled_parity(o, q, k_ring, v_ring, time_sizes, ctx_window, rows, what):
 def run_case(fa2, name: str, dev, reps: int):
     import torch
 
+    from g4b_b200.kernels import fa2 as our_fa2
+
     gen = torch.Generator(device=dev).manual_seed(17)
     rnd = lambda *s, dt: torch.randn(*s, generator=gen, device=dev, dtype=torch.float32).to(dt)
     picked = {}
@@ -168,6 +171,8 @@ def run_case(fa2, name: str, dev, reps: int):
         t = torch.full((B,), S, dtype=torch.int32, device=dev)
         ph = torch.full((B,), fa2.PHASE_PREFILL, dtype=torch.uint8, device=dev)
         fn = lambda: fa2.flash_attention(q, k, v, o, t, ph, S, fa2.PHASE_PREFILL)
+        o2 = torch.zeros(B, S, H, D, device=dev, dtype=dt).permute(0, 2, 1, 3)
+        ours = lambda: our_fa2.flash_attention(q, k, v, o2, t, ph, S, our_fa2.PHASE_PREFILL)
         work, unit, div = 4.0 * B * H * D * (S * (S + 1) // 2), "TFLOP/s", 1e12
         rows, ctx = (0, 4097, S - 1), S
     elif name == "decode_ring":           # benchmark configuration 4, laid out as rings
@@ -182,6 +187,8 @@ def run_case(fa2, name: str, dev, reps: int):
         po = torch.empty(S_, B, H, 1, D, device=dev, dtype=dt)       # the engine's partial_o is f16 (gemma4e.py:819-821)
         pl, pm = torch.empty(S_, B, H, 1, device=dev), torch.empty(S_, B, H, 1, device=dev)
         fn = lambda: fa2.flash_attention(q, k, v, o, t, ph, T, fa2.PHASE_DECODE, po, pl, pm)
+        o2 = torch.zeros(B, 1, H, D, device=dev, dtype=dt).permute(0, 2, 1, 3)
+        ours = lambda: our_fa2.flash_attention(q, k, v, o2, t, ph, T, our_fa2.PHASE_DECODE, po, pl, pm)
         work, unit, div = float(lens.sum()) * G * D * 2 * 2, "GB/s", 1e9
         rows, ctx = (0,), T
     else:
@@ -196,9 +203,14 @@ def run_case(fa2, name: str, dev, reps: int):
     if best is not None:
         picked = {**best.kwargs, "num_warps": best.num_warps, "num_stages": best.num_stages}
     parity = _sampled_parity(o, q, k, v, t.cpu(), ctx, rows, name)
+    ms_ours = _time_launches(ours, max(reps, 10))
+    parity_ours = _sampled_parity(o2, q, k, v, t.cpu(), ctx, rows, name)
     return {"case": name, "ms_per_launch": round(ms, 4), "value": round(work / (ms * 1e-3) / div, 3), "unit": unit,
             "picked": picked, "first_call_s": round(first_call_s, 1), "parity_vs_oracle": parity,
-            "dtype": str(q.dtype).replace("torch.", "")}
+            "dtype": str(q.dtype).replace("torch.", ""),
+            "this_library_same_tensors": {"ms_per_launch": round(ms_ours, 4),
+                                          "value": round(work / (ms_ours * 1e-3) / div, 3),
+                                          "parity_vs_oracle": parity_ours, "speedup": round(ms / ms_ours, 2)}}
 
 
 def run(cases, tuned: bool, reps: int = 5):

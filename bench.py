@@ -1009,8 +1009,11 @@ def run_ours(args):
                             "value": round(v2, 3), "unit": wl.unit, "clocks": c2,
                             "ms_x_mhz": (round(ms_s * c2["sm_mhz"], 1) if c2 and c2["sm_mhz"] else None),
                             "roofline": roofline_of(wl, v2, world, peaks, sustained=True)}
-    # the CPU legs get every core this process started with, not only those near the GPU
+    # the CPU legs get every core this process started with, not only those near the GPU (and
+    # not the single thread that torchrun's OMP_NUM_THREADS=1 leaves a rank with)
     os.sched_setaffinity(0, host.pop("affinity_before"))
+    if rank == 0:
+        torch.set_num_threads(len(os.sched_getaffinity(0)))
     if rank == 0 and not args.no_cpu:
         v, sample = wl.cpu_sample()
         out["cpu_baseline"] = {"value": round(v, 5), "unit": wl.unit, "cores": torch.get_num_threads(),
