@@ -590,13 +590,15 @@ class DecodeWorkload:
     (dist.split_pages); its K/V values come from one seed, so that every rank's share belongs
     to the same sequence and the merged output can be checked against the oracle."""
 
-    def __init__(self, name, dev, seed, rank=0, world=1, sequences=256, nccl_gather=False, kv_splits=0, shard=False):
+    def __init__(self, name, dev, seed, rank=0, world=1, sequences=256, nccl_gather=False, kv_splits=0, shard=False,
+                 fused=True):
         from g4b_b200 import dist as gdist
         from g4b_b200.kernels import fa2
         from g4b_b200.kernels.rope import rope_norm_append
 
         self.fa2, self.append = fa2, rope_norm_append
         self.name, self.dev, self.rank, self.world = name, dev, rank, world
+        self.fused = fused      # the whole step as one launch (decode_step) or as append + decode + merge
         gen = torch.Generator(device="cpu").manual_seed(seed)
         self.scaling = "weak"
         if name == "decode_paged":
@@ -677,11 +679,13 @@ class DecodeWorkload:
         if self.long_split:
             self.gathered = torch.empty(world * S, B, H, 1, D + 2, device=dev, dtype=torch.float32)
             self.exchange = gdist.PartialExchange(B * H, D, device=dev)
+            if not fused:
+                self.launches_per_step = 3 if self.rank == world - 1 else 2
         kv_bytes = float(self.local_lens.sum()) * G * D * 2 * 2
         self.units = kv_bytes                                    # K/V bytes per step (this rank)
         self.total_units = float(self.all_lens.sum()) * G * D * 2 * 2 if self.scaling == "strong" else None
         self.metric, self.unit, self.bound, self.div = "decode_attn_hbm_gbs", "GB/s", "hbm", 1e9
-        self.launches_per_step = 3                               # append (K and V) + decode + combine
+        self.launches_per_step = 1 if fused else 3               # one launch, or append (K and V) + decode + combine
         self.h2d = (self.h_q.numel() + self.h_kn.numel() + self.h_vn.numel()) * 2
         self.d2h = self.h_o.numel() * 2
         self.config = {"workload": name, "sequences": len(self.all_lens), "ctx_sum": int(self.all_lens.sum()),
@@ -690,9 +694,10 @@ class DecodeWorkload:
                        "l2": "K/V (%d MB per GPU) larger than L2" % (int(kv_bytes) >> 20)}
         if self.scaling == "strong":
             self.config.update({"sequences_this_rank": B, "ctx_sum_this_rank": int(self.local_lens.sum())})
+        self.config["step"] = "one launch (append + attention + merge)" if fused else "three launches (append, attention, merge)"
         if self.long_split:
             self.config["merge"] = "all-gather + second merge launch (NCCL)" if nccl_gather else \
-                "one kernel: local merge, exchange through peer memory, final merge"
+                "inside the launch: local merge, exchange through peer memory, final merge"
         # a K/V set that is not several times the 126 MB L2 would be served from cache on the
         # next step: rotate over copies (same block table, distinct memory) totalling >= 1 GB
         self.pools = [(self.k_pool, self.v_pool)]
@@ -717,7 +722,15 @@ class DecodeWorkload:
     def step(self, i=0):
         self.k_pool, self.v_pool = self.pools[i % len(self.pools)]
         last = (not self.long_split) or self.rank == self.world - 1
-        if last:   # the new token's row lives on the rank that owns the tail of the sequence
+        if self.fused and not self.nccl_gather:
+            # the new token's row lives on the rank that owns the tail of the sequence
+            self.fa2.decode_step(self.q, self.k_pool, self.v_pool, self.o, self.time, None, self.max_len,
+                                 self.fa2.PHASE_DECODE, self.po, self.pl, self.pm,
+                                 k_new=self.kn if last else None, v_new=self.vn if last else None,
+                                 exchange=self.exchange if self.long_split else None, num_kv_splits=self.splits,
+                                 scale=SCALE, block_tables=self.bt, page_size=PAGE)
+            return
+        if last:
             # K and V rows in one launch (no rotation, no norm: a plain append of both)
             self.append(self.q, self.kn, self.vn, None, self.off, self.k_pool, self.v_pool, 1e-6,
                         norm_qk=False, norm_v=False, block_tables=self.bt, page_size=PAGE)
@@ -807,7 +820,7 @@ class DecodeWorkload:
         return touched / dt / 1e9, f"{n} of {self.B} sequences ({touched >> 20} MB of K/V), page gather + fp32 attention"
 
 
-def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_splits=0, strong=False):
+def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_splits=0, strong=False, fused=True):
     """``strong``: the workload is ONE job dealt over the ranks (strong scaling) instead of the
     same per-GPU batch on every rank."""
     from g4b_b200 import dist as gdist
@@ -827,7 +840,7 @@ def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_s
             units = gdist.shard_prefill_units(nreq, G, S, world, rank, W)
         return PrefillWorkload(name, dev, seeds[name] + 100 * rank, units=units)
     return DecodeWorkload(name, dev, seeds[name] + (0 if name == "decode_long" else 100 * rank), rank, world,
-                          sequences, nccl_gather, kv_splits, shard=strong)
+                          sequences, nccl_gather, kv_splits, shard=strong, fused=fused)
 
 
 # ------------------------------------------------------------------------------------------
@@ -954,7 +967,7 @@ def run_ours(args):
     peaks = measured_peaks()
     headline = args.workload == "prefill_causal" and not args.no_extras
     wl = make_workload(args.workload, dev, rank, world, args.sequences, args.nccl_gather, args.kv_splits,
-                       strong=args.strong)
+                       strong=args.strong, fused=not args.unfused)
     parity = None
     if hasattr(wl, "parity"):
         good, excess = wl.parity()
@@ -1214,6 +1227,8 @@ def main():
                          "instead of the one-kernel exchange over peer memory")
     ap.add_argument("--strong", action="store_true",
                     help="N > 1: deal ONE job over the ranks (prefill units, decode sequences) instead of the same batch on every rank")
+    ap.add_argument("--unfused", action="store_true",
+                    help="decode workloads: append, attention and merge as three launches instead of one decode_step launch")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of replaying CUDA graphs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
     ap.add_argument("--no-extras", action="store_true", help="default workload: only the headline, none of the other configurations' blocks")

@@ -87,6 +87,14 @@ class G4bExchangeArgs(ctypes.Structure):
     ]
 
 
+class G4bDecodeStepArgs(ctypes.Structure):
+    _fields_ = [
+        ("attn", G4bAttnArgs), ("k_new", G4bTensor), ("v_new", G4bTensor),
+        ("xbuf", ctypes.c_void_p * 8), ("state", ctypes.c_void_p), ("xbuf_bytes", ctypes.c_int64),
+        ("world", ctypes.c_int32), ("rank", ctypes.c_int32),
+    ]
+
+
 class G4bAdvanceArgs(ctypes.Structure):
     _fields_ = [
         ("input_token_ids", G4bTensor), ("out_token_ids", G4bTensor), ("cache_offsets", G4bTensor),
@@ -100,6 +108,7 @@ EXPORTS = {
     "g4b_attn_prefill": (ctypes.c_int, [ctypes.POINTER(G4bAttnArgs), ctypes.c_void_p]),
     "g4b_attn_decode": (ctypes.c_int, [ctypes.POINTER(G4bAttnArgs), ctypes.c_void_p]),
     "g4b_attn_decode_static_scratch": (ctypes.c_int, [ctypes.POINTER(G4bAttnArgs), ctypes.c_void_p]),
+    "g4b_decode_step": (ctypes.c_int, [ctypes.POINTER(G4bDecodeStepArgs), ctypes.c_void_p]),
     "g4b_attn_combine": (ctypes.c_int, [ctypes.POINTER(G4bCombineArgs), ctypes.c_void_p]),
     "g4b_attn_combine_exchange": (ctypes.c_int, [ctypes.POINTER(G4bExchangeArgs), ctypes.c_void_p]),
     "g4b_exchange_buffer_bytes": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int64, ctypes.c_int]),

@@ -19,7 +19,7 @@ LIBDIR = PKG / "lib"
 LIB = LIBDIR / "libg4b_attn.so"
 INCLUDE = PKG.parent / "include"
 
-SOURCES = ["api.cu", "kv_append.cu", "rope_append.cu", "combine.cu", "combine_exchange.cu", "decode.cu", "decode_static.cu", "prefill_sm100.cu"]
+SOURCES = ["api.cu", "kv_append.cu", "rope_append.cu", "combine.cu", "combine_exchange.cu", "decode.cu", "decode_stream.cu", "decode_static.cu", "tensor_map.cu", "prefill_sm100.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a",

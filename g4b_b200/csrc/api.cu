@@ -60,7 +60,7 @@ static int check_tensor(const G4bTensor& t, const char* name, int ndim, bool inn
 static bool is_pow2(int v) { return v > 0 && (v & (v - 1)) == 0; }
 
 // Shape rules shared by prefill and decode (fa2.py:289-320).
-static int validate_attn(const G4bAttnArgs& a, bool need_partials, int splits) {
+static int validate_attn(const G4bAttnArgs& a, bool need_partials, int splits, bool tq1 = false) {
   int rc;
   if ((rc = check_tensor(a.q, "q", 4, true))) return rc;
   if ((rc = check_tensor(a.o, "o", 4, true))) return rc;
@@ -88,7 +88,8 @@ static int validate_attn(const G4bAttnArgs& a, bool need_partials, int splits) {
   if (a.k_cache.shape[3] != D) return fail(G4B_ERR_BAD_ARG, "head dim of q and cache differ");
   const int64_t G = a.k_cache.shape[1];
   if (G <= 0 || H % G != 0) return fail(G4B_ERR_BAD_ARG, "query heads must be a multiple of kv heads");
-  if (D != 256) return fail(G4B_ERR_UNSUPPORTED, "head dim %lld not supported (kernels are built for 256)", (long long)D);
+  if (D != 256 && !(tq1 && (D == 128 || D == 512)))
+    return fail(G4B_ERR_UNSUPPORTED, "head dim %lld not supported (Tq == 1: 128, 256, 512; Tq > 1: 256)", (long long)D);
   if ((((uintptr_t)a.k_cache.ptr) | ((uintptr_t)a.v_cache.ptr)) & 15)
     return fail(G4B_ERR_BAD_STRIDE, "k_cache/v_cache must be 16-byte aligned");
   if (a.stage != G4B_STAGE_CAUSAL && a.stage != G4B_STAGE_FULL)
@@ -187,12 +188,33 @@ int g4b_attn_decode(const G4bAttnArgs* args, void* cuda_stream) {
   if (args == nullptr) return fail(G4B_ERR_BAD_ARG, "args is null");
   const G4bAttnArgs& a = *args;
   const int splits = a.num_kv_splits > 0 ? a.num_kv_splits : 1;
-  int rc = validate_attn(a, splits > 1, splits);
+  const bool tq1 = a.q.ndim == 4 && a.q.shape[2] == 1;
+  int rc = validate_attn(a, splits > 1, splits, tq1);
   if (rc) return rc;
   if (a.q.shape[2] != 1) return fail(G4B_ERR_UNSUPPORTED, "decode kernel needs Tq == 1");
   if (a.q.shape[1] / a.k_cache.shape[1] > 8)
     return fail(G4B_ERR_UNSUPPORTED, "decode kernel supports at most 8 query heads per kv head");
+  if (decode_stream_supports(a)) return launch_decode_stream(a, splits, nullptr, (cudaStream_t)cuda_stream);
+  if (a.q.shape[3] != 256) return fail(G4B_ERR_UNSUPPORTED, "decode: ring caches shorter than 16 rows need head dim 256");
   return launch_decode(a, splits, (cudaStream_t)cuda_stream);
+}
+
+int g4b_decode_step(const G4bDecodeStepArgs* args, void* cuda_stream) {
+  if (args == nullptr) return fail(G4B_ERR_BAD_ARG, "args is null");
+  G4bAttnArgs a = args->attn;
+  if (a.q.ndim != 4 || a.q.shape[2] != 1) return fail(G4B_ERR_UNSUPPORTED, "decode step needs q of shape [B,H,1,D]");
+  if (a.k_cache.ndim != 4) return fail(G4B_ERR_BAD_ARG, "k_cache: expected rank 4");
+  const int splits = resolve_splits(a);
+  a.num_kv_splits = splits;
+  int rc = validate_attn(a, true, splits, true);
+  if (rc) return rc;
+  if (a.q.shape[1] / a.k_cache.shape[1] > 8)
+    return fail(G4B_ERR_UNSUPPORTED, "decode step supports at most 8 query heads per kv head");
+  if (!decode_stream_supports(a))
+    return fail(G4B_ERR_UNSUPPORTED, "decode step needs pages or a ring of at least 16 rows");
+  G4bDecodeStepArgs s = *args;
+  s.attn = a;
+  return launch_decode_stream(a, splits, &s, (cudaStream_t)cuda_stream);
 }
 
 int g4b_attn_prefill(const G4bAttnArgs* args, void* cuda_stream) {

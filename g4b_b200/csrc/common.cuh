@@ -66,7 +66,9 @@ int32_t* device_status_ptr();  // address of the __device__ word on the current 
 int launch_kv_append(const G4bAppendArgs& a, cudaStream_t st);
 int launch_advance(const G4bAdvanceArgs& a, cudaStream_t st);
 int launch_combine(const G4bCombineArgs& a, cudaStream_t st);
-int launch_decode(const G4bAttnArgs& a, int num_splits, cudaStream_t st);
+int launch_decode(const G4bAttnArgs& a, int num_splits, cudaStream_t st);            // register-streaming kernel (head dim 256)
+bool decode_stream_supports(const G4bAttnArgs& a);                                    // shapes the TMA-fed kernel takes
+int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeStepArgs* step, cudaStream_t st);
 int launch_prefill(const G4bAttnArgs& a, cudaStream_t st);
 
 // ---------------------------------------------------------------------------------------

@@ -1,0 +1,794 @@
+// Single-token decode attention as a TMA-fed stream: K/V tiles go HBM -> shared memory through
+// a ring of mbarrier-guarded stages that one producer warp keeps full, independent of the
+// registers of the warps that compute; optionally the whole decode step -- append of the new
+// token's K/V rows, attention, merge of the splits, exchange with peer GPUs -- is this one
+// launch.
+//
+// Replaces _attn_kernel (g4b/kernels/fa2.py:256-480) for Tq == 1 and, in the fused form,
+// _reduce_split_kv_kernel (fa2.py:546-631) and the two add_kv_to_cache launches before it
+// (g4b/models/gemma4e.py:575-592), in the reference's ring layout (fa2.py:52-55,75) and in
+// the paged layout.
+//
+// A CTA = one (slot b, kv head g, split s): 3 consumer warps + 1 producer warp.
+//   producer   walks the split's 16-key blocks; per block one stage = a K tile and a V tile
+//              [16 keys x D], fetched as 128-byte-swizzled TMA boxes of 16 rows x 64 elements
+//              (one (page, kv head) run in paged mode; ring rows in ring mode, the block that
+//              crosses the end of the ring as two stages whose boxes start past the end /
+//              before row 0 and read zeros there).  Every stage carries its key range, so
+//              partial blocks (window edges, the ring's wrap, a bad table entry) are masked
+//              by the consumer, never computed with.
+//   consumers  warp w takes stages w, w+3, ...: S = Q K^T and O^T = V^T P^T with warp-level
+//              m16n8k16 instructions whose K / V operand fragments come out of the swizzled
+//              tiles by ldmatrix (V transposed on the way); base-2 online softmax per head;
+//              all (<= 8) query heads of the kv head share every byte.
+// The 3 warps merge through shared memory; the CTA writes o (one split) or the (acc, l, m)
+// partial of fa2.py:438-472.
+//
+// Fused merge (tickets != null): after its partial is written a CTA takes a ticket of its
+// group of 8 splits; the last one merges the group, takes a ticket of the (slot, kv head), and
+// the last of those merges the groups and writes o.  No CTA waits for another.  With peers
+// (world > 1) that last CTA instead pushes the merged partial to every GPU as self-announcing
+// 8-byte words {value, launch count}, polls (bounded) its own buffer for the peers' words and
+// finishes the merge (the word format of combine_exchange.cu).
+#include "common.cuh"
+#include "mma16816.cuh"
+#include "sm100_ptx.cuh"
+
+namespace g4b {
+namespace {
+
+constexpr int kConsumers = 3;   // + 1 producer = 4 warps: two CTAs are 8 warps, 2 per SM sub-partition, so 255 registers each
+constexpr int kStreamThreads = (kConsumers + 1) * 32;
+constexpr int kGroup = 8;                     // splits per first-level ticket
+constexpr int kMaxLevel2 = 128;               // groups per (slot, kv head): 1024 splits
+constexpr int kMaxTickets1 = 1 << 16;
+constexpr int kMaxTickets2 = 1 << 14;
+constexpr long long kPeerWaitLimit = 1ll << 31;   // SM cycles (about a second)
+
+enum : int32_t { kErrBadEntry = 0x201, kErrStageFull = 0x211, kErrStageEmpty = 0x212, kErrPeerWait = 0x401 };
+
+// Tickets of the fused merge: zero between launches (the CTA that takes the last ticket of a
+// counter puts it back to zero).  One set per GPU, shared by every launch on it.
+__device__ uint32_t g_tickets1[kMaxTickets1];
+__device__ uint32_t g_tickets2[kMaxTickets2];
+
+template <int D> struct StreamCfg {
+  static constexpr int kSlabs = D / 64;                  // 64-element (128-byte) column slabs of a row
+  static constexpr int kTileBytes = 16 * D * 2;          // 16 keys of K, or of V
+  static constexpr int kStageBytes = 2 * kTileBytes;
+  static constexpr int kStages = D == 128 ? 8 : 6;       // 64 / 96 / 192 KB in flight per CTA
+  static constexpr int kRingBytes = kStages * kStageBytes;
+  static constexpr int kCtasPerSm = D >= 512 ? 1 : 2;
+};
+
+struct StreamParams {
+  const void* q; void* o;
+  const int32_t* time_dim_sizes; const uint8_t* user_phase; const int32_t* block_tables;
+  void* po; float* pl; float* pm;
+  int64_t q_s0, q_s1, o_s0, o_s1;
+  int64_t po_s0, po_s1, po_s2, pl_s0, pl_s1, pl_s2, pm_s0, pm_s1, pm_s2;
+  int64_t time_stride, phase_stride, bt_s0, bt_s1;
+  int B, H, G, T;
+  int page_shift, num_pages, max_pages;
+  int ctx_window, sliding_window, phase, num_splits;
+  int q_dtype, o_dtype, po_dtype;
+  float scale_log2;
+  int32_t* status;
+  // fused step
+  uint32_t* tickets1; uint32_t* tickets2;
+  void* k_cache; void* v_cache;
+  const void* k_new; const void* v_new;
+  int64_t kn_s0, kn_s1, vn_s0, vn_s1;
+  unsigned long long* xbuf[8];
+  uint32_t* xstate;
+  int world, rank;
+};
+
+template <int kStages> struct alignas(16) Ctl {
+  uint64_t full[kStages];
+  uint64_t empty[kStages];
+  int4 meta[kStages];          // x: logical key of tile row 0, y / z: valid rows [y, z), w: cache row of tile row 0
+  float sm_m[kConsumers][8];
+  float sm_l[kConsumers][8];
+  float ml[8][2];              // merged (l, m) per head
+  uint32_t epoch;
+  int flag;
+  volatile int fail;
+};
+
+__device__ __forceinline__ void ldsm_x4(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t& r1, uint32_t& r2, uint32_t& r3) {
+  asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];"
+               : "=r"(r0), "=r"(r1), "=r"(r2), "=r"(r3) : "r"(addr) : "memory");
+}
+__device__ __forceinline__ void st_word_sys(unsigned long long* p, unsigned long long v) {
+  asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
+}
+__device__ __forceinline__ unsigned long long ld_word_sys(const unsigned long long* p) {
+  unsigned long long v;
+  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// Byte offset, inside a [16 rows x D] tile of 128-byte-swizzled 64-element slabs, of the
+// 16-byte chunk `chunk` (8 elements) of row `row`.
+__device__ __forceinline__ uint32_t tile_off(int row, int chunk) {
+  return (uint32_t)((chunk >> 3) * 2048 + row * 128 + (((chunk & 7) ^ (row & 7)) << 4));
+}
+
+template <int D> struct WarpAcc {
+  float oacc[D / 16][4];   // O^T: rows d = 16 i + gi (regs 0, 1) and + 8 (regs 2, 3), columns heads 2c, 2c + 1
+  float m_run;             // running max of head gi (log2 units), identical in the 4 lanes of a row
+  float l_run;             // this lane's share of the running sum
+};
+
+// One stage: 16 keys.  qa[ks]: A fragments (a0, a2) of Q for contraction step ks (head gi).
+template <typename T, int D>
+__device__ __forceinline__ void stage_step(WarpAcc<D>& st, const uint32_t (&qa)[D / 16][2], uint32_t k_tile,
+                                           uint32_t v_tile, int vlo, int vhi, float scale_log2, int lane) {
+  const int gi = lane >> 2, c = lane & 3;
+  const bool full = vlo == 0 && vhi == 16;
+  // ---------------- S = Q K^T: two groups of 8 keys, two accumulator chains each ----------------
+  float s[2][4], s2[2][4];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
+    s2[t][0] = s2[t][1] = s2[t][2] = s2[t][3] = 0.f;
+  }
+#pragma unroll
+  for (int kk = 0; kk < D / 32; ++kk) {
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      // matrices: (keys 8t.., chunk 4kk), (.., 4kk+1), (.., 4kk+2), (.., 4kk+3)
+      uint32_t r0, r1, r2, r3;
+      ldsm_x4(k_tile + tile_off(8 * t + (lane & 7), 4 * kk + (lane >> 3)), r0, r1, r2, r3);
+      Mma<T>::run(s[t], qa[2 * kk][0], 0u, qa[2 * kk][1], 0u, r0, r1);
+      Mma<T>::run(s2[t], qa[2 * kk + 1][0], 0u, qa[2 * kk + 1][1], 0u, r2, r3);
+    }
+  }
+  // ---------------- online softmax (head gi; keys 8t + 2c, 8t + 2c + 1) ----------------
+  float sv[4];
+#pragma unroll
+  for (int t = 0; t < 2; ++t)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int key = 8 * t + 2 * c + e;
+      float x = (s[t][e] + s2[t][e]) * scale_log2;
+      if (!full && (key < vlo || key >= vhi)) x = -INFINITY;
+      sv[2 * t + e] = x;
+    }
+  float mb = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+  mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 1));
+  mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 2));
+  const float m_new = fmaxf(st.m_run, mb);
+  const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+  const float alpha = exp2f(st.m_run - m_use);   // 0 on the first block
+  const bool moved = m_new > st.m_run;
+  st.m_run = m_new;
+  float pr[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) pr[e] = exp2f(sv[e] - m_use);
+  if (__any_sync(0xffffffffu, moved)) {
+    // O^T columns are heads 2c, 2c+1: fetch their factors from the rows that own them
+    const float a0 = __shfl_sync(0xffffffffu, alpha, (2 * c) * 4);
+    const float a1 = __shfl_sync(0xffffffffu, alpha, (2 * c + 1) * 4);
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) {
+      st.oacc[i][0] *= a0; st.oacc[i][1] *= a1; st.oacc[i][2] *= a0; st.oacc[i][3] *= a1;
+    }
+  }
+  const uint32_t pb0 = Mma<T>::pack(pr[0], pr[1]);
+  const uint32_t pb1 = Mma<T>::pack(pr[2], pr[3]);
+  // row sum over the ROUNDED probabilities the tensor instruction multiplies, so numerator
+  // and denominator stay consistent (exact for a single visible key)
+  st.l_run = st.l_run * alpha + Mma<T>::sum2(pb0) + Mma<T>::sum2(pb1);
+  // bf16 keeps 8 significant bits of p: feed the rounding residue through a second product
+  uint32_t pl0 = 0u, pl1 = 0u;
+  if constexpr (Mma<T>::kSplitP) {
+    pl0 = Mma<T>::pack(pr[0] - __uint_as_float(pb0 << 16), pr[1] - __uint_as_float(pb0 & 0xffff0000u));
+    pl1 = Mma<T>::pack(pr[2] - __uint_as_float(pb1 << 16), pr[3] - __uint_as_float(pb1 & 0xffff0000u));
+    st.l_run += Mma<T>::sum2(pl0) + Mma<T>::sum2(pl1);
+  }
+  // ---------------- O^T += V^T P^T ----------------
+  // rows outside the stage's key range may hold anything (NaN included): clear their bits
+  uint32_t m01 = 0xffffffffu, m23 = 0xffffffffu;
+  if (!full) {
+    auto ok = [&](int key) { return key >= vlo && key < vhi; };
+    m01 = (ok(2 * c) ? 0x0000ffffu : 0u) | (ok(2 * c + 1) ? 0xffff0000u : 0u);
+    m23 = (ok(2 * c + 8) ? 0x0000ffffu : 0u) | (ok(2 * c + 9) ? 0xffff0000u : 0u);
+  }
+#pragma unroll
+  for (int i = 0; i < D / 16; ++i) {
+    // matrices: (keys 0-7, chunk 2i), (keys 0-7, chunk 2i+1), (keys 8-15, chunk 2i), (keys 8-15, chunk 2i+1)
+    uint32_t a0, a1, a2, a3;
+    ldsm_x4_t(v_tile + tile_off((lane & 7) + 8 * (lane >> 4), 2 * i + ((lane >> 3) & 1)), a0, a1, a2, a3);
+    if (!full) { a0 &= m01; a1 &= m01; a2 &= m23; a3 &= m23; }
+    Mma<T>::run(st.oacc[i], a0, a1, a2, a3, pb0, pb1);
+    if constexpr (Mma<T>::kSplitP) Mma<T>::run(st.oacc[i], a0, a1, a2, a3, pl0, pl1);
+  }
+}
+
+// Word offset inside one rank's exchange buffer: [parity][source rank][row][D + 2].
+__device__ __forceinline__ int64_t xword(const StreamParams& p, int D, int par, int src, int row) {
+  return (((int64_t)par * p.world + src) * ((int64_t)p.B * p.H) + row) * (D + 2);
+}
+
+// Merges `count` partials of heads [h0, h0 + R) of slot b, at split indices first + i * step.
+// kFinal = false: the merged (acc, l, m) replace the partial at split `first`.
+// kFinal = true : the merged row sums / maxima go to ctl.ml and the merged un-normalised
+//                 accumulator to acc_out[h][d] in shared memory (row pitch D + 2).
+template <int D, bool kFinal, int kSt>
+__device__ __forceinline__ void merge_partials(const StreamParams& p, Ctl<kSt>* ctl, float* s_w, float* acc_out, int b,
+                                               int h0, int R, int first, int step, int count) {
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const float* pof = (const float*)p.po;
+  // weights 2^(m_i - M) and the merged row sum, one warp per head
+  for (int hh = warp; hh < R; hh += kStreamThreads / 32) {
+    const int h = h0 + hh;
+    float m = -INFINITY;
+    for (int i = lane; i < count; i += 32) {
+      const float mi = __ldcg(p.pm + (int64_t)(first + i * step) * p.pm_s0 + b * p.pm_s1 + h * p.pm_s2);
+      s_w[hh * kMaxLevel2 + i] = mi;
+      m = fmaxf(m, mi);
+    }
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float l = 0.f;
+    for (int i = lane; i < count; i += 32) {
+      const float mi = s_w[hh * kMaxLevel2 + i];
+      const float w = (mi == -INFINITY) ? 0.f : exp2f(mi - m);
+      s_w[hh * kMaxLevel2 + i] = w;
+      if (w != 0.f) l += __ldcg(p.pl + (int64_t)(first + i * step) * p.pl_s0 + b * p.pl_s1 + h * p.pl_s2) * w;
+    }
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) { ctl->ml[hh][0] = l; ctl->ml[hh][1] = m; }
+  }
+  __syncthreads();
+  // accumulators: 2 elements per thread and step (rows of a packed [.., D + 2] buffer start on
+  // 8-byte boundaries only)
+  for (int idx = tid; idx < R * (D / 2); idx += kStreamThreads) {
+    const int hh = idx / (D / 2), d = 2 * (idx - hh * (D / 2));
+    const float* src = pof + b * p.po_s1 + (h0 + hh) * p.po_s2 + d;
+    float2 acc = make_float2(0.f, 0.f);
+#pragma unroll 4
+    for (int i = 0; i < count; ++i) {
+      const float w = s_w[hh * kMaxLevel2 + i];
+      if (w == 0.f) continue;
+      const float2 x = __ldcg(reinterpret_cast<const float2*>(src + (int64_t)(first + i * step) * p.po_s0));
+      acc.x += x.x * w; acc.y += x.y * w;
+    }
+    if constexpr (kFinal) {
+      acc_out[hh * (D + 2) + d] = acc.x; acc_out[hh * (D + 2) + d + 1] = acc.y;
+    } else {
+      *reinterpret_cast<float2*>(const_cast<float*>(src) + (int64_t)first * p.po_s0) = acc;
+    }
+  }
+  if constexpr (!kFinal) {
+    if (tid < R) {
+      p.pl[(int64_t)first * p.pl_s0 + b * p.pl_s1 + (h0 + tid) * p.pl_s2] = ctl->ml[tid][0];
+      p.pm[(int64_t)first * p.pm_s0 + b * p.pm_s1 + (h0 + tid) * p.pm_s2] = ctl->ml[tid][1];
+    }
+  }
+  __syncthreads();
+}
+
+template <typename T, int D, bool kPaged>
+__global__ void __launch_bounds__(kStreamThreads, StreamCfg<D>::kCtasPerSm)
+decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+                     StreamParams p) {
+  using Cfg = StreamCfg<D>;
+  constexpr int kSt = Cfg::kStages;
+  extern __shared__ __align__(1024) uint8_t smem_raw[];
+  const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
+  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+  const int gi = lane >> 2, c = lane & 3;   // mma fragment coordinates
+  const int R = p.H / p.G;                  // query heads per kv head (<= 8)
+  uint8_t* ring = smem_raw;
+  Ctl<kSt>* ctl = reinterpret_cast<Ctl<kSt>*>(smem_raw + Cfg::kRingBytes);
+  // after the stream the ring is scratch: warp accumulators / peers' partials, then merge weights
+  float* sm_o = reinterpret_cast<float*>(ring);                                   // [kConsumers][8][D + 4]
+  float* s_w = reinterpret_cast<float*>(ring + Cfg::kRingBytes - 8 * kMaxLevel2 * 4);   // [8][kMaxLevel2]
+
+  if (tid == 0) {
+    for (int s = 0; s < kSt; ++s) {
+      ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), 1);
+      ptx::mbar_init(ptx::smem_u32(&ctl->empty[s]), 1);
+    }
+    ptx::fence_barrier_init();
+    ctl->fail = 0;
+    ctl->flag = 0;
+    ctl->epoch = p.xstate != nullptr ? p.xstate[0] + 1u : 0u;
+    ptx::prefetch_tensormap(&k_map);
+    ptx::prefetch_tensormap(&v_map);
+  }
+  __syncthreads();
+
+  // every CTA of the launch, whatever it did, counts towards the launch count of the exchange
+  auto finish = [&]() {
+    if (p.xstate == nullptr) return;
+    __syncthreads();
+    if (tid == 0) {
+      const uint32_t n_ctas = gridDim.x * gridDim.y * gridDim.z;
+      __threadfence();
+      if (atomicAdd(&p.xstate[1], 1u) == n_ctas - 1) {
+        p.xstate[1] = 0;
+        __threadfence();
+        p.xstate[0] = ctl->epoch;
+      }
+    }
+  };
+
+  if (p.user_phase != nullptr && p.user_phase[b * p.phase_stride] != (uint8_t)p.phase) { finish(); return; }
+
+  // ---- key range of this split (fa2.py:52-67, with block-aligned split boundaries) ----
+  const int time = p.time_dim_sizes[b * p.time_stride];
+  const int window = min(time, p.ctx_window);
+  // Ring mode counts keys from the oldest one the cache exposes; a paged cache is addressed by
+  // absolute position, so there the exposed window is just another lower bound.
+  int lo_all = kPaged ? time - window : 0;
+  const int hi_all = kPaged ? time : window;
+  if (p.sliding_window > 0) lo_all = max(lo_all, hi_all - p.sliding_window);
+  const int lo_al = lo_all & ~15;
+  const int nblk = hi_all > lo_al ? (hi_all - lo_al + 15) >> 4 : 0;
+  const int bps = (nblk + p.num_splits - 1) / p.num_splits;   // blocks per split
+  const int blk_lo = min(nblk, split * bps);
+  const int blk_hi = min(nblk, blk_lo + bps);
+  // ring: logical key jw is the first one stored at row 0 again; the block that holds it in
+  // its middle (if any, and if it is ours) becomes two stages
+  int ring_start = 0, jw = 0x7fffffff, wrap_blk = -1;
+  if constexpr (!kPaged) {
+    ring_start = max(time - p.ctx_window, 0) % p.T;
+    jw = p.T - ring_start;
+    if (jw > lo_al && jw < hi_all && ((jw - lo_al) & 15) != 0) wrap_blk = (jw - lo_al) >> 4;
+  }
+  const bool has_wrap = wrap_blk >= blk_lo && wrap_blk < blk_hi;
+  const int n_stages = (blk_hi - blk_lo) + (has_wrap ? 1 : 0);
+  const int pnew = (p.k_new != nullptr) ? hi_all - 1 : -1;   // logical key of the appended token
+
+  WarpAcc<D> acc;
+  if (warp == kConsumers) {
+    // =============================== producer ===============================
+    const int32_t* bt = kPaged ? p.block_tables + b * p.bt_s0 : nullptr;
+    const int page_mask = kPaged ? (1 << p.page_shift) - 1 : 0;
+    int my_page = 0;
+    for (int n = 0; n < n_stages; ++n) {
+      const int stg = n % kSt;
+      // every decision to leave the loop is taken by the whole warp
+      if (__any_sync(0xffffffffu, ctl->fail != 0)) break;
+      if (n >= kSt) {
+        const bool ok = ptx::mbar_wait(ptx::smem_u32(&ctl->empty[stg]), (uint32_t)((n / kSt) - 1) & 1u);
+        if (!__all_sync(0xffffffffu, ok)) {
+          if (lane == 0) { atomicCAS(p.status, 0, kErrStageEmpty); ctl->fail = 1; }
+          break;
+        }
+      }
+      // stage n -> (block, part of the wrap block)
+      int blk = blk_lo + n, part = 0;
+      if (has_wrap) {
+        const int w_off = wrap_blk - blk_lo;
+        if (n == w_off) part = 1;
+        else if (n == w_off + 1) { blk = wrap_blk; part = 2; }
+        else if (n > w_off + 1) blk = blk_lo + n - 1;
+      }
+      const int j0 = lo_al + (blk << 4);
+      int vlo = max(0, lo_all - j0), vhi = min(16, hi_all - j0);
+      int row0;   // cache row (paged: row of the pool seen as [num_pages * G * page, D]) of tile row 0
+      int page = 0;
+      if constexpr (kPaged) {
+        // page ids of the next 32 blocks, one per lane
+        if ((n & 31) == 0) {
+          const int bl = blk_lo + n + lane;
+          my_page = 0;
+          if (bl < blk_hi) {
+            const int pg = (lo_al + (bl << 4)) >> p.page_shift;
+            my_page = pg < p.max_pages ? bt[pg * p.bt_s1] : -1;
+          }
+        }
+        page = __shfl_sync(0xffffffffu, my_page, n & 31);
+        if (page < 0 || page >= p.num_pages) {   // never follow a bad table entry: the stage counts for nothing
+          if (lane == 0) atomicCAS(p.status, 0, kErrBadEntry);
+          page = 0; vlo = vhi = 0;
+        }
+        row0 = ((page * p.G + g) << p.page_shift) + (j0 & page_mask);
+      } else {
+        row0 = ring_start + j0;
+        if (row0 >= p.T) row0 -= p.T;
+        if (part == 1) vhi = min(vhi, jw - j0);                      // rows up to the end of the ring
+        if (part == 2) { vlo = max(vlo, jw - j0); row0 -= p.T; }     // the rest, from row 0 on (box starts before it)
+      }
+      if (lane == 0) {
+        ctl->meta[stg] = make_int4(j0, vlo, vhi, row0);
+        const uint32_t bar = ptx::smem_u32(&ctl->full[stg]);
+        ptx::mbar_arrive_expect_tx(bar, (uint32_t)Cfg::kStageBytes);
+        const uint32_t kdst = ptx::smem_u32(ring + stg * Cfg::kStageBytes);
+        const uint32_t vdst = kdst + Cfg::kTileBytes;
+#pragma unroll
+        for (int s = 0; s < Cfg::kSlabs; ++s) {
+          if constexpr (kPaged) {
+            ptx::tma_load_4d(kdst + s * 2048, &k_map, bar, 64 * s, j0 & page_mask, g, page);
+            ptx::tma_load_4d(vdst + s * 2048, &v_map, bar, 64 * s, j0 & page_mask, g, page);
+          } else {
+            ptx::tma_load_3d(kdst + s * 2048, &k_map, bar, 64 * s, row0, b * p.G + g);
+            ptx::tma_load_3d(vdst + s * 2048, &v_map, bar, 64 * s, row0, b * p.G + g);
+          }
+        }
+      }
+      __syncwarp();
+    }
+  } else {
+    // =============================== consumers ===============================
+    // Q fragments of head gi: a0 = q[16 ks + 2c, +1], a2 = q[16 ks + 8 + 2c, +1]
+    uint32_t qa[D / 16][2];
+#pragma unroll
+    for (int ks = 0; ks < D / 16; ++ks) qa[ks][0] = qa[ks][1] = 0u;
+    if (gi < R) {
+      const int h = g * R + gi;
+      const int64_t qoff = b * p.q_s0 + h * p.q_s1;
+      if (p.q_dtype == ElemTraits<T>::kDtype && ((reinterpret_cast<uintptr_t>((const T*)p.q + qoff) & 3) == 0)) {
+        const uint32_t* qw = reinterpret_cast<const uint32_t*>((const T*)p.q + qoff);
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) { qa[ks][0] = qw[8 * ks + c]; qa[ks][1] = qw[8 * ks + 4 + c]; }
+      } else {
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+          const int64_t e = qoff + 16 * ks + 2 * c;
+          qa[ks][0] = Mma<T>::pack(load_as_float(p.q, e, p.q_dtype), load_as_float(p.q, e + 1, p.q_dtype));
+          qa[ks][1] = Mma<T>::pack(load_as_float(p.q, e + 8, p.q_dtype), load_as_float(p.q, e + 9, p.q_dtype));
+        }
+      }
+    }
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) { acc.oacc[i][0] = acc.oacc[i][1] = acc.oacc[i][2] = acc.oacc[i][3] = 0.f; }
+    acc.m_run = -INFINITY;
+    acc.l_run = 0.f;
+
+    for (int n = warp; n < n_stages; n += kConsumers) {
+      const int stg = n % kSt;
+      if (__any_sync(0xffffffffu, ctl->fail != 0)) break;
+      {
+        const bool ok = ptx::mbar_wait(ptx::smem_u32(&ctl->full[stg]), (uint32_t)(n / kSt) & 1u);
+        if (!__all_sync(0xffffffffu, ok)) {
+          if (lane == 0) { atomicCAS(p.status, 0, kErrStageFull); ctl->fail = 1; }
+          break;
+        }
+      }
+      const int4 meta = ctl->meta[stg];
+      uint8_t* kt = ring + stg * Cfg::kStageBytes;
+      uint8_t* vt = kt + Cfg::kTileBytes;
+      if (pnew >= 0 && pnew - meta.x >= meta.y && pnew - meta.x < meta.z) {
+        // the appended token lives in this stage: its K / V rows come from k_new / v_new (into
+        // the tile, in place of whatever the cache held) and go to the cache for later steps
+        const int rr = pnew - meta.x;
+        const T* kn = (const T*)p.k_new + b * p.kn_s0 + g * p.kn_s1;
+        const T* vn = (const T*)p.v_new + b * p.vn_s0 + g * p.vn_s1;
+        int64_t crow = (int64_t)meta.w + rr;
+        if constexpr (!kPaged) crow += ((int64_t)b * p.G + g) * p.T;
+        for (int ch = lane; ch < D / 8; ch += 32) {
+          const uint4 kv = *reinterpret_cast<const uint4*>(kn + 8 * ch);
+          const uint4 vv = *reinterpret_cast<const uint4*>(vn + 8 * ch);
+          *reinterpret_cast<uint4*>(kt + tile_off(rr, ch)) = kv;
+          *reinterpret_cast<uint4*>(vt + tile_off(rr, ch)) = vv;
+          *reinterpret_cast<uint4*>((T*)p.k_cache + crow * D + 8 * ch) = kv;
+          *reinterpret_cast<uint4*>((T*)p.v_cache + crow * D + 8 * ch) = vv;
+        }
+        __syncwarp();
+      }
+      if (meta.z > meta.y)
+        stage_step<T, D>(acc, qa, ptx::smem_u32(kt), ptx::smem_u32(vt), meta.y, meta.z, p.scale_log2, lane);
+      __syncwarp();
+      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->empty[stg]));
+    }
+  }
+  __syncthreads();   // every stage has been consumed: the ring is scratch from here on
+
+  // ---- merge the warps ----
+  constexpr int kPitch = D + 4;
+  if (warp < kConsumers) {
+    float l_run = acc.l_run;
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 1);
+    l_run += __shfl_xor_sync(0xffffffffu, l_run, 2);
+    if (c == 0) { ctl->sm_m[warp][gi] = acc.m_run; ctl->sm_l[warp][gi] = l_run; }
+    float* so = sm_o + warp * 8 * kPitch;
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) {
+      const int d = 16 * i + gi;
+      so[(2 * c) * kPitch + d] = acc.oacc[i][0];
+      so[(2 * c + 1) * kPitch + d] = acc.oacc[i][1];
+      so[(2 * c) * kPitch + d + 8] = acc.oacc[i][2];
+      so[(2 * c + 1) * kPitch + d + 8] = acc.oacc[i][3];
+    }
+  }
+  __syncthreads();
+
+  const bool fused = p.tickets1 != nullptr;
+  for (int idx = tid; idx < R * D; idx += kStreamThreads) {
+    const int hh = idx / D, d = idx - hh * D;
+    float m = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kConsumers; ++w) m = fmaxf(m, ctl->sm_m[w][hh]);
+    float a = 0.f, l = 0.f;
+#pragma unroll
+    for (int w = 0; w < kConsumers; ++w) {
+      const float mw = ctl->sm_m[w][hh];
+      if (mw == -INFINITY) continue;
+      const float sc = exp2f(mw - m);
+      a += sm_o[(w * 8 + hh) * kPitch + d] * sc;
+      l += ctl->sm_l[w][hh] * sc;
+    }
+    const int h = g * R + hh;
+    if (p.num_splits == 1 && !fused) {
+      store_from_float(p.o, b * p.o_s0 + h * p.o_s1 + d, p.o_dtype, l > 0.f ? a / l : 0.f);
+    } else {
+      store_from_float(p.po, split * p.po_s0 + b * p.po_s1 + h * p.po_s2 + d, p.po_dtype, a);
+      if (d == 0) {
+        p.pl[split * p.pl_s0 + b * p.pl_s1 + h * p.pl_s2] = l;
+        p.pm[split * p.pm_s0 + b * p.pm_s1 + h * p.pm_s2] = m;
+      }
+    }
+  }
+  if (!fused) return;   // the caller merges (never with an exchange: the launcher sees to that)
+
+  // =============================== fused merge ===============================
+  const int unit = b * p.G + g;
+  const int n_groups = (p.num_splits + kGroup - 1) / kGroup;
+  const int grp = split / kGroup;
+  const int in_group = min(kGroup, p.num_splits - grp * kGroup);
+  // level 1: the last CTA of a group of splits to get here merges the group
+  __threadfence();
+  __syncthreads();
+  if (tid == 0) {
+    uint32_t* t1 = p.tickets1 + (int64_t)unit * n_groups + grp;
+    const bool last = atomicAdd(t1, 1u) == (uint32_t)in_group - 1;
+    if (last) *t1 = 0;
+    ctl->flag = last ? 1 : 0;
+  }
+  __syncthreads();
+  if (!ctl->flag) { finish(); return; }
+  __threadfence();
+  float* x_acc = sm_o;   // merged accumulator [R][D + 2], then the peers' pieces behind it
+  if (n_groups > 1) {
+    merge_partials<D, false, kSt>(p, ctl, s_w, nullptr, b, g * R, R, grp * kGroup, 1, in_group);
+    // level 2: the last group of the (slot, kv head) merges the groups
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) {
+      uint32_t* t2 = p.tickets2 + unit;
+      const bool last = atomicAdd(t2, 1u) == (uint32_t)n_groups - 1;
+      if (last) *t2 = 0;
+      ctl->flag = last ? 1 : 0;
+    }
+    __syncthreads();
+    if (!ctl->flag) { finish(); return; }
+    __threadfence();
+    merge_partials<D, true, kSt>(p, ctl, s_w, x_acc, b, g * R, R, 0, kGroup, n_groups);
+  } else {
+    merge_partials<D, true, kSt>(p, ctl, s_w, x_acc, b, g * R, R, 0, 1, in_group);
+  }
+
+  if (p.world <= 1) {
+    for (int idx = tid; idx < R * D; idx += kStreamThreads) {
+      const int hh = idx / D, d = idx - hh * D;
+      const float l = ctl->ml[hh][0];
+      store_from_float(p.o, b * p.o_s0 + (g * R + hh) * p.o_s1 + d, p.o_dtype, l > 0.f ? x_acc[hh * (D + 2) + d] / l : 0.f);
+    }
+    return;
+  }
+
+  // ---- exchange: push this GPU's merged piece to every GPU, wait for theirs, merge ----
+  const uint32_t epoch = ctl->epoch;
+  const int par = (int)(epoch & 1u);
+  if (tid < R) { x_acc[tid * (D + 2) + D] = ctl->ml[tid][0]; x_acc[tid * (D + 2) + D + 1] = ctl->ml[tid][1]; }
+  __syncthreads();
+  const int n_words = R * (D + 2);
+  for (int idx = tid; idx < n_words; idx += kStreamThreads) {
+    const int hh = idx / (D + 2), e = idx - hh * (D + 2);
+    const int64_t off = xword(p, D, par, p.rank, g * R + hh + b * p.H) + e;
+    const unsigned long long word = ((unsigned long long)epoch << 32) | __float_as_uint(x_acc[idx]);
+    for (int r = 0; r < p.world; ++r) st_word_sys(p.xbuf[r] + off, word);
+  }
+  float* x_all = x_acc + R * (D + 2);   // [world][R][D + 2]
+  const long long t0 = clock64();
+  for (int idx = tid; idx < p.world * n_words; idx += kStreamThreads) {
+    const int r = idx / n_words, rem = idx - r * n_words;
+    const int hh = rem / (D + 2), e = rem - hh * (D + 2);
+    const unsigned long long* src = p.xbuf[p.rank] + xword(p, D, par, r, g * R + hh + b * p.H) + e;
+    unsigned long long w = ld_word_sys(src);
+    while ((uint32_t)(w >> 32) != epoch) {
+      if (ctl->fail || clock64() - t0 > kPeerWaitLimit) { atomicCAS(p.status, 0, kErrPeerWait); ctl->fail = 1; break; }
+      w = ld_word_sys(src);
+    }
+    x_all[idx] = __uint_as_float((uint32_t)w);
+  }
+  __syncthreads();
+  if (!ctl->fail) {
+    for (int idx = tid; idx < R * D; idx += kStreamThreads) {
+      const int hh = idx / D, d = idx - hh * D;
+      float mm = -INFINITY;
+      for (int r = 0; r < p.world; ++r) mm = fmaxf(mm, x_all[(r * R + hh) * (D + 2) + D + 1]);
+      float num = 0.f, den = 0.f;
+      for (int r = 0; r < p.world; ++r) {
+        const float* row = x_all + (r * R + hh) * (D + 2);
+        const float w = (row[D + 1] == -INFINITY) ? 0.f : exp2f(row[D + 1] - mm);
+        num += row[d] * w;
+        den += row[D] * w;
+      }
+      store_from_float(p.o, b * p.o_s0 + (g * R + hh) * p.o_s1 + d, p.o_dtype, den > 0.f ? num / den : 0.f);
+    }
+  }
+  finish();
+}
+
+template <typename T, int D, bool kPaged>
+int launch_variant(const CUtensorMap& km, const CUtensorMap& vm, const StreamParams& p, dim3 grid, cudaStream_t st) {
+  using Cfg = StreamCfg<D>;
+  constexpr int kSmem = Cfg::kRingBytes + (int)sizeof(Ctl<Cfg::kStages>);
+  static bool attr_set[64] = {false};
+  int dev = 0;
+  G4B_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    G4B_CUDA_CHECK(cudaFuncSetAttribute(decode_stream_kernel<T, D, kPaged>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    attr_set[dev] = true;
+  }
+  decode_stream_kernel<T, D, kPaged><<<grid, kStreamThreads, kSmem, st>>>(km, vm, p);
+  G4B_CUDA_CHECK(cudaGetLastError());
+  return G4B_OK;
+}
+
+template <typename T, int D>
+int launch_layout(bool paged, const CUtensorMap& km, const CUtensorMap& vm, const StreamParams& p, dim3 grid, cudaStream_t st) {
+  return paged ? launch_variant<T, D, true>(km, vm, p, grid, st) : launch_variant<T, D, false>(km, vm, p, grid, st);
+}
+
+template <typename T>
+int launch_dim(int D, bool paged, const CUtensorMap& km, const CUtensorMap& vm, const StreamParams& p, dim3 grid, cudaStream_t st) {
+  switch (D) {
+    case 128: return launch_layout<T, 128>(paged, km, vm, p, grid, st);
+    case 256: return launch_layout<T, 256>(paged, km, vm, p, grid, st);
+    case 512: return launch_layout<T, 512>(paged, km, vm, p, grid, st);
+  }
+  return fail(G4B_ERR_UNSUPPORTED, "decode: head dim %d not supported (128, 256 or 512)", D);
+}
+
+// Device addresses of the ticket arrays on the current device (looked up once per device).
+int ticket_arrays(uint32_t** t1, uint32_t** t2) {
+  constexpr int kMaxDev = 64;
+  // Filled without a lock: threads that race on an entry all store the same addresses.
+  static uint32_t* c1[kMaxDev] = {nullptr};
+  static uint32_t* c2[kMaxDev] = {nullptr};
+  int dev = 0;
+  G4B_CUDA_CHECK(cudaGetDevice(&dev));
+  if (dev < 0 || dev >= kMaxDev) return fail(G4B_ERR_CUDA, "device index %d outside 0..%d", dev, kMaxDev - 1);
+  if (c1[dev] == nullptr || c2[dev] == nullptr) {
+    void *a = nullptr, *b = nullptr;
+    G4B_CUDA_CHECK(cudaGetSymbolAddress(&a, g_tickets1));
+    G4B_CUDA_CHECK(cudaGetSymbolAddress(&b, g_tickets2));
+    c2[dev] = (uint32_t*)b;
+    c1[dev] = (uint32_t*)a;
+  }
+  *t1 = c1[dev]; *t2 = c2[dev];
+  return G4B_OK;
+}
+
+}  // namespace
+
+bool decode_stream_supports(const G4bAttnArgs& a) {
+  const int64_t D = a.q.shape[3];
+  if (D != 128 && D != 256 && D != 512) return false;
+  if (a.q.shape[1] / a.k_cache.shape[1] > 8) return false;
+  if (a.block_tables.ptr != nullptr) return a.page_size >= 16;
+  return a.k_cache.shape[2] >= 16;
+}
+
+// `step` == nullptr: plain decode (o for one split, partials otherwise).  Otherwise the fused
+// step: merge in the launch, optional append and exchange.
+int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeStepArgs* step, cudaStream_t st) {
+  const bool paged = a.block_tables.ptr != nullptr;
+  const int64_t B = a.q.shape[0], H = a.q.shape[1], D = a.q.shape[3], G = a.k_cache.shape[1];
+  StreamParams p{};
+  p.q = a.q.ptr; p.o = a.o.ptr;
+  p.time_dim_sizes = (const int32_t*)a.time_dim_sizes.ptr;
+  p.user_phase = (const uint8_t*)a.user_phase.ptr;
+  p.block_tables = (const int32_t*)a.block_tables.ptr;
+  p.po = a.partial_o.ptr; p.pl = (float*)a.partial_l.ptr; p.pm = (float*)a.partial_m.ptr;
+  p.q_s0 = a.q.stride[0]; p.q_s1 = a.q.stride[1];
+  p.o_s0 = a.o.stride[0]; p.o_s1 = a.o.stride[1];
+  p.po_s0 = a.partial_o.stride[0]; p.po_s1 = a.partial_o.stride[1]; p.po_s2 = a.partial_o.stride[2];
+  p.pl_s0 = a.partial_l.stride[0]; p.pl_s1 = a.partial_l.stride[1]; p.pl_s2 = a.partial_l.stride[2];
+  p.pm_s0 = a.partial_m.stride[0]; p.pm_s1 = a.partial_m.stride[1]; p.pm_s2 = a.partial_m.stride[2];
+  p.time_stride = a.time_dim_sizes.stride[0]; p.phase_stride = a.user_phase.stride[0];
+  p.bt_s0 = a.block_tables.stride[0]; p.bt_s1 = a.block_tables.stride[1];
+  p.B = (int)B; p.H = (int)H; p.G = (int)G;
+  p.ctx_window = a.ctx_window_size; p.sliding_window = a.sliding_window; p.phase = a.phase;
+  p.num_splits = num_splits;
+  p.q_dtype = a.q.dtype; p.o_dtype = a.o.dtype; p.po_dtype = a.partial_o.dtype;
+  p.scale_log2 = a.scale * 1.4426950408889634f;
+  p.world = 1;
+  if (paged) {
+    while ((1 << p.page_shift) < a.page_size) ++p.page_shift;
+    p.num_pages = (int)a.k_cache.shape[0];
+    p.max_pages = (int)a.block_tables.shape[1];
+    if ((int64_t)p.num_pages * G * a.page_size > 0x7fffffffLL) return fail(G4B_ERR_TOO_LARGE, "decode: page pool beyond 2^31 rows");
+  } else {
+    p.T = (int)a.k_cache.shape[2];
+  }
+  const bool fused = step != nullptr;
+  if (fused) {
+    if (num_splits > kGroup * kMaxLevel2) return fail(G4B_ERR_TOO_LARGE, "decode step: at most %d splits", kGroup * kMaxLevel2);
+    const int64_t n_groups = (num_splits + kGroup - 1) / kGroup;
+    if (B * G * n_groups > kMaxTickets1 || B * G > kMaxTickets2)
+      return fail(G4B_ERR_TOO_LARGE, "decode step: %lld (slot, kv head) units x %lld split groups exceed the ticket arrays "
+                  "(%d / %d); use g4b_flash_attention", (long long)(B * G), (long long)n_groups, kMaxTickets2, kMaxTickets1);
+    if (a.partial_o.dtype != G4B_F32) return fail(G4B_ERR_BAD_DTYPE, "decode step: partial_o must be f32");
+    if ((((uintptr_t)a.partial_o.ptr) & 7) || (a.partial_o.stride[0] | a.partial_o.stride[1] | a.partial_o.stride[2]) % 2 != 0)
+      return fail(G4B_ERR_BAD_STRIDE, "decode step: partial_o rows must start on 8-byte boundaries");
+    if (step->k_new.ptr != nullptr || step->v_new.ptr != nullptr) {
+      const G4bTensor* nt[2] = {&step->k_new, &step->v_new};
+      for (const G4bTensor* t : nt) {
+        if (t->ptr == nullptr) return fail(G4B_ERR_BAD_ARG, "decode step: k_new and v_new must be given together");
+        if (t->ndim != 4 || t->shape[0] != B || t->shape[1] != G || t->shape[2] != 1 || t->shape[3] != D)
+          return fail(G4B_ERR_BAD_ARG, "decode step: k_new / v_new must be [B,G,1,D]");
+        if (t->dtype != a.k_cache.dtype) return fail(G4B_ERR_BAD_DTYPE, "decode step: k_new / v_new must have the cache dtype");
+        if (t->stride[3] != 1 || (((uintptr_t)t->ptr) & 15) || (t->stride[0] % 8) || (t->stride[1] % 8))
+          return fail(G4B_ERR_BAD_STRIDE, "decode step: k_new / v_new rows must be contiguous and 16-byte aligned");
+      }
+      p.k_new = step->k_new.ptr; p.v_new = step->v_new.ptr;
+      p.kn_s0 = step->k_new.stride[0]; p.kn_s1 = step->k_new.stride[1];
+      p.vn_s0 = step->v_new.stride[0]; p.vn_s1 = step->v_new.stride[1];
+      p.k_cache = a.k_cache.ptr; p.v_cache = a.v_cache.ptr;
+    }
+    if (step->world > 1) {
+      if (step->world > 8 || step->rank < 0 || step->rank >= step->world) return fail(G4B_ERR_BAD_ARG, "decode step: bad world / rank");
+      if (step->state == nullptr) return fail(G4B_ERR_BAD_ARG, "decode step: state is null");
+      const int64_t need = 2ll * step->world * B * H * (D + 2) * 8;
+      if (step->xbuf_bytes < need) return fail(G4B_ERR_BAD_ARG, "decode step: exchange buffers too small (need %lld bytes per rank)", (long long)need);
+      for (int r = 0; r < step->world; ++r) {
+        if (step->xbuf[r] == nullptr || (((uintptr_t)step->xbuf[r]) & 7)) return fail(G4B_ERR_BAD_ARG, "decode step: exchange buffer of rank %d missing or misaligned", r);
+        p.xbuf[r] = (unsigned long long*)step->xbuf[r];
+      }
+      // a CTA that waits for a peer holds its SM slot: every CTA of the launch must be resident
+      // at once on every GPU, or two GPUs could each wait for a group the other has not started
+      int dev = 0, sms = 0;
+      G4B_STOP_IF_VALIDATE_ONLY();
+      G4B_CUDA_CHECK(cudaGetDevice(&dev));
+      G4B_CUDA_CHECK(cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev));
+      const int64_t resident = (int64_t)sms * (D >= 512 ? 1 : 2);
+      if ((int64_t)num_splits * G * B > resident)
+        return fail(G4B_ERR_TOO_LARGE, "decode step with peers: %lld CTAs do not fit the GPU at once (%lld); use fewer splits",
+                    (long long)((int64_t)num_splits * G * B), (long long)resident);
+      p.xstate = (uint32_t*)step->state; p.world = step->world; p.rank = step->rank;
+    }
+  }
+  G4B_STOP_IF_VALIDATE_ONLY();
+  if (fused) {
+    int rc = ticket_arrays(&p.tickets1, &p.tickets2);
+    if (rc) return rc;
+  }
+  p.status = device_status_ptr();
+  if (p.status == nullptr) return G4B_ERR_CUDA;
+  if (B == 0) return G4B_OK;
+  CUtensorMap km, vm;
+  int rc;
+  const int esz = 2;
+  if (paged) {
+    const uint64_t P = (uint64_t)a.k_cache.shape[2], NP = (uint64_t)a.k_cache.shape[0];
+    const uint64_t dims[4] = {(uint64_t)D, P, (uint64_t)G, NP};
+    const uint64_t strides[3] = {(uint64_t)D * esz, P * D * esz, (uint64_t)G * P * D * esz};
+    const uint32_t box[4] = {64, 16, 1, 1};
+    if ((rc = encode_map(&km, a.k_cache.dtype, 4, a.k_cache.ptr, dims, strides, box, "k pool"))) return rc;
+    if ((rc = encode_map(&vm, a.v_cache.dtype, 4, a.v_cache.ptr, dims, strides, box, "v pool"))) return rc;
+  } else {
+    const uint64_t dims[3] = {(uint64_t)D, (uint64_t)p.T, (uint64_t)(B * G)};
+    const uint64_t strides[2] = {(uint64_t)D * esz, (uint64_t)p.T * D * esz};
+    const uint32_t box[3] = {64, 16, 1};
+    if ((rc = encode_map(&km, a.k_cache.dtype, 3, a.k_cache.ptr, dims, strides, box, "k_cache"))) return rc;
+    if ((rc = encode_map(&vm, a.v_cache.dtype, 3, a.v_cache.ptr, dims, strides, box, "v_cache"))) return rc;
+  }
+  dim3 grid((unsigned)num_splits, (unsigned)G, (unsigned)B);
+  if (a.k_cache.dtype == G4B_BF16) return launch_dim<__nv_bfloat16>((int)D, paged, km, vm, p, grid, st);
+  if (a.k_cache.dtype == G4B_F16) return launch_dim<__half>((int)D, paged, km, vm, p, grid, st);
+  return fail(G4B_ERR_BAD_DTYPE, "decode: KV cache must be f16 or bf16");
+}
+
+}  // namespace g4b

@@ -1294,36 +1294,6 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
 // ---------------------------------------------------------------------------------------
 // host side: tensor maps + launch
 // ---------------------------------------------------------------------------------------
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
-                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
-                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-
-static EncodeTiledFn encode_fn() {
-  static EncodeTiledFn fn = nullptr;
-  if (fn == nullptr) {
-    void* ptr = nullptr;
-    cudaDriverEntryPointQueryResult qres;
-    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
-        qres == cudaDriverEntryPointSuccess)
-      fn = (EncodeTiledFn)ptr;
-  }
-  return fn;
-}
-
-static int encode_map(CUtensorMap* map, int dtype, int rank, void* base, const uint64_t* dims,
-                      const uint64_t* strides_bytes, const uint32_t* box, const char* what) {
-  EncodeTiledFn fn = encode_fn();
-  if (fn == nullptr) return fail(G4B_ERR_CUDA, "cuTensorMapEncodeTiled is not available from the driver");
-  cuuint64_t gdim[5]; cuuint64_t gstr[4]; cuuint32_t bx[5]; cuuint32_t es[5];
-  for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
-  for (int i = 0; i < rank - 1; ++i) gstr[i] = strides_bytes[i];
-  const CUtensorMapDataType dt = dtype == G4B_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-  CUresult r = fn(map, dt, (cuuint32_t)rank, base, gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                  CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-  if (r != CUDA_SUCCESS) return fail(G4B_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);
-  return G4B_OK;
-}
-
 template <typename T, bool kPair, bool kStageOut, bool kShortItems, bool kSplit>
 static int launch_variant(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const PrefillParams& p,
                           dim3 grid, cudaStream_t st) {

@@ -114,6 +114,41 @@ def attention_decode_partials(q, k_cache, v_cache, o, time_dim_sizes, user_phase
     _cabi.check(_cabi.load().g4b_attn_decode(ctypes.byref(a), ctypes.c_void_p(_cabi.current_stream(stream))))
 
 
+def decode_step(q, k_cache, v_cache, o, time_dim_sizes, user_phase, ctx_window_size, phase, partial_o, partial_l,
+                partial_m, *, k_new=None, v_new=None, exchange=None, num_kv_splits=None, scale=1.0,
+                sliding_window=None, block_tables=None, page_size=16, stage=STAGE_CAUSAL, stream=None):
+    """The decode step of one attention layer in ONE launch (``g4b_decode_step``): what the
+    reference issues as two add_kv_to_cache launches, the attention launch and the split-KV
+    reduce launch (g4b/models/gemma4e.py:575-607, fa2.py:702-714).
+
+    ``q [B,H,1,D]``; ``partial_*`` (f32) are the split workspace, merged inside the launch by
+    whichever CTA finishes last.  ``k_new, v_new [B,G,1,D]`` (cache dtype), if given, are written
+    to the cache at position ``time_dim_sizes[b] - 1`` of every slot in phase and attended to.
+    ``exchange`` (a ``g4b_b200.dist.PartialExchange``): this rank holds only its share of one
+    sequence's keys; the merged partials of all ranks are exchanged through peer memory and
+    merged in the same launch.
+
+    The merge uses ticket counters inside the library, one set per GPU: calls of this function
+    that overlap on one GPU (two streams) would share them -- keep them on one stream or order
+    them.  ``flash_attention`` has no such restriction."""
+    if (k_new is None) != (v_new is None):
+        raise ValueError("k_new and v_new must be given together")
+    s = _cabi.G4bDecodeStepArgs()
+    s.attn = _attn_args(q, k_cache, v_cache, o, time_dim_sizes, user_phase, ctx_window_size, phase,
+                        partial_o, partial_l, partial_m, stage, scale, sliding_window, block_tables,
+                        page_size, num_kv_splits)
+    s.k_new = _cabi.as_tensor(k_new)
+    s.v_new = _cabi.as_tensor(v_new)
+    s.world, s.rank = 1, 0
+    if exchange is not None:
+        for r in range(exchange.world):
+            s.xbuf[r] = exchange.xbuf_ptrs[r]
+        s.state = exchange.state.data_ptr()
+        s.xbuf_bytes = exchange.xbuf_bytes
+        s.world, s.rank = exchange.world, exchange.rank
+    _cabi.check(_cabi.load().g4b_decode_step(ctypes.byref(s), ctypes.c_void_p(_cabi.current_stream(stream))))
+
+
 def combine_partials(partial_o, partial_l, partial_m, o, num_splits, *, user_phase=None, phase=0, stream=None):
     """Log-sum-exp merge of ``num_splits`` partials into ``o`` (fa2.py:546-631)."""
     c = _cabi.G4bCombineArgs()

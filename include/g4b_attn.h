@@ -102,6 +102,10 @@ typedef struct G4bAttnArgs {
   int32_t reserved;
 } G4bAttnArgs;
 
+/* Head dims: the Tq == 1 path (g4b_attn_decode, g4b_decode_step, g4b_attn_combine, and
+ * g4b_flash_attention when Tq == 1 with at most 8 query heads per kv head) takes 128, 256 and
+ * 512; the Tq > 1 kernel (g4b_attn_prefill) takes 256. */
+
 /* replaces flash_attention() as a whole (fa2.py:634-715): picks the prefill or the
  * decode kernel, the split count, and runs the combine when splits > 1. */
 int g4b_flash_attention(const G4bAttnArgs* args, void* cuda_stream);
@@ -118,6 +122,46 @@ int g4b_attn_prefill(const G4bAttnArgs* args, void* cuda_stream);
  * NUM_KV_SPLITS >= 1): streams K/V once from HBM; writes o when the split count is 1,
  * else un-normalised partials (fa2.py:438-472) and leaves the merge to the caller. */
 int g4b_attn_decode(const G4bAttnArgs* args, void* cuda_stream);
+
+/*
+ * The whole decode step of one attention layer in ONE launch; replaces, for Tq == 1, the two
+ * add_kv_to_cache launches, the _attn_kernel launch and the _reduce_split_kv_kernel launch of
+ * the reference's decode phase (g4b/models/gemma4e.py:575-607, fa2.py:702-714).
+ *
+ *   attn            as for g4b_attn_decode; partial_* (f32, rows on 8-byte boundaries) are the
+ *                   split workspace; num_kv_splits > 0 forces the split count, 0 picks it as
+ *                   g4b_flash_attention does
+ *   k_new, v_new    optional, together: [B, G, 1, D] rows in the cache dtype.  For every slot in
+ *                   phase they are written to the cache at position time_dim_sizes[b] - 1
+ *                   (ring row (time - 1) % T, or the page the block table names) and used as
+ *                   that position's K / V, whatever the cache held there before
+ *   world > 1       one sequence's KV range is split over `world` GPUs (one process each, the
+ *                   same call sequence and shapes on every rank): after the local merge the
+ *                   merged (acc, l, m) travel to every rank's exchange buffer as 8-byte words
+ *                   {value, launch count} through peer-mapped memory and every rank finishes
+ *                   the merge.  xbuf / state / xbuf_bytes as for g4b_attn_combine_exchange
+ *                   (the buffers are interchangeable but must not be shared between the two
+ *                   entry points).  Every CTA of the launch must be resident at once
+ *                   (splits * G * B <= 2 x the SM count), else G4B_ERR_TOO_LARGE.  A peer that
+ *                   does not show up within about a second leaves 0x401 in the status word;
+ *                   after that the buffers and `state` must be zeroed again on every rank
+ *                   before the next call.
+ *
+ * The splits are merged by whichever CTA finishes last, found through ticket counters that
+ * live inside the library (one set per GPU, zero between launches).  Two launches of this
+ * entry point that overlap on one GPU would share them: keep such calls on one stream or
+ * order them.  g4b_flash_attention does not use the counters and has no such restriction.
+ */
+typedef struct G4bDecodeStepArgs {
+  G4bAttnArgs attn;
+  G4bTensor k_new, v_new;
+  void* xbuf[8];
+  void* state;
+  int64_t xbuf_bytes;
+  int32_t world;
+  int32_t rank;
+} G4bDecodeStepArgs;
+int g4b_decode_step(const G4bDecodeStepArgs* args, void* cuda_stream);
 
 /* replaces _reduce_split_kv_kernel (fa2.py:546-631): log-sum-exp merge of the first
  * num_splits partials into o.  Also merges partials gathered from other GPUs. */
@@ -281,9 +325,9 @@ int g4b_abi_version(void);
 /*
  * Reads (and clears) the device-side status word of the current device after
  * synchronising the given stream.  Kernels never trap: one that meets a block-table entry
- * outside the pool skips it and records 0x1xx (append) / 0x2xx (decode) / 0x309 (prefill); a
- * bounded wait that runs out makes the kernel return early and record 0x3xx (prefill) or
- * 0x4xx (a peer GPU that did not show up).  The word keeps the FIRST code until this call
+ * outside the pool skips it and records 0x1xx (append) / 0x201 (decode) / 0x309 (prefill); a
+ * bounded wait that runs out makes the kernel return early and record 0x21x (decode), 0x3xx
+ * (prefill) or 0x4xx (a peer GPU that did not show up).  The word keeps the FIRST code until this call
  * clears it.  While it holds a 0x3xx wait code every later prefill launch returns at once
  * without computing (the tensor pipe may be in an unknown state); codes of other kernels do
  * not stop any launch.  Returns G4B_OK with *status_out = 0, or G4B_ERR_DEVICE_WAIT with the

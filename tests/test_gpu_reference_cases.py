@@ -3,9 +3,7 @@
 oracle: same shapes, same fp16 ring caches filled everywhere, same time_dim_sizes pattern
 (ctx_window for even slots, ctx_window + 17 for odd ones, so that odd slots wrap the ring,
 test_fa2.py:285-290), same split workspace sizes.  The script itself asserts nothing and
-seeds nothing; the oracle is what pins the numbers.  Its one head-dim-128 case
-(decode_small_w1024) is outside what these kernels are built for (head dim 256) and is
-checked to be refused."""
+seeds nothing; the oracle is what pins the numbers."""
 import pytest
 import torch
 
@@ -75,11 +73,28 @@ def test_reference_prefill_t65536_sampled_rows(cuda):
         assert_close(o[0, r:r + 1].permute(1, 0, 2), want, f"row {r}")
 
 
-def test_reference_head_dim_128_case_is_refused(cuda):
-    """decode_small_w1024 (B4 H8 G2 D128): not a shape these kernels cover; the call must say
-    so instead of computing something."""
-    q = torch.zeros(4, 8, 1, 128, dtype=torch.float16, device=cuda)
-    k = torch.zeros(4, 2, 1024, 128, dtype=torch.float16, device=cuda)
-    time = torch.full((4,), 1024, dtype=torch.int32, device=cuda)
-    with pytest.raises(ValueError):
-        fa2.flash_attention(q, k, k.clone(), torch.zeros_like(q), time, None, 1024, fa2.PHASE_DECODE)
+@pytest.mark.parametrize("with_splits", [False, True])
+def test_reference_head_dim_128_decode_case(cuda, with_splits):
+    """decode_small_w1024 (B4 H8 G2 D128, test_fa2.py:52), with the script's time pattern (odd
+    slots wrap the ring) and, as its grouped_split variant, a 4-split workspace."""
+    B, H, G, T, D = 4, 8, 2, 1024, 128
+    case = make_ring_case(917, B=B, H=H, G=G, Tq=1, T=T, D=D, dtype=torch.float16)
+    q, k, v, time = (case[n].to(cuda) for n in ("q", "k", "v", "time"))
+    o = torch.zeros(B, H, 1, D, dtype=torch.float16, device=cuda)
+    parts = ()
+    if with_splits:
+        parts = (torch.empty(4, B, H, 1, D, dtype=torch.float16, device=cuda), torch.empty(4, B, H, 1, device=cuda),
+                 torch.empty(4, B, H, 1, device=cuda))
+    fa2.flash_attention(q, k, v, o, time, None, T, fa2.PHASE_DECODE, *parts, num_kv_splits=4 if with_splits else None)
+    want = orc.flash_attention(case["q"], case["k"], case["v"], torch.zeros(B, H, 1, D), case["time"], None, T, 2)
+    assert_close(o, want, "decode_small_w1024")
+
+
+def test_prefill_head_dim_128_is_refused(cuda):
+    """The Tq > 1 kernel is built for head dim 256 only; other head dims must be refused, not
+    computed."""
+    q = torch.zeros(1, 8, 64, 128, dtype=torch.float16, device=cuda)
+    k = torch.zeros(1, 2, 1024, 128, dtype=torch.float16, device=cuda)
+    time = torch.full((1,), 1024, dtype=torch.int32, device=cuda)
+    with pytest.raises(ValueError, match="head dim"):
+        fa2.flash_attention(q, k, k.clone(), torch.zeros_like(q), time, None, 1024, fa2.PHASE_PREFILL)
