@@ -591,7 +591,7 @@ class DecodeWorkload:
     to the same sequence and the merged output can be checked against the oracle."""
 
     def __init__(self, name, dev, seed, rank=0, world=1, sequences=256, nccl_gather=False, kv_splits=0, shard=False,
-                 fused=True):
+                 fused=True, merge_in_launch=None):
         from g4b_b200 import dist as gdist
         from g4b_b200.kernels import fa2
         from g4b_b200.kernels.rope import rope_norm_append
@@ -599,6 +599,11 @@ class DecodeWorkload:
         self.fa2, self.append = fa2, rope_norm_append
         self.name, self.dev, self.rank, self.world = name, dev, rank, world
         self.fused = fused      # the whole step as one launch (decode_step) or as append + decode + merge
+        # on one GPU the merge as a second launch is the faster form (every CTA's ticket costs a
+        # fence and an atomic; the merge launch is scheduled while the attention drains); with the
+        # KV range split over GPUs the merge has to be in the launch that exchanges
+        self.merge_in_launch = (name == "decode_long" and world > 1) if merge_in_launch is None else \
+            (merge_in_launch or (name == "decode_long" and world > 1))
         gen = torch.Generator(device="cpu").manual_seed(seed)
         self.scaling = "weak"
         if name == "decode_paged":
@@ -685,7 +690,8 @@ class DecodeWorkload:
         self.units = kv_bytes                                    # K/V bytes per step (this rank)
         self.total_units = float(self.all_lens.sum()) * G * D * 2 * 2 if self.scaling == "strong" else None
         self.metric, self.unit, self.bound, self.div = "decode_attn_hbm_gbs", "GB/s", "hbm", 1e9
-        self.launches_per_step = 1 if fused else 3               # one launch, or append (K and V) + decode + combine
+        # one launch; or append + attention, then the merge; or append (K and V), decode, merge
+        self.launches_per_step = (1 if self.merge_in_launch else 2) if fused else 3
         self.h2d = (self.h_q.numel() + self.h_kn.numel() + self.h_vn.numel()) * 2
         self.d2h = self.h_o.numel() * 2
         self.config = {"workload": name, "sequences": len(self.all_lens), "ctx_sum": int(self.all_lens.sum()),
@@ -694,7 +700,8 @@ class DecodeWorkload:
                        "l2": "K/V (%d MB per GPU) larger than L2" % (int(kv_bytes) >> 20)}
         if self.scaling == "strong":
             self.config.update({"sequences_this_rank": B, "ctx_sum_this_rank": int(self.local_lens.sum())})
-        self.config["step"] = "one launch (append + attention + merge)" if fused else "three launches (append, attention, merge)"
+        self.config["step"] = ("one launch (append + attention + merge)" if self.merge_in_launch else
+                               "two launches (append + attention, merge)") if fused else "three launches (append, attention, merge)"
         if self.long_split:
             self.config["merge"] = "all-gather + second merge launch (NCCL)" if nccl_gather else \
                 "inside the launch: local merge, exchange through peer memory, final merge"
@@ -728,7 +735,7 @@ class DecodeWorkload:
                                  self.fa2.PHASE_DECODE, self.po, self.pl, self.pm,
                                  k_new=self.kn if last else None, v_new=self.vn if last else None,
                                  exchange=self.exchange if self.long_split else None, num_kv_splits=self.splits,
-                                 scale=SCALE, block_tables=self.bt, page_size=PAGE)
+                                 scale=SCALE, block_tables=self.bt, page_size=PAGE, merge_in_launch=self.merge_in_launch)
             return
         if last:
             # K and V rows in one launch (no rotation, no norm: a plain append of both)
@@ -820,7 +827,8 @@ class DecodeWorkload:
         return touched / dt / 1e9, f"{n} of {self.B} sequences ({touched >> 20} MB of K/V), page gather + fp32 attention"
 
 
-def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_splits=0, strong=False, fused=True):
+def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_splits=0, strong=False, fused=True,
+                  merge_in_launch=None):
     """``strong``: the workload is ONE job dealt over the ranks (strong scaling) instead of the
     same per-GPU batch on every rank."""
     from g4b_b200 import dist as gdist
@@ -840,7 +848,7 @@ def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_s
             units = gdist.shard_prefill_units(nreq, G, S, world, rank, W)
         return PrefillWorkload(name, dev, seeds[name] + 100 * rank, units=units)
     return DecodeWorkload(name, dev, seeds[name] + (0 if name == "decode_long" else 100 * rank), rank, world,
-                          sequences, nccl_gather, kv_splits, shard=strong, fused=fused)
+                          sequences, nccl_gather, kv_splits, shard=strong, fused=fused, merge_in_launch=merge_in_launch)
 
 
 # ------------------------------------------------------------------------------------------
@@ -967,7 +975,8 @@ def run_ours(args):
     peaks = measured_peaks()
     headline = args.workload == "prefill_causal" and not args.no_extras
     wl = make_workload(args.workload, dev, rank, world, args.sequences, args.nccl_gather, args.kv_splits,
-                       strong=args.strong, fused=not args.unfused)
+                       strong=args.strong, fused=not args.unfused,
+                       merge_in_launch={"auto": None, "kernel": True, "launch": False}[args.step_merge])
     parity = None
     if hasattr(wl, "parity"):
         good, excess = wl.parity()
@@ -1229,6 +1238,9 @@ def main():
                     help="N > 1: deal ONE job over the ranks (prefill units, decode sequences) instead of the same batch on every rank")
     ap.add_argument("--unfused", action="store_true",
                     help="decode workloads: append, attention and merge as three launches instead of one decode_step launch")
+    ap.add_argument("--step-merge", default="auto", choices=["auto", "kernel", "launch"],
+                    help="decode workloads: merge the splits inside the decode_step launch (kernel) or in a second "
+                         "launch (launch); auto = second launch on one GPU, inside the launch when GPUs exchange")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of replaying CUDA graphs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
     ap.add_argument("--no-extras", action="store_true", help="default workload: only the headline, none of the other configurations' blocks")

@@ -214,7 +214,14 @@ int g4b_decode_step(const G4bDecodeStepArgs* args, void* cuda_stream) {
     return fail(G4B_ERR_UNSUPPORTED, "decode step needs pages or a ring of at least 16 rows");
   G4bDecodeStepArgs s = *args;
   s.attn = a;
-  return launch_decode_stream(a, splits, &s, (cudaStream_t)cuda_stream);
+  rc = launch_decode_stream(a, splits, &s, (cudaStream_t)cuda_stream);
+  if (rc != G4B_OK || s.world > 1 || (a.reserved & 1) == 0) return rc;
+  // the merge as a launch of its own was asked for
+  if (splits == 1) return rc;
+  G4bCombineArgs c{};
+  c.partial_o = a.partial_o; c.partial_l = a.partial_l; c.partial_m = a.partial_m; c.o = a.o;
+  c.user_phase = a.user_phase; c.num_splits = splits; c.phase = a.phase;
+  return g4b_attn_combine(&c, cuda_stream);
 }
 
 int g4b_attn_prefill(const G4bAttnArgs* args, void* cuda_stream) {

@@ -74,6 +74,10 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams 
   const int h = (int)(bh - (uint32_t)b * (uint32_t)p.H);
   if (p.user_phase != nullptr && p.user_phase[b * p.phase_stride] != (uint8_t)p.phase) return;
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
+  // Launched with programmatic stream serialization: the grid may be resident before the
+  // kernel that writes the partials has finished; nothing of theirs is read before this wait
+  // (which returns at once when the launch before was an ordinary one).
+  asm volatile("griddepcontrol.wait;" ::: "memory");
   const int64_t ml_off = b * p.pm_s[1] + h * p.pm_s[2] + t * p.pm_s[3];
   const int64_t l_off = b * p.pl_s[1] + h * p.pl_s[2] + t * p.pl_s[3];
 
@@ -121,12 +125,22 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams 
   }
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   if (n_valid > 0) {
-#pragma unroll 4
-    for (int s = grp; s < p.S; s += p.groups) {
-      const float w = s_w[s];
-      if (w == 0.f) continue;
-      const float4 x = load4_partial<TP>(po + s * p.po_s[0] + d, vmode, n_valid);
-      acc.x += x.x * w; acc.y += x.y * w; acc.z += x.z * w; acc.w += x.w * w;
+    // four independent loads in flight per thread; a partial with weight 0 (a split that saw
+    // no key) is loaded like the others and then left out, whatever its accumulator holds
+    for (int s0 = grp; s0 < p.S; s0 += 4 * p.groups) {
+      float4 x[4];
+      float w[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int s = s0 + j * p.groups;
+        w[j] = s < p.S ? s_w[s] : 0.f;
+        x[j] = load4_partial<TP>(po + (int64_t)min(s, p.S - 1) * p.po_s[0] + d, vmode, n_valid);
+      }
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        if (w[j] == 0.f) continue;
+        acc.x += x[j].x * w[j]; acc.y += x[j].y * w[j]; acc.z += x[j].z * w[j]; acc.w += x[j].w * w[j];
+      }
     }
   }
   s_acc[tid] = acc;
@@ -167,11 +181,25 @@ int launch_combine(const G4bCombineArgs& a, cudaStream_t st) {
     p.groups *= 2;
   const int cols = kCombineThreads / p.groups * 4;
   const dim3 grid((unsigned)rows, (unsigned)((p.D + cols - 1) / cols), 1);
+  // The merge always follows the kernel that wrote the partials on the same stream: let its
+  // blocks be scheduled while that kernel drains (they wait inside before reading anything).
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = dim3(kCombineThreads, 1, 1);
+  cfg.dynamicSmemBytes = 0;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
   bool launched = false;
+  cudaError_t err = cudaSuccess;
   G4B_DISPATCH_FLOAT(a.partial_o.dtype, TP,
     G4B_DISPATCH_FLOAT(a.o.dtype, TO,
-      combine_kernel<TP, TO><<<grid, kCombineThreads, 0, st>>>(p); launched = true));
+      err = cudaLaunchKernelEx(&cfg, combine_kernel<TP, TO>, p); launched = true));
   if (!launched) return fail(G4B_ERR_BAD_DTYPE, "combine: partial_o/o dtypes must be f32, f16 or bf16");
+  G4B_CUDA_CHECK(err);
   G4B_CUDA_CHECK(cudaGetLastError());
   return G4B_OK;
 }

@@ -225,22 +225,31 @@ __device__ __forceinline__ void merge_partials(const StreamParams& p, Ctl<kSt>* 
                                                int h0, int R, int first, int step, int count) {
   const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
   const float* pof = (const float*)p.po;
-  // weights 2^(m_i - M) and the merged row sum, one warp per head
+  // weights 2^(m_i - M) and the merged row sum, one warp per head; every (m, l) pair is
+  // requested before any is used, so the warp pays one trip to L2, not two per partial
   for (int hh = warp; hh < R; hh += kStreamThreads / 32) {
     const int h = h0 + hh;
-    float m = -INFINITY;
-    for (int i = lane; i < count; i += 32) {
-      const float mi = __ldcg(p.pm + (int64_t)(first + i * step) * p.pm_s0 + b * p.pm_s1 + h * p.pm_s2);
-      s_w[hh * kMaxLevel2 + i] = mi;
-      m = fmaxf(m, mi);
+    float mi[kMaxLevel2 / 32], li[kMaxLevel2 / 32];
+#pragma unroll
+    for (int j = 0; j < kMaxLevel2 / 32; ++j) {
+      const int i = lane + 32 * j;
+      mi[j] = -INFINITY; li[j] = 0.f;
+      if (i < count) {
+        mi[j] = __ldcg(p.pm + (int64_t)(first + i * step) * p.pm_s0 + b * p.pm_s1 + h * p.pm_s2);
+        li[j] = __ldcg(p.pl + (int64_t)(first + i * step) * p.pl_s0 + b * p.pl_s1 + h * p.pl_s2);
+      }
     }
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kMaxLevel2 / 32; ++j) m = fmaxf(m, mi[j]);
     for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
     float l = 0.f;
-    for (int i = lane; i < count; i += 32) {
-      const float mi = s_w[hh * kMaxLevel2 + i];
-      const float w = (mi == -INFINITY) ? 0.f : exp2f(mi - m);
-      s_w[hh * kMaxLevel2 + i] = w;
-      if (w != 0.f) l += __ldcg(p.pl + (int64_t)(first + i * step) * p.pl_s0 + b * p.pl_s1 + h * p.pl_s2) * w;
+#pragma unroll
+    for (int j = 0; j < kMaxLevel2 / 32; ++j) {
+      const int i = lane + 32 * j;
+      const float w = (mi[j] == -INFINITY) ? 0.f : exp2f(mi[j] - m);
+      if (i < count) s_w[hh * kMaxLevel2 + i] = w;
+      l += li[j] * w;
     }
     for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
     if (lane == 0) { ctl->ml[hh][0] = l; ctl->ml[hh][1] = m; }
@@ -252,12 +261,20 @@ __device__ __forceinline__ void merge_partials(const StreamParams& p, Ctl<kSt>* 
     const int hh = idx / (D / 2), d = 2 * (idx - hh * (D / 2));
     const float* src = pof + b * p.po_s1 + (h0 + hh) * p.po_s2 + d;
     float2 acc = make_float2(0.f, 0.f);
-#pragma unroll 4
-    for (int i = 0; i < count; ++i) {
-      const float w = s_w[hh * kMaxLevel2 + i];
-      if (w == 0.f) continue;
-      const float2 x = __ldcg(reinterpret_cast<const float2*>(src + (int64_t)(first + i * step) * p.po_s0));
-      acc.x += x.x * w; acc.y += x.y * w;
+    // eight independent loads in flight per thread (a partial that saw no key holds zeros and
+    // has weight 0, so nothing needs to be skipped)
+    for (int i0 = 0; i0 < count; i0 += 8) {
+      float2 x[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const int i = min(i0 + j, count - 1);
+        x[j] = __ldcg(reinterpret_cast<const float2*>(src + (int64_t)(first + i * step) * p.po_s0));
+      }
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        const float w = i0 + j < count ? s_w[hh * kMaxLevel2 + i0 + j] : 0.f;
+        acc.x += x[j].x * w; acc.y += x[j].y * w;
+      }
     }
     if constexpr (kFinal) {
       acc_out[hh * (D + 2) + d] = acc.x; acc_out[hh * (D + 2) + d + 1] = acc.y;
@@ -291,6 +308,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   float* sm_o = reinterpret_cast<float*>(ring);                                   // [kConsumers][8][D + 4]
   float* s_w = reinterpret_cast<float*>(ring + Cfg::kRingBytes - 8 * kMaxLevel2 * 4);   // [8][kMaxLevel2]
 
+  // a merge launch that follows may be scheduled as soon as SM resources free up (it waits for
+  // this grid to finish before it reads the partials)
+  asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
   if (tid == 0) {
     for (int s = 0; s < kSt; ++s) {
       ptx::mbar_init(ptx::smem_u32(&ctl->full[s]), 1);
@@ -713,11 +733,13 @@ int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeSt
   } else {
     p.T = (int)a.k_cache.shape[2];
   }
+  // step->attn.reserved bit 0: leave the merge to a second launch (the append stays in this one)
   const bool fused = step != nullptr;
+  const bool tickets = fused && (step->world > 1 || (step->attn.reserved & 1) == 0);
   if (fused) {
     if (num_splits > kGroup * kMaxLevel2) return fail(G4B_ERR_TOO_LARGE, "decode step: at most %d splits", kGroup * kMaxLevel2);
     const int64_t n_groups = (num_splits + kGroup - 1) / kGroup;
-    if (B * G * n_groups > kMaxTickets1 || B * G > kMaxTickets2)
+    if (tickets && (B * G * n_groups > kMaxTickets1 || B * G > kMaxTickets2))
       return fail(G4B_ERR_TOO_LARGE, "decode step: %lld (slot, kv head) units x %lld split groups exceed the ticket arrays "
                   "(%d / %d); use g4b_flash_attention", (long long)(B * G), (long long)n_groups, kMaxTickets2, kMaxTickets1);
     if (a.partial_o.dtype != G4B_F32) return fail(G4B_ERR_BAD_DTYPE, "decode step: partial_o must be f32");
@@ -761,7 +783,7 @@ int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeSt
     }
   }
   G4B_STOP_IF_VALIDATE_ONLY();
-  if (fused) {
+  if (tickets) {
     int rc = ticket_arrays(&p.tickets1, &p.tickets2);
     if (rc) return rc;
   }

@@ -116,7 +116,8 @@ def attention_decode_partials(q, k_cache, v_cache, o, time_dim_sizes, user_phase
 
 def decode_step(q, k_cache, v_cache, o, time_dim_sizes, user_phase, ctx_window_size, phase, partial_o, partial_l,
                 partial_m, *, k_new=None, v_new=None, exchange=None, num_kv_splits=None, scale=1.0,
-                sliding_window=None, block_tables=None, page_size=16, stage=STAGE_CAUSAL, stream=None):
+                sliding_window=None, block_tables=None, page_size=16, stage=STAGE_CAUSAL, merge_in_launch=True,
+                stream=None):
     """The decode step of one attention layer in ONE launch (``g4b_decode_step``): what the
     reference issues as two add_kv_to_cache launches, the attention launch and the split-KV
     reduce launch (g4b/models/gemma4e.py:575-607, fa2.py:702-714).
@@ -137,6 +138,7 @@ def decode_step(q, k_cache, v_cache, o, time_dim_sizes, user_phase, ctx_window_s
     s.attn = _attn_args(q, k_cache, v_cache, o, time_dim_sizes, user_phase, ctx_window_size, phase,
                         partial_o, partial_l, partial_m, stage, scale, sliding_window, block_tables,
                         page_size, num_kv_splits)
+    s.attn.reserved = 0 if merge_in_launch else 1      # else the merge is a second launch (no tickets)
     s.k_new = _cabi.as_tensor(k_new)
     s.v_new = _cabi.as_tensor(v_new)
     s.world, s.rank = 1, 0

@@ -131,6 +131,8 @@ int g4b_attn_decode(const G4bAttnArgs* args, void* cuda_stream);
  *   attn            as for g4b_attn_decode; partial_* (f32, rows on 8-byte boundaries) are the
  *                   split workspace; num_kv_splits > 0 forces the split count, 0 picks it as
  *                   g4b_flash_attention does
+ *   attn.reserved   bit 0 set (and world <= 1): the splits are merged by a second launch
+ *                   (g4b_attn_combine) instead of inside this one; the append stays in it
  *   k_new, v_new    optional, together: [B, G, 1, D] rows in the cache dtype.  For every slot in
  *                   phase they are written to the cache at position time_dim_sizes[b] - 1
  *                   (ring row (time - 1) % T, or the page the block table names) and used as
