@@ -17,7 +17,9 @@
 //              before row 0 and read zeros there).  Every stage carries its key range, so
 //              partial blocks (window edges, the ring's wrap, a bad table entry) are masked
 //              by the consumer, never computed with.
-//   consumers  warp w takes stages w, w+3, ...: S = Q K^T and O^T = V^T P^T with warp-level
+//   consumers  take the stages in order, whichever warp is free next (a shared counter), so
+//              all stages of the ring are in flight or in work whatever the warps' pace;
+//              S = Q K^T and O^T = V^T P^T with warp-level
 //              m16n8k16 instructions whose K / V operand fragments come out of the swizzled
 //              tiles by ldmatrix (V transposed on the way); base-2 online softmax per head;
 //              all (<= 8) query heads of the kv head share every byte.
@@ -45,7 +47,8 @@ constexpr int kMaxTickets1 = 1 << 16;
 constexpr int kMaxTickets2 = 1 << 14;
 constexpr long long kPeerWaitLimit = 1ll << 31;   // SM cycles (about a second)
 
-enum : int32_t { kErrBadEntry = 0x201, kErrStageFull = 0x211, kErrStageEmpty = 0x212, kErrPeerWait = 0x401 };
+enum : int32_t { kErrBadEntry = 0x201, kErrStageFull = 0x211, kErrStageEmpty = 0x212, kErrStageOrder = 0x213,
+                 kErrAppendRow = 0x214, kErrPeerWait = 0x401 };
 
 // Tickets of the fused merge: zero between launches (the CTA that takes the last ticket of a
 // counter puts it back to zero).  One set per GPU, shared by every launch on it.
@@ -93,6 +96,8 @@ template <int kStages> struct alignas(16) Ctl {
   float ml[8][2];              // merged (l, m) per head
   uint32_t epoch;
   int flag;
+  int next_stage;              // next stage no consumer has claimed yet
+  volatile int done[kStages];  // uses of a ring slot that have been consumed
   volatile int fail;
 };
 
@@ -110,6 +115,13 @@ __device__ __forceinline__ void st_word_sys(unsigned long long* p, unsigned long
 __device__ __forceinline__ unsigned long long ld_word_sys(const unsigned long long* p) {
   unsigned long long v;
   asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
+  return v;
+}
+
+// two neighbouring words in one request; each 8-byte half arrives whole
+__device__ __forceinline__ ulonglong2 ld_pair_sys(const ulonglong2* p) {
+  ulonglong2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u64 {%0, %1}, [%2];" : "=l"(v.x), "=l"(v.y) : "l"(p) : "memory");
   return v;
 }
 
@@ -319,6 +331,8 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
     ptx::fence_barrier_init();
     ctl->fail = 0;
     ctl->flag = 0;
+    ctl->next_stage = 0;
+    for (int s = 0; s < kSt; ++s) ctl->done[s] = 0;
     ctl->epoch = p.xstate != nullptr ? p.xstate[0] + 1u : 0u;
     ptx::prefetch_tensormap(&k_map);
     ptx::prefetch_tensormap(&v_map);
@@ -464,11 +478,30 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
     acc.m_run = -INFINITY;
     acc.l_run = 0.f;
 
-    for (int n = warp; n < n_stages; n += kConsumers) {
-      const int stg = n % kSt;
+    for (;;) {
+      int n = 0;
+      if (lane == 0) n = atomicAdd(&ctl->next_stage, 1);
+      n = __shfl_sync(0xffffffffu, n, 0);
+      if (n >= n_stages) break;
+      const int stg = n % kSt, use = n / kSt;
       if (__any_sync(0xffffffffu, ctl->fail != 0)) break;
       {
-        const bool ok = ptx::mbar_wait(ptx::smem_u32(&ctl->full[stg]), (uint32_t)(n / kSt) & 1u);
+        // A parity wait can only tell the current phase from the one before.  Warps claim
+        // stages out of step with each other, so first make sure that the slot's previous use
+        // has been consumed (by whichever warp had it): then the barrier is in this use's phase
+        // or just past it, never one behind.
+        bool ok = true;
+        if (ctl->done[stg] < use) {
+          const long long t0 = clock64();
+          while (ctl->done[stg] < use) {
+            if (clock64() - t0 > ptx::kWaitLimitCycles) { ok = false; break; }
+          }
+        }
+        if (!__all_sync(0xffffffffu, ok)) {
+          if (lane == 0) { atomicCAS(p.status, 0, kErrStageOrder); ctl->fail = 1; }
+          break;
+        }
+        ok = ptx::mbar_wait(ptx::smem_u32(&ctl->full[stg]), (uint32_t)use & 1u);
         if (!__all_sync(0xffffffffu, ok)) {
           if (lane == 0) { atomicCAS(p.status, 0, kErrStageFull); ctl->fail = 1; }
           break;
@@ -485,7 +518,11 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
         const T* vn = (const T*)p.v_new + b * p.vn_s0 + g * p.vn_s1;
         int64_t crow = (int64_t)meta.w + rr;
         if constexpr (!kPaged) crow += ((int64_t)b * p.G + g) * p.T;
-        for (int ch = lane; ch < D / 8; ch += 32) {
+        // the row must lie inside the cache: a row outside it is reported and not written
+        const int64_t cache_rows = kPaged ? ((int64_t)p.num_pages * p.G) << p.page_shift : (int64_t)p.B * p.G * p.T;
+        const bool row_ok = rr >= 0 && rr < 16 && crow >= 0 && crow < cache_rows;
+        if (!row_ok && lane == 0) atomicCAS(p.status, 0, kErrAppendRow);
+        for (int ch = lane; row_ok && ch < D / 8; ch += 32) {
           const uint4 kv = *reinterpret_cast<const uint4*>(kn + 8 * ch);
           const uint4 vv = *reinterpret_cast<const uint4*>(vn + 8 * ch);
           *reinterpret_cast<uint4*>(kt + tile_off(rr, ch)) = kv;
@@ -498,7 +535,10 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
       if (meta.z > meta.y)
         stage_step<T, D>(acc, qa, ptx::smem_u32(kt), ptx::smem_u32(vt), meta.y, meta.z, p.scale_log2, lane);
       __syncwarp();
-      if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&ctl->empty[stg]));
+      if (lane == 0) {
+        ctl->done[stg] = use + 1;
+        ptx::mbar_arrive(ptx::smem_u32(&ctl->empty[stg]));   // (a release: the count above is visible with it)
+      }
     }
   }
   __syncthreads();   // every stage has been consumed: the ring is scratch from here on
@@ -609,17 +649,44 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
     for (int r = 0; r < p.world; ++r) st_word_sys(p.xbuf[r] + off, word);
   }
   float* x_all = x_acc + R * (D + 2);   // [world][R][D + 2]
+  // Every word announces itself, so any number of them can be asked for at once: a thread
+  // requests its next eight pairs of words together and asks again only for those that have
+  // not arrived (rows are D + 2 words: an even count, so pairs never straddle rows).
   const long long t0 = clock64();
-  for (int idx = tid; idx < p.world * n_words; idx += kStreamThreads) {
-    const int r = idx / n_words, rem = idx - r * n_words;
-    const int hh = rem / (D + 2), e = rem - hh * (D + 2);
-    const unsigned long long* src = p.xbuf[p.rank] + xword(p, D, par, r, g * R + hh + b * p.H) + e;
-    unsigned long long w = ld_word_sys(src);
-    while ((uint32_t)(w >> 32) != epoch) {
-      if (ctl->fail || clock64() - t0 > kPeerWaitLimit) { atomicCAS(p.status, 0, kErrPeerWait); ctl->fail = 1; break; }
-      w = ld_word_sys(src);
+  const int n_pairs = p.world * n_words / 2;
+  for (int base = tid; base < n_pairs; base += 8 * kStreamThreads) {
+    const ulonglong2* src[8];
+    bool have[8];
+#pragma unroll
+    for (int j = 0; j < 8; ++j) {
+      const int idx = 2 * (base + j * kStreamThreads);
+      have[j] = idx >= 2 * n_pairs;        // nothing to fetch
+      const int ic = min(idx, 2 * n_pairs - 2);
+      const int r = ic / n_words, rem = ic - r * n_words;
+      const int hh = rem / (D + 2), e = rem - hh * (D + 2);
+      src[j] = reinterpret_cast<const ulonglong2*>(p.xbuf[p.rank] + xword(p, D, par, r, g * R + hh + b * p.H) + e);
     }
-    x_all[idx] = __uint_as_float((uint32_t)w);
+    for (;;) {
+      ulonglong2 w[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j)
+        if (!have[j]) w[j] = ld_pair_sys(src[j]);
+      bool all = true;
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        if (have[j]) continue;
+        if ((uint32_t)(w[j].x >> 32) == epoch && (uint32_t)(w[j].y >> 32) == epoch) {
+          const int idx = 2 * (base + j * kStreamThreads);
+          x_all[idx] = __uint_as_float((uint32_t)w[j].x);
+          x_all[idx + 1] = __uint_as_float((uint32_t)w[j].y);
+          have[j] = true;
+        } else {
+          all = false;
+        }
+      }
+      if (all) break;
+      if (ctl->fail || clock64() - t0 > kPeerWaitLimit) { atomicCAS(p.status, 0, kErrPeerWait); ctl->fail = 1; break; }
+    }
   }
   __syncthreads();
   if (!ctl->fail) {
@@ -766,7 +833,8 @@ int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeSt
       const int64_t need = 2ll * step->world * B * H * (D + 2) * 8;
       if (step->xbuf_bytes < need) return fail(G4B_ERR_BAD_ARG, "decode step: exchange buffers too small (need %lld bytes per rank)", (long long)need);
       for (int r = 0; r < step->world; ++r) {
-        if (step->xbuf[r] == nullptr || (((uintptr_t)step->xbuf[r]) & 7)) return fail(G4B_ERR_BAD_ARG, "decode step: exchange buffer of rank %d missing or misaligned", r);
+        if (step->xbuf[r] == nullptr || (((uintptr_t)step->xbuf[r]) & 15))
+          return fail(G4B_ERR_BAD_ARG, "decode step: exchange buffer of rank %d missing or not 16-byte aligned", r);
         p.xbuf[r] = (unsigned long long*)step->xbuf[r];
       }
       // a CTA that waits for a peer holds its SM slot: every CTA of the launch must be resident
