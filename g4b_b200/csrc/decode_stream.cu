@@ -432,22 +432,20 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
         if (part == 1) vhi = min(vhi, jw - j0);                      // rows up to the end of the ring
         if (part == 2) { vlo = max(vlo, jw - j0); row0 -= p.T; }     // the rest, from row 0 on (box starts before it)
       }
+      // One box per tile: the descriptor's third dimension walks the D / 64 column slabs of a
+      // row (stride 128 bytes), so a box [64 elements x 16 rows x D / 64 slabs] lands as the
+      // slab-major swizzled tile the consumers read.  Lane 0 fetches K, lane 1 fetches V.
+      const uint32_t bar = ptx::smem_u32(&ctl->full[stg]);
       if (lane == 0) {
         ctl->meta[stg] = make_int4(j0, vlo, vhi, row0);
-        const uint32_t bar = ptx::smem_u32(&ctl->full[stg]);
         ptx::mbar_arrive_expect_tx(bar, (uint32_t)Cfg::kStageBytes);
-        const uint32_t kdst = ptx::smem_u32(ring + stg * Cfg::kStageBytes);
-        const uint32_t vdst = kdst + Cfg::kTileBytes;
-#pragma unroll
-        for (int s = 0; s < Cfg::kSlabs; ++s) {
-          if constexpr (kPaged) {
-            ptx::tma_load_4d(kdst + s * 2048, &k_map, bar, 64 * s, j0 & page_mask, g, page);
-            ptx::tma_load_4d(vdst + s * 2048, &v_map, bar, 64 * s, j0 & page_mask, g, page);
-          } else {
-            ptx::tma_load_3d(kdst + s * 2048, &k_map, bar, 64 * s, row0, b * p.G + g);
-            ptx::tma_load_3d(vdst + s * 2048, &v_map, bar, 64 * s, row0, b * p.G + g);
-          }
-        }
+      }
+      __syncwarp();
+      if (lane < 2) {
+        const uint32_t dst = ptx::smem_u32(ring + stg * Cfg::kStageBytes) + (lane ? Cfg::kTileBytes : 0);
+        const CUtensorMap* map = lane ? &v_map : &k_map;
+        if constexpr (kPaged) ptx::tma_load_5d(dst, map, bar, 0, j0 & page_mask, 0, g, page);
+        else ptx::tma_load_4d(dst, map, bar, 0, row0, 0, b * p.G + g);
       }
       __syncwarp();
     }
@@ -861,19 +859,22 @@ int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeSt
   CUtensorMap km, vm;
   int rc;
   const int esz = 2;
+  // A row of D elements is described as D / 64 slabs of 64: dims (element in slab, row, slab,
+  // ...), the slab stride (128 bytes) below the row stride, so that one box holds a whole tile.
+  const uint64_t slabs = (uint64_t)D / 64;
   if (paged) {
     const uint64_t P = (uint64_t)a.k_cache.shape[2], NP = (uint64_t)a.k_cache.shape[0];
-    const uint64_t dims[4] = {(uint64_t)D, P, (uint64_t)G, NP};
-    const uint64_t strides[3] = {(uint64_t)D * esz, P * D * esz, (uint64_t)G * P * D * esz};
-    const uint32_t box[4] = {64, 16, 1, 1};
-    if ((rc = encode_map(&km, a.k_cache.dtype, 4, a.k_cache.ptr, dims, strides, box, "k pool"))) return rc;
-    if ((rc = encode_map(&vm, a.v_cache.dtype, 4, a.v_cache.ptr, dims, strides, box, "v pool"))) return rc;
+    const uint64_t dims[5] = {64, P, slabs, (uint64_t)G, NP};
+    const uint64_t strides[4] = {(uint64_t)D * esz, 64 * esz, P * D * esz, (uint64_t)G * P * D * esz};
+    const uint32_t box[5] = {64, 16, (uint32_t)slabs, 1, 1};
+    if ((rc = encode_map(&km, a.k_cache.dtype, 5, a.k_cache.ptr, dims, strides, box, "k pool"))) return rc;
+    if ((rc = encode_map(&vm, a.v_cache.dtype, 5, a.v_cache.ptr, dims, strides, box, "v pool"))) return rc;
   } else {
-    const uint64_t dims[3] = {(uint64_t)D, (uint64_t)p.T, (uint64_t)(B * G)};
-    const uint64_t strides[2] = {(uint64_t)D * esz, (uint64_t)p.T * D * esz};
-    const uint32_t box[3] = {64, 16, 1};
-    if ((rc = encode_map(&km, a.k_cache.dtype, 3, a.k_cache.ptr, dims, strides, box, "k_cache"))) return rc;
-    if ((rc = encode_map(&vm, a.v_cache.dtype, 3, a.v_cache.ptr, dims, strides, box, "v_cache"))) return rc;
+    const uint64_t dims[4] = {64, (uint64_t)p.T, slabs, (uint64_t)(B * G)};
+    const uint64_t strides[3] = {(uint64_t)D * esz, 64 * esz, (uint64_t)p.T * D * esz};
+    const uint32_t box[4] = {64, 16, (uint32_t)slabs, 1};
+    if ((rc = encode_map(&km, a.k_cache.dtype, 4, a.k_cache.ptr, dims, strides, box, "k_cache"))) return rc;
+    if ((rc = encode_map(&vm, a.v_cache.dtype, 4, a.v_cache.ptr, dims, strides, box, "v_cache"))) return rc;
   }
   dim3 grid((unsigned)num_splits, (unsigned)G, (unsigned)B);
   if (a.k_cache.dtype == G4B_BF16) return launch_dim<__nv_bfloat16>((int)D, paged, km, vm, p, grid, st);
