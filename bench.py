@@ -591,7 +591,7 @@ class DecodeWorkload:
     to the same sequence and the merged output can be checked against the oracle."""
 
     def __init__(self, name, dev, seed, rank=0, world=1, sequences=256, nccl_gather=False, kv_splits=0, shard=False,
-                 fused=True, merge_in_launch=None):
+                 fused=True):
         from g4b_b200 import dist as gdist
         from g4b_b200.kernels import fa2
         from g4b_b200.kernels.rope import rope_norm_append
@@ -599,11 +599,7 @@ class DecodeWorkload:
         self.fa2, self.append = fa2, rope_norm_append
         self.name, self.dev, self.rank, self.world = name, dev, rank, world
         self.fused = fused      # the whole step as one launch (decode_step) or as append + decode + merge
-        # on one GPU the merge as a second launch is the faster form (every CTA's ticket costs a
-        # fence and an atomic; the merge launch is scheduled while the attention drains); with the
-        # KV range split over GPUs the merge has to be in the launch that exchanges
-        self.merge_in_launch = (name == "decode_long" and world > 1) if merge_in_launch is None else \
-            (merge_in_launch or (name == "decode_long" and world > 1))
+        self.merge_in_launch = name == "decode_long" and world > 1     # with peers: one launch
         gen = torch.Generator(device="cpu").manual_seed(seed)
         self.scaling = "weak"
         if name == "decode_paged":
@@ -700,7 +696,7 @@ class DecodeWorkload:
                        "l2": "K/V (%d MB per GPU) larger than L2" % (int(kv_bytes) >> 20)}
         if self.scaling == "strong":
             self.config.update({"sequences_this_rank": B, "ctx_sum_this_rank": int(self.local_lens.sum())})
-        self.config["step"] = ("one launch (append + attention + merge)" if self.merge_in_launch else
+        self.config["step"] = ("one launch (append + attention + merge + exchange)" if self.merge_in_launch else
                                "two launches (append + attention, merge)") if fused else "three launches (append, attention, merge)"
         if self.long_split:
             self.config["merge"] = "all-gather + second merge launch (NCCL)" if nccl_gather else \
@@ -735,7 +731,7 @@ class DecodeWorkload:
                                  self.fa2.PHASE_DECODE, self.po, self.pl, self.pm,
                                  k_new=self.kn if last else None, v_new=self.vn if last else None,
                                  exchange=self.exchange if self.long_split else None, num_kv_splits=self.splits,
-                                 scale=SCALE, block_tables=self.bt, page_size=PAGE, merge_in_launch=self.merge_in_launch)
+                                 scale=SCALE, block_tables=self.bt, page_size=PAGE)
             return
         if last:
             # K and V rows in one launch (no rotation, no norm: a plain append of both)
@@ -827,8 +823,7 @@ class DecodeWorkload:
         return touched / dt / 1e9, f"{n} of {self.B} sequences ({touched >> 20} MB of K/V), page gather + fp32 attention"
 
 
-def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_splits=0, strong=False, fused=True,
-                  merge_in_launch=None):
+def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_splits=0, strong=False, fused=True):
     """``strong``: the workload is ONE job dealt over the ranks (strong scaling) instead of the
     same per-GPU batch on every rank."""
     from g4b_b200 import dist as gdist
@@ -848,7 +843,7 @@ def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_s
             units = gdist.shard_prefill_units(nreq, G, S, world, rank, W)
         return PrefillWorkload(name, dev, seeds[name] + 100 * rank, units=units)
     return DecodeWorkload(name, dev, seeds[name] + (0 if name == "decode_long" else 100 * rank), rank, world,
-                          sequences, nccl_gather, kv_splits, shard=strong, fused=fused, merge_in_launch=merge_in_launch)
+                          sequences, nccl_gather, kv_splits, shard=strong, fused=fused)
 
 
 # ------------------------------------------------------------------------------------------
@@ -975,8 +970,7 @@ def run_ours(args):
     peaks = measured_peaks()
     headline = args.workload == "prefill_causal" and not args.no_extras
     wl = make_workload(args.workload, dev, rank, world, args.sequences, args.nccl_gather, args.kv_splits,
-                       strong=args.strong, fused=not args.unfused,
-                       merge_in_launch={"auto": None, "kernel": True, "launch": False}[args.step_merge])
+                       strong=args.strong, fused=not args.unfused)
     parity = None
     if hasattr(wl, "parity"):
         good, excess = wl.parity()
@@ -1237,10 +1231,7 @@ def main():
     ap.add_argument("--strong", action="store_true",
                     help="N > 1: deal ONE job over the ranks (prefill units, decode sequences) instead of the same batch on every rank")
     ap.add_argument("--unfused", action="store_true",
-                    help="decode workloads: append, attention and merge as three launches instead of one decode_step launch")
-    ap.add_argument("--step-merge", default="auto", choices=["auto", "kernel", "launch"],
-                    help="decode workloads: merge the splits inside the decode_step launch (kernel) or in a second "
-                         "launch (launch); auto = second launch on one GPU, inside the launch when GPUs exchange")
+                    help="decode workloads: append, attention and merge as three launches instead of decode_step")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of replaying CUDA graphs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
     ap.add_argument("--no-extras", action="store_true", help="default workload: only the headline, none of the other configurations' blocks")

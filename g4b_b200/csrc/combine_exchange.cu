@@ -72,7 +72,6 @@ __global__ void __launch_bounds__(kXThreads) combine_exchange_kernel(ExchangePar
   __shared__ uint32_t s_epoch;
   __shared__ int s_fail;
   const int row = blockIdx.x, slice = blockIdx.y;
-  const int blk = row * p.slices + slice;
   const int t = row % p.Tq, h = (row / p.Tq) % p.H, b = row / (p.Tq * p.H);
   const int tid = threadIdx.x, lane = tid & 31, warp = tid >> 5;
   if (tid == 0) { s_epoch = p.state[0] + 1; s_fail = 0; }
@@ -236,6 +235,10 @@ extern "C" int g4b_attn_combine_exchange(const G4bExchangeArgs* args, void* cuda
 }
 
 extern "C" int64_t g4b_exchange_buffer_bytes(int world, int64_t rows, int head_dim) {
+  // large enough for either entry point: g4b_attn_combine_exchange moves pieces of 32 columns
+  // (+ l, m), g4b_decode_step pieces of 8 columns (+ l, m)
   const int64_t slices = (head_dim + g4b::kXCols - 1) / g4b::kXCols;
-  return 2ll * world * rows * slices * (g4b::kXCols + 2) * 8;
+  const int64_t a = 2ll * world * rows * slices * (g4b::kXCols + 2) * 8;
+  const int64_t b = 2ll * world * rows * ((head_dim + 7) / 8) * 10 * 8;
+  return a > b ? a : b;
 }

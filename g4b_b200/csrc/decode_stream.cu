@@ -26,12 +26,13 @@
 // The 3 warps merge through shared memory; the CTA writes o (one split) or the (acc, l, m)
 // partial of fa2.py:438-472.
 //
-// Fused merge (tickets != null): after its partial is written a CTA takes a ticket of its
-// group of 8 splits; the last one merges the group, takes a ticket of the (slot, kv head), and
-// the last of those merges the groups and writes o.  No CTA waits for another.  With peers
-// (world > 1) that last CTA instead pushes the merged partial to every GPU as self-announcing
-// 8-byte words {value, launch count}, polls (bounded) its own buffer for the peers' words and
-// finishes the merge (the word format of combine_exchange.cu).
+// Exchange form (world > 1: one sequence's KV range split over GPUs; every CTA of the launch is
+// resident at once, which the launcher checks).  After its partial is written a CTA arrives at a
+// grid-wide count.  The first D / 8 CTAs of every (slot, kv head) then each own 8 columns of the
+// head dim: they wait (bounded) for the count, merge all local partials for their columns,
+// push the merged piece to every GPU as self-announcing 8-byte words {value, launch count}, poll
+// (bounded) their own buffer for the peers' pieces and finish the merge -- the word format of
+// combine_exchange.cu, in the same launch as the attention.
 #include "common.cuh"
 #include "mma16816.cuh"
 #include "sm100_ptx.cuh"
@@ -41,22 +42,19 @@ namespace {
 
 constexpr int kConsumers = 3;   // + 1 producer = 4 warps: two CTAs are 8 warps, 2 per SM sub-partition, so 255 registers each
 constexpr int kStreamThreads = (kConsumers + 1) * 32;
-constexpr int kGroup = 8;                     // splits per first-level ticket
-constexpr int kMaxLevel2 = 128;               // groups per (slot, kv head): 1024 splits
-constexpr int kMaxTickets1 = 1 << 16;
-constexpr int kMaxTickets2 = 1 << 14;
+constexpr int kXCols = 8;                     // head-dim columns a merging CTA owns
+constexpr int kXWords = kXCols + 2;           // its piece per query head: the columns, the row sum, the row maximum
+constexpr int kMaxResidentSplits = 320;       // splits of one (slot, kv head) when every CTA is resident
 constexpr long long kPeerWaitLimit = 1ll << 31;   // SM cycles (about a second)
 
 enum : int32_t { kErrBadEntry = 0x201, kErrStageFull = 0x211, kErrStageEmpty = 0x212, kErrStageOrder = 0x213,
-                 kErrAppendRow = 0x214, kErrPeerWait = 0x401 };
+                 kErrAppendRow = 0x214, kErrGridWait = 0x215, kErrPeerWait = 0x401 };
 
-// Tickets of the fused merge: zero between launches (the CTA that takes the last ticket of a
-// counter puts it back to zero).  One set per GPU, shared by every launch on it.
-__device__ uint32_t g_tickets1[kMaxTickets1];
-__device__ uint32_t g_tickets2[kMaxTickets2];
+// Grid-wide counts of the exchange form, {arrived, finished}: zero between launches (the CTA
+// that finishes last puts both back).  One pair per GPU, shared by every launch on it.
+__device__ uint32_t g_step_sync[2];
 
 template <int D> struct StreamCfg {
-  static constexpr int kSlabs = D / 64;                  // 64-element (128-byte) column slabs of a row
   static constexpr int kTileBytes = 16 * D * 2;          // 16 keys of K, or of V
   static constexpr int kStageBytes = 2 * kTileBytes;
   static constexpr int kStages = D == 128 ? 8 : 6;       // 64 / 96 / 192 KB in flight per CTA
@@ -77,8 +75,8 @@ struct StreamParams {
   int q_dtype, o_dtype, po_dtype;
   float scale_log2;
   int32_t* status;
-  // fused step
-  uint32_t* tickets1; uint32_t* tickets2;
+  // decode step
+  uint32_t* sync;              // {arrived, finished} (exchange form), else null
   void* k_cache; void* v_cache;
   const void* k_new; const void* v_new;
   int64_t kn_s0, kn_s1, vn_s0, vn_s1;
@@ -112,12 +110,6 @@ __device__ __forceinline__ void ldsm_x4_t(uint32_t addr, uint32_t& r0, uint32_t&
 __device__ __forceinline__ void st_word_sys(unsigned long long* p, unsigned long long v) {
   asm volatile("st.relaxed.sys.global.u64 [%0], %1;" ::"l"(p), "l"(v) : "memory");
 }
-__device__ __forceinline__ unsigned long long ld_word_sys(const unsigned long long* p) {
-  unsigned long long v;
-  asm volatile("ld.relaxed.sys.global.u64 %0, [%1];" : "=l"(v) : "l"(p) : "memory");
-  return v;
-}
-
 // two neighbouring words in one request; each 8-byte half arrives whole
 __device__ __forceinline__ ulonglong2 ld_pair_sys(const ulonglong2* p) {
   ulonglong2 v;
@@ -141,7 +133,7 @@ template <int D> struct WarpAcc {
 template <typename T, int D>
 __device__ __forceinline__ void stage_step(WarpAcc<D>& st, const uint32_t (&qa)[D / 16][2], uint32_t k_tile,
                                            uint32_t v_tile, int vlo, int vhi, float scale_log2, int lane) {
-  const int gi = lane >> 2, c = lane & 3;
+  const int c = lane & 3;
   const bool full = vlo == 0 && vhi == 16;
   // ---------------- S = Q K^T: two groups of 8 keys, two accumulator chains each ----------------
   float s[2][4], s2[2][4];
@@ -223,84 +215,9 @@ __device__ __forceinline__ void stage_step(WarpAcc<D>& st, const uint32_t (&qa)[
   }
 }
 
-// Word offset inside one rank's exchange buffer: [parity][source rank][row][D + 2].
-__device__ __forceinline__ int64_t xword(const StreamParams& p, int D, int par, int src, int row) {
-  return (((int64_t)par * p.world + src) * ((int64_t)p.B * p.H) + row) * (D + 2);
-}
-
-// Merges `count` partials of heads [h0, h0 + R) of slot b, at split indices first + i * step.
-// kFinal = false: the merged (acc, l, m) replace the partial at split `first`.
-// kFinal = true : the merged row sums / maxima go to ctl.ml and the merged un-normalised
-//                 accumulator to acc_out[h][d] in shared memory (row pitch D + 2).
-template <int D, bool kFinal, int kSt>
-__device__ __forceinline__ void merge_partials(const StreamParams& p, Ctl<kSt>* ctl, float* s_w, float* acc_out, int b,
-                                               int h0, int R, int first, int step, int count) {
-  const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-  const float* pof = (const float*)p.po;
-  // weights 2^(m_i - M) and the merged row sum, one warp per head; every (m, l) pair is
-  // requested before any is used, so the warp pays one trip to L2, not two per partial
-  for (int hh = warp; hh < R; hh += kStreamThreads / 32) {
-    const int h = h0 + hh;
-    float mi[kMaxLevel2 / 32], li[kMaxLevel2 / 32];
-#pragma unroll
-    for (int j = 0; j < kMaxLevel2 / 32; ++j) {
-      const int i = lane + 32 * j;
-      mi[j] = -INFINITY; li[j] = 0.f;
-      if (i < count) {
-        mi[j] = __ldcg(p.pm + (int64_t)(first + i * step) * p.pm_s0 + b * p.pm_s1 + h * p.pm_s2);
-        li[j] = __ldcg(p.pl + (int64_t)(first + i * step) * p.pl_s0 + b * p.pl_s1 + h * p.pl_s2);
-      }
-    }
-    float m = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < kMaxLevel2 / 32; ++j) m = fmaxf(m, mi[j]);
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    float l = 0.f;
-#pragma unroll
-    for (int j = 0; j < kMaxLevel2 / 32; ++j) {
-      const int i = lane + 32 * j;
-      const float w = (mi[j] == -INFINITY) ? 0.f : exp2f(mi[j] - m);
-      if (i < count) s_w[hh * kMaxLevel2 + i] = w;
-      l += li[j] * w;
-    }
-    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-    if (lane == 0) { ctl->ml[hh][0] = l; ctl->ml[hh][1] = m; }
-  }
-  __syncthreads();
-  // accumulators: 2 elements per thread and step (rows of a packed [.., D + 2] buffer start on
-  // 8-byte boundaries only)
-  for (int idx = tid; idx < R * (D / 2); idx += kStreamThreads) {
-    const int hh = idx / (D / 2), d = 2 * (idx - hh * (D / 2));
-    const float* src = pof + b * p.po_s1 + (h0 + hh) * p.po_s2 + d;
-    float2 acc = make_float2(0.f, 0.f);
-    // eight independent loads in flight per thread (a partial that saw no key holds zeros and
-    // has weight 0, so nothing needs to be skipped)
-    for (int i0 = 0; i0 < count; i0 += 8) {
-      float2 x[8];
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const int i = min(i0 + j, count - 1);
-        x[j] = __ldcg(reinterpret_cast<const float2*>(src + (int64_t)(first + i * step) * p.po_s0));
-      }
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        const float w = i0 + j < count ? s_w[hh * kMaxLevel2 + i0 + j] : 0.f;
-        acc.x += x[j].x * w; acc.y += x[j].y * w;
-      }
-    }
-    if constexpr (kFinal) {
-      acc_out[hh * (D + 2) + d] = acc.x; acc_out[hh * (D + 2) + d + 1] = acc.y;
-    } else {
-      *reinterpret_cast<float2*>(const_cast<float*>(src) + (int64_t)first * p.po_s0) = acc;
-    }
-  }
-  if constexpr (!kFinal) {
-    if (tid < R) {
-      p.pl[(int64_t)first * p.pl_s0 + b * p.pl_s1 + (h0 + tid) * p.pl_s2] = ctl->ml[tid][0];
-      p.pm[(int64_t)first * p.pm_s0 + b * p.pm_s1 + (h0 + tid) * p.pm_s2] = ctl->ml[tid][1];
-    }
-  }
-  __syncthreads();
+// Word offset inside one rank's exchange buffer: [parity][source rank][row][slice of 8 columns][8 + 2].
+__device__ __forceinline__ int64_t xword(const StreamParams& p, int D, int par, int src, int row, int slice) {
+  return ((((int64_t)par * p.world + src) * ((int64_t)p.B * p.H) + row) * (D / kXCols) + slice) * kXWords;
 }
 
 template <typename T, int D, bool kPaged>
@@ -318,7 +235,6 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   Ctl<kSt>* ctl = reinterpret_cast<Ctl<kSt>*>(smem_raw + Cfg::kRingBytes);
   // after the stream the ring is scratch: warp accumulators / peers' partials, then merge weights
   float* sm_o = reinterpret_cast<float*>(ring);                                   // [kConsumers][8][D + 4]
-  float* s_w = reinterpret_cast<float*>(ring + Cfg::kRingBytes - 8 * kMaxLevel2 * 4);   // [8][kMaxLevel2]
 
   // a merge launch that follows may be scheduled as soon as SM resources free up (it waits for
   // this grid to finish before it reads the partials)
@@ -339,22 +255,32 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   }
   __syncthreads();
 
-  // every CTA of the launch, whatever it did, counts towards the launch count of the exchange
+  // Exchange form: every CTA of the launch, whatever it did, arrives once (its partial, if it
+  // has one, is written) and finishes once; the last to finish puts the counts back to zero and
+  // advances the caller's launch count.
+  const uint32_t n_ctas = gridDim.x * gridDim.y * gridDim.z;
+  auto grid_arrive = [&]() {
+    __threadfence();
+    __syncthreads();
+    if (tid == 0) atomicAdd(&p.sync[0], 1u);
+  };
   auto finish = [&]() {
-    if (p.xstate == nullptr) return;
     __syncthreads();
     if (tid == 0) {
-      const uint32_t n_ctas = gridDim.x * gridDim.y * gridDim.z;
       __threadfence();
-      if (atomicAdd(&p.xstate[1], 1u) == n_ctas - 1) {
-        p.xstate[1] = 0;
+      if (atomicAdd(&p.sync[1], 1u) == n_ctas - 1) {
+        p.sync[0] = 0;
+        p.sync[1] = 0;
         __threadfence();
         p.xstate[0] = ctl->epoch;
       }
     }
   };
 
-  if (p.user_phase != nullptr && p.user_phase[b * p.phase_stride] != (uint8_t)p.phase) { finish(); return; }
+  if (p.user_phase != nullptr && p.user_phase[b * p.phase_stride] != (uint8_t)p.phase) {
+    if (p.sync != nullptr) { grid_arrive(); finish(); }
+    return;
+  }
 
   // ---- key range of this split (fa2.py:52-67, with block-aligned split boundaries) ----
   const int time = p.time_dim_sizes[b * p.time_stride];
@@ -560,7 +486,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   }
   __syncthreads();
 
-  const bool fused = p.tickets1 != nullptr;
+  const bool exchange = p.sync != nullptr;
   for (int idx = tid; idx < R * D; idx += kStreamThreads) {
     const int hh = idx / D, d = idx - hh * D;
     float m = -INFINITY;
@@ -576,7 +502,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
       l += ctl->sm_l[w][hh] * sc;
     }
     const int h = g * R + hh;
-    if (p.num_splits == 1 && !fused) {
+    if (p.num_splits == 1 && !exchange) {
       store_from_float(p.o, b * p.o_s0 + h * p.o_s1 + d, p.o_dtype, l > 0.f ? a / l : 0.f);
     } else {
       store_from_float(p.po, split * p.po_s0 + b * p.po_s1 + h * p.po_s2 + d, p.po_dtype, a);
@@ -586,121 +512,165 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
       }
     }
   }
-  if (!fused) return;   // the caller merges (never with an exchange: the launcher sees to that)
+  if (!exchange) return;   // the caller merges in a second launch
 
-  // =============================== fused merge ===============================
-  const int unit = b * p.G + g;
-  const int n_groups = (p.num_splits + kGroup - 1) / kGroup;
-  const int grp = split / kGroup;
-  const int in_group = min(kGroup, p.num_splits - grp * kGroup);
-  // level 1: the last CTA of a group of splits to get here merges the group
-  __threadfence();
-  __syncthreads();
+  // =============================== merge + exchange ===============================
+  grid_arrive();
+  constexpr int kSlices = D / kXCols;
+  if (split >= kSlices) { finish(); return; }
+  // a merging CTA: wait until every CTA of the launch has arrived (all are resident)
   if (tid == 0) {
-    uint32_t* t1 = p.tickets1 + (int64_t)unit * n_groups + grp;
-    const bool last = atomicAdd(t1, 1u) == (uint32_t)in_group - 1;
-    if (last) *t1 = 0;
-    ctl->flag = last ? 1 : 0;
+    const long long t0 = clock64();
+    int ok = 1;
+    while (*reinterpret_cast<volatile uint32_t*>(&p.sync[0]) < n_ctas) {
+      if (clock64() - t0 > ptx::kWaitLimitCycles) { atomicCAS(p.status, 0, kErrGridWait); ok = 0; break; }
+    }
+    ctl->flag = ok;
   }
   __syncthreads();
   if (!ctl->flag) { finish(); return; }
   __threadfence();
-  float* x_acc = sm_o;   // merged accumulator [R][D + 2], then the peers' pieces behind it
-  if (n_groups > 1) {
-    merge_partials<D, false, kSt>(p, ctl, s_w, nullptr, b, g * R, R, grp * kGroup, 1, in_group);
-    // level 2: the last group of the (slot, kv head) merges the groups
-    __threadfence();
-    __syncthreads();
-    if (tid == 0) {
-      uint32_t* t2 = p.tickets2 + unit;
-      const bool last = atomicAdd(t2, 1u) == (uint32_t)n_groups - 1;
-      if (last) *t2 = 0;
-      ctl->flag = last ? 1 : 0;
-    }
-    __syncthreads();
-    if (!ctl->flag) { finish(); return; }
-    __threadfence();
-    merge_partials<D, true, kSt>(p, ctl, s_w, x_acc, b, g * R, R, 0, kGroup, n_groups);
-  } else {
-    merge_partials<D, true, kSt>(p, ctl, s_w, x_acc, b, g * R, R, 0, 1, in_group);
-  }
 
-  if (p.world <= 1) {
-    for (int idx = tid; idx < R * D; idx += kStreamThreads) {
-      const int hh = idx / D, d = idx - hh * D;
-      const float l = ctl->ml[hh][0];
-      store_from_float(p.o, b * p.o_s0 + (g * R + hh) * p.o_s1 + d, p.o_dtype, l > 0.f ? x_acc[hh * (D + 2) + d] / l : 0.f);
+  const int S = p.num_splits;
+  float* s_wt = reinterpret_cast<float*>(ring);                 // [R][S] weights 2^(m_i - M)
+  float2* s_red = reinterpret_cast<float2*>(s_wt + 8 * kMaxResidentSplits);   // [groups][pairs]
+  float* x_own = reinterpret_cast<float*>(s_red + kStreamThreads);            // [R][kXWords]
+  float* x_all = x_own + 8 * kXWords;                                          // [world][R][kXWords]
+  const float* pof = (const float*)p.po;
+  // weights and merged row sums of the local splits, one warp per head; every (m, l) pair is
+  // requested before any is used
+  for (int hh = warp; hh < R; hh += kStreamThreads / 32) {
+    const int h = g * R + hh;
+    constexpr int kPer = kMaxResidentSplits / 32;
+    float mi[kPer], li[kPer];
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int i = lane + 32 * j;
+      mi[j] = -INFINITY; li[j] = 0.f;
+      if (i < S) {
+        mi[j] = __ldcg(p.pm + (int64_t)i * p.pm_s0 + b * p.pm_s1 + h * p.pm_s2);
+        li[j] = __ldcg(p.pl + (int64_t)i * p.pl_s0 + b * p.pl_s1 + h * p.pl_s2);
+      }
     }
-    return;
+    float m = -INFINITY;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) m = fmaxf(m, mi[j]);
+    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+    float l = 0.f;
+#pragma unroll
+    for (int j = 0; j < kPer; ++j) {
+      const int i = lane + 32 * j;
+      const float w = (mi[j] == -INFINITY) ? 0.f : exp2f(mi[j] - m);
+      if (i < S) s_wt[hh * kMaxResidentSplits + i] = w;
+      l += li[j] * w;
+    }
+    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+    if (lane == 0) { ctl->ml[hh][0] = l; ctl->ml[hh][1] = m; }
   }
+  __syncthreads();
 
-  // ---- exchange: push this GPU's merged piece to every GPU, wait for theirs, merge ----
   const uint32_t epoch = ctl->epoch;
   const int par = (int)(epoch & 1u);
-  if (tid < R) { x_acc[tid * (D + 2) + D] = ctl->ml[tid][0]; x_acc[tid * (D + 2) + D + 1] = ctl->ml[tid][1]; }
-  __syncthreads();
-  const int n_words = R * (D + 2);
-  for (int idx = tid; idx < n_words; idx += kStreamThreads) {
-    const int hh = idx / (D + 2), e = idx - hh * (D + 2);
-    const int64_t off = xword(p, D, par, p.rank, g * R + hh + b * p.H) + e;
-    const unsigned long long word = ((unsigned long long)epoch << 32) | __float_as_uint(x_acc[idx]);
-    for (int r = 0; r < p.world; ++r) st_word_sys(p.xbuf[r] + off, word);
-  }
-  float* x_all = x_acc + R * (D + 2);   // [world][R][D + 2]
-  // Every word announces itself, so any number of them can be asked for at once: a thread
-  // requests its next eight pairs of words together and asks again only for those that have
-  // not arrived (rows are D + 2 words: an even count, so pairs never straddle rows).
-  const long long t0 = clock64();
-  const int n_pairs = p.world * n_words / 2;
-  for (int base = tid; base < n_pairs; base += 8 * kStreamThreads) {
-    const ulonglong2* src[8];
-    bool have[8];
+  // threads = (group of splits) x (pair of columns of one head); R * 4 pairs, padded to 16 or 32
+  const int pairs = R * (kXCols / 2);
+  const int pad = pairs > 16 ? 32 : 16;
+  const int n_grp = kStreamThreads / pad;
+  const int pi = tid % pad, sg = tid / pad;
+  for (int sl = split; sl < kSlices; sl += S) {
+    // ---- this GPU's merged accumulator for columns [8 sl, 8 sl + 8) of the R heads ----
+    float2 acc = make_float2(0.f, 0.f);
+    if (pi < pairs) {
+      const int hh = pi / (kXCols / 2), d = sl * kXCols + 2 * (pi % (kXCols / 2));
+      const float* src = pof + b * p.po_s1 + (g * R + hh) * p.po_s2 + d;
+      const float* wt = s_wt + hh * kMaxResidentSplits;
+      for (int i0 = sg; i0 < S; i0 += 10 * n_grp) {
+        float2 x[10];
 #pragma unroll
-    for (int j = 0; j < 8; ++j) {
-      const int idx = 2 * (base + j * kStreamThreads);
-      have[j] = idx >= 2 * n_pairs;        // nothing to fetch
-      const int ic = min(idx, 2 * n_pairs - 2);
-      const int r = ic / n_words, rem = ic - r * n_words;
-      const int hh = rem / (D + 2), e = rem - hh * (D + 2);
-      src[j] = reinterpret_cast<const ulonglong2*>(p.xbuf[p.rank] + xword(p, D, par, r, g * R + hh + b * p.H) + e);
-    }
-    for (;;) {
-      ulonglong2 w[8];
+        for (int j = 0; j < 10; ++j) {
+          const int i = min(i0 + j * n_grp, S - 1);
+          x[j] = __ldcg(reinterpret_cast<const float2*>(src + (int64_t)i * p.po_s0));
+        }
 #pragma unroll
-      for (int j = 0; j < 8; ++j)
-        if (!have[j]) w[j] = ld_pair_sys(src[j]);
-      bool all = true;
-#pragma unroll
-      for (int j = 0; j < 8; ++j) {
-        if (have[j]) continue;
-        if ((uint32_t)(w[j].x >> 32) == epoch && (uint32_t)(w[j].y >> 32) == epoch) {
-          const int idx = 2 * (base + j * kStreamThreads);
-          x_all[idx] = __uint_as_float((uint32_t)w[j].x);
-          x_all[idx + 1] = __uint_as_float((uint32_t)w[j].y);
-          have[j] = true;
-        } else {
-          all = false;
+        for (int j = 0; j < 10; ++j) {
+          const int i = i0 + j * n_grp;
+          const float w = i < S ? wt[i] : 0.f;
+          acc.x += x[j].x * w; acc.y += x[j].y * w;
         }
       }
-      if (all) break;
-      if (ctl->fail || clock64() - t0 > kPeerWaitLimit) { atomicCAS(p.status, 0, kErrPeerWait); ctl->fail = 1; break; }
     }
-  }
-  __syncthreads();
-  if (!ctl->fail) {
-    for (int idx = tid; idx < R * D; idx += kStreamThreads) {
-      const int hh = idx / D, d = idx - hh * D;
+    s_red[sg * pad + pi] = acc;
+    __syncthreads();
+    if (tid < pairs) {
+      float2 sum = make_float2(0.f, 0.f);
+      for (int q = 0; q < n_grp; ++q) { const float2 v = s_red[q * pad + tid]; sum.x += v.x; sum.y += v.y; }
+      const int hh = tid / (kXCols / 2), cp = tid % (kXCols / 2);
+      x_own[hh * kXWords + 2 * cp] = sum.x;
+      x_own[hh * kXWords + 2 * cp + 1] = sum.y;
+      if (cp == 0) { x_own[hh * kXWords + kXCols] = ctl->ml[hh][0]; x_own[hh * kXWords + kXCols + 1] = ctl->ml[hh][1]; }
+    }
+    __syncthreads();
+    // ---- push the piece to every GPU (own copy included) ----
+    for (int idx = tid; idx < R * kXWords; idx += kStreamThreads) {
+      const int hh = idx / kXWords, e = idx - hh * kXWords;
+      const int64_t off = xword(p, D, par, p.rank, b * p.H + g * R + hh, sl) + e;
+      const unsigned long long word = ((unsigned long long)epoch << 32) | __float_as_uint(x_own[idx]);
+      for (int r = 0; r < p.world; ++r) st_word_sys(p.xbuf[r] + off, word);
+    }
+    // ---- wait for every GPU's piece: a word has arrived once it carries this launch's count ----
+    const long long t0 = clock64();
+    const int n_pairs = p.world * R * (kXWords / 2);
+    for (int base = tid; base < n_pairs; base += 4 * kStreamThreads) {
+      const ulonglong2* src[4];
+      bool have[4];
+      int where[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int pr = base + j * kStreamThreads;
+        have[j] = pr >= n_pairs;
+        const int pc = min(pr, n_pairs - 1);
+        const int r = pc / (R * (kXWords / 2)), rem = pc - r * (R * (kXWords / 2));
+        const int hh = rem / (kXWords / 2), e = 2 * (rem - hh * (kXWords / 2));
+        where[j] = (r * R + hh) * kXWords + e;
+        src[j] = reinterpret_cast<const ulonglong2*>(p.xbuf[p.rank] + xword(p, D, par, r, b * p.H + g * R + hh, sl) + e);
+      }
+      for (;;) {
+        ulonglong2 w[4];
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          if (!have[j]) w[j] = ld_pair_sys(src[j]);
+        bool all = true;
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+          if (have[j]) continue;
+          if ((uint32_t)(w[j].x >> 32) == epoch && (uint32_t)(w[j].y >> 32) == epoch) {
+            x_all[where[j]] = __uint_as_float((uint32_t)w[j].x);
+            x_all[where[j] + 1] = __uint_as_float((uint32_t)w[j].y);
+            have[j] = true;
+          } else {
+            all = false;
+          }
+        }
+        if (all) break;
+        if (ctl->fail || clock64() - t0 > kPeerWaitLimit) { atomicCAS(p.status, 0, kErrPeerWait); ctl->fail = 1; break; }
+      }
+    }
+    __syncthreads();
+    if (ctl->fail) break;
+    // ---- final merge of the GPUs' pieces ----
+    if (tid < R * kXCols) {
+      const int hh = tid / kXCols, col = tid - hh * kXCols;
       float mm = -INFINITY;
-      for (int r = 0; r < p.world; ++r) mm = fmaxf(mm, x_all[(r * R + hh) * (D + 2) + D + 1]);
+      for (int r = 0; r < p.world; ++r) mm = fmaxf(mm, x_all[(r * R + hh) * kXWords + kXCols + 1]);
       float num = 0.f, den = 0.f;
       for (int r = 0; r < p.world; ++r) {
-        const float* row = x_all + (r * R + hh) * (D + 2);
-        const float w = (row[D + 1] == -INFINITY) ? 0.f : exp2f(row[D + 1] - mm);
-        num += row[d] * w;
-        den += row[D] * w;
+        const float* row = x_all + (r * R + hh) * kXWords;
+        const float w = (row[kXCols + 1] == -INFINITY) ? 0.f : exp2f(row[kXCols + 1] - mm);
+        num += row[col] * w;
+        den += row[kXCols] * w;
       }
-      store_from_float(p.o, b * p.o_s0 + (g * R + hh) * p.o_s1 + d, p.o_dtype, den > 0.f ? num / den : 0.f);
+      store_from_float(p.o, b * p.o_s0 + (g * R + hh) * p.o_s1 + sl * kXCols + col, p.o_dtype, den > 0.f ? num / den : 0.f);
     }
+    __syncthreads();
   }
   finish();
 }
@@ -736,23 +706,20 @@ int launch_dim(int D, bool paged, const CUtensorMap& km, const CUtensorMap& vm, 
   return fail(G4B_ERR_UNSUPPORTED, "decode: head dim %d not supported (128, 256 or 512)", D);
 }
 
-// Device addresses of the ticket arrays on the current device (looked up once per device).
-int ticket_arrays(uint32_t** t1, uint32_t** t2) {
+// Device address of the grid counters on the current device (looked up once per device).
+int step_sync_ptr(uint32_t** out) {
   constexpr int kMaxDev = 64;
-  // Filled without a lock: threads that race on an entry all store the same addresses.
-  static uint32_t* c1[kMaxDev] = {nullptr};
-  static uint32_t* c2[kMaxDev] = {nullptr};
+  // Filled without a lock: threads that race on an entry all store the same address.
+  static uint32_t* cache[kMaxDev] = {nullptr};
   int dev = 0;
   G4B_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev < 0 || dev >= kMaxDev) return fail(G4B_ERR_CUDA, "device index %d outside 0..%d", dev, kMaxDev - 1);
-  if (c1[dev] == nullptr || c2[dev] == nullptr) {
-    void *a = nullptr, *b = nullptr;
-    G4B_CUDA_CHECK(cudaGetSymbolAddress(&a, g_tickets1));
-    G4B_CUDA_CHECK(cudaGetSymbolAddress(&b, g_tickets2));
-    c2[dev] = (uint32_t*)b;
-    c1[dev] = (uint32_t*)a;
+  if (cache[dev] == nullptr) {
+    void* a = nullptr;
+    G4B_CUDA_CHECK(cudaGetSymbolAddress(&a, g_step_sync));
+    cache[dev] = (uint32_t*)a;
   }
-  *t1 = c1[dev]; *t2 = c2[dev];
+  *out = cache[dev];
   return G4B_OK;
 }
 
@@ -766,7 +733,7 @@ bool decode_stream_supports(const G4bAttnArgs& a) {
   return a.k_cache.shape[2] >= 16;
 }
 
-// `step` == nullptr: plain decode (o for one split, partials otherwise).  Otherwise the fused
+// `step` == nullptr: plain decode (o for one split, partials otherwise).  Otherwise the decode
 // step: merge in the launch, optional append and exchange.
 int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeStepArgs* step, cudaStream_t st) {
   const bool paged = a.block_tables.ptr != nullptr;
@@ -798,15 +765,8 @@ int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeSt
   } else {
     p.T = (int)a.k_cache.shape[2];
   }
-  // step->attn.reserved bit 0: leave the merge to a second launch (the append stays in this one)
   const bool fused = step != nullptr;
-  const bool tickets = fused && (step->world > 1 || (step->attn.reserved & 1) == 0);
   if (fused) {
-    if (num_splits > kGroup * kMaxLevel2) return fail(G4B_ERR_TOO_LARGE, "decode step: at most %d splits", kGroup * kMaxLevel2);
-    const int64_t n_groups = (num_splits + kGroup - 1) / kGroup;
-    if (tickets && (B * G * n_groups > kMaxTickets1 || B * G > kMaxTickets2))
-      return fail(G4B_ERR_TOO_LARGE, "decode step: %lld (slot, kv head) units x %lld split groups exceed the ticket arrays "
-                  "(%d / %d); use g4b_flash_attention", (long long)(B * G), (long long)n_groups, kMaxTickets2, kMaxTickets1);
     if (a.partial_o.dtype != G4B_F32) return fail(G4B_ERR_BAD_DTYPE, "decode step: partial_o must be f32");
     if ((((uintptr_t)a.partial_o.ptr) & 7) || (a.partial_o.stride[0] | a.partial_o.stride[1] | a.partial_o.stride[2]) % 2 != 0)
       return fail(G4B_ERR_BAD_STRIDE, "decode step: partial_o rows must start on 8-byte boundaries");
@@ -828,7 +788,8 @@ int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeSt
     if (step->world > 1) {
       if (step->world > 8 || step->rank < 0 || step->rank >= step->world) return fail(G4B_ERR_BAD_ARG, "decode step: bad world / rank");
       if (step->state == nullptr) return fail(G4B_ERR_BAD_ARG, "decode step: state is null");
-      const int64_t need = 2ll * step->world * B * H * (D + 2) * 8;
+      if (num_splits > kMaxResidentSplits) return fail(G4B_ERR_TOO_LARGE, "decode step with peers: at most %d splits", kMaxResidentSplits);
+      const int64_t need = 2ll * step->world * B * H * (D / kXCols) * kXWords * 8;
       if (step->xbuf_bytes < need) return fail(G4B_ERR_BAD_ARG, "decode step: exchange buffers too small (need %lld bytes per rank)", (long long)need);
       for (int r = 0; r < step->world; ++r) {
         if (step->xbuf[r] == nullptr || (((uintptr_t)step->xbuf[r]) & 15))
@@ -849,8 +810,8 @@ int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeSt
     }
   }
   G4B_STOP_IF_VALIDATE_ONLY();
-  if (tickets) {
-    int rc = ticket_arrays(&p.tickets1, &p.tickets2);
+  if (p.world > 1) {
+    int rc = step_sync_ptr(&p.sync);
     if (rc) return rc;
   }
   p.status = device_status_ptr();

@@ -116,29 +116,26 @@ def attention_decode_partials(q, k_cache, v_cache, o, time_dim_sizes, user_phase
 
 def decode_step(q, k_cache, v_cache, o, time_dim_sizes, user_phase, ctx_window_size, phase, partial_o, partial_l,
                 partial_m, *, k_new=None, v_new=None, exchange=None, num_kv_splits=None, scale=1.0,
-                sliding_window=None, block_tables=None, page_size=16, stage=STAGE_CAUSAL, merge_in_launch=True,
-                stream=None):
-    """The decode step of one attention layer in ONE launch (``g4b_decode_step``): what the
-    reference issues as two add_kv_to_cache launches, the attention launch and the split-KV
-    reduce launch (g4b/models/gemma4e.py:575-607, fa2.py:702-714).
+                sliding_window=None, block_tables=None, page_size=16, stage=STAGE_CAUSAL, stream=None):
+    """The decode step of one attention layer (``g4b_decode_step``): what the reference issues as
+    two add_kv_to_cache launches, the attention launch and the split-KV reduce launch
+    (g4b/models/gemma4e.py:575-607, fa2.py:702-714) as two launches -- attention with the append
+    inside it, then the merge, scheduled while the first drains -- or, with ``exchange``, as one.
 
-    ``q [B,H,1,D]``; ``partial_*`` (f32) are the split workspace, merged inside the launch by
-    whichever CTA finishes last.  ``k_new, v_new [B,G,1,D]`` (cache dtype), if given, are written
-    to the cache at position ``time_dim_sizes[b] - 1`` of every slot in phase and attended to.
-    ``exchange`` (a ``g4b_b200.dist.PartialExchange``): this rank holds only its share of one
-    sequence's keys; the merged partials of all ranks are exchanged through peer memory and
-    merged in the same launch.
-
-    The merge uses ticket counters inside the library, one set per GPU: calls of this function
-    that overlap on one GPU (two streams) would share them -- keep them on one stream or order
-    them.  ``flash_attention`` has no such restriction."""
+    ``q [B,H,1,D]``; ``partial_*`` (f32) are the split workspace.  ``k_new, v_new [B,G,1,D]``
+    (cache dtype), if given, are written to the cache at position ``time_dim_sizes[b] - 1`` of
+    every slot in phase and attended to.  ``exchange`` (a ``g4b_b200.dist.PartialExchange``):
+    this rank holds only its share of one sequence's keys; the local splits are merged, the
+    merged partials of all ranks are exchanged through peer memory and merged again, all in the
+    attention launch.  That form counts its CTAs in two words inside the library, one pair per
+    GPU: calls with ``exchange`` that overlap on one GPU (two streams) would share them -- keep
+    them on one stream or order them."""
     if (k_new is None) != (v_new is None):
         raise ValueError("k_new and v_new must be given together")
     s = _cabi.G4bDecodeStepArgs()
     s.attn = _attn_args(q, k_cache, v_cache, o, time_dim_sizes, user_phase, ctx_window_size, phase,
                         partial_o, partial_l, partial_m, stage, scale, sliding_window, block_tables,
                         page_size, num_kv_splits)
-    s.attn.reserved = 0 if merge_in_launch else 1      # else the merge is a second launch (no tickets)
     s.k_new = _cabi.as_tensor(k_new)
     s.v_new = _cabi.as_tensor(v_new)
     s.world, s.rank = 1, 0

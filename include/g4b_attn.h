@@ -124,35 +124,33 @@ int g4b_attn_prefill(const G4bAttnArgs* args, void* cuda_stream);
 int g4b_attn_decode(const G4bAttnArgs* args, void* cuda_stream);
 
 /*
- * The whole decode step of one attention layer in ONE launch; replaces, for Tq == 1, the two
- * add_kv_to_cache launches, the _attn_kernel launch and the _reduce_split_kv_kernel launch of
- * the reference's decode phase (g4b/models/gemma4e.py:575-607, fa2.py:702-714).
+ * The decode step of one attention layer; replaces, for Tq == 1, the two add_kv_to_cache
+ * launches, the _attn_kernel launch and the _reduce_split_kv_kernel launch of the reference's
+ * decode phase (g4b/models/gemma4e.py:575-607, fa2.py:702-714) by two launches (attention
+ * with the append inside it, then the merge, scheduled while the first drains) or, when the
+ * KV range of one sequence is split over GPUs, by ONE launch that also exchanges and merges.
  *
  *   attn            as for g4b_attn_decode; partial_* (f32, rows on 8-byte boundaries) are the
  *                   split workspace; num_kv_splits > 0 forces the split count, 0 picks it as
  *                   g4b_flash_attention does
- *   attn.reserved   bit 0 set (and world <= 1): the splits are merged by a second launch
- *                   (g4b_attn_combine) instead of inside this one; the append stays in it
  *   k_new, v_new    optional, together: [B, G, 1, D] rows in the cache dtype.  For every slot in
  *                   phase they are written to the cache at position time_dim_sizes[b] - 1
  *                   (ring row (time - 1) % T, or the page the block table names) and used as
  *                   that position's K / V, whatever the cache held there before
  *   world > 1       one sequence's KV range is split over `world` GPUs (one process each, the
- *                   same call sequence and shapes on every rank): after the local merge the
- *                   merged (acc, l, m) travel to every rank's exchange buffer as 8-byte words
- *                   {value, launch count} through peer-mapped memory and every rank finishes
- *                   the merge.  xbuf / state / xbuf_bytes as for g4b_attn_combine_exchange
- *                   (the buffers are interchangeable but must not be shared between the two
- *                   entry points).  Every CTA of the launch must be resident at once
- *                   (splits * G * B <= 2 x the SM count), else G4B_ERR_TOO_LARGE.  A peer that
- *                   does not show up within about a second leaves 0x401 in the status word;
- *                   after that the buffers and `state` must be zeroed again on every rank
- *                   before the next call.
- *
- * The splits are merged by whichever CTA finishes last, found through ticket counters that
- * live inside the library (one set per GPU, zero between launches).  Two launches of this
- * entry point that overlap on one GPU would share them: keep such calls on one stream or
- * order them.  g4b_flash_attention does not use the counters and has no such restriction.
+ *                   same call sequence and shapes on every rank): the local splits are merged,
+ *                   the merged (acc, l, m) travel to every rank's exchange buffer as 8-byte
+ *                   words {value, launch count} through peer-mapped memory, and every rank
+ *                   finishes the merge, all inside the attention launch.  xbuf / state /
+ *                   xbuf_bytes as for g4b_attn_combine_exchange (same size; a buffer must not be
+ *                   shared between the two entry points).  Every CTA of the launch must be
+ *                   resident at once (splits * G * B <= 2 x the SM count; 1 x at head dim 512)
+ *                   and splits <= 320, else G4B_ERR_TOO_LARGE.  A peer that does not show up
+ *                   within about a second leaves 0x401 in the status word; after that the
+ *                   buffers and `state` must be zeroed again on every rank before the next call.
+ *                   The launch counts its CTAs in two words inside the library (one pair per
+ *                   GPU, zero between launches): two such launches that overlap on one GPU
+ *                   would share them -- keep them on one stream or order them.
  */
 typedef struct G4bDecodeStepArgs {
   G4bAttnArgs attn;

@@ -136,11 +136,13 @@ def test_tensor_like_duck_typing():
 
 
 def test_exchange_buffer_sizes_host_only():
-    """g4b_exchange_buffer_bytes is pure host arithmetic: 2 parities x world x rows x 32-element
-    slices x (32 + l + m) words of 8 bytes (value, launch count)."""
+    """g4b_exchange_buffer_bytes is pure host arithmetic: 2 parities x world x rows x slices x
+    (columns + l + m) words of 8 bytes (value, launch count), the larger of the two entry points'
+    layouts (32-column slices for g4b_attn_combine_exchange, 8-column slices for
+    g4b_decode_step)."""
     lib = _cabi.load()
-    assert lib.g4b_exchange_buffer_bytes(8, 8, 256) == 2 * 8 * 8 * 8 * 34 * 8
-    assert lib.g4b_exchange_buffer_bytes(2, 3, 40) == 2 * 2 * 3 * 2 * 34 * 8      # head dim rounds up to 2 slices
+    assert lib.g4b_exchange_buffer_bytes(8, 8, 256) == 2 * 8 * 8 * 32 * 10 * 8
+    assert lib.g4b_exchange_buffer_bytes(2, 3, 40) == 2 * 2 * 3 * 2 * 34 * 8      # 2 slices of 32 > 5 slices of 8
 
 
 def test_valid_arguments_pass_validation_without_a_launch():

@@ -1,6 +1,7 @@
-"""g4b_decode_step: append + decode attention + merge of the splits (+ exchange with peers) in
-one launch, against the oracle; and the TMA-fed decode kernel under it at head dims 128 / 512,
-at the ring's wrap, with ragged edges and with splits that see no key.
+"""g4b_decode_step: append + decode attention, then the merge of the splits (or, with peers, the
+merge and the exchange inside the attention launch), against the oracle; and the TMA-fed decode
+kernel under it at head dims 128 / 512, at the ring's wrap, with ragged edges and with splits
+that see no key.
 
 The exchange is tested on one GPU with the test playing the peers: their words are in this
 rank's buffer before the launch, so no kernel waits for another kernel."""
@@ -79,9 +80,8 @@ def test_ring_wrap_positions(cuda, seed):
 @pytest.mark.parametrize("S", [1, 2, 8, 9, 16, 40, 148])
 @pytest.mark.parametrize("packed", [False, True])
 def test_decode_step_paged_with_append(cuda, S, packed):
-    """One launch = append + attention + merge, for split counts on either side of the group
-    size of the ticket tree; called three times in a row (the tickets must be back at zero and
-    the workspace holds the previous call's partials).  Slot 2 is off phase."""
+    """Append + attention + merge for a range of split counts; called three times in a row (the
+    workspace holds the previous call's partials).  Slot 2 is off phase."""
     lens = [3000, 17, 555, 1, 4096]
     B, H, G, D = len(lens), 8, 2, 256
     case = make_paged_case(400 + S, lens=lens, H=H, G=G, dtype=torch.bfloat16)
@@ -176,7 +176,7 @@ def test_decode_step_matches_two_launch_path_at_benchmark_size(cuda):
         o = torch.zeros(1, H, 1, D, dtype=torch.bfloat16, device=cuda)
         fa2.decode_step(q, kp, vp, o, time, None, L, fa2.PHASE_DECODE, po, pl, pm, num_kv_splits=S, scale=1 / 16,
                         block_tables=bt, page_size=16)
-        assert_close(o, want, f"one launch, {S} splits")
+        assert_close(o, want, f"decode step, {S} splits")
         o2 = torch.zeros_like(o)
         fa2.flash_attention(q, kp, vp, o2, time, None, L, fa2.PHASE_DECODE, po, pl, pm, num_kv_splits=S, scale=1 / 16,
                             block_tables=bt, page_size=16)
@@ -185,13 +185,19 @@ def test_decode_step_matches_two_launch_path_at_benchmark_size(cuda):
     assert float((outs[0] - outs[2]).abs().max()) < 4e-3
 
 
+def _word_view(exchange_buf, world, rank_rows, D):
+    """Layout of the decode step's exchange: [parity][source][row][slice of 8 columns][8 + l + m]."""
+    return exchange_buf[: 2 * world * rank_rows * (D // 8) * 10].view(2, world, rank_rows, D // 8, 10)
+
+
 def _peer_words(exchange_buf, world, rank_rows, D, epoch, src, row0, acc, l, m):
-    """Writes what rank `src` would push for rows [row0, row0 + R): words {value, epoch} in the
-    layout of the one-launch step, [parity][source][row][D + 2]."""
-    words = exchange_buf[: 2 * world * rank_rows * (D + 2)].view(2, world, rank_rows, D + 2)
-    vals = torch.cat([acc, l[:, None], m[:, None]], dim=1).contiguous()       # [R, D + 2] f32
+    """Writes what rank `src` would push for rows [row0, row0 + R): words {value, epoch}."""
+    words = _word_view(exchange_buf, world, rank_rows, D)
+    R = acc.shape[0]
+    vals = torch.cat([acc.reshape(R, D // 8, 8), l[:, None, None].expand(R, D // 8, 1),
+                      m[:, None, None].expand(R, D // 8, 1)], dim=2).contiguous()       # [R, D/8, 10] f32
     bits = vals.view(torch.int32).to(torch.int64) & 0xFFFFFFFF
-    words[epoch & 1, src, row0:row0 + vals.shape[0]] = (bits | (int(epoch) << 32)).to(words.device)
+    words[epoch & 1, src, row0:row0 + R] = (bits | (int(epoch) << 32)).to(words.device)
 
 
 @pytest.mark.parametrize("world,rank", [(2, 0), (2, 1), (4, 2)])
@@ -230,22 +236,22 @@ def test_decode_step_exchange_with_played_peers(cuda, world, rank):
         fa2.decode_step(q.to(cuda), kp.to(cuda), vp.to(cuda), o, time, None, share, fa2.PHASE_DECODE, po, pl, pm,
                         exchange=ex, num_kv_splits=S, scale=1 / 16, block_tables=bt, page_size=16)
         assert_close(o, want, f"world {world} rank {rank} step {step}")
-        assert ex.state.tolist() == [step + 1, 0]
+        assert ex.state.tolist()[0] == step + 1
         # what this rank pushed to a peer is its own merged partial
         acc, l, m = orc.split_partials(q[0], k[:, lo:lo + share], v[:, lo:lo + share], scale=1 / 16, num_splits=1)
         peer = (rank + 1) % world
-        words = bufs[peer][: 2 * world * H * (D + 2)].view(2, world, H, D + 2)[(step + 1) & 1, rank].cpu()
+        words = _word_view(bufs[peer], world, H, D)[(step + 1) & 1, rank].cpu()                 # [H, D/8, 10]
         assert bool(((words >> 32) == step + 1).all()), "a pushed word does not carry the launch count"
         got = (words & 0xFFFFFFFF).to(torch.int32).view(torch.float32)
-        m_got, m_want = got[:, D + 1], m[0, :, 0]
+        m_got, m_want = got[:, 0, 9], m[0, :, 0]
         scale_to = torch.exp2(m_got - m_want)[:, None]                  # same partial up to the choice of maximum
-        assert torch.allclose(got[:, :D] * scale_to, acc[0, :, 0], atol=2e-2, rtol=2e-2)
+        assert torch.allclose(got[:, :, :8].reshape(H, D) * scale_to, acc[0, :, 0], atol=2e-2, rtol=2e-2)
     assert _cabi.device_status() == 0
 
 
 def test_decode_step_absent_peer_times_out(cuda):
-    """Nobody writes the peer's words: the merging CTA gives up after its bounded wait, records
-    0x401, leaves o alone, and the context stays usable."""
+    """Nobody writes the peer's words: the merging CTAs give up after their bounded wait, record
+    0x401, leave o alone, and the context stays usable."""
     H, G, D, S = 8, 2, 256, 2
     case = make_paged_case(950, lens=[64], H=H, G=G, dtype=torch.float16)
     bufs = [torch.zeros(_cabi.load().g4b_exchange_buffer_bytes(2, H, D) // 8, dtype=torch.int64, device=cuda)

@@ -21,13 +21,18 @@ def merged_partial(po, pl, pm):
 
 
 def new_buffers(cuda, world, rows, slices):
-    """One zeroed exchange buffer per rank: [parity, source rank, row, slice, 34 words] of int64."""
-    return [torch.zeros(2 * world * rows * slices * (COLS + 2), dtype=torch.int64, device=cuda) for _ in range(world)]
+    """One zeroed exchange buffer per rank, of the size the library asks for; the merge kernel
+    uses its head as [parity, source rank, row, slice, 34 words] of int64."""
+    from g4b_b200 import _cabi
+
+    n = _cabi.load().g4b_exchange_buffer_bytes(world, rows, slices * COLS) // 8
+    assert n >= 2 * world * rows * slices * (COLS + 2)
+    return [torch.zeros(n, dtype=torch.int64, device=cuda) for _ in range(world)]
 
 
 def words(buf, world, rows, slices):
     """The buffer as int32 [2, world, rows, slices, 34, 2]: [..., 0] the value's bits, [..., 1] the count."""
-    return buf.view(torch.int32).view(2, world, rows, slices, COLS + 2, 2)
+    return buf[: 2 * world * rows * slices * (COLS + 2)].view(torch.int32).view(2, world, rows, slices, COLS + 2, 2)
 
 
 def deliver(buf, world, rows, slices, par, r, merged, epoch, cuda):
