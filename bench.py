@@ -591,7 +591,7 @@ class DecodeWorkload:
     to the same sequence and the merged output can be checked against the oracle."""
 
     def __init__(self, name, dev, seed, rank=0, world=1, sequences=256, nccl_gather=False, kv_splits=0, shard=False,
-                 fused=True):
+                 fused=True, self_exchange=False):
         from g4b_b200 import dist as gdist
         from g4b_b200.kernels import fa2
         from g4b_b200.kernels.rope import rope_norm_append
@@ -599,7 +599,9 @@ class DecodeWorkload:
         self.fa2, self.append = fa2, rope_norm_append
         self.name, self.dev, self.rank, self.world = name, dev, rank, world
         self.fused = fused      # the whole step as one launch (decode_step) or as append + decode + merge
-        self.merge_in_launch = name == "decode_long" and world > 1     # with peers: one launch
+        # with peers the merge and the exchange are inside the attention launch; --self-exchange runs
+        # that form on one GPU (pushing to itself), to time the in-launch merge without a link
+        self.merge_in_launch = (name == "decode_long" and world > 1) or self_exchange
         gen = torch.Generator(device="cpu").manual_seed(seed)
         self.scaling = "weak"
         if name == "decode_paged":
@@ -677,6 +679,12 @@ class DecodeWorkload:
         self.packed = torch.empty(S, B, H, 1, D + 2, device=dev, dtype=torch.float32)
         self.po, self.pl, self.pm = self.packed[..., :D], self.packed[..., D], self.packed[..., D + 1]
         self.nccl_gather = nccl_gather
+        self.exchange = None
+        if self_exchange and world == 1:
+            from g4b_b200 import _cabi
+
+            xb = torch.zeros(_cabi.load().g4b_exchange_buffer_bytes(1, B * H, D) // 8, dtype=torch.int64, device=dev)
+            self.exchange = gdist.PartialExchange(B * H, D, peers=[xb], rank=0)
         if self.long_split:
             self.gathered = torch.empty(world * S, B, H, 1, D + 2, device=dev, dtype=torch.float32)
             self.exchange = gdist.PartialExchange(B * H, D, device=dev)
@@ -730,7 +738,7 @@ class DecodeWorkload:
             self.fa2.decode_step(self.q, self.k_pool, self.v_pool, self.o, self.time, None, self.max_len,
                                  self.fa2.PHASE_DECODE, self.po, self.pl, self.pm,
                                  k_new=self.kn if last else None, v_new=self.vn if last else None,
-                                 exchange=self.exchange if self.long_split else None, num_kv_splits=self.splits,
+                                 exchange=self.exchange, num_kv_splits=self.splits,
                                  scale=SCALE, block_tables=self.bt, page_size=PAGE)
             return
         if last:
@@ -823,7 +831,8 @@ class DecodeWorkload:
         return touched / dt / 1e9, f"{n} of {self.B} sequences ({touched >> 20} MB of K/V), page gather + fp32 attention"
 
 
-def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_splits=0, strong=False, fused=True):
+def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_splits=0, strong=False, fused=True,
+                  self_exchange=False):
     """``strong``: the workload is ONE job dealt over the ranks (strong scaling) instead of the
     same per-GPU batch on every rank."""
     from g4b_b200 import dist as gdist
@@ -843,7 +852,7 @@ def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_s
             units = gdist.shard_prefill_units(nreq, G, S, world, rank, W)
         return PrefillWorkload(name, dev, seeds[name] + 100 * rank, units=units)
     return DecodeWorkload(name, dev, seeds[name] + (0 if name == "decode_long" else 100 * rank), rank, world,
-                          sequences, nccl_gather, kv_splits, shard=strong, fused=fused)
+                          sequences, nccl_gather, kv_splits, shard=strong, fused=fused, self_exchange=self_exchange)
 
 
 # ------------------------------------------------------------------------------------------
@@ -970,7 +979,7 @@ def run_ours(args):
     peaks = measured_peaks()
     headline = args.workload == "prefill_causal" and not args.no_extras
     wl = make_workload(args.workload, dev, rank, world, args.sequences, args.nccl_gather, args.kv_splits,
-                       strong=args.strong, fused=not args.unfused)
+                       strong=args.strong, fused=not args.unfused, self_exchange=args.self_exchange)
     parity = None
     if hasattr(wl, "parity"):
         good, excess = wl.parity()
@@ -1232,6 +1241,9 @@ def main():
                     help="N > 1: deal ONE job over the ranks (prefill units, decode sequences) instead of the same batch on every rank")
     ap.add_argument("--unfused", action="store_true",
                     help="decode workloads: append, attention and merge as three launches instead of decode_step")
+    ap.add_argument("--self-exchange", action="store_true",
+                    help="decode workloads on one GPU: the one-launch form of decode_step (merge inside the launch, "
+                         "pieces pushed to this GPU's own exchange buffer)")
     ap.add_argument("--no-graph", action="store_true", help="launch every step from Python instead of replaying CUDA graphs")
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline legs")
     ap.add_argument("--no-extras", action="store_true", help="default workload: only the headline, none of the other configurations' blocks")

@@ -216,7 +216,7 @@ int g4b_decode_step(const G4bDecodeStepArgs* args, void* cuda_stream) {
   s.attn = a;
   rc = launch_decode_stream(a, splits, &s, (cudaStream_t)cuda_stream);
   // without peers the splits are merged by a second launch, scheduled while the first drains
-  if (rc != G4B_OK || s.world > 1 || splits == 1) return rc;
+  if (rc != G4B_OK || s.world > 1 || (s.world == 1 && s.state != nullptr) || splits == 1) return rc;
   G4bCombineArgs c{};
   c.partial_o = a.partial_o; c.partial_l = a.partial_l; c.partial_m = a.partial_m; c.o = a.o;
   c.user_phase = a.user_phase; c.num_splits = splits; c.phase = a.phase;

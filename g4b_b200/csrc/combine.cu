@@ -81,34 +81,9 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams 
   const int64_t ml_off = b * p.pm_s[1] + h * p.pm_s[2] + t * p.pm_s[3];
   const int64_t l_off = b * p.pl_s[1] + h * p.pl_s[2] + t * p.pl_s[3];
 
-  // ---- phase 1 ----
-  float m = -INFINITY;
-  for (int s = tid; s < p.S; s += kCombineThreads) {
-    const float ms = p.pm[s * p.pm_s[0] + ml_off];
-    s_w[s] = ms;
-    m = fmaxf(m, ms);
-  }
-  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-  if (lane == 0) s_red[warp] = m;
-  __syncthreads();
-  m = s_red[0];
-  for (int w = 1; w < kCombineThreads / 32; ++w) m = fmaxf(m, s_red[w]);
-  __syncthreads();
-  float l = 0.f;
-  for (int s = tid; s < p.S; s += kCombineThreads) {
-    const float ms = s_w[s];
-    const float w = (ms == -INFINITY) ? 0.f : exp2f(ms - m);
-    s_w[s] = w;
-    if (w != 0.f) l += p.pl[s * p.pl_s[0] + l_off] * w;
-  }
-  for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-  if (lane == 0) s_red[warp] = l;
-  __syncthreads();
-  l = 0.f;
-  for (int w = 0; w < kCombineThreads / 32; ++w) l += s_red[w];
-  const float inv_l = l > 0.f ? 1.0f / l : 0.f;
-
-  // ---- phase 2 ----
+  // Everything the block needs from memory is asked for first -- the (m, l) pairs of the
+  // thread's splits and its first eight accumulator pieces, none of which depends on another --
+  // so the block pays one trip to L2 where the two phases used to pay three or four.
   const TP* po = (const TP*)p.po + b * p.po_s[1] + h * p.po_s[2] + t * p.po_s[3];
   TO* o = (TO*)p.o + b * p.o_s[0] + h * p.o_s[1] + t * p.o_s[2];
   const int lanes = kCombineThreads / p.groups;               // threads per split group
@@ -123,23 +98,74 @@ __global__ void __launch_bounds__(kCombineThreads) combine_kernel(CombineParams 
     if (a0 % (4 * sizeof(TP)) == 0 && p.po_s[0] % 4 == 0) vmode = 2;
     else if (sizeof(TP) == 4 && a0 % 8 == 0 && p.po_s[0] % 2 == 0) vmode = 1;
   }
+  constexpr int kMl = kCombineMaxSplits / kCombineThreads;    // (m, l) pairs per thread
+  constexpr int kPre = 8;                                     // accumulator pieces requested up front
+  float ms[kMl], ls[kMl];
+#pragma unroll
+  for (int j = 0; j < kMl; ++j) {
+    const int s = tid + j * kCombineThreads;
+    ms[j] = -INFINITY; ls[j] = 0.f;
+    if (s < p.S) { ms[j] = p.pm[s * p.pm_s[0] + ml_off]; ls[j] = p.pl[s * p.pl_s[0] + l_off]; }
+  }
+  float4 x[kPre];
+  if (n_valid > 0) {
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) {
+      const int sj = grp + j * p.groups;
+      x[j] = make_float4(0.f, 0.f, 0.f, 0.f);
+      if (sj < p.S) x[j] = load4_partial<TP>(po + (int64_t)sj * p.po_s[0] + d, vmode, n_valid);
+    }
+  }
+
+  // ---- phase 1: weights 2^(m_s - m) and the row sum ----
+  float m = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < kMl; ++j) m = fmaxf(m, ms[j]);
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if (lane == 0) s_red[warp] = m;
+  __syncthreads();
+  m = s_red[0];
+  for (int w = 1; w < kCombineThreads / 32; ++w) m = fmaxf(m, s_red[w]);
+  __syncthreads();
+  float l = 0.f;
+#pragma unroll
+  for (int j = 0; j < kMl; ++j) {
+    const int s = tid + j * kCombineThreads;
+    const float w = (ms[j] == -INFINITY) ? 0.f : exp2f(ms[j] - m);
+    if (s < p.S) s_w[s] = w;
+    if (w != 0.f) l += ls[j] * w;
+  }
+  for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
+  if (lane == 0) s_red[warp] = l;
+  __syncthreads();
+  l = 0.f;
+  for (int w = 0; w < kCombineThreads / 32; ++w) l += s_red[w];
+  const float inv_l = l > 0.f ? 1.0f / l : 0.f;
+
+  // ---- phase 2: weighted sum of the accumulators; a partial with weight 0 (a split that saw
+  // no key) is loaded like the others and then left out, whatever its accumulator holds ----
   float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
   if (n_valid > 0) {
-    // four independent loads in flight per thread; a partial with weight 0 (a split that saw
-    // no key) is loaded like the others and then left out, whatever its accumulator holds
-    for (int s0 = grp; s0 < p.S; s0 += 4 * p.groups) {
-      float4 x[4];
+#pragma unroll
+    for (int j = 0; j < kPre; ++j) {
+      const int s = grp + j * p.groups;
+      const float w = s < p.S ? s_w[s] : 0.f;
+      if (w == 0.f) continue;
+      acc.x += x[j].x * w; acc.y += x[j].y * w; acc.z += x[j].z * w; acc.w += x[j].w * w;
+    }
+    for (int s0 = grp + kPre * p.groups; s0 < p.S; s0 += 4 * p.groups) {
+      float4 y[4];
       float w[4];
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         const int s = s0 + j * p.groups;
         w[j] = s < p.S ? s_w[s] : 0.f;
-        x[j] = load4_partial<TP>(po + (int64_t)min(s, p.S - 1) * p.po_s[0] + d, vmode, n_valid);
+        y[j] = load4_partial<TP>(po + (int64_t)min(s, p.S - 1) * p.po_s[0] + d, vmode, n_valid);
       }
 #pragma unroll
       for (int j = 0; j < 4; ++j) {
         if (w[j] == 0.f) continue;
-        acc.x += x[j].x * w[j]; acc.y += x[j].y * w[j]; acc.z += x[j].z * w[j]; acc.w += x[j].w * w[j];
+        acc.x += y[j].x * w[j]; acc.y += y[j].y * w[j]; acc.z += y[j].z * w[j]; acc.w += y[j].w * w[j];
       }
     }
   }

@@ -236,6 +236,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   // after the stream the ring is scratch: warp accumulators / peers' partials, then merge weights
   float* sm_o = reinterpret_cast<float*>(ring);                                   // [kConsumers][8][D + 4]
 
+  // asked for before anything else: the split's key range, then its block-table entries, then
+  // its first tiles each wait for the one before
+  const int time = p.time_dim_sizes[b * p.time_stride];
   // a merge launch that follows may be scheduled as soon as SM resources free up (it waits for
   // this grid to finish before it reads the partials)
   asm volatile("griddepcontrol.launch_dependents;" ::: "memory");
@@ -283,7 +286,6 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   }
 
   // ---- key range of this split (fa2.py:52-67, with block-aligned split boundaries) ----
-  const int time = p.time_dim_sizes[b * p.time_stride];
   const int window = min(time, p.ctx_window);
   // Ring mode counts keys from the oldest one the cache exposes; a paged cache is addressed by
   // absolute position, so there the exposed window is just another lower bound.
@@ -537,6 +539,20 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   float* x_own = reinterpret_cast<float*>(s_red + kStreamThreads);            // [R][kXWords]
   float* x_all = x_own + 8 * kXWords;                                          // [world][R][kXWords]
   const float* pof = (const float*)p.po;
+  // threads = (group of splits) x (pair of columns of one head); R * 4 pairs, padded to 16 or 32
+  const int pairs = R * (kXCols / 2);
+  const int pad = pairs > 16 ? 32 : 16;
+  const int n_grp = kStreamThreads / pad;
+  const int pi = tid % pad, sg = tid / pad;
+  // the first accumulator pieces of the CTA's first slice are asked for before the weights
+  // (they do not depend on them): one trip to L2 less on the way to the exchange
+  float2 x0[10];
+  if (pi < pairs) {
+    const float* src = pof + b * p.po_s1 + (g * R + pi / (kXCols / 2)) * p.po_s2 + split * kXCols + 2 * (pi % (kXCols / 2));
+#pragma unroll
+    for (int j = 0; j < 10; ++j)
+      x0[j] = __ldcg(reinterpret_cast<const float2*>(src + (int64_t)min(sg + j * n_grp, S - 1) * p.po_s0));
+  }
   // weights and merged row sums of the local splits, one warp per head; every (m, l) pair is
   // requested before any is used
   for (int hh = warp; hh < R; hh += kStreamThreads / 32) {
@@ -571,11 +587,6 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
 
   const uint32_t epoch = ctl->epoch;
   const int par = (int)(epoch & 1u);
-  // threads = (group of splits) x (pair of columns of one head); R * 4 pairs, padded to 16 or 32
-  const int pairs = R * (kXCols / 2);
-  const int pad = pairs > 16 ? 32 : 16;
-  const int n_grp = kStreamThreads / pad;
-  const int pi = tid % pad, sg = tid / pad;
   for (int sl = split; sl < kSlices; sl += S) {
     // ---- this GPU's merged accumulator for columns [8 sl, 8 sl + 8) of the R heads ----
     float2 acc = make_float2(0.f, 0.f);
@@ -587,6 +598,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
         float2 x[10];
 #pragma unroll
         for (int j = 0; j < 10; ++j) {
+          if (sl == split && i0 == sg) { x[j] = x0[j]; continue; }
           const int i = min(i0 + j * n_grp, S - 1);
           x[j] = __ldcg(reinterpret_cast<const float2*>(src + (int64_t)i * p.po_s0));
         }
@@ -614,7 +626,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
       const int hh = idx / kXWords, e = idx - hh * kXWords;
       const int64_t off = xword(p, D, par, p.rank, b * p.H + g * R + hh, sl) + e;
       const unsigned long long word = ((unsigned long long)epoch << 32) | __float_as_uint(x_own[idx]);
-      for (int r = 0; r < p.world; ++r) st_word_sys(p.xbuf[r] + off, word);
+      for (int r = 0; r < p.world; ++r)
+        if (r != p.rank) st_word_sys(p.xbuf[r] + off, word);
+      x_all[(p.rank * R + hh) * kXWords + e] = x_own[idx];      // this GPU's own piece needs no trip
     }
     // ---- wait for every GPU's piece: a word has arrived once it carries this launch's count ----
     const long long t0 = clock64();
@@ -630,6 +644,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
         const int pc = min(pr, n_pairs - 1);
         const int r = pc / (R * (kXWords / 2)), rem = pc - r * (R * (kXWords / 2));
         const int hh = rem / (kXWords / 2), e = 2 * (rem - hh * (kXWords / 2));
+        have[j] = have[j] || r == p.rank;
         where[j] = (r * R + hh) * kXWords + e;
         src[j] = reinterpret_cast<const ulonglong2*>(p.xbuf[p.rank] + xword(p, D, par, r, b * p.H + g * R + hh, sl) + e);
       }
@@ -785,7 +800,8 @@ int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeSt
       p.vn_s0 = step->v_new.stride[0]; p.vn_s1 = step->v_new.stride[1];
       p.k_cache = a.k_cache.ptr; p.v_cache = a.v_cache.ptr;
     }
-    if (step->world > 1) {
+    // the exchange form: with peers, or (world == 1 with a state given) alone, pushing to itself
+    if (step->world > 1 || (step->world == 1 && step->state != nullptr)) {
       if (step->world > 8 || step->rank < 0 || step->rank >= step->world) return fail(G4B_ERR_BAD_ARG, "decode step: bad world / rank");
       if (step->state == nullptr) return fail(G4B_ERR_BAD_ARG, "decode step: state is null");
       if (num_splits > kMaxResidentSplits) return fail(G4B_ERR_TOO_LARGE, "decode step with peers: at most %d splits", kMaxResidentSplits);
@@ -810,7 +826,7 @@ int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeSt
     }
   }
   G4B_STOP_IF_VALIDATE_ONLY();
-  if (p.world > 1) {
+  if (p.xstate != nullptr) {
     int rc = step_sync_ptr(&p.sync);
     if (rc) return rc;
   }

@@ -138,7 +138,7 @@ def decode_step(q, k_cache, v_cache, o, time_dim_sizes, user_phase, ctx_window_s
                         page_size, num_kv_splits)
     s.k_new = _cabi.as_tensor(k_new)
     s.v_new = _cabi.as_tensor(v_new)
-    s.world, s.rank = 1, 0
+    s.world, s.rank = 0, 0
     if exchange is not None:
         for r in range(exchange.world):
             s.xbuf[r] = exchange.xbuf_ptrs[r]

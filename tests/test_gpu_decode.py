@@ -198,7 +198,8 @@ def test_decode_one_long_sequence_full_size(cuda):
         got, (po, pl, pm) = run_paged(case, cuda, splits=splits, max_splits=splits)
         assert_close(got[0], want, f"{splits} splits")
     # the same partials through the one-kernel cross-GPU merge (a world of one)
-    peers = [torch.zeros(2 * 8 * 8 * 34, dtype=torch.int64, device=cuda)]
+    from g4b_b200 import _cabi
+    peers = [torch.zeros(_cabi.load().g4b_exchange_buffer_bytes(1, 8, 256) // 8, dtype=torch.int64, device=cuda)]
     ex = PartialExchange(8, 256, peers=peers, rank=0)
     o = torch.zeros(1, 8, 1, 256, dtype=torch.bfloat16, device=cuda)
     ex.combine(po, pl, pm, o, 148)
