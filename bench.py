@@ -13,6 +13,8 @@ Prints ONE JSON line.  Workloads (shapes of the five benchmark configurations):
                     --kv-splits -1 runs it unsplit)
     rope_append     the launch before attention: norm + rotary embedding + KV append, GB/s
     kv_append       add_kv_to_cache alone on a prefill chunk (V norm, f32 -> f16), GB/s
+    decode_paged_fp8  decode_paged over 8-bit (e4m3) pages with a scale per (page, kv head):
+                    1024 bytes of K/V per token instead of 2048
 A step is one pass of the hot path over one batch.  ``value`` has inputs resident in HBM;
 ``e2e`` goes through the public Python operators with pinned host buffers, host<->device
 copies inside the timed region.
@@ -596,7 +598,9 @@ class DecodeWorkload:
         from g4b_b200.kernels import fa2
         from g4b_b200.kernels.rope import rope_norm_append
 
-        self.fa2, self.append = fa2, rope_norm_append
+        from g4b_b200.kernels.add_kv_to_cache import add_kv_to_cache_fp8
+
+        self.fa2, self.append, self.append_fp8 = fa2, rope_norm_append, add_kv_to_cache_fp8
         self.name, self.dev, self.rank, self.world = name, dev, rank, world
         self.fused = fused      # the whole step as one launch (decode_step) or as append + decode + merge
         # with peers the merge and the exchange are inside the attention launch; --self-exchange runs
@@ -604,7 +608,8 @@ class DecodeWorkload:
         self.merge_in_launch = (name == "decode_long" and world > 1) or self_exchange
         gen = torch.Generator(device="cpu").manual_seed(seed)
         self.scaling = "weak"
-        if name == "decode_paged":
+        self.fp8 = name == "decode_paged_fp8"
+        if name in ("decode_paged", "decode_paged_fp8"):
             self.dtype = torch.float16
             self.all_lens = torch.randint(1024, 32769, (sequences,), generator=gen, dtype=torch.int64)
             self.lens = self.all_lens
@@ -652,6 +657,16 @@ class DecodeWorkload:
             self.k_pool, self.v_pool = to_pool(self.seq_k), to_pool(self.seq_v)
             if rank != 0:
                 self.seq_k = self.seq_v = None                     # only rank 0 computes the oracle
+        elif self.fp8:
+            # bytes of finite e4m3 values (0x7f / 0xff are NaN) and scales as an append would leave them
+            gdev = torch.Generator(device=dev).manual_seed(seed + 1 + rank)
+            def bytes_pool():
+                mag = torch.randint(0, 0x7f, (num_pages, G, PAGE, D), generator=gdev, device=dev, dtype=torch.int16)
+                sign = torch.randint(0, 2, (num_pages, G, PAGE, D), generator=gdev, device=dev, dtype=torch.int16) << 7
+                return (mag | sign).to(torch.uint8)
+            self.k_pool, self.v_pool = bytes_pool(), bytes_pool()
+            self.k_sc = 0.004 + 0.004 * torch.rand(num_pages, G, generator=gdev, device=dev)
+            self.v_sc = 0.004 + 0.004 * torch.rand(num_pages, G, generator=gdev, device=dev)
         else:
             gdev = torch.Generator(device=dev).manual_seed(seed + 1 + rank)
             self.k_pool = self._big_randn((num_pages, G, PAGE, D), gdev)
@@ -690,17 +705,19 @@ class DecodeWorkload:
             self.exchange = gdist.PartialExchange(B * H, D, device=dev)
             if not fused:
                 self.launches_per_step = 3 if self.rank == world - 1 else 2
-        kv_bytes = float(self.local_lens.sum()) * G * D * 2 * 2
+        esz = 1 if self.fp8 else 2
+        kv_bytes = float(self.local_lens.sum()) * G * D * 2 * esz
         self.units = kv_bytes                                    # K/V bytes per step (this rank)
-        self.total_units = float(self.all_lens.sum()) * G * D * 2 * 2 if self.scaling == "strong" else None
+        self.total_units = float(self.all_lens.sum()) * G * D * 2 * esz if self.scaling == "strong" else None
         self.metric, self.unit, self.bound, self.div = "decode_attn_hbm_gbs", "GB/s", "hbm", 1e9
         # one launch; or append + attention, then the merge; or append (K and V), decode, merge
-        self.launches_per_step = (1 if self.merge_in_launch else 2) if fused else 3
+        self.launches_per_step = 4 if self.fp8 else ((1 if self.merge_in_launch else 2) if fused else 3)
         self.h2d = (self.h_q.numel() + self.h_kn.numel() + self.h_vn.numel()) * 2
         self.d2h = self.h_o.numel() * 2
         self.config = {"workload": name, "sequences": len(self.all_lens), "ctx_sum": int(self.all_lens.sum()),
                        "ctx_min": int(self.all_lens.min()), "ctx_max": int(self.all_lens.max()), "page_size": PAGE,
-                       "kv_dtype": str(self.dtype).replace("torch.", ""), "kv_splits": self.splits, "scale": SCALE,
+                       "kv_dtype": "e4m3 + f32 scale per (page, kv head)" if self.fp8 else str(self.dtype).replace("torch.", ""),
+                       "kv_splits": self.splits, "scale": SCALE,
                        "l2": "K/V (%d MB per GPU) larger than L2" % (int(kv_bytes) >> 20)}
         if self.scaling == "strong":
             self.config.update({"sequences_this_rank": B, "ctx_sum_this_rank": int(self.local_lens.sum())})
@@ -732,6 +749,14 @@ class DecodeWorkload:
 
     def step(self, i=0):
         self.k_pool, self.v_pool = self.pools[i % len(self.pools)]
+        if self.fp8:
+            # the new token's K and V rows are quantised into their pages, then attention over the bytes
+            self.append_fp8(self.kn, self.k_pool, self.k_sc, self.off, 1e-6, block_tables=self.bt, page_size=PAGE)
+            self.append_fp8(self.vn, self.v_pool, self.v_sc, self.off, 1e-6, block_tables=self.bt, page_size=PAGE)
+            self.fa2.flash_attention_fp8(self.q, self.k_pool, self.v_pool, self.k_sc, self.v_sc, self.o, self.time, None,
+                                         self.max_len, self.fa2.PHASE_DECODE, self.po, self.pl, self.pm, scale=SCALE,
+                                         block_tables=self.bt, page_size=PAGE, num_kv_splits=self.splits)
+            return
         last = (not self.long_split) or self.rank == self.world - 1
         if self.fused and not self.nccl_gather:
             # the new token's row lives on the rank that owns the tail of the sequence
@@ -799,8 +824,13 @@ class DecodeWorkload:
         for b in sorted({0, self.B - 1}):
             L = int(self.local_lens[b])
             pages = self.h_bt[b, : (L + PAGE - 1) // PAGE].long()
-            k = kp[pages.to(self.dev)].float().cpu().permute(1, 0, 2, 3).reshape(G, -1, D)[:, :L]
-            v = vp[pages.to(self.dev)].float().cpu().permute(1, 0, 2, 3).reshape(G, -1, D)[:, :L]
+            if self.fp8:
+                k = orc.dequantise_fp8_pool(kp[pages.to(self.dev)].cpu(), self.k_sc[pages.to(self.dev)].cpu())
+                v = orc.dequantise_fp8_pool(vp[pages.to(self.dev)].cpu(), self.v_sc[pages.to(self.dev)].cpu())
+                k, v = (torch.nan_to_num(x).permute(1, 0, 2, 3).reshape(G, -1, D)[:, :L] for x in (k, v))
+            else:
+                k = kp[pages.to(self.dev)].float().cpu().permute(1, 0, 2, 3).reshape(G, -1, D)[:, :L]
+                v = vp[pages.to(self.dev)].float().cpu().permute(1, 0, 2, 3).reshape(G, -1, D)[:, :L]
             want = orc.attention_core(self.h_q[b].float(), k, v, scale=SCALE)
             good, ex = within_tolerance(self.o[b], want)
             ok, worst = ok and good, max(worst, ex)
@@ -818,7 +848,14 @@ class DecodeWorkload:
 
         n = min(8, self.B)
         idx = list(range(n))
-        kp, vp = self.k_pool.cpu(), self.v_pool.cpu()
+        if self.fp8:     # the CPU side has no 8-bit path: it attends over the de-quantised values of the sample
+            used = torch.unique(self.h_bt[:n].flatten().long().clamp(min=0)).to(self.dev)
+            kp = torch.zeros(self.k_pool.shape, dtype=torch.float16)
+            vp = torch.zeros(self.v_pool.shape, dtype=torch.float16)
+            kp[used.cpu()] = torch.nan_to_num(orc.dequantise_fp8_pool(self.k_pool[used].cpu(), self.k_sc[used].cpu())).half()
+            vp[used.cpu()] = torch.nan_to_num(orc.dequantise_fp8_pool(self.v_pool[used].cpu(), self.v_sc[used].cpu())).half()
+        else:
+            kp, vp = self.k_pool.cpu(), self.v_pool.cpu()
         t0 = time.perf_counter()
         touched = 0
         for b in idx:
@@ -826,7 +863,7 @@ class DecodeWorkload:
             k = orc.gather_pages(kp, self.h_bt[b], L, PAGE)
             v = orc.gather_pages(vp, self.h_bt[b], L, PAGE)
             orc.attention_core(self.h_q[b].float(), k, v, scale=SCALE)
-            touched += L * G * D * 2 * 2
+            touched += L * G * D * 2 * (1 if self.fp8 else 2)
         dt = time.perf_counter() - t0
         return touched / dt / 1e9, f"{n} of {self.B} sequences ({touched >> 20} MB of K/V), page gather + fp32 attention"
 
@@ -838,7 +875,7 @@ def make_workload(name, dev, rank, world, sequences=256, nccl_gather=False, kv_s
     from g4b_b200 import dist as gdist
 
     seeds = {"prefill_causal": 1, "prefill_swa": 2, "decode_paged": 3, "decode_long": 4, "rope_append": 5,
-             "kv_append": 7}
+             "kv_append": 7, "decode_paged_fp8": 3}
     if name == "kv_append":
         return KVAppendWorkload(name, dev, seeds[name] + 100 * rank)
     if name == "rope_append":
@@ -1175,7 +1212,7 @@ def run_reference(args):
     else:
         # decode_paged: the first 8 sequences of the benchmark's seeded set (what the GPU arm's
         # cpu_baseline leg runs); decode_long: the one sequence
-        if name == "decode_paged":
+        if name in ("decode_paged", "decode_paged_fp8"):   # (the CPU side has no 8-bit path: same f16 sample)
             lens = torch.randint(1024, 32769, (256,), generator=torch.Generator().manual_seed(3), dtype=torch.int64)[:8]
             dt_kv = torch.float16
         else:
@@ -1200,7 +1237,7 @@ def run_reference(args):
 
         metric, unit, div = "decode_attn_hbm_gbs", "GB/s", 1e9
         sample = f"{len(lens)} sequence(s), {int(lens.sum())} tokens per step, page gather + fp32 attention"
-        config = {"workload": name, "sequences": 256 if name == "decode_paged" else 1, "page_size": PAGE,
+        config = {"workload": name, "sequences": 256 if name.startswith("decode_paged") else 1, "page_size": PAGE,
                   "kv_dtype": str(dt_kv).replace("torch.", ""), "scale": SCALE, "reference_sample": sample}
     for _ in range(args.warmup):
         fn()
@@ -1229,7 +1266,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="prefill_causal",
                     choices=["prefill_causal", "prefill_swa", "prefill_chunk", "decode_paged", "decode_long", "rope_append",
-                             "kv_append"])
+                             "kv_append", "decode_paged_fp8"])
     ap.add_argument("--sequences", type=int, default=256,
                     help="decode_paged only: number of sequences (256 = the benchmark configuration; "
                          "smaller values are for profiler captures)")

@@ -14,7 +14,7 @@ from pathlib import Path
 _LIB_PATH = Path(__file__).resolve().parent / "lib" / "libg4b_attn.so"
 
 # enum G4bDtype
-F32, F16, BF16, I32, I64, U8 = 0, 1, 2, 3, 4, 5
+F32, F16, BF16, I32, I64, U8, FP8_E4M3 = 0, 1, 2, 3, 4, 5, 6
 
 _DTYPE_NAMES = {
     "float32": F32, "f32": F32, "float": F32,
@@ -23,6 +23,7 @@ _DTYPE_NAMES = {
     "int32": I32, "i32": I32,
     "int64": I64, "i64": I64, "long": I64,
     "uint8": U8, "u8": U8,
+    "float8_e4m3fn": FP8_E4M3, "fp8_e4m3": FP8_E4M3,
 }
 
 
@@ -95,6 +96,15 @@ class G4bDecodeStepArgs(ctypes.Structure):
     ]
 
 
+class G4bFp8AppendArgs(ctypes.Structure):
+    _fields_ = [
+        ("x", G4bTensor), ("cache", G4bTensor), ("scales", G4bTensor), ("cache_offsets", G4bTensor),
+        ("x_rsos", G4bTensor), ("user_phase", G4bTensor), ("block_tables", G4bTensor),
+        ("rmsnorm_eps", ctypes.c_float), ("headroom", ctypes.c_float), ("phase", ctypes.c_int32),
+        ("page_size", ctypes.c_int32),
+    ]
+
+
 class G4bAdvanceArgs(ctypes.Structure):
     _fields_ = [
         ("input_token_ids", G4bTensor), ("out_token_ids", G4bTensor), ("cache_offsets", G4bTensor),
@@ -109,6 +119,9 @@ EXPORTS = {
     "g4b_attn_decode": (ctypes.c_int, [ctypes.POINTER(G4bAttnArgs), ctypes.c_void_p]),
     "g4b_attn_decode_static_scratch": (ctypes.c_int, [ctypes.POINTER(G4bAttnArgs), ctypes.c_void_p]),
     "g4b_decode_step": (ctypes.c_int, [ctypes.POINTER(G4bDecodeStepArgs), ctypes.c_void_p]),
+    "g4b_kv_append_fp8": (ctypes.c_int, [ctypes.POINTER(G4bFp8AppendArgs), ctypes.c_void_p]),
+    "g4b_flash_attention_fp8": (ctypes.c_int, [ctypes.POINTER(G4bAttnArgs), ctypes.POINTER(G4bTensor),
+                                               ctypes.POINTER(G4bTensor), ctypes.c_void_p]),
     "g4b_attn_combine": (ctypes.c_int, [ctypes.POINTER(G4bCombineArgs), ctypes.c_void_p]),
     "g4b_attn_combine_exchange": (ctypes.c_int, [ctypes.POINTER(G4bExchangeArgs), ctypes.c_void_p]),
     "g4b_exchange_buffer_bytes": (ctypes.c_int64, [ctypes.c_int, ctypes.c_int64, ctypes.c_int]),

@@ -317,6 +317,75 @@ int g4b_kv_append(const G4bAppendArgs* args, void* cuda_stream) {
   return launch_kv_append(a, (cudaStream_t)cuda_stream);
 }
 
+static bool is_byte_dtype(int dt) { return dt == G4B_U8 || dt == G4B_FP8_E4M3; }
+
+int g4b_kv_append_fp8(const G4bFp8AppendArgs* args, void* cuda_stream) {
+  if (args == nullptr) return fail(G4B_ERR_BAD_ARG, "args is null");
+  const G4bFp8AppendArgs& a = *args;
+  int rc;
+  if ((rc = check_tensor(a.x, "x", 4, true))) return rc;
+  if ((rc = check_tensor(a.cache, "cache", 4, true))) return rc;
+  if ((rc = check_tensor(a.scales, "scales", 2, false))) return rc;
+  if ((rc = check_tensor(a.cache_offsets, "cache_offsets", 1, false))) return rc;
+  if ((rc = check_tensor(a.block_tables, "block_tables", 2, false))) return rc;
+  if (!is_float_dtype(a.x.dtype)) return fail(G4B_ERR_BAD_DTYPE, "x must be f32, f16 or bf16");
+  if (!is_byte_dtype(a.cache.dtype)) return fail(G4B_ERR_BAD_DTYPE, "cache must hold one byte per element (e4m3)");
+  if (a.scales.dtype != G4B_F32) return fail(G4B_ERR_BAD_DTYPE, "scales must be f32");
+  if (a.cache_offsets.dtype != G4B_I32 && a.cache_offsets.dtype != G4B_I64)
+    return fail(G4B_ERR_BAD_DTYPE, "cache_offsets must be int32 or int64");
+  if (a.block_tables.dtype != G4B_I32) return fail(G4B_ERR_BAD_DTYPE, "block_tables must be int32");
+  const int64_t B = a.x.shape[0], G = a.x.shape[1], Tq = a.x.shape[2], D = a.x.shape[3];
+  if (a.cache_offsets.shape[0] != B || a.block_tables.shape[0] != B)
+    return fail(G4B_ERR_BAD_ARG, "cache_offsets and block_tables must have B entries / rows");
+  if (!contiguous_from(a.cache, 0)) return fail(G4B_ERR_BAD_STRIDE, "cache must be contiguous");
+  if (a.cache.shape[1] != G || a.cache.shape[3] != D) return fail(G4B_ERR_BAD_ARG, "x and cache disagree on kv heads or head dim");
+  if (!is_pow2(a.page_size) || a.cache.shape[2] != a.page_size) return fail(G4B_ERR_BAD_ARG, "pool dim 2 must equal page_size, a power of two");
+  if (a.scales.shape[0] != a.cache.shape[0] || a.scales.shape[1] != G) return fail(G4B_ERR_BAD_ARG, "scales must be [num_pages, G]");
+  if (!(a.headroom >= 1.f)) return fail(G4B_ERR_BAD_ARG, "headroom must be >= 1");
+  if (a.x_rsos.ptr != nullptr) {
+    if ((rc = check_tensor(a.x_rsos, "x_rsos", 3, false))) return rc;
+    if (a.x_rsos.dtype != G4B_F32 || a.x_rsos.shape[0] != B || a.x_rsos.shape[1] != G || a.x_rsos.shape[2] != Tq)
+      return fail(G4B_ERR_BAD_ARG, "x_rsos must be f32 [B,G,Tq]");
+  }
+  if (a.user_phase.ptr != nullptr) {
+    if ((rc = check_tensor(a.user_phase, "user_phase", 1, false))) return rc;
+    if (a.user_phase.dtype != G4B_U8 || a.user_phase.shape[0] != B) return fail(G4B_ERR_BAD_ARG, "user_phase must be uint8 [B]");
+  }
+  return launch_kv_append_fp8(a, (cudaStream_t)cuda_stream);
+}
+
+int g4b_flash_attention_fp8(const G4bAttnArgs* args, const G4bTensor* k_scales, const G4bTensor* v_scales,
+                            void* cuda_stream) {
+  if (args == nullptr || k_scales == nullptr || v_scales == nullptr) return fail(G4B_ERR_BAD_ARG, "args or scales null");
+  G4bAttnArgs a = *args;
+  const int given = (a.partial_o.ptr != nullptr) + (a.partial_l.ptr != nullptr) + (a.partial_m.ptr != nullptr);
+  if (given != 0 && given != 3) return fail(G4B_ERR_BAD_ARG, "partial_o, partial_l, and partial_m must be provided together");
+  if (a.q.ndim != 4 || a.q.shape[2] != 1) return fail(G4B_ERR_UNSUPPORTED, "e4m3 caches: Tq == 1 only");
+  if (a.k_cache.ndim != 4 || a.v_cache.ndim != 4) return fail(G4B_ERR_BAD_ARG, "k_cache / v_cache: expected rank 4");
+  if (!is_byte_dtype(a.k_cache.dtype) || !is_byte_dtype(a.v_cache.dtype))
+    return fail(G4B_ERR_BAD_DTYPE, "e4m3 caches must hold one byte per element");
+  if (a.block_tables.ptr == nullptr) return fail(G4B_ERR_UNSUPPORTED, "e4m3 caches: paged only");
+  // the shape rules are those of the 16-bit path: check them on a copy that claims f16 caches
+  G4bAttnArgs chk = a;
+  chk.k_cache.dtype = chk.v_cache.dtype = G4B_F16;
+  const int splits = resolve_splits(a);
+  a.num_kv_splits = chk.num_kv_splits = splits;
+  int rc = validate_attn(chk, splits > 1, splits, true);
+  if (rc) return rc;
+  if (a.q.shape[1] / a.k_cache.shape[1] > 8) return fail(G4B_ERR_UNSUPPORTED, "at most 8 query heads per kv head");
+  const G4bTensor* sc[2] = {k_scales, v_scales};
+  for (const G4bTensor* t : sc) {
+    if (t->ptr == nullptr || t->ndim != 2 || t->dtype != G4B_F32 || t->shape[0] != a.k_cache.shape[0] || t->shape[1] != a.k_cache.shape[1])
+      return fail(G4B_ERR_BAD_ARG, "k_scales / v_scales must be f32 [num_pages, G]");
+  }
+  rc = launch_decode_stream(a, splits, nullptr, (cudaStream_t)cuda_stream, k_scales, v_scales);
+  if (rc || splits == 1) return rc;
+  G4bCombineArgs c{};
+  c.partial_o = a.partial_o; c.partial_l = a.partial_l; c.partial_m = a.partial_m; c.o = a.o;
+  c.user_phase = a.user_phase; c.num_splits = splits; c.phase = a.phase;
+  return g4b_attn_combine(&c, cuda_stream);
+}
+
 int g4b_advance_decode_state(const G4bAdvanceArgs* args, void* cuda_stream) {
   if (args == nullptr) return fail(G4B_ERR_BAD_ARG, "args is null");
   const G4bAdvanceArgs& a = *args;

@@ -37,7 +37,7 @@ inline int dtype_size(int dt) {
     case G4B_F32: case G4B_I32: return 4;
     case G4B_F16: case G4B_BF16: return 2;
     case G4B_I64: return 8;
-    case G4B_U8: return 1;
+    case G4B_U8: case G4B_FP8_E4M3: return 1;
   }
   return 0;
 }
@@ -68,7 +68,9 @@ int launch_advance(const G4bAdvanceArgs& a, cudaStream_t st);
 int launch_combine(const G4bCombineArgs& a, cudaStream_t st);
 int launch_decode(const G4bAttnArgs& a, int num_splits, cudaStream_t st);            // register-streaming kernel (head dim 256)
 bool decode_stream_supports(const G4bAttnArgs& a);                                    // shapes the TMA-fed kernel takes
-int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeStepArgs* step, cudaStream_t st);
+int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeStepArgs* step, cudaStream_t st,
+                         const G4bTensor* k_scales = nullptr, const G4bTensor* v_scales = nullptr);
+int launch_kv_append_fp8(const G4bFp8AppendArgs& a, cudaStream_t st);
 int launch_prefill(const G4bAttnArgs& a, cudaStream_t st);
 
 // ---------------------------------------------------------------------------------------

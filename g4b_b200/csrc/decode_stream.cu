@@ -54,12 +54,12 @@ enum : int32_t { kErrBadEntry = 0x201, kErrStageFull = 0x211, kErrStageEmpty = 0
 // that finishes last puts both back).  One pair per GPU, shared by every launch on it.
 __device__ uint32_t g_step_sync[2];
 
-template <int D> struct StreamCfg {
-  static constexpr int kTileBytes = 16 * D * 2;          // 16 keys of K, or of V
+template <int D, bool kFp8 = false> struct StreamCfg {
+  static constexpr int kTileBytes = 16 * D * (kFp8 ? 1 : 2);   // 16 keys of K, or of V
   static constexpr int kStageBytes = 2 * kTileBytes;
-  static constexpr int kStages = D == 128 ? 8 : 6;       // 64 / 96 / 192 KB in flight per CTA
+  static constexpr int kStages = kFp8 ? (D == 512 ? 6 : 12) : (D == 128 ? 8 : 6);   // 64 / 96 / 192 KB in flight per CTA (16-bit)
   static constexpr int kRingBytes = kStages * kStageBytes;
-  static constexpr int kCtasPerSm = D >= 512 ? 1 : 2;
+  static constexpr int kCtasPerSm = (D >= 512 && !kFp8) ? 1 : 2;
 };
 
 struct StreamParams {
@@ -75,6 +75,9 @@ struct StreamParams {
   int q_dtype, o_dtype, po_dtype;
   float scale_log2;
   int32_t* status;
+  // e4m3 pools: one f32 scale per (page, kv head), value = stored byte's value x scale
+  const float* k_scales; const float* v_scales;
+  int64_t ks_s0, ks_s1, vs_s0, vs_s1;
   // decode step
   uint32_t* sync;              // {arrived, finished} (exchange form), else null
   void* k_cache; void* v_cache;
@@ -89,6 +92,7 @@ template <int kStages> struct alignas(16) Ctl {
   uint64_t full[kStages];
   uint64_t empty[kStages];
   int4 meta[kStages];          // x: logical key of tile row 0, y / z: valid rows [y, z), w: cache row of tile row 0
+  float2 scl[kStages];         // e4m3 pools: the stage's page scales (K, V)
   float sm_m[kConsumers][8];
   float sm_l[kConsumers][8];
   float ml[8][2];              // merged (l, m) per head
@@ -215,16 +219,118 @@ __device__ __forceinline__ void stage_step(WarpAcc<D>& st, const uint32_t (&qa)[
   }
 }
 
+// e4m3 pair -> f16 pair
+__device__ __forceinline__ uint32_t e4m3x2_to_f16x2(uint32_t two_bytes) {
+  uint32_t r;
+  asm("{\n\t.reg .b16 lo;\n\tcvt.u16.u32 lo, %1;\n\tcvt.rn.f16x2.e4m3x2 %0, lo;\n\t}" : "=r"(r) : "r"(two_bytes));
+  return r;
+}
+
+// One stage of an e4m3 pool: 16 keys, rows of D bytes.  The tensor instructions run on f16:
+// an e4m3 value is exact in f16, q is rounded to f16, and the page's scales go into the
+// scores (K) and into the probabilities handed to the second product (V).
+//   K: an 8 x 8 "b16" ldmatrix tile is 8 keys x 16 bytes; a thread gets 4 consecutive bytes of
+//      key gi, d = 16 ks + 4c .. + 3, which become the two B registers of contraction step ks.
+//      q's A registers are loaded in the same order (qa[ks] = q[16 ks + 4c, +1], q[16 ks + 4c + 2, +3]).
+//   V: the transposing ldmatrix hands a thread bytes (key 2c: d, d + 1 | key 2c + 1: d, d + 1),
+//      d = 2 gi of a 16-byte chunk; the even bytes form the A registers of one product (output
+//      rows d = 32 j + 2 gi and + 16), the odd bytes those of a second (rows + 1).
+// oacc[2 j + par]: rows d = 32 j + 2 gi + par (regs 0, 1) and + 16 (regs 2, 3).
+template <int D>
+__device__ __forceinline__ void stage_step_fp8(WarpAcc<D>& st, const uint32_t (&qa)[D / 16][2], uint32_t k_tile,
+                                               uint32_t v_tile, int vlo, int vhi, float scale_log2_k, float v_scale,
+                                               int lane) {
+  using M = Mma<__half>;
+  const int c = lane & 3;
+  const bool full = vlo == 0 && vhi == 16;
+  float s[2][4], s2[2][4];
+#pragma unroll
+  for (int t = 0; t < 2; ++t) {
+    s[t][0] = s[t][1] = s[t][2] = s[t][3] = 0.f;
+    s2[t][0] = s2[t][1] = s2[t][2] = s2[t][3] = 0.f;
+  }
+#pragma unroll
+  for (int kk = 0; kk < D / 64; ++kk) {
+#pragma unroll
+    for (int t = 0; t < 2; ++t) {
+      uint32_t r[4];
+      ldsm_x4(k_tile + tile_off(8 * t + (lane & 7), 4 * kk + (lane >> 3)), r[0], r[1], r[2], r[3]);
+#pragma unroll
+      for (int q4 = 0; q4 < 4; ++q4) {
+        const int ks = 4 * kk + q4;
+        const uint32_t b0 = e4m3x2_to_f16x2(r[q4] & 0xffffu), b1 = e4m3x2_to_f16x2(r[q4] >> 16);
+        if (q4 & 1) M::run(s2[t], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+        else M::run(s[t], qa[ks][0], 0u, qa[ks][1], 0u, b0, b1);
+      }
+    }
+  }
+  float sv[4];
+#pragma unroll
+  for (int t = 0; t < 2; ++t)
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int key = 8 * t + 2 * c + e;
+      float x = (s[t][e] + s2[t][e]) * scale_log2_k;
+      if (!full && (key < vlo || key >= vhi)) x = -INFINITY;
+      sv[2 * t + e] = x;
+    }
+  float mb = fmaxf(fmaxf(sv[0], sv[1]), fmaxf(sv[2], sv[3]));
+  mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 1));
+  mb = fmaxf(mb, __shfl_xor_sync(0xffffffffu, mb, 2));
+  const float m_new = fmaxf(st.m_run, mb);
+  const float m_use = (m_new == -INFINITY) ? 0.f : m_new;
+  const float alpha = exp2f(st.m_run - m_use);
+  const bool moved = m_new > st.m_run;
+  st.m_run = m_new;
+  float pr[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) pr[e] = exp2f(sv[e] - m_use);
+  if (__any_sync(0xffffffffu, moved)) {
+    const float a0 = __shfl_sync(0xffffffffu, alpha, (2 * c) * 4);
+    const float a1 = __shfl_sync(0xffffffffu, alpha, (2 * c + 1) * 4);
+#pragma unroll
+    for (int i = 0; i < D / 16; ++i) {
+      st.oacc[i][0] *= a0; st.oacc[i][1] *= a1; st.oacc[i][2] *= a0; st.oacc[i][3] *= a1;
+    }
+  }
+  st.l_run = st.l_run * alpha + (pr[0] + pr[1]) + (pr[2] + pr[3]);
+  // the page's V scale rides on the probabilities: O += (p * scale) * v_bytes
+  const uint32_t pb0 = M::pack(pr[0] * v_scale, pr[1] * v_scale);
+  const uint32_t pb1 = M::pack(pr[2] * v_scale, pr[3] * v_scale);
+  uint32_t m01 = 0xffffffffu, m23 = 0xffffffffu;
+  if (!full) {
+    auto ok = [&](int key) { return key >= vlo && key < vhi; };
+    m01 = (ok(2 * c) ? 0x0000ffffu : 0u) | (ok(2 * c + 1) ? 0xffff0000u : 0u);
+    m23 = (ok(2 * c + 8) ? 0x0000ffffu : 0u) | (ok(2 * c + 9) ? 0xffff0000u : 0u);
+  }
+#pragma unroll
+  for (int j = 0; j < D / 32; ++j) {
+    // matrices: (keys 0-7, chunk 2j), (keys 8-15, chunk 2j), (keys 0-7, chunk 2j+1), (keys 8-15, chunk 2j+1)
+    uint32_t v[4];
+    ldsm_x4_t(v_tile + tile_off((lane & 7) + 8 * ((lane >> 3) & 1), 2 * j + (lane >> 4)), v[0], v[1], v[2], v[3]);
+#pragma unroll
+    for (int par = 0; par < 2; ++par) {
+      const uint32_t sel = par ? 0x4431u : 0x4420u;      // bytes (1, 3) or (0, 2) into the low half
+      uint32_t a0 = e4m3x2_to_f16x2(__byte_perm(v[0], 0u, sel));
+      uint32_t a1 = e4m3x2_to_f16x2(__byte_perm(v[2], 0u, sel));
+      uint32_t a2 = e4m3x2_to_f16x2(__byte_perm(v[1], 0u, sel));
+      uint32_t a3 = e4m3x2_to_f16x2(__byte_perm(v[3], 0u, sel));
+      if (!full) { a0 &= m01; a1 &= m01; a2 &= m23; a3 &= m23; }
+      M::run(st.oacc[2 * j + par], a0, a1, a2, a3, pb0, pb1);
+    }
+  }
+}
+
 // Word offset inside one rank's exchange buffer: [parity][source rank][row][slice of 8 columns][8 + 2].
 __device__ __forceinline__ int64_t xword(const StreamParams& p, int D, int par, int src, int row, int slice) {
   return ((((int64_t)par * p.world + src) * ((int64_t)p.B * p.H) + row) * (D / kXCols) + slice) * kXWords;
 }
 
-template <typename T, int D, bool kPaged>
-__global__ void __launch_bounds__(kStreamThreads, StreamCfg<D>::kCtasPerSm)
+template <typename T, int D, bool kPaged, bool kFp8>
+__global__ void __launch_bounds__(kStreamThreads, StreamCfg<D, kFp8>::kCtasPerSm)
 decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
                      StreamParams p) {
-  using Cfg = StreamCfg<D>;
+  using Cfg = StreamCfg<D, kFp8>;
   constexpr int kSt = Cfg::kStages;
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int split = blockIdx.x, g = blockIdx.y, b = blockIdx.z;
@@ -315,6 +421,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
     const int32_t* bt = kPaged ? p.block_tables + b * p.bt_s0 : nullptr;
     const int page_mask = kPaged ? (1 << p.page_shift) - 1 : 0;
     int my_page = 0;
+    float my_ks = 1.f, my_vs = 1.f;
     for (int n = 0; n < n_stages; ++n) {
       const int stg = n % kSt;
       // every decision to leave the loop is taken by the whole warp
@@ -346,9 +453,19 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
           if (bl < blk_hi) {
             const int pg = (lo_al + (bl << 4)) >> p.page_shift;
             my_page = pg < p.max_pages ? bt[pg * p.bt_s1] : -1;
+            if constexpr (kFp8) {
+              if (my_page >= 0 && my_page < p.num_pages) {
+                my_ks = p.k_scales[my_page * p.ks_s0 + g * p.ks_s1];
+                my_vs = p.v_scales[my_page * p.vs_s0 + g * p.vs_s1];
+              }
+            }
           }
         }
         page = __shfl_sync(0xffffffffu, my_page, n & 31);
+        if constexpr (kFp8) {
+          const float ks = __shfl_sync(0xffffffffu, my_ks, n & 31), vs = __shfl_sync(0xffffffffu, my_vs, n & 31);
+          if (lane == 0) ctl->scl[stg] = make_float2(ks, vs);
+        }
         if (page < 0 || page >= p.num_pages) {   // never follow a bad table entry: the stage counts for nothing
           if (lane == 0) atomicCAS(p.status, 0, kErrBadEntry);
           page = 0; vlo = vhi = 0;
@@ -383,7 +500,16 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
     uint32_t qa[D / 16][2];
 #pragma unroll
     for (int ks = 0; ks < D / 16; ++ks) qa[ks][0] = qa[ks][1] = 0u;
-    if (gi < R) {
+    if (kFp8 && gi < R) {
+      // e4m3 pools: q as f16, in the byte order of the K tiles (4 consecutive d per thread and step)
+      const int64_t qoff = b * p.q_s0 + (g * R + gi) * p.q_s1;
+#pragma unroll
+      for (int ks = 0; ks < D / 16; ++ks) {
+        const int64_t e = qoff + 16 * ks + 4 * c;
+        qa[ks][0] = Mma<T>::pack(load_as_float(p.q, e, p.q_dtype), load_as_float(p.q, e + 1, p.q_dtype));
+        qa[ks][1] = Mma<T>::pack(load_as_float(p.q, e + 2, p.q_dtype), load_as_float(p.q, e + 3, p.q_dtype));
+      }
+    } else if (gi < R) {
       const int h = g * R + gi;
       const int64_t qoff = b * p.q_s0 + h * p.q_s1;
       if (p.q_dtype == ElemTraits<T>::kDtype && ((reinterpret_cast<uintptr_t>((const T*)p.q + qoff) & 3) == 0)) {
@@ -436,7 +562,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
       const int4 meta = ctl->meta[stg];
       uint8_t* kt = ring + stg * Cfg::kStageBytes;
       uint8_t* vt = kt + Cfg::kTileBytes;
-      if (pnew >= 0 && pnew - meta.x >= meta.y && pnew - meta.x < meta.z) {
+      if (!kFp8 && pnew >= 0 && pnew - meta.x >= meta.y && pnew - meta.x < meta.z) {
         // the appended token lives in this stage: its K / V rows come from k_new / v_new (into
         // the tile, in place of whatever the cache held) and go to the cache for later steps
         const int rr = pnew - meta.x;
@@ -458,8 +584,14 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
         }
         __syncwarp();
       }
-      if (meta.z > meta.y)
-        stage_step<T, D>(acc, qa, ptx::smem_u32(kt), ptx::smem_u32(vt), meta.y, meta.z, p.scale_log2, lane);
+      if (meta.z > meta.y) {
+        if constexpr (kFp8) {
+          const float2 sc = ctl->scl[stg];
+          stage_step_fp8<D>(acc, qa, ptx::smem_u32(kt), ptx::smem_u32(vt), meta.y, meta.z, p.scale_log2 * sc.x, sc.y, lane);
+        } else {
+          stage_step<T, D>(acc, qa, ptx::smem_u32(kt), ptx::smem_u32(vt), meta.y, meta.z, p.scale_log2, lane);
+        }
+      }
       __syncwarp();
       if (lane == 0) {
         ctl->done[stg] = use + 1;
@@ -479,11 +611,13 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
     float* so = sm_o + warp * 8 * kPitch;
 #pragma unroll
     for (int i = 0; i < D / 16; ++i) {
-      const int d = 16 * i + gi;
+      // rows of accumulator i: 16-bit pools d = 16 i + gi and + 8; e4m3 pools d = 32 (i / 2) + 2 gi + i % 2 and + 16
+      const int d = kFp8 ? 32 * (i >> 1) + 2 * gi + (i & 1) : 16 * i + gi;
+      const int d2 = d + (kFp8 ? 16 : 8);
       so[(2 * c) * kPitch + d] = acc.oacc[i][0];
       so[(2 * c + 1) * kPitch + d] = acc.oacc[i][1];
-      so[(2 * c) * kPitch + d + 8] = acc.oacc[i][2];
-      so[(2 * c + 1) * kPitch + d + 8] = acc.oacc[i][3];
+      so[(2 * c) * kPitch + d2] = acc.oacc[i][2];
+      so[(2 * c + 1) * kPitch + d2] = acc.oacc[i][3];
     }
   }
   __syncthreads();
@@ -690,18 +824,18 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   finish();
 }
 
-template <typename T, int D, bool kPaged>
+template <typename T, int D, bool kPaged, bool kFp8 = false>
 int launch_variant(const CUtensorMap& km, const CUtensorMap& vm, const StreamParams& p, dim3 grid, cudaStream_t st) {
-  using Cfg = StreamCfg<D>;
+  using Cfg = StreamCfg<D, kFp8>;
   constexpr int kSmem = Cfg::kRingBytes + (int)sizeof(Ctl<Cfg::kStages>);
   static bool attr_set[64] = {false};
   int dev = 0;
   G4B_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    G4B_CUDA_CHECK(cudaFuncSetAttribute(decode_stream_kernel<T, D, kPaged>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+    G4B_CUDA_CHECK(cudaFuncSetAttribute(decode_stream_kernel<T, D, kPaged, kFp8>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
     attr_set[dev] = true;
   }
-  decode_stream_kernel<T, D, kPaged><<<grid, kStreamThreads, kSmem, st>>>(km, vm, p);
+  decode_stream_kernel<T, D, kPaged, kFp8><<<grid, kStreamThreads, kSmem, st>>>(km, vm, p);
   G4B_CUDA_CHECK(cudaGetLastError());
   return G4B_OK;
 }
@@ -750,8 +884,10 @@ bool decode_stream_supports(const G4bAttnArgs& a) {
 
 // `step` == nullptr: plain decode (o for one split, partials otherwise).  Otherwise the decode
 // step: merge in the launch, optional append and exchange.
-int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeStepArgs* step, cudaStream_t st) {
+int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeStepArgs* step, cudaStream_t st,
+                         const G4bTensor* k_scales, const G4bTensor* v_scales) {
   const bool paged = a.block_tables.ptr != nullptr;
+  const bool fp8 = k_scales != nullptr;
   const int64_t B = a.q.shape[0], H = a.q.shape[1], D = a.q.shape[3], G = a.k_cache.shape[1];
   StreamParams p{};
   p.q = a.q.ptr; p.o = a.o.ptr;
@@ -779,6 +915,12 @@ int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeSt
     if ((int64_t)p.num_pages * G * a.page_size > 0x7fffffffLL) return fail(G4B_ERR_TOO_LARGE, "decode: page pool beyond 2^31 rows");
   } else {
     p.T = (int)a.k_cache.shape[2];
+  }
+  if (fp8) {
+    if (!paged || step != nullptr) return fail(G4B_ERR_UNSUPPORTED, "e4m3 caches: paged decode only");
+    p.k_scales = (const float*)k_scales->ptr; p.v_scales = (const float*)v_scales->ptr;
+    p.ks_s0 = k_scales->stride[0]; p.ks_s1 = k_scales->stride[1];
+    p.vs_s0 = v_scales->stride[0]; p.vs_s1 = v_scales->stride[1];
   }
   const bool fused = step != nullptr;
   if (fused) {
@@ -835,15 +977,16 @@ int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeSt
   if (B == 0) return G4B_OK;
   CUtensorMap km, vm;
   int rc;
-  const int esz = 2;
-  // A row of D elements is described as D / 64 slabs of 64: dims (element in slab, row, slab,
+  const int esz = fp8 ? 1 : 2;
+  // A row of D elements is described as slabs of 128 bytes: dims (element in slab, row, slab,
   // ...), the slab stride (128 bytes) below the row stride, so that one box holds a whole tile.
-  const uint64_t slabs = (uint64_t)D / 64;
+  const uint64_t per_slab = 128 / esz;
+  const uint64_t slabs = (uint64_t)D / per_slab;
   if (paged) {
     const uint64_t P = (uint64_t)a.k_cache.shape[2], NP = (uint64_t)a.k_cache.shape[0];
-    const uint64_t dims[5] = {64, P, slabs, (uint64_t)G, NP};
-    const uint64_t strides[4] = {(uint64_t)D * esz, 64 * esz, P * D * esz, (uint64_t)G * P * D * esz};
-    const uint32_t box[5] = {64, 16, (uint32_t)slabs, 1, 1};
+    const uint64_t dims[5] = {per_slab, P, slabs, (uint64_t)G, NP};
+    const uint64_t strides[4] = {(uint64_t)D * esz, 128, P * D * esz, (uint64_t)G * P * D * esz};
+    const uint32_t box[5] = {(uint32_t)per_slab, 16, (uint32_t)slabs, 1, 1};
     if ((rc = encode_map(&km, a.k_cache.dtype, 5, a.k_cache.ptr, dims, strides, box, "k pool"))) return rc;
     if ((rc = encode_map(&vm, a.v_cache.dtype, 5, a.v_cache.ptr, dims, strides, box, "v pool"))) return rc;
   } else {
@@ -854,6 +997,14 @@ int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeSt
     if ((rc = encode_map(&vm, a.v_cache.dtype, 4, a.v_cache.ptr, dims, strides, box, "v_cache"))) return rc;
   }
   dim3 grid((unsigned)num_splits, (unsigned)G, (unsigned)B);
+  if (fp8) {
+    switch ((int)D) {
+      case 128: return launch_variant<__half, 128, true, true>(km, vm, p, grid, st);
+      case 256: return launch_variant<__half, 256, true, true>(km, vm, p, grid, st);
+      case 512: return launch_variant<__half, 512, true, true>(km, vm, p, grid, st);
+    }
+    return fail(G4B_ERR_UNSUPPORTED, "decode: head dim %d not supported (128, 256 or 512)", (int)D);
+  }
   if (a.k_cache.dtype == G4B_BF16) return launch_dim<__nv_bfloat16>((int)D, paged, km, vm, p, grid, st);
   if (a.k_cache.dtype == G4B_F16) return launch_dim<__half>((int)D, paged, km, vm, p, grid, st);
   return fail(G4B_ERR_BAD_DTYPE, "decode: KV cache must be f16 or bf16");

@@ -217,6 +217,102 @@ int launch_kv_append(const G4bAppendArgs& a, cudaStream_t st) {
 }
 
 // ---------------------------------------------------------------------------------------
+// append into an e4m3 pool with one scale per (page, kv head)
+// ---------------------------------------------------------------------------------------
+struct Fp8AppendParams {
+  const void* x; uint8_t* cache; float* scales; const void* cache_offsets; const float* x_rsos;
+  const uint8_t* user_phase; const int32_t* block_tables;
+  int64_t xs0, xs1, xs2, rs0, rs1, rs2, ss0, ss1, off_stride, phase_stride, bt_s0, bt_s1;
+  int B, G, Tq, D, page_shift, num_pages, max_pages, phase, x_dtype;
+  bool offsets_are_i64;
+  float eps, headroom;
+  int32_t* status;
+};
+
+__device__ __forceinline__ float ld_any(const void* base, int64_t i, int dt) {
+  if (dt == G4B_F32) return ((const float*)base)[i];
+  if (dt == G4B_F16) return __half2float(((const __half*)base)[i]);
+  return __bfloat162float(((const __nv_bfloat16*)base)[i]);
+}
+
+// One warp per (slot, kv head, token).  The page's scale comes from the page's first row: from
+// x when that row is part of this call (every row of the page then computes the same value;
+// the first row's warp stores it), else from the scale tensor.
+__global__ void __launch_bounds__(32) kv_append_fp8_kernel(Fp8AppendParams p) {
+  const int lane = threadIdx.x;
+  const uint32_t idx = blockIdx.x;
+  const int t = (int)(idx % (uint32_t)p.Tq);
+  const int g = (int)((idx / (uint32_t)p.Tq) % (uint32_t)p.G);
+  const int b = (int)(idx / ((uint32_t)p.Tq * (uint32_t)p.G));
+  if (p.user_phase != nullptr && p.user_phase[b * p.phase_stride] != (uint8_t)p.phase) return;
+  const int64_t off = p.offsets_are_i64 ? ((const int64_t*)p.cache_offsets)[b * p.off_stride]
+                                        : (int64_t)((const int32_t*)p.cache_offsets)[b * p.off_stride];
+  const int64_t pos = off + t;
+  const int page_size = 1 << p.page_shift;
+  const int64_t pg = pos >> p.page_shift;
+  const int row = (int)(pos & (page_size - 1));
+  int page = pg < p.max_pages ? p.block_tables[b * p.bt_s0 + pg * p.bt_s1] : -1;
+  if (page < 0 || page >= p.num_pages) {     // never follow a bad table entry
+    if (lane == 0) atomicCAS(p.status, 0, 0x100 | 3);
+    return;
+  }
+  auto row_scale = [&](int tt) -> float {    // V norm factor of token tt
+    if (p.x_rsos == nullptr) return 1.f;
+    return rsqrtf(p.x_rsos[b * p.rs0 + g * p.rs1 + tt * p.rs2] / (float)p.D + p.eps);
+  };
+  const int64_t xrow = b * p.xs0 + g * p.xs1;
+  const int t0 = t - row;                    // token that is the page's first row (may lie before this call)
+  float scale;
+  if (t0 >= 0) {
+    const float r0 = row_scale(t0);
+    float amax = 0.f;
+    for (int d = lane; d < p.D; d += 32) amax = fmaxf(amax, fabsf(ld_any(p.x, xrow + t0 * p.xs2 + d, p.x_dtype) * r0));
+    for (int o = 16; o > 0; o >>= 1) amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, o));
+    scale = fmaxf(amax * p.headroom / 448.f, 5.9604644775390625e-8f);
+    if (row == 0 && lane == 0) p.scales[page * p.ss0 + g * p.ss1] = scale;
+  } else {
+    scale = p.scales[page * p.ss0 + g * p.ss1];
+  }
+  const float r = row_scale(t);
+  uint8_t* dst = p.cache + ((((int64_t)page * p.G + g) << p.page_shift) + row) * p.D;
+  for (int d = 2 * lane; d < p.D; d += 64) {
+    const float a = ld_any(p.x, xrow + t * p.xs2 + d, p.x_dtype) * r / scale;
+    const float c = d + 1 < p.D ? ld_any(p.x, xrow + t * p.xs2 + d + 1, p.x_dtype) * r / scale : 0.f;
+    uint16_t two;
+    asm("cvt.rn.satfinite.e4m3x2.f32 %0, %1, %2;" : "=h"(two) : "f"(c), "f"(a));   // high byte <- first source
+    dst[d] = (uint8_t)(two & 0xff);
+    if (d + 1 < p.D) dst[d + 1] = (uint8_t)(two >> 8);
+  }
+}
+
+int launch_kv_append_fp8(const G4bFp8AppendArgs& a, cudaStream_t st) {
+  Fp8AppendParams p{};
+  p.x = a.x.ptr; p.cache = (uint8_t*)a.cache.ptr; p.scales = (float*)a.scales.ptr;
+  p.cache_offsets = a.cache_offsets.ptr; p.x_rsos = (const float*)a.x_rsos.ptr;
+  p.user_phase = (const uint8_t*)a.user_phase.ptr; p.block_tables = (const int32_t*)a.block_tables.ptr;
+  p.xs0 = a.x.stride[0]; p.xs1 = a.x.stride[1]; p.xs2 = a.x.stride[2];
+  p.rs0 = a.x_rsos.stride[0]; p.rs1 = a.x_rsos.stride[1]; p.rs2 = a.x_rsos.stride[2];
+  p.ss0 = a.scales.stride[0]; p.ss1 = a.scales.stride[1];
+  p.off_stride = a.cache_offsets.stride[0]; p.phase_stride = a.user_phase.stride[0];
+  p.bt_s0 = a.block_tables.stride[0]; p.bt_s1 = a.block_tables.stride[1];
+  p.B = (int)a.x.shape[0]; p.G = (int)a.x.shape[1]; p.Tq = (int)a.x.shape[2]; p.D = (int)a.x.shape[3];
+  while ((1 << p.page_shift) < a.page_size) ++p.page_shift;
+  p.num_pages = (int)a.cache.shape[0]; p.max_pages = (int)a.block_tables.shape[1];
+  p.phase = a.phase; p.x_dtype = a.x.dtype;
+  p.offsets_are_i64 = a.cache_offsets.dtype == G4B_I64;
+  p.eps = a.rmsnorm_eps; p.headroom = a.headroom;
+  const int64_t blocks = (int64_t)p.B * p.G * p.Tq;
+  if (blocks == 0) return G4B_OK;
+  if (blocks > 0x7fffffffLL) return fail(G4B_ERR_UNSUPPORTED, "kv_append_fp8: too many rows");
+  G4B_STOP_IF_VALIDATE_ONLY();
+  p.status = device_status_ptr();
+  if (p.status == nullptr) return G4B_ERR_CUDA;
+  kv_append_fp8_kernel<<<(unsigned)blocks, 32, 0, st>>>(p);
+  G4B_CUDA_CHECK(cudaGetLastError());
+  return G4B_OK;
+}
+
+// ---------------------------------------------------------------------------------------
 // advance_decode_state
 // ---------------------------------------------------------------------------------------
 __global__ void advance_kernel(int32_t* in_tok, const int32_t* out_tok, int32_t* cache_offsets,

@@ -10,7 +10,7 @@
 
 namespace g4b {
 
-// host: a tiled descriptor over `rank` dims of f16 / bf16 elements (dims and box innermost
+// host: a tiled descriptor over `rank` dims of f16 / bf16 elements, or bytes for any other dtype (dims and box innermost
 // first, strides in bytes for dims 1..rank-1), 128-byte swizzle, no out-of-bounds fill value
 // (out-of-range elements read as zero).  Defined in tensor_map.cu.
 int encode_map(CUtensorMap* map, int dtype, int rank, void* base, const uint64_t* dims,

@@ -1,4 +1,4 @@
-// Tiled TMA descriptors (CUtensorMap) for 2-byte element tensors, 128-byte swizzle: shared by
+// Tiled TMA descriptors (CUtensorMap) for f16 / bf16 / byte tensors, 128-byte swizzle: shared by
 // the prefill and the decode kernels.  The driver entry point is looked up through the
 // runtime, so the library does not link against libcuda.
 #include "common.cuh"
@@ -29,7 +29,9 @@ int encode_map(CUtensorMap* map, int dtype, int rank, void* base, const uint64_t
   cuuint64_t gdim[5]; cuuint64_t gstr[4]; cuuint32_t bx[5]; cuuint32_t es[5];
   for (int i = 0; i < rank; ++i) { gdim[i] = dims[i]; bx[i] = box[i]; es[i] = 1; }
   for (int i = 0; i < rank - 1; ++i) gstr[i] = strides_bytes[i];
-  const CUtensorMapDataType dt = dtype == G4B_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+  const CUtensorMapDataType dt = dtype == G4B_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16
+                                 : dtype == G4B_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                    : CU_TENSOR_MAP_DATA_TYPE_UINT8;   // e4m3 bytes travel as they are
   CUresult r = fn(map, dt, (cuuint32_t)rank, base, gdim, gstr, bx, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
                   CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) return fail(G4B_ERR_CUDA, "cuTensorMapEncodeTiled(%s) failed with CUresult %d", what, (int)r);

@@ -39,3 +39,25 @@ def add_kv_to_cache(
     a.page_size = int(page_size)
     _cabi.check(_cabi.load().g4b_kv_append(ctypes.byref(a), ctypes.c_void_p(_cabi.current_stream(stream))))
     return None
+
+
+def add_kv_to_cache_fp8(x, cache, scales, cache_offsets, rmsnorm_eps, x_rsos=None, user_phase=None, phase=0, *,
+                        block_tables, page_size: int = 16, headroom: float = 2.0, stream=None):
+    """``add_kv_to_cache`` into an 8-bit (e4m3) page pool ``[num_pages,G,page,D]`` with one f32 scale
+    per (page, kv head) in ``scales [num_pages,G]`` (``g4b_kv_append_fp8``).  A page's scale is
+    fixed by its first row: ``max|row| x headroom / 448``; every row of the page is stored as
+    round-to-nearest, saturating e4m3 of ``row / scale``.  No counterpart in the reference."""
+    import ctypes
+
+    a = _cabi.G4bFp8AppendArgs()
+    a.x = _cabi.as_tensor(x)
+    a.cache = _cabi.as_tensor(cache)
+    a.scales = _cabi.as_tensor(scales)
+    a.cache_offsets = _cabi.as_tensor(cache_offsets)
+    a.x_rsos = _cabi.as_tensor(x_rsos)
+    a.user_phase = _cabi.as_tensor(user_phase)
+    a.block_tables = _cabi.as_tensor(block_tables)
+    a.rmsnorm_eps, a.headroom = float(rmsnorm_eps), float(headroom)
+    a.phase, a.page_size = int(phase), int(page_size)
+    _cabi.check(_cabi.load().g4b_kv_append_fp8(ctypes.byref(a), ctypes.c_void_p(_cabi.current_stream(stream))))
+    return None

@@ -148,6 +148,23 @@ def decode_step(q, k_cache, v_cache, o, time_dim_sizes, user_phase, ctx_window_s
     _cabi.check(_cabi.load().g4b_decode_step(ctypes.byref(s), ctypes.c_void_p(_cabi.current_stream(stream))))
 
 
+def flash_attention_fp8(q, k_pool, v_pool, k_scales, v_scales, o, time_dim_sizes, user_phase, ctx_window_size,
+                        phase, partial_o=None, partial_l=None, partial_m=None, *, block_tables, page_size=16,
+                        scale=1.0, sliding_window=None, num_kv_splits=None, stage=STAGE_CAUSAL, stream=None):
+    """Tq == 1 attention over 8-bit (e4m3) page pools ``[num_pages,G,page,D]`` with one f32 scale per
+    (page, kv head), ``k_scales / v_scales [num_pages,G]``: the attention of ``flash_attention`` on the
+    values ``e4m3(byte) x scale`` (``g4b_flash_attention_fp8``).  The reference has no 8-bit
+    cache; pools are filled by ``add_kv_to_cache_fp8``."""
+    if (partial_o is None) != (partial_l is None) or (partial_o is None) != (partial_m is None):
+        raise ValueError("partial_o, partial_l, and partial_m must be provided together")
+    a = _attn_args(q, k_pool, v_pool, o, time_dim_sizes, user_phase, ctx_window_size, phase,
+                   partial_o, partial_l, partial_m, stage, scale, sliding_window, block_tables,
+                   page_size, num_kv_splits)
+    ks, vs = _cabi.as_tensor(k_scales), _cabi.as_tensor(v_scales)
+    _cabi.check(_cabi.load().g4b_flash_attention_fp8(ctypes.byref(a), ctypes.byref(ks), ctypes.byref(vs),
+                                                     ctypes.c_void_p(_cabi.current_stream(stream))))
+
+
 def combine_partials(partial_o, partial_l, partial_m, o, num_splits, *, user_phase=None, phase=0, stream=None):
     """Log-sum-exp merge of ``num_splits`` partials into ``o`` (fa2.py:546-631)."""
     c = _cabi.G4bCombineArgs()

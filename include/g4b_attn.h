@@ -28,7 +28,8 @@ enum G4bDtype {
   G4B_BF16 = 2,
   G4B_I32 = 3,
   G4B_I64 = 4,
-  G4B_U8 = 5
+  G4B_U8 = 5,
+  G4B_FP8_E4M3 = 6 /* one byte per element; caches only (g4b_kv_append_fp8, g4b_flash_attention_fp8) */
 };
 
 /* per-slot phase encoding, g4b/kernels/fa2.py:26-31 */
@@ -214,6 +215,42 @@ typedef struct G4bAdvanceArgs {
   G4bTensor user_phase;      /* uint8 [B] */
 } G4bAdvanceArgs;
 int g4b_advance_decode_state(const G4bAdvanceArgs* args, void* cuda_stream);
+
+/*
+ * KV cache in 8 bits (e4m3), paged.  No counterpart in the reference, whose caches are f16
+ * (g4b/models/gemma4e.py:32,866-870); the arithmetic is the reference's attention on the
+ * de-quantised values.  A pool is [num_pages, G, page_size, D] bytes with one f32 scale per
+ * (page, kv head) beside it, [num_pages, G]: value = e4m3(byte) x scale.
+ *
+ * g4b_kv_append_fp8: as g4b_kv_append in paged mode (same index arithmetic, same optional V
+ * norm and phase gate), then quantised.  The scale of a (page, kv head) is fixed by the FIRST
+ * row of the page, whichever call appends it and however the rows are chunked:
+ *     scale = max(max_d |row[d]| x headroom / 448, 2^-24)
+ * and every row of the page is stored as round-to-nearest-even, saturating e4m3 of
+ * row[d] / scale.  `headroom` (>= 1, e.g. 2) leaves later rows of the page room above the first
+ * row's maximum before they saturate.  A call that appends rows to a page whose first row an
+ * earlier call wrote reads the scale that call left.
+ *
+ * g4b_flash_attention_fp8: Tq == 1 attention over such pools (head dims 128, 256, 512; at most
+ * 8 query heads per kv head), split-KV and merge as g4b_flash_attention.  q / o may be f32, f16
+ * or bf16; products run in f16 with f32 accumulation.
+ */
+typedef struct G4bFp8AppendArgs {
+  G4bTensor x;             /* [B, G, Tq, D] view, last stride 1; f32, f16 or bf16 */
+  G4bTensor cache;         /* pool [num_pages, G, page_size, D], 1 byte per element */
+  G4bTensor scales;        /* f32 [num_pages, G] */
+  G4bTensor cache_offsets; /* [B] int32 or int64 */
+  G4bTensor x_rsos;        /* optional [B, G, Tq] f32 view */
+  G4bTensor user_phase;    /* optional uint8 [B] */
+  G4bTensor block_tables;  /* int32 [B, max_pages] */
+  float rmsnorm_eps;
+  float headroom;
+  int32_t phase;
+  int32_t page_size;
+} G4bFp8AppendArgs;
+int g4b_kv_append_fp8(const G4bFp8AppendArgs* args, void* cuda_stream);
+int g4b_flash_attention_fp8(const G4bAttnArgs* args, const G4bTensor* k_scales, const G4bTensor* v_scales,
+                            void* cuda_stream);
 
 /*
  * Tq == 1 attention with split-KV and merge, for callers that cannot allocate device memory

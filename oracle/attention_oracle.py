@@ -22,6 +22,10 @@ What each function follows:
   advance_decode_state  g4b/kernels/advance_decode_state.py:52-63
   combine_partials      g4b/kernels/fa2.py:618-626
   select_kv_splits      g4b/kernels/fa2.py:201-212
+  add_kv_to_cache_fp8   new (8-bit cache): the append of add_kv_to_cache.py:148-158 followed by the
+                        quantiser stated in include/g4b_attn.h (scale of a page from its first row)
+  dequantise_fp8_pool   new: e4m3(byte) x scale; attention over an 8-bit pool is the attention
+                        above over these values
 """
 from __future__ import annotations
 
@@ -272,3 +276,43 @@ def select_kv_splits(ctx_window_size: int, max_kv_splits: int, phase: int, tq: i
     else:
         target = 16
     return max(1, min(target, max_kv_splits))
+
+
+def add_kv_to_cache_fp8(x, cache_u8, scales, cache_offsets, rmsnorm_eps, x_rsos=None, user_phase=None, phase=0, *,
+                        block_tables, page_size=16, headroom=2.0):
+    """Returns (pool bytes, scales) after the append (copies).  Row p = off[b] + t of slot b goes
+    to page block_tables[b, p // page], row p % page; the page's scale is
+    max(max|first row| * headroom / 448, 2^-24), taken from the page's first row whichever call
+    appends it, and a row is stored as the round-to-nearest-even, saturating e4m3 of row / scale
+    (fp32 arithmetic throughout)."""
+    pool = cache_u8.detach().clone().view(torch.uint8)
+    sc = scales.detach().clone()
+    B, G, Tq, D = x.shape
+    xf = x.detach().to(torch.float32)
+    if x_rsos is not None:
+        xf = xf * (1.0 / torch.sqrt(x_rsos.detach().to(torch.float32) / D + rmsnorm_eps))[..., None]
+    for b in range(B):
+        if user_phase is not None and int(user_phase[b]) != int(phase):
+            continue
+        off = int(cache_offsets[b])
+        for t in range(Tq):
+            pos = off + t
+            page, row = int(block_tables[b, pos // page_size]), pos % page_size
+            t0 = t - row
+            for g in range(G):
+                if t0 >= 0:
+                    amax = xf[b, g, t0].abs().max()
+                    s = torch.maximum(amax * torch.tensor(headroom, dtype=torch.float32) / 448.0,
+                                      torch.tensor(2.0 ** -24, dtype=torch.float32))
+                    if row == 0:
+                        sc[page, g] = s
+                else:
+                    s = sc[page, g]
+                q = torch.clamp(xf[b, g, t] / s, -448.0, 448.0).to(torch.float8_e4m3fn)
+                pool[page, g, row] = q.view(torch.uint8)
+    return pool, sc
+
+
+def dequantise_fp8_pool(pool_u8, scales) -> torch.Tensor:
+    """[num_pages,G,page,D] bytes + [num_pages,G] scales -> fp32 values e4m3(byte) * scale."""
+    return pool_u8.view(torch.float8_e4m3fn).to(torch.float32) * scales.to(torch.float32)[:, :, None, None]

@@ -1,0 +1,126 @@
+"""The 8-bit (e4m3) paged KV cache: the quantising append bit-exact against the CPU restatement
+of the quantiser, and Tq == 1 attention over the 8-bit pools against the oracle's attention on
+the de-quantised values, at the tolerance of every other parity test."""
+import random
+
+import pytest
+import torch
+
+from g4b_b200.kernels import fa2
+from g4b_b200.kernels.add_kv_to_cache import add_kv_to_cache_fp8
+from helpers import assert_close, orc, randn
+
+pytestmark = pytest.mark.gpu
+
+
+def _tables(gen, lens, page, extra=2):
+    pages_per = [(n + page - 1) // page for n in lens]
+    num_pages = sum(pages_per) + extra
+    perm = torch.randperm(num_pages, generator=gen)
+    bt = torch.full((len(lens), max(pages_per)), -1, dtype=torch.int32)
+    at = 0
+    for b, n in enumerate(pages_per):
+        bt[b, :n] = perm[at:at + n].to(torch.int32)
+        at += n
+    return bt, num_pages
+
+
+@pytest.mark.parametrize("in_dtype", [torch.float32, torch.bfloat16])
+@pytest.mark.parametrize("D,page", [(256, 16), (128, 32), (512, 16)])
+def test_append_quantises_bit_exactly_however_the_rows_are_chunked(cuda, in_dtype, D, page):
+    gen = torch.Generator().manual_seed(D + page)
+    B, G = 3, 2
+    lens = [3 * page + 5, page, 2 * page + 1]
+    bt, num_pages = _tables(gen, lens, page)
+    x = [randn(gen, 1, G, n, D, dtype=in_dtype) * (0.2 + b) for b, n in enumerate(lens)]
+    # oracle: every sequence in one go
+    want_pool = torch.zeros(num_pages, G, page, D, dtype=torch.uint8)
+    want_sc = torch.zeros(num_pages, G)
+    for b, n in enumerate(lens):
+        want_pool, want_sc = orc.add_kv_to_cache_fp8(x[b], want_pool, want_sc, torch.tensor([0]), 1e-6,
+                                                     block_tables=bt[b:b + 1], page_size=page)
+    # GPU: a first chunk of 1.5 pages for all slots at once (padded batch), then the rest row by row
+    pool = torch.zeros(num_pages, G, page, D, dtype=torch.uint8, device=cuda)
+    sc = torch.zeros(num_pages, G, device=cuda)
+    btd = bt.to(cuda)
+    first = page + page // 2
+    for b, n in enumerate(lens):
+        c = min(first, n)
+        add_kv_to_cache_fp8(x[b][:, :, :c].to(cuda), pool, sc, torch.tensor([0], dtype=torch.int32, device=cuda), 1e-6,
+                            block_tables=btd[b:b + 1], page_size=page)
+        for t in range(c, n, 7):
+            e = min(n, t + 7)
+            add_kv_to_cache_fp8(x[b][:, :, t:e].to(cuda), pool, sc, torch.tensor([t], dtype=torch.int64, device=cuda), 1e-6,
+                                block_tables=btd[b:b + 1], page_size=page)
+    assert torch.equal(sc.cpu(), want_sc), "page scales differ"
+    assert torch.equal(pool.cpu(), want_pool), "stored bytes differ"
+
+
+def test_append_with_v_norm_and_phase_gate(cuda):
+    gen = torch.Generator().manual_seed(5)
+    B, G, D, page, Tq = 2, 2, 256, 16, 16
+    bt, num_pages = _tables(gen, [Tq, Tq], page)
+    x = randn(gen, B, G, Tq, D)
+    rsos = (x ** 2).sum(-1)
+    phase = torch.tensor([1, 2], dtype=torch.uint8)
+    off = torch.zeros(B, dtype=torch.int32)
+    want_pool, want_sc = orc.add_kv_to_cache_fp8(x, torch.zeros(num_pages, G, page, D, dtype=torch.uint8),
+                                                 torch.zeros(num_pages, G), off, 1e-6, rsos, phase, 2, block_tables=bt,
+                                                 page_size=page)
+    pool = torch.zeros(num_pages, G, page, D, dtype=torch.uint8, device=cuda)
+    sc = torch.zeros(num_pages, G, device=cuda)
+    add_kv_to_cache_fp8(x.to(cuda), pool, sc, off.to(cuda), 1e-6, rsos.to(cuda), phase.to(cuda), 2, block_tables=bt.to(cuda),
+                        page_size=page)
+    # the norm's rsqrt is an approximation on both sides: scales agree to a few ulp, values to one e4m3 step
+    assert torch.allclose(sc.cpu(), want_sc, rtol=1e-6, atol=0)
+    got, want = orc.dequantise_fp8_pool(pool.cpu(), sc.cpu()), orc.dequantise_fp8_pool(want_pool, want_sc)
+    assert bool(((got - want).abs() <= 0.125 * want.abs() + 1e-6).all())
+    assert float(((got != want).float().mean())) < 1e-3
+    assert float(pool.cpu()[bt[0, 0].long()].float().abs().sum()) == 0, "the off-phase slot's page was written"
+
+
+@pytest.mark.parametrize("seed", range(10))
+def test_attention_over_fp8_pools(cuda, seed):
+    rng = random.Random(9100 + seed)
+    D = rng.choice([128, 256, 256, 512])
+    H, G = rng.choice([(8, 2), (4, 4), (16, 4), (16, 2)])
+    page = rng.choice([16, 32])
+    B = rng.randint(1, 4)
+    lens = [rng.choice([1, page, page + 1, rng.randint(1, 2500)]) for _ in range(B)]
+    gen = torch.Generator().manual_seed(seed)
+    bt, num_pages = _tables(gen, lens, page)
+    # pools filled by the quantising append (so scales and bytes are what a serving loop would hold)
+    kp = torch.zeros(num_pages, G, page, D, dtype=torch.uint8)
+    vp = torch.zeros_like(kp)
+    ks, vs = torch.zeros(num_pages, G), torch.zeros(num_pages, G)
+    for b, n in enumerate(lens):
+        kx, vx = randn(gen, 1, G, n, D), randn(gen, 1, G, n, D)
+        kp, ks = orc.add_kv_to_cache_fp8(kx, kp, ks, torch.tensor([0]), 1e-6, block_tables=bt[b:b + 1], page_size=page)
+        vp, vs = orc.add_kv_to_cache_fp8(vx, vp, vs, torch.tensor([0]), 1e-6, block_tables=bt[b:b + 1], page_size=page)
+    # unused rows of the last pages hold NaN bytes: they must never be multiplied in
+    for b, n in enumerate(lens):
+        if n % page:
+            last = int(bt[b, (n - 1) // page])
+            kp[last, :, n % page:] = 0x7f
+            vp[last, :, n % page:] = 0xff
+    q_dtype = rng.choice([torch.float16, torch.bfloat16, torch.float32])
+    q = randn(gen, B, H, 1, D, dtype=q_dtype)
+    time = torch.tensor(lens, dtype=torch.int32)
+    cw = bt.shape[1] * page
+    sw = rng.choice([None, None, rng.randint(1, 300)])
+    S = rng.choice([1, 3, 8])
+    ph = torch.tensor([rng.choice([2, 2, 0]) for _ in range(B)], dtype=torch.uint8)
+    o0 = torch.full((B, H, 1, D), 1.5)
+    kd, vd = orc.dequantise_fp8_pool(kp, ks), orc.dequantise_fp8_pool(vp, vs)
+    kd, vd = torch.nan_to_num(kd), torch.nan_to_num(vd)           # only rows past the contexts
+    # q reaches the tensor cores as f16
+    want = orc.flash_attention(q.to(torch.float16), kd, vd, o0, time, ph, cw, 2, scale=1 / 16, sliding_window=sw,
+                               block_tables=bt, page_size=page)
+    o = o0.to(torch.float16).to(cuda)
+    parts = ()
+    if S > 1:
+        parts = (torch.empty(S, B, H, 1, D, device=cuda), torch.empty(S, B, H, 1, device=cuda), torch.empty(S, B, H, 1, device=cuda))
+    fa2.flash_attention_fp8(q.to(cuda), kp.to(cuda), vp.to(cuda), ks.to(cuda), vs.to(cuda), o, time.to(cuda), ph.to(cuda), cw,
+                            fa2.PHASE_DECODE, *parts, block_tables=bt.to(cuda), page_size=page, scale=1 / 16,
+                            sliding_window=sw, num_kv_splits=S if S > 1 else None)
+    assert_close(o, want, f"seed {seed}: D{D} H{H} G{G} page{page} lens{lens} S{S} sw{sw}")
