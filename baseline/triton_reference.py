@@ -24,7 +24,9 @@ prints one JSON line: per case the time per launch, TFLOP/s or GB/s, the block s
 reference picked, the parity of its output against the CPU oracle on sampled rows, and the
 time of this library's flash_attention on the very same tensors.
 Without --tuned the reference's G4B_SKIP_TUNING=1 mode is used (its hand-picked production
-configurations, fa2.py:152-158); with --tuned its whole autotune space is searched first.
+configurations, fa2.py:152-158); with --tuned its whole autotune space is searched first;
+--force M,N,SPLITS,WARPS,STAGES pins one configuration through the reference's own
+G4B_FA_FORCE_CONFIG switch (fa2.py:147-149), for tile shapes its autotuner would have to find.
 """
 from __future__ import annotations
 
@@ -50,9 +52,14 @@ def available() -> bool:
     return (REF / "g4b" / "kernels" / "fa2.py").exists()
 
 
-def load_reference_fa2(skip_tuning: bool = True):
+def load_reference_fa2(skip_tuning: bool = True, force: str | None = None):
     """Imports baseline/_ref/g4b/kernels/fa2.py with the stand-ins described above."""
     import torch
+
+    if force:
+        os.environ["G4B_FA_FORCE_CONFIG"] = force
+    else:
+        os.environ.pop("G4B_FA_FORCE_CONFIG", None)
 
     if not available():
         raise RuntimeError("baseline/_ref is empty: run `python oracle/make_ref.py` where the reference checkout is")
@@ -213,7 +220,7 @@ def run_case(fa2, name: str, dev, reps: int):
                                           "parity_vs_oracle": parity_ours, "speedup": round(ms / ms_ours, 2)}}
 
 
-def run(cases, tuned: bool, reps: int = 5):
+def run(cases, tuned: bool, reps: int = 5, force: str | None = None):
     """Returns {"skip_tuning": ..., "cases": [...]} or {"unavailable": reason}."""
     import torch
 
@@ -222,11 +229,11 @@ def run(cases, tuned: bool, reps: int = 5):
     try:
         import triton
 
-        fa2 = load_reference_fa2(skip_tuning=not tuned)
+        fa2 = load_reference_fa2(skip_tuning=not tuned, force=force)
     except Exception as exc:
         return {"unavailable": f"import of the reference kernel failed: {type(exc).__name__}: {str(exc)[:300]}"}
     dev = torch.device("cuda", torch.cuda.current_device())
-    out = {"triton": triton.__version__, "skip_tuning": not tuned, "cases": []}
+    out = {"triton": triton.__version__, "skip_tuning": not tuned, "forced_config": force, "cases": []}
     for name in cases:
         try:
             out["cases"].append(run_case(fa2, name, dev, reps))
@@ -242,8 +249,9 @@ def main():
     ap.add_argument("--tuned", action="store_true", help="search the reference's whole autotune space first")
     ap.add_argument("--case", action="append", choices=["prefill_causal", "decode_ring"])
     ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--force", help="Q_BLOCKSIZE_T,KV_BLOCKSIZE_T,NUM_KV_SPLITS,num_warps,num_stages")
     args = ap.parse_args()
-    print(json.dumps(run(args.case or ["prefill_causal", "decode_ring"], args.tuned, args.reps)))
+    print(json.dumps(run(args.case or ["prefill_causal", "decode_ring"], args.tuned, args.reps, args.force)))
 
 
 if __name__ == "__main__":
