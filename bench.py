@@ -946,10 +946,36 @@ def run_block(name, dev, rank, world, peaks, args, steps, warmup, *, strong, cpu
         ms2, _, _ = measure(wl, steps, warmup, world, dev, False)
         out["nccl_all_gather_form_ms_per_step"] = round(ms2, 5)
     if cpu and rank == 0 and not args.no_cpu:
-        v, sample = wl.cpu_sample()
-        out["cpu_baseline"] = {"value": round(v, 5), "unit": wl.unit, "cores": torch.get_num_threads(),
-                               "kind": "port", "sample": sample}
+        out["cpu_baseline"] = cpu_baseline_of(wl, world, args.no_cpu)
     return out
+
+
+def cpu_leg_in_child(argv):
+    """Under torchrun every rank starts with OMP_NUM_THREADS=1 and its BLAS initialised for one
+    thread; raising the count afterwards oversubscribes instead of helping.  So a rank that wants
+    a CPU leg with all cores runs it in a fresh interpreter without the launcher's variables and
+    reads the JSON line that prints."""
+    import subprocess
+
+    env = {k: v for k, v in os.environ.items()
+           if not (k.startswith(("OMP_", "MKL_", "TORCHELASTIC", "GROUP_", "ROLE_")) or k in (
+               "RANK", "LOCAL_RANK", "WORLD_SIZE", "LOCAL_WORLD_SIZE", "MASTER_ADDR", "MASTER_PORT"))}
+    res = subprocess.run([sys.executable, str(ROOT / "bench.py"), *argv], env=env, capture_output=True, text=True, timeout=900)
+    lines = [ln for ln in res.stdout.strip().splitlines() if ln.startswith("{")]
+    if res.returncode != 0 or not lines:
+        return {"unavailable": f"CPU leg exited {res.returncode}: {res.stderr.strip()[-200:]}"}
+    return json.loads(lines[-1])
+
+
+def cpu_baseline_of(wl, world, no_cpu):
+    """The workload's CPU baseline block: in this process on one GPU, in a child under torchrun."""
+    if no_cpu:
+        return None
+    if world == 1:
+        v, sample = wl.cpu_sample()
+        return {"value": round(v, 5), "unit": wl.unit, "cores": torch.get_num_threads(), "kind": "port", "sample": sample}
+    line = cpu_leg_in_child(["--impl", "reference", "--port", "--workload", wl.name, "--steps", "2", "--warmup", "3"])
+    return line.get("cpu_baseline", line)
 
 
 def cpu_config1():
@@ -1071,15 +1097,10 @@ def run_ours(args):
                             "value": round(v2, 3), "unit": wl.unit, "clocks": c2,
                             "ms_x_mhz": (round(ms_s * c2["sm_mhz"], 1) if c2 and c2["sm_mhz"] else None),
                             "roofline": roofline_of(wl, v2, world, peaks, sustained=True)}
-    # the CPU legs get every core this process started with, not only those near the GPU (and
-    # not the single thread that torchrun's OMP_NUM_THREADS=1 leaves a rank with)
+    # the CPU legs get every core this process started with, not only those near the GPU
     os.sched_setaffinity(0, host.pop("affinity_before"))
-    if rank == 0:
-        torch.set_num_threads(len(os.sched_getaffinity(0)))
     if rank == 0 and not args.no_cpu:
-        v, sample = wl.cpu_sample()
-        out["cpu_baseline"] = {"value": round(v, 5), "unit": wl.unit, "cores": torch.get_num_threads(),
-                               "kind": "port", "sample": sample}
+        out["cpu_baseline"] = cpu_baseline_of(wl, world, args.no_cpu)
     if headline:
         # the other configurations of the metric, each with its own oracle check
         del wl, run_step
@@ -1095,7 +1116,7 @@ def run_ours(args):
         if status != 0:
             raise SystemExit(f"device status word {status:#x} after the extra blocks")
         if rank == 0 and not args.no_cpu:
-            out["cpu_config1"] = cpu_config1()
+            out["cpu_config1"] = cpu_config1() if world == 1 else cpu_leg_in_child(["--cpu-config1"])
         if rank == 0 and not args.no_triton:
             try:
                 from baseline import triton_reference
@@ -1287,8 +1308,13 @@ def main():
     ap.add_argument("--no-triton", action="store_true", help="default line: skip the reference's Triton kernel")
     ap.add_argument("--sustained", action="store_true", help="add the two-second replay to a single-workload line")
     ap.add_argument("--port", action="store_true", help="--impl reference: time the oracle port even where the reference's own torch code is present")
+    ap.add_argument("--cpu-config1", action="store_true", help="only time configuration 1 on the host cores and print it")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
+    if args.cpu_config1:
+        torch.set_num_threads(os.cpu_count() or 1)
+        print(json.dumps(cpu_config1()))
+        return
     if args.impl == "reference":
         run_reference(args)
     else:
