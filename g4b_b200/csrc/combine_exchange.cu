@@ -19,7 +19,8 @@
 // per piece against 5 us for the same merge without peers).
 //
 // Blocks wait only for blocks of OTHER GPUs (same index there), never for blocks of their own
-// grid, so nothing depends on co-residency of the grid.  Every wait is bounded; on a timeout
+// grid.  (With more blocks than a GPU holds at once, a block can only be served if the peer
+// gets to the same block; shapes that large may end in the time-out code below.)  Every wait is bounded; on a timeout
 // the block records a code in the device status word and gives up.  Buffers are double
 // buffered by launch parity: a peer can be at most one launch ahead, because its next launch
 // cannot finish without this GPU's next contribution; a word of the same parity therefore

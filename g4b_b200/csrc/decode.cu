@@ -1,6 +1,7 @@
-// Single-token decode attention: streams the K/V of one (slot, kv head, split) through
-// registers exactly once and writes either the normalised output or un-normalised split
-// partials.
+// Single-token decode attention, register-streaming form: the K/V of one (slot, kv head,
+// split) go global -> registers exactly once.  The TMA-fed kernel in decode_stream.cu has
+// replaced it wherever its 16-row boxes fit; this one remains for ring caches shorter than
+// 16 rows (head dim 256).
 //
 // Replaces _attn_kernel (g4b/kernels/fa2.py:256-480) for Tq == 1, in the reference's ring
 // layout (fa2.py:52-55,75) and in the paged layout (16-token pages behind a block table).

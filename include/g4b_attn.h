@@ -332,7 +332,13 @@ int g4b_rope_norm_append(const G4bRopeAppendArgs* args, void* cuda_stream);
  * memory; others: peer mappings), 8-byte aligned.  Size per rank from
  * g4b_exchange_buffer_bytes(); it must start zeroed and be used for nothing else.  state:
  * two zero-initialised uint32 in local memory.  A peer that does not show up within about a
- * second leaves code 0x401 in the device status word.
+ * second leaves code 0x401 in the device status word; after that the buffers and `state` must
+ * be zeroed again on every rank (and the ranks brought back in step) before the next call: a
+ * rank that gave up may otherwise run ahead and overwrite words of the same parity that a peer
+ * has not read.  Block (row, slice) of this launch waits for the same block of every peer; with
+ * more blocks (rows x ceil(D / 32)) than one GPU holds at once this relies on every GPU getting
+ * to the same blocks, which CUDA does not promise -- such shapes can end in 0x401 too.
+ * g4b_decode_step's exchange form checks residency on the host instead.
  */
 typedef struct G4bExchangeArgs {
   G4bTensor partial_o;     /* local [S, B, H, Tq, D] f32/f16/bf16 */
