@@ -57,9 +57,11 @@ __device__ uint32_t g_step_sync[2];
 template <int D, bool kFp8 = false> struct StreamCfg {
   static constexpr int kTileBytes = 16 * D * (kFp8 ? 1 : 2);   // 16 keys of K, or of V
   static constexpr int kStageBytes = 2 * kTileBytes;
-  static constexpr int kStages = kFp8 ? (D == 512 ? 6 : 12) : (D == 128 ? 8 : 6);   // 64 / 96 / 192 KB in flight per CTA (16-bit)
+  // 16-bit pools: 64 / 96 / 192 KB in flight per CTA.  e4m3 pools at head dim <= 256: three CTAs
+  // per SM (nine consumer warps: at half the bytes per key the tensor work, not HBM, sets the pace)
+  static constexpr int kStages = kFp8 ? (D == 512 ? 6 : 8) : (D == 128 ? 8 : 6);
   static constexpr int kRingBytes = kStages * kStageBytes;
-  static constexpr int kCtasPerSm = (D >= 512 && !kFp8) ? 1 : 2;
+  static constexpr int kCtasPerSm = kFp8 ? (D >= 512 ? 2 : 3) : (D >= 512 ? 1 : 2);
 };
 
 struct StreamParams {
