@@ -1,33 +1,37 @@
 // Single-token decode attention as a TMA-fed stream: K/V tiles go HBM -> shared memory through
 // a ring of mbarrier-guarded stages that one producer warp keeps full, independent of the
-// registers of the warps that compute; optionally the whole decode step -- append of the new
-// token's K/V rows, attention, merge of the splits, exchange with peer GPUs -- is this one
-// launch.
+// registers of the warps that compute.  The same launch can append the new token's K/V rows
+// and, when one sequence's KV range is split over GPUs, merge the splits and exchange the
+// merged partials with the peers.
 //
-// Replaces _attn_kernel (g4b/kernels/fa2.py:256-480) for Tq == 1 and, in the fused form,
-// _reduce_split_kv_kernel (fa2.py:546-631) and the two add_kv_to_cache launches before it
-// (g4b/models/gemma4e.py:575-592), in the reference's ring layout (fa2.py:52-55,75) and in
-// the paged layout.
+// Replaces _attn_kernel (g4b/kernels/fa2.py:256-480) for Tq == 1 and, in the decode step,
+// the two add_kv_to_cache launches before it (g4b/models/gemma4e.py:575-592) and (exchange
+// form) _reduce_split_kv_kernel (fa2.py:546-631), in the reference's ring layout
+// (fa2.py:52-55,75) and in the paged layout.  Head dims 128, 256, 512; f16 / bf16 caches, or
+// e4m3 pages with a scale per (page, kv head).
 //
 // A CTA = one (slot b, kv head g, split s): 3 consumer warps + 1 producer warp.
 //   producer   walks the split's 16-key blocks; per block one stage = a K tile and a V tile
-//              [16 keys x D], fetched as 128-byte-swizzled TMA boxes of 16 rows x 64 elements
-//              (one (page, kv head) run in paged mode; ring rows in ring mode, the block that
-//              crosses the end of the ring as two stages whose boxes start past the end /
-//              before row 0 and read zeros there).  Every stage carries its key range, so
-//              partial blocks (window edges, the ring's wrap, a bad table entry) are masked
+//              [16 keys x D], each ONE 128-byte-swizzled TMA box: the descriptor describes a
+//              row as slabs of 128 bytes (a slab dimension whose stride lies below the row
+//              stride), so [128 bytes x 16 rows x slabs] lands slab-major, the layout ldmatrix
+//              reads without bank conflicts.  Paged: a box is one (page, kv head) run.  Ring:
+//              the block that crosses the end of the ring becomes two stages whose boxes start
+//              past the end / before row 0 and read zeros there.  Every stage carries its key
+//              range, so partial blocks (window edges, the wrap, a bad table entry) are masked
 //              by the consumer, never computed with.
 //   consumers  take the stages in order, whichever warp is free next (a shared counter), so
 //              all stages of the ring are in flight or in work whatever the warps' pace;
-//              S = Q K^T and O^T = V^T P^T with warp-level
-//              m16n8k16 instructions whose K / V operand fragments come out of the swizzled
-//              tiles by ldmatrix (V transposed on the way); base-2 online softmax per head;
-//              all (<= 8) query heads of the kv head share every byte.
+//              S = Q K^T and O^T = V^T P^T with warp-level m16n8k16 instructions whose K / V
+//              operand fragments come out of the swizzled tiles by ldmatrix (V transposed on
+//              the way); base-2 online softmax per head; all (<= 8) query heads of the kv head
+//              share every byte.  The warp that meets the stage of the new token's position
+//              overwrites that row of its tiles with k_new / v_new and stores them to the cache.
 // The 3 warps merge through shared memory; the CTA writes o (one split) or the (acc, l, m)
-// partial of fa2.py:438-472.
+// partial of fa2.py:438-472, which a merge launch (combine.cu) picks up.
 //
-// Exchange form (world > 1: one sequence's KV range split over GPUs; every CTA of the launch is
-// resident at once, which the launcher checks).  After its partial is written a CTA arrives at a
+// Exchange form (one sequence's KV range split over GPUs; every CTA of the launch is resident
+// at once, which the launcher checks).  After its partial is written a CTA arrives at a
 // grid-wide count.  The first D / 8 CTAs of every (slot, kv head) then each own 8 columns of the
 // head dim: they wait (bounded) for the count, merge all local partials for their columns,
 // push the merged piece to every GPU as self-announcing 8-byte words {value, launch count}, poll

@@ -200,7 +200,7 @@ def _peer_words(exchange_buf, world, rank_rows, D, epoch, src, row0, acc, l, m):
     words[epoch & 1, src, row0:row0 + R] = (bits | (int(epoch) << 32)).to(words.device)
 
 
-@pytest.mark.parametrize("world,rank", [(2, 0), (2, 1), (4, 2)])
+@pytest.mark.parametrize("world,rank", [(2, 0), (2, 1), (4, 2), (8, 5)])
 def test_decode_step_exchange_with_played_peers(cuda, world, rank):
     """One sequence split over `world` ranks; this GPU is `rank` and holds its share of the
     pages, the other ranks' merged partials (computed by the oracle) are already in its exchange

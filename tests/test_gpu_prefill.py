@@ -351,3 +351,29 @@ def test_prefill_ignores_f16_partials(cuda):
     with pytest.raises(ValueError):
         fa2.flash_attention(q_phys.permute(0, 2, 1, 3), k, v, o.permute(0, 2, 1, 3), time, None, 2048, 1, po, pl, pm,
                             scale=1 / 16, num_kv_splits=4)
+
+
+def test_sliding_window_unit_of_a_query_range_split(cuda):
+    """The unit a rank gets when the query range of a (request, kv head) pair is halved over
+    GPUs (g4b_b200.dist.shard_prefill_units at 8 GPUs on the sliding-window benchmark): 4 query
+    heads, 1 kv head, the second half of 32768 queries over its own keys plus the 511 before it
+    (16895 keys, not a multiple of the tile).  Sampled rows against the oracle."""
+    from g4b_b200.dist import shard_prefill_units
+
+    (r, g, q_lo, q_hi, k_lo), = shard_prefill_units(2, 2, 32768, 8, 1, 512)
+    assert (q_lo, q_hi, k_lo) == (16384, 32768, 16384 - 511)
+    Tq, Tk, H, D, W = q_hi - q_lo, q_hi - k_lo, 4, 256, 512
+    gen = torch.Generator(device=cuda).manual_seed(12)
+    q = torch.randn(1, Tq, H, D, generator=gen, device=cuda).to(torch.bfloat16)
+    k = torch.randn(1, 1, Tk, D, generator=gen, device=cuda).to(torch.bfloat16)
+    v = torch.randn(1, 1, Tk, D, generator=gen, device=cuda).to(torch.bfloat16)
+    o = torch.zeros_like(q)
+    time = torch.tensor([Tk], dtype=torch.int32, device=cuda)
+    fa2.flash_attention(q.permute(0, 2, 1, 3), k, v, o.permute(0, 2, 1, 3), time, None, Tk, fa2.PHASE_PREFILL,
+                        scale=1 / 16, sliding_window=W)
+    kc, vc = k[0].float().cpu(), v[0].float().cpu()
+    for row in (0, 1, 127, 128, 511, 512, 8191, Tq - 2, Tq - 1):
+        pos = Tk - Tq + row
+        want = orc.attention_core(q[0, row:row + 1].permute(1, 0, 2).float().cpu(), kc[:, :pos + 1], vc[:, :pos + 1],
+                                  scale=1 / 16, sliding_window=W)
+        assert_close(o[0, row:row + 1].permute(1, 0, 2), want, f"row {row}")
