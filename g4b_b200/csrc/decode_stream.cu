@@ -37,6 +37,8 @@
 // push the merged piece to every GPU as self-announcing 8-byte words {value, launch count}, poll
 // (bounded) their own buffer for the peers' pieces and finish the merge -- the word format of
 // combine_exchange.cu, in the same launch as the attention.
+#include <type_traits>
+
 #include "common.cuh"
 #include "mma16816.cuh"
 #include "sm100_ptx.cuh"
@@ -426,6 +428,9 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
     // =============================== producer ===============================
     const int32_t* bt = kPaged ? p.block_tables + b * p.bt_s0 : nullptr;
     const int page_mask = kPaged ? (1 << p.page_shift) - 1 : 0;
+    // K / V rows are read once: they leave L2 first, so that the block tables, the partials and
+    // the kernel's own instructions stay there while hundreds of megabytes stream through
+    const uint64_t pol_stream = ptx::policy_evict_first();
     int my_page = 0;
     float my_ks = 1.f, my_vs = 1.f;
     for (int n = 0; n < n_stages; ++n) {
@@ -495,8 +500,8 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
       if (lane < 2) {
         const uint32_t dst = ptx::smem_u32(ring + stg * Cfg::kStageBytes) + (lane ? Cfg::kTileBytes : 0);
         const CUtensorMap* map = lane ? &v_map : &k_map;
-        if constexpr (kPaged) ptx::tma_load_5d(dst, map, bar, 0, j0 & page_mask, 0, g, page);
-        else ptx::tma_load_4d(dst, map, bar, 0, row0, 0, b * p.G + g);
+        if constexpr (kPaged) ptx::tma_load_5d_hint(dst, map, bar, 0, j0 & page_mask, 0, g, page, pol_stream);
+        else ptx::tma_load_4d_hint(dst, map, bar, 0, row0, 0, b * p.G + g, pol_stream);
       }
       __syncwarp();
     }
@@ -629,30 +634,74 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   __syncthreads();
 
   const bool exchange = p.sync != nullptr;
-  for (int idx = tid; idx < R * D; idx += kStreamThreads) {
-    const int hh = idx / D, d = idx - hh * D;
-    float m = -INFINITY;
+  // The warps' accumulators become the split's partial (or, with one split and no exchange,
+  // the output row).  Every load of an iteration is asked for before the first use and nothing
+  // branches: at two warps per scheduler a chain of dependent shared-memory loads is what this
+  // costs.  V columns per thread: as wide as the partial buffer's alignment lets one store be.
+  const bool to_o = p.num_splits == 1 && !exchange;
+  auto merge_warps = [&](auto vc) {
+    constexpr int V = decltype(vc)::value;
+    for (int idx = tid; idx < R * (D / V); idx += kStreamThreads) {
+      const int hh = idx / (D / V), d = V * (idx - hh * (D / V));
+      float mw[kConsumers], lw[kConsumers], x[kConsumers][V];
 #pragma unroll
-    for (int w = 0; w < kConsumers; ++w) m = fmaxf(m, ctl->sm_m[w][hh]);
-    float a = 0.f, l = 0.f;
+      for (int w = 0; w < kConsumers; ++w) {
+        mw[w] = ctl->sm_m[w][hh];
+        lw[w] = ctl->sm_l[w][hh];
+        const float* src = sm_o + (w * 8 + hh) * kPitch + d;
+        if constexpr (V == 4) {
+          const float4 t = *reinterpret_cast<const float4*>(src);
+          x[w][0] = t.x; x[w][1] = t.y; x[w][2] = t.z; x[w][3] = t.w;
+        } else if constexpr (V == 2) {
+          const float2 t = *reinterpret_cast<const float2*>(src);
+          x[w][0] = t.x; x[w][1] = t.y;
+        } else {
+          x[w][0] = src[0];
+        }
+      }
+      float m = mw[0];
 #pragma unroll
-    for (int w = 0; w < kConsumers; ++w) {
-      const float mw = ctl->sm_m[w][hh];
-      if (mw == -INFINITY) continue;
-      const float sc = exp2f(mw - m);
-      a += sm_o[(w * 8 + hh) * kPitch + d] * sc;
-      l += ctl->sm_l[w][hh] * sc;
-    }
-    const int h = g * R + hh;
-    if (p.num_splits == 1 && !exchange) {
-      store_from_float(p.o, b * p.o_s0 + h * p.o_s1 + d, p.o_dtype, l > 0.f ? a / l : 0.f);
-    } else {
-      store_from_float(p.po, split * p.po_s0 + b * p.po_s1 + h * p.po_s2 + d, p.po_dtype, a);
+      for (int w = 1; w < kConsumers; ++w) m = fmaxf(m, mw[w]);
+      float a[V], l = 0.f;
+#pragma unroll
+      for (int v = 0; v < V; ++v) a[v] = 0.f;
+#pragma unroll
+      for (int w = 0; w < kConsumers; ++w) {
+        const float sc = mw[w] == -INFINITY ? 0.f : exp2f(mw[w] - m);   // (a warp that saw no key holds zeros)
+        l += lw[w] * sc;
+#pragma unroll
+        for (int v = 0; v < V; ++v) a[v] += x[w][v] * sc;
+      }
+      const int h = g * R + hh;
+      if (to_o) {
+#pragma unroll
+        for (int v = 0; v < V; ++v)
+          store_from_float(p.o, b * p.o_s0 + h * p.o_s1 + d + v, p.o_dtype, l > 0.f ? a[v] / l : 0.f);
+        continue;
+      }
+      const int64_t off = split * p.po_s0 + b * p.po_s1 + h * p.po_s2 + d;
+      if (p.po_dtype == G4B_F32) {
+        float* dst = (float*)p.po + off;
+        if constexpr (V == 4) *reinterpret_cast<float4*>(dst) = make_float4(a[0], a[1], a[2], a[3]);
+        else if constexpr (V == 2) *reinterpret_cast<float2*>(dst) = make_float2(a[0], a[1]);
+        else dst[0] = a[0];
+      } else {
+#pragma unroll
+        for (int v = 0; v < V; ++v) store_from_float(p.po, off + v, p.po_dtype, a[v]);
+      }
       if (d == 0) {
         p.pl[split * p.pl_s0 + b * p.pl_s1 + h * p.pl_s2] = l;
         p.pm[split * p.pm_s0 + b * p.pm_s1 + h * p.pm_s2] = m;
       }
     }
+  };
+  {
+    const int64_t strides = p.po_s0 | p.po_s1 | p.po_s2;
+    const uintptr_t base = (uintptr_t)p.po;
+    const bool f32 = p.po_dtype == G4B_F32;
+    if (to_o || !f32 || ((strides & 3) == 0 && (base & 15) == 0)) merge_warps(std::integral_constant<int, 4>{});
+    else if ((strides & 1) == 0 && (base & 7) == 0) merge_warps(std::integral_constant<int, 2>{});
+    else merge_warps(std::integral_constant<int, 1>{});
   }
   if (!exchange) return;   // the caller merges in a second launch
 
