@@ -33,8 +33,9 @@
 // Exchange form (one sequence's KV range split over GPUs; every CTA of the launch is resident
 // at once, which the launcher checks).  After its partial is written a CTA arrives at a
 // grid-wide count.  The first D / 8 CTAs of every (slot, kv head) then each own 8 columns of the
-// head dim: they wait (bounded) for the count, merge all local partials for their columns,
-// push the merged piece to every GPU as self-announcing 8-byte words {value, launch count}, poll
+// head dim: they wait (bounded) for the count, merge all local partials for their columns (one
+// trip to L2: every thread asks for the pieces of its splits before it uses one and merges
+// with a running maximum), push the merged piece to every GPU as self-announcing 8-byte words {value, launch count}, poll
 // (bounded) their own buffer for the peers' pieces and finish the merge -- the word format of
 // combine_exchange.cu, in the same launch as the attention.
 #include <type_traits>
@@ -56,9 +57,11 @@ constexpr long long kPeerWaitLimit = 1ll << 31;   // SM cycles (about a second)
 enum : int32_t { kErrBadEntry = 0x201, kErrStageFull = 0x211, kErrStageEmpty = 0x212, kErrStageOrder = 0x213,
                  kErrAppendRow = 0x214, kErrGridWait = 0x215, kErrPeerWait = 0x401 };
 
-// Grid-wide counts of the exchange form, {arrived, finished}: zero between launches (the CTA
-// that finishes last puts both back).  One pair per GPU, shared by every launch on it.
-__device__ uint32_t g_step_sync[2];
+// Grid-wide arrival counts of the exchange form: {arrivals of even turns, of odd turns, whose
+// turn it is}.  A launch counts on its turn's word and, once full, zeroes the other one and
+// hands the turn over, so nothing is counted or reset at the end of a launch.  One set per
+// GPU, shared by every launch on it.
+__device__ uint32_t g_step_sync[3];
 
 template <int D, bool kFp8 = false> struct StreamCfg {
   static constexpr int kTileBytes = 16 * D * (kFp8 ? 1 : 2);   // 16 keys of K, or of V
@@ -87,7 +90,7 @@ struct StreamParams {
   const float* k_scales; const float* v_scales;
   int64_t ks_s0, ks_s1, vs_s0, vs_s1;
   // decode step
-  uint32_t* sync;              // {arrived, finished} (exchange form), else null
+  uint32_t* sync;              // {arrivals of even turns, of odd turns, turn} (exchange form), else null
   void* k_cache; void* v_cache;
   const void* k_new; const void* v_new;
   int64_t kn_s0, kn_s1, vn_s0, vn_s1;
@@ -103,8 +106,8 @@ template <int kStages> struct alignas(16) Ctl {
   float2 scl[kStages];         // e4m3 pools: the stage's page scales (K, V)
   float sm_m[kConsumers][8];
   float sm_l[kConsumers][8];
-  float ml[8][2];              // merged (l, m) per head
   uint32_t epoch;
+  uint32_t turn;               // which of the two arrival counters this launch counts on
   int flag;
   int next_stage;              // next stage no consumer has claimed yet
   volatile int done[kStages];  // uses of a ring slot that have been consumed
@@ -367,35 +370,52 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
     ctl->next_stage = 0;
     for (int s = 0; s < kSt; ++s) ctl->done[s] = 0;
     ctl->epoch = p.xstate != nullptr ? p.xstate[0] + 1u : 0u;
+    ctl->turn = p.sync != nullptr ? (p.sync[2] & 1u) : 0u;
     ptx::prefetch_tensormap(&k_map);
     ptx::prefetch_tensormap(&v_map);
   }
   __syncthreads();
 
-  // Exchange form: every CTA of the launch, whatever it did, arrives once (its partial, if it
-  // has one, is written) and finishes once; the last to finish puts the counts back to zero and
-  // advances the caller's launch count.
+  // Exchange form: every CTA of the launch, whatever it did, arrives once on the arrival
+  // counter of this launch's turn (its partial, if it has one, is written by then).  Launches
+  // take turns on two counters: once all have arrived, the launch's first CTA zeroes the OTHER
+  // counter (the previous launch's, which nobody polls any more), hands the turn over and
+  // advances the caller's launch count; a CTA that does not merge leaves as soon as it has
+  // arrived and nothing is counted at the end of the launch.
   const uint32_t n_ctas = gridDim.x * gridDim.y * gridDim.z;
+  const bool first_cta = (blockIdx.x | blockIdx.y | blockIdx.z) == 0;
   auto grid_arrive = [&]() {
-    __threadfence();
     __syncthreads();
-    if (tid == 0) atomicAdd(&p.sync[0], 1u);
+    // (a release after the barrier covers the stores of every thread of the CTA)
+    if (tid == 0) asm volatile("red.release.gpu.global.add.u32 [%0], 1;" ::"l"(p.sync + ctl->turn) : "memory");
   };
-  auto finish = [&]() {
-    __syncthreads();
+  // every thread returns whether all CTAs arrived in time; the loads after it see their stores
+  auto all_arrived = [&]() -> bool {
     if (tid == 0) {
-      __threadfence();
-      if (atomicAdd(&p.sync[1], 1u) == n_ctas - 1) {
-        p.sync[0] = 0;
-        p.sync[1] = 0;
-        __threadfence();
+      const long long t0 = clock64();
+      int ok = 1;
+      for (;;) {
+        uint32_t n;
+        asm volatile("ld.acquire.gpu.global.u32 %0, [%1];" : "=r"(n) : "l"(p.sync + ctl->turn) : "memory");
+        if (n >= n_ctas) break;
+        if (clock64() - t0 > ptx::kWaitLimitCycles) { atomicCAS(p.status, 0, kErrGridWait); ok = 0; break; }
+      }
+      ctl->flag = ok;
+      if (first_cta) {
+        p.sync[ctl->turn ^ 1u] = 0;
+        p.sync[2] = ctl->turn ^ 1u;
         p.xstate[0] = ctl->epoch;
       }
     }
+    __syncthreads();
+    return ctl->flag != 0;
   };
 
   if (p.user_phase != nullptr && p.user_phase[b * p.phase_stride] != (uint8_t)p.phase) {
-    if (p.sync != nullptr) { grid_arrive(); finish(); }
+    if (p.sync != nullptr) {
+      grid_arrive();
+      if (first_cta) all_arrived();
+    }
     return;
   }
 
@@ -708,106 +728,84 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   // =============================== merge + exchange ===============================
   grid_arrive();
   constexpr int kSlices = D / kXCols;
-  if (split >= kSlices) { finish(); return; }
+  if (split >= kSlices) return;          // (the launch's first CTA, split 0, always merges)
   // a merging CTA: wait until every CTA of the launch has arrived (all are resident)
-  if (tid == 0) {
-    const long long t0 = clock64();
-    int ok = 1;
-    while (*reinterpret_cast<volatile uint32_t*>(&p.sync[0]) < n_ctas) {
-      if (clock64() - t0 > ptx::kWaitLimitCycles) { atomicCAS(p.status, 0, kErrGridWait); ok = 0; break; }
-    }
-    ctl->flag = ok;
-  }
-  __syncthreads();
-  if (!ctl->flag) { finish(); return; }
-  __threadfence();
+  const bool arrived = all_arrived();
+  if (!arrived) return;
 
   const int S = p.num_splits;
-  float* s_wt = reinterpret_cast<float*>(ring);                 // [R][S] weights 2^(m_i - M)
-  float2* s_red = reinterpret_cast<float2*>(s_wt + 8 * kMaxResidentSplits);   // [groups][pairs]
-  float* x_own = reinterpret_cast<float*>(s_red + kStreamThreads);            // [R][kXWords]
-  float* x_all = x_own + 8 * kXWords;                                          // [world][R][kXWords]
+  float4* s_red = reinterpret_cast<float4*>(ring);                              // [groups][pairs]: acc.x, acc.y, l, m
+  float* x_own = reinterpret_cast<float*>(s_red + kStreamThreads);             // [R][kXWords]
+  float* x_all = x_own + 8 * kXWords;                                           // [world][R][kXWords]
   const float* pof = (const float*)p.po;
   // threads = (group of splits) x (pair of columns of one head); R * 4 pairs, padded to 16 or 32
   const int pairs = R * (kXCols / 2);
   const int pad = pairs > 16 ? 32 : 16;
   const int n_grp = kStreamThreads / pad;
   const int pi = tid % pad, sg = tid / pad;
-  // the first accumulator pieces of the CTA's first slice are asked for before the weights
-  // (they do not depend on them): one trip to L2 less on the way to the exchange
-  float2 x0[10];
-  if (pi < pairs) {
-    const float* src = pof + b * p.po_s1 + (g * R + pi / (kXCols / 2)) * p.po_s2 + split * kXCols + 2 * (pi % (kXCols / 2));
-#pragma unroll
-    for (int j = 0; j < 10; ++j)
-      x0[j] = __ldcg(reinterpret_cast<const float2*>(src + (int64_t)min(sg + j * n_grp, S - 1) * p.po_s0));
-  }
-  // weights and merged row sums of the local splits, one warp per head; every (m, l) pair is
-  // requested before any is used
-  for (int hh = warp; hh < R; hh += kStreamThreads / 32) {
-    const int h = g * R + hh;
-    constexpr int kPer = kMaxResidentSplits / 32;
-    float mi[kPer], li[kPer];
-#pragma unroll
-    for (int j = 0; j < kPer; ++j) {
-      const int i = lane + 32 * j;
-      mi[j] = -INFINITY; li[j] = 0.f;
-      if (i < S) {
-        mi[j] = __ldcg(p.pm + (int64_t)i * p.pm_s0 + b * p.pm_s1 + h * p.pm_s2);
-        li[j] = __ldcg(p.pl + (int64_t)i * p.pl_s0 + b * p.pl_s1 + h * p.pl_s2);
-      }
-    }
-    float m = -INFINITY;
-#pragma unroll
-    for (int j = 0; j < kPer; ++j) m = fmaxf(m, mi[j]);
-    for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
-    float l = 0.f;
-#pragma unroll
-    for (int j = 0; j < kPer; ++j) {
-      const int i = lane + 32 * j;
-      const float w = (mi[j] == -INFINITY) ? 0.f : exp2f(mi[j] - m);
-      if (i < S) s_wt[hh * kMaxResidentSplits + i] = w;
-      l += li[j] * w;
-    }
-    for (int o = 16; o > 0; o >>= 1) l += __shfl_xor_sync(0xffffffffu, l, o);
-    if (lane == 0) { ctl->ml[hh][0] = l; ctl->ml[hh][1] = m; }
-  }
-  __syncthreads();
-
   const uint32_t epoch = ctl->epoch;
   const int par = (int)(epoch & 1u);
   for (int sl = split; sl < kSlices; sl += S) {
     // ---- this GPU's merged accumulator for columns [8 sl, 8 sl + 8) of the R heads ----
+    // A thread merges every n_grp-th split of its column pair with a running maximum; the
+    // (acc, l, m) of up to kJ splits are all asked for before the first is used, so that a merge
+    // of 128 splits costs one trip to L2.
+    constexpr int kJ = 16;
     float2 acc = make_float2(0.f, 0.f);
+    float run_l = 0.f, run_m = -INFINITY;
     if (pi < pairs) {
       const int hh = pi / (kXCols / 2), d = sl * kXCols + 2 * (pi % (kXCols / 2));
-      const float* src = pof + b * p.po_s1 + (g * R + hh) * p.po_s2 + d;
-      const float* wt = s_wt + hh * kMaxResidentSplits;
-      for (int i0 = sg; i0 < S; i0 += 10 * n_grp) {
-        float2 x[10];
+      const int h = g * R + hh;
+      const float* src = pof + b * p.po_s1 + h * p.po_s2 + d;
+      const float* srcm = p.pm + b * p.pm_s1 + h * p.pm_s2;
+      const float* srcl = p.pl + b * p.pl_s1 + h * p.pl_s2;
+      for (int i0 = sg; i0 < S; i0 += kJ * n_grp) {
+        float2 x[kJ];
+        float mi[kJ], li[kJ];
 #pragma unroll
-        for (int j = 0; j < 10; ++j) {
-          if (sl == split && i0 == sg) { x[j] = x0[j]; continue; }
+        for (int j = 0; j < kJ; ++j) {
           const int i = min(i0 + j * n_grp, S - 1);
           x[j] = __ldcg(reinterpret_cast<const float2*>(src + (int64_t)i * p.po_s0));
+          mi[j] = __ldcg(srcm + (int64_t)i * p.pm_s0);
+          li[j] = __ldcg(srcl + (int64_t)i * p.pl_s0);
         }
+        float m_new = run_m;
 #pragma unroll
-        for (int j = 0; j < 10; ++j) {
-          const int i = i0 + j * n_grp;
-          const float w = i < S ? wt[i] : 0.f;
-          acc.x += x[j].x * w; acc.y += x[j].y * w;
+        for (int j = 0; j < kJ; ++j) {
+          if (i0 + j * n_grp >= S) mi[j] = -INFINITY;
+          m_new = fmaxf(m_new, mi[j]);
         }
+        const float keep = run_m == -INFINITY ? 0.f : exp2f(run_m - m_new);
+        acc.x *= keep; acc.y *= keep; run_l *= keep;
+#pragma unroll
+        for (int j = 0; j < kJ; ++j) {
+          const float w = mi[j] == -INFINITY ? 0.f : exp2f(mi[j] - m_new);
+          acc.x += x[j].x * w; acc.y += x[j].y * w;
+          run_l += li[j] * w;
+        }
+        run_m = m_new;
       }
     }
-    s_red[sg * pad + pi] = acc;
+    s_red[sg * pad + pi] = make_float4(acc.x, acc.y, run_l, run_m);
     __syncthreads();
     if (tid < pairs) {
+      float4 v[8];                                  // n_grp is 4 or 8
+#pragma unroll
+      for (int q = 0; q < 8; ++q) v[q] = s_red[min(q, n_grp - 1) * pad + tid];
+      float m = -INFINITY;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) m = fmaxf(m, v[q].w);
       float2 sum = make_float2(0.f, 0.f);
-      for (int q = 0; q < n_grp; ++q) { const float2 v = s_red[q * pad + tid]; sum.x += v.x; sum.y += v.y; }
+      float l = 0.f;
+#pragma unroll
+      for (int q = 0; q < 8; ++q) {
+        const float w = (q >= n_grp || v[q].w == -INFINITY) ? 0.f : exp2f(v[q].w - m);
+        sum.x += v[q].x * w; sum.y += v[q].y * w; l += v[q].z * w;
+      }
       const int hh = tid / (kXCols / 2), cp = tid % (kXCols / 2);
       x_own[hh * kXWords + 2 * cp] = sum.x;
       x_own[hh * kXWords + 2 * cp + 1] = sum.y;
-      if (cp == 0) { x_own[hh * kXWords + kXCols] = ctl->ml[hh][0]; x_own[hh * kXWords + kXCols + 1] = ctl->ml[hh][1]; }
+      if (cp == 0) { x_own[hh * kXWords + kXCols] = l; x_own[hh * kXWords + kXCols + 1] = m; }
     }
     __syncthreads();
     // ---- push the piece to every GPU (own copy included) ----
@@ -876,7 +874,6 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
     }
     __syncthreads();
   }
-  finish();
 }
 
 template <typename T, int D, bool kPaged, bool kFp8 = false>

@@ -149,9 +149,10 @@ int g4b_attn_decode(const G4bAttnArgs* args, void* cuda_stream);
  *                   and splits <= 320, else G4B_ERR_TOO_LARGE.  A peer that does not show up
  *                   within about a second leaves 0x401 in the status word; after that the
  *                   buffers and `state` must be zeroed again on every rank before the next call.
- *                   The launch counts its CTAs in two words inside the library (one pair per
- *                   GPU, zero between launches): two such launches that overlap on one GPU
- *                   would share them -- keep them on one stream or order them.
+ *                   The launch counts its CTAs in three words inside the library (one set per
+ *                   GPU: two arrival counts used in turns, and the turn): two such launches
+ *                   that overlap on one GPU would share them -- keep them on one stream or
+ *                   order them.
  */
 typedef struct G4bDecodeStepArgs {
   G4bAttnArgs attn;
