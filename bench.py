@@ -172,8 +172,12 @@ def timed_region(step_fn, steps, warmup, world, dev, sampler=None, begin=None, e
     bracketed by barrier + synchronize; returns the max over ranks in ms."""
     if begin is not None:
         begin()
-    for i in range(warmup):
-        step_fn(i)
+    many = getattr(step_fn, "run_many", None)
+    if many is not None:
+        many(0, warmup)
+    else:
+        for i in range(warmup):
+            step_fn(i)
     if end is not None:
         end()
     barrier_sync(world)
@@ -181,8 +185,11 @@ def timed_region(step_fn, steps, warmup, world, dev, sampler=None, begin=None, e
         sampler.start()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
-    for i in range(steps):
-        step_fn(warmup + i)
+    if many is not None:
+        many(warmup, steps)
+    else:
+        for i in range(steps):
+            step_fn(warmup + i)
     if end is not None:
         end()                     # side streams join the launching stream before the stop event
     e1.record()
@@ -195,10 +202,16 @@ class GraphRunner:
     """Replays a step from CUDA graphs (one per input variant), as the reference engine does
     in deployment (g4b/lifecycle.py:39-51): the operators neither allocate nor synchronise, so
     a step is capturable, and replay removes the Python launch overhead that otherwise
-    dominates microsecond-scale decode steps.  Falls back to direct launches if capture fails."""
+    dominates microsecond-scale decode steps.  A workload that rotates over several input
+    variants also gets graphs that hold GROUP consecutive steps (consecutive variants, back to
+    back): the engine's graph holds a model step with one attention call per layer, so
+    consecutive calls there are graph nodes too, not separate graph launches.  Falls back to
+    direct launches if capture fails."""
+
+    GROUP = 4
 
     def __init__(self, step_fn, variants: int, enabled: bool):
-        self.step_fn, self.graphs, self.mode = step_fn, [], "direct"
+        self.step_fn, self.graphs, self.groups, self.mode = step_fn, [], {}, "direct"
         if not enabled:
             return
         try:
@@ -210,11 +223,18 @@ class GraphRunner:
                     with torch.cuda.graph(g, stream=side):
                         step_fn(i)
                     self.graphs.append(g)
+                size = min(self.GROUP, variants)
+                for first in range(0, variants - size + 1, size) if size > 1 else ():
+                    g = torch.cuda.CUDAGraph()
+                    with torch.cuda.graph(g, stream=side):
+                        for i in range(first, first + size):
+                            step_fn(i)
+                    self.groups[first] = (g, size)
             torch.cuda.current_stream().wait_stream(side)
             torch.cuda.synchronize()
-            self.mode = "cuda_graph"
+            self.mode = "cuda_graph" if not self.groups else "cuda_graph (%d steps per replay)" % min(self.GROUP, variants)
         except Exception as exc:  # keep measuring, but say how
-            self.graphs, self.mode = [], f"direct (graph capture failed: {type(exc).__name__})"
+            self.graphs, self.groups, self.mode = [], {}, f"direct (graph capture failed: {type(exc).__name__})"
             torch.cuda.synchronize()
 
     def __call__(self, i: int):
@@ -222,6 +242,18 @@ class GraphRunner:
             self.graphs[i % len(self.graphs)].replay()
         else:
             self.step_fn(i)
+
+    def run_many(self, start: int, count: int):
+        """Steps start .. start + count - 1: whole groups from the group graphs, the rest one by one."""
+        i, end = start, start + count
+        while i < end:
+            g, size = self.groups.get(i % len(self.graphs), (None, 0)) if self.graphs else (None, 0)
+            if g is not None and end - i >= size:
+                g.replay()
+                i += size
+            else:
+                self(i)
+                i += 1
 
 
 def within_tolerance(got, want):
