@@ -259,7 +259,7 @@ template <> struct PackT<__half> {
 template <typename T, bool kPair, bool kStageOut, bool kShortItems, bool kSplit>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
-               const __grid_constant__ CUtensorMap v_map, PrefillParams p) {
+               const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap o_map, PrefillParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // kStageOut: the epilogue turns the output block through shared memory to store whole
@@ -321,6 +321,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     ptx::prefetch_tensormap(&q_map);
     ptx::prefetch_tensormap(&k_map);
     ptx::prefetch_tensormap(&v_map);
+    if constexpr (kStageOut) ptx::prefetch_tensormap(&o_map);
     // An earlier CTA gave up on a wait: drain the grid.  One thread reads so all agree (in a
     // pair: CTA 0 decides for both).  The swizzled tiles need the buffer on a 1024-byte
     // boundary: refuse to run otherwise.
@@ -910,12 +911,29 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     bool ok = true;
     int tg = 0;       // tiles seen so far: S buffer and barrier phases run on across items
     int n_done = 0;
+    // The ring slot borrowed for the last item's output goes back to the producer once the copy
+    // engine has read the boxes out of it.  Called a tile into the next item (the producer needs
+    // the slot for that item's fifth chunk at the earliest, or for its second if it has one
+    // tile), when the read has long ended, instead of waiting for it in the epilogue.  (Giving
+    // the slot back before the first tile instead cost 1.5 % on long items: the wait sits in
+    // front of the tile that the tensor pipe is waiting for.)
+    bool stage_held = false;
+    auto release_stage = [&]() {
+      if (!stage_held) return;
+      stage_held = false;
+      if (lane == 0) {
+        ptx::bulk_wait_read_all();
+        ptx::mbar_arrive(ptx::smem_u32(&bars->stage_free));
+      }
+      __syncwarp();
+    };
     G4B_ITEM_LOOP_PROLOGUE();
     for (int round = 0; round * n_workers < n_items && ok; ++round) {
     G4B_ITEM_LOOP_HEAD(round);
     if (item < 0) continue;
     G4B_ITEM_GEOMETRY(item);
     if (n_tiles <= 0) {
+      release_stage();
       if constexpr (kSplit) {
         // an empty key range: the merge skips a partial with m = -inf, l = 0 (fa2.py:466-472)
         if (active && half == 0 && r < rows_valid) {
@@ -943,6 +961,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     for (int j = 0; j < n_tiles && ok; ++j) {
       const int t = tg + j;
       const uint32_t s_col = (t & 1) ? kColS1 : kColS0;
+      if (j == 1) release_stage();
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(ptx::smem_u32(&bars->s_full[t & 1]), (t >> 1) & 1))) {
         record(p.status, kErrSFull); ok = false; break;
       }
@@ -1157,6 +1176,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     }
 
     // ---- epilogue: O / l -> global ----
+    release_stage();   // (an item of one tile: its only V chunk may be the one that waits for the slot)
     if (ok) {
       if (!__all_sync(0xffffffffu, ptx::mbar_wait(bar_pv, (tg + n_tiles - 1) & 1))) { record(p.status, kErrPvDone); ok = false; }
       ptx::tc_fence_after();
@@ -1214,6 +1234,53 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         ptx::tc_fence_before();
         arrive_issuer(issuer_bar(&bars->o_free));
       } else {
+        if constexpr (kStageOut) {
+          // A lane owns a row, and rows are kilobytes apart in memory: stored directly, every
+          // 16-byte store touches its own line, and 64 KB of stores per item queue up in front
+          // of the warps that should be exponentiating the next item's scores.  Instead the warp
+          // writes its [32 rows x 64 columns] block into shared memory in the 128-byte-swizzled
+          // layout of a TMA box (4 KB per warp, twice) and one lane hands it to the copy engine,
+          // which stores whole rows while the warp moves on (rows past Tq are clipped by the
+          // box).  The second half is pulled out of tensor memory while the engine reads the
+          // first; the wait for the second, and the hand-back of the slot, are left to
+          // release_stage() a tile later.
+          // (2 chunks per tile in the pair form: the item's last V chunk is chunk 2 (tg + n_tiles) - 1)
+          const int stage_slot = (2 * (tg + n_tiles) - 1) % kStages;
+          uint8_t* stage = sRing + stage_slot * kChunkBytes + (warp - 2) * 4096;
+#pragma unroll
+          for (int cp = 0; cp < 2; ++cp) {
+            uint32_t pk[2][16];
+#pragma unroll
+            for (int c2 = 0; c2 < 2; ++c2) {
+              uint32_t ov[32];
+              ptx::tmem_ld32(trow + kColO + half * 128 + (2 * cp + c2) * 32, ov);
+              ptx::tc_wait_ld();
+#pragma unroll
+              for (int i = 0; i < 16; ++i)
+                pk[c2][i] = PackT<T>::pack(__uint_as_float(ov[2 * i]) * inv_l, __uint_as_float(ov[2 * i + 1]) * inv_l);
+            }
+            if (cp == 1) {
+              // O is out of tensor memory: the next item's first P.V may overwrite it
+              ptx::tc_fence_before();
+              arrive_issuer(issuer_bar(&bars->o_free));
+              // the first box must have been read out of the stage before it is overwritten
+              if (lane == 0) ptx::bulk_wait_read_all();
+              __syncwarp();
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) {
+              const uint32_t* src = &pk[c >> 2][(c & 3) * 4];
+              *reinterpret_cast<uint4*>(stage + lane * 128 + ((c ^ (lane & 7)) << 4)) = make_uint4(src[0], src[1], src[2], src[3]);
+            }
+            ptx::fence_proxy_async_smem();
+            __syncwarp();
+            if (lane == 0 && lane_base < rows_valid) {   // (a box wholly past Tq is not issued at all)
+              ptx::tma_store_4d_hint(&o_map, ptx::smem_u32(stage), half * 128 + cp * 64, m0 + lane_base, h, b, pol_o);
+              ptx::bulk_commit();
+            }
+          }
+          stage_held = true;
+        } else {
         // pull this thread's 128 accumulator columns out (normalised and packed: 64 registers),
         // hand O back to the MMA issuer -- the next item's first P.V overwrites it -- then store
         uint32_t pk[4][16];
@@ -1228,37 +1295,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         }
         ptx::tc_fence_before();
         arrive_issuer(issuer_bar(&bars->o_free));
-        if constexpr (kStageOut) {
-          // A lane owns a row, and rows are kilobytes apart in memory: stored directly, every
-          // 16-byte store touches its own line.  Instead the warp turns its [32 rows x 64
-          // columns] block through shared memory (4 KB per warp, 16-byte chunks XOR-swizzled by
-          // row so neither side has bank conflicts) and stores whole 128-byte row segments.
-          // (2 chunks per tile in the pair form: the item's last V chunk is chunk 2 (tg + n_tiles) - 1)
-          const int stage_slot = (2 * (tg + n_tiles) - 1) % kStages;
-          uint8_t* stage = sRing + stage_slot * kChunkBytes + (warp - 2) * 4096;
-          const int64_t row_base = b * p.o_s0 + h * p.o_s1 + (int64_t)(m0 + lane_base) * p.o_s2 + half * 128;
-#pragma unroll
-          for (int cp = 0; cp < 2; ++cp) {
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              const uint32_t* src = &pk[2 * cp + (c >> 2)][(c & 3) * 4];
-              *reinterpret_cast<uint4*>(stage + lane * 128 + ((c ^ (lane & 7)) << 4)) = make_uint4(src[0], src[1], src[2], src[3]);
-            }
-            __syncwarp();
-#pragma unroll
-            for (int i = 0; i < 8; ++i) {
-              const int rr = 4 * i + (lane >> 3), c = lane & 7;
-              const uint4 w = *reinterpret_cast<const uint4*>(stage + rr * 128 + ((c ^ (rr & 7)) << 4));
-              if (lane_base + rr < rows_valid)
-                ptx::st_global_v4_hint((T*)p.o + row_base + (int64_t)rr * p.o_s2 + cp * 64 + c * 8, w, pol_o);
-            }
-            __syncwarp();
-          }
-          // the slot goes back to the producer, whose TMA writes must come after these accesses
-          ptx::fence_proxy_async_smem();
-          __syncwarp();
-          if (lane == 0) ptx::mbar_arrive(ptx::smem_u32(&bars->stage_free));
-        } else if (row_ok) {
+        if (row_ok) {
+
 #pragma unroll
           for (int c4 = 0; c4 < 4; ++c4) {
             uint4* dst = reinterpret_cast<uint4*>((T*)p.o + off + c4 * 32);
@@ -1268,14 +1306,19 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
                                      pol_o);
           }
         }
+        }
       }
     }
     tg += n_tiles;
     ++n_done;
     }   // work items
+    release_stage();
   }
 
   // ---- teardown: every thread arrives here, on success and after a failed wait ----
+  if constexpr (kStageOut) {
+    if (warp >= 2 && lane == 0) ptx::bulk_wait_all();   // the output boxes handed to the copy engine are stored
+  }
   ptx::tc_fence_before();
   __syncthreads();
   if constexpr (kPair) {
@@ -1295,8 +1338,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
 // host side: tensor maps + launch
 // ---------------------------------------------------------------------------------------
 template <typename T, bool kPair, bool kStageOut, bool kShortItems, bool kSplit>
-static int launch_variant(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const PrefillParams& p,
-                          dim3 grid, cudaStream_t st) {
+static int launch_variant(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const CUtensorMap& om,
+                          const PrefillParams& p, dim3 grid, cudaStream_t st) {
   static bool attr_set[64] = {false};
   int dev = 0;
   G4B_CUDA_CHECK(cudaGetDevice(&dev));
@@ -1316,21 +1359,22 @@ static int launch_variant(const CUtensorMap& qm, const CUtensorMap& km, const CU
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  G4B_CUDA_CHECK(cudaLaunchKernelEx(&cfg, prefill_kernel<T, kPair, kStageOut, kShortItems, kSplit>, qm, km, vm, p));
+  G4B_CUDA_CHECK(cudaLaunchKernelEx(&cfg, prefill_kernel<T, kPair, kStageOut, kShortItems, kSplit>, qm, km, vm, om, p));
   return G4B_OK;
 }
 
 template <typename T>
-static int launch_typed(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const PrefillParams& p,
-                        dim3 grid, bool pair, bool stage_out, bool short_items, bool split, cudaStream_t st) {
+static int launch_typed(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const CUtensorMap& om,
+                        const PrefillParams& p, dim3 grid, bool pair, bool stage_out, bool short_items, bool split,
+                        cudaStream_t st) {
   if (split) {
-    if (pair) return launch_variant<T, true, false, false, true>(qm, km, vm, p, grid, st);
-    return launch_variant<T, false, false, false, true>(qm, km, vm, p, grid, st);
+    if (pair) return launch_variant<T, true, false, false, true>(qm, km, vm, om, p, grid, st);
+    return launch_variant<T, false, false, false, true>(qm, km, vm, om, p, grid, st);
   }
-  if (pair && stage_out && short_items) return launch_variant<T, true, true, true, false>(qm, km, vm, p, grid, st);
-  if (pair && stage_out) return launch_variant<T, true, true, false, false>(qm, km, vm, p, grid, st);
-  if (pair) return launch_variant<T, true, false, false, false>(qm, km, vm, p, grid, st);
-  return launch_variant<T, false, false, false, false>(qm, km, vm, p, grid, st);
+  if (pair && stage_out && short_items) return launch_variant<T, true, true, true, false>(qm, km, vm, om, p, grid, st);
+  if (pair && stage_out) return launch_variant<T, true, true, false, false>(qm, km, vm, om, p, grid, st);
+  if (pair) return launch_variant<T, true, false, false, false>(qm, km, vm, om, p, grid, st);
+  return launch_variant<T, false, false, false, false>(qm, km, vm, om, p, grid, st);
 }
 
 }  // namespace
@@ -1473,8 +1517,16 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
     p.q_f32 = (const float*)a.q.ptr;
     p.q_s0 = a.q.stride[0]; p.q_s1 = a.q.stride[1]; p.q_s2 = a.q.stride[2];
   }
-  if (a.k_cache.dtype == G4B_BF16) rc = launch_typed<__nv_bfloat16>(qm, km, vm, p, grid, pair, stage, short_items, p.n_splits > 1, st);
-  else rc = launch_typed<__half>(qm, km, vm, p, grid, pair, stage, short_items, p.n_splits > 1, st);
+  // the output as the copy engine stores it: boxes of 32 rows x 64 columns of one (slot, head)
+  CUtensorMap om = km;   // (never used when the output is not staged)
+  if (stage) {
+    const uint64_t dims[4] = {(uint64_t)D, (uint64_t)Tq, (uint64_t)H, (uint64_t)B};
+    const uint64_t strides[3] = {(uint64_t)a.o.stride[2] * esz, (uint64_t)a.o.stride[1] * esz, (uint64_t)a.o.stride[0] * esz};
+    const uint32_t box[4] = {64, 32, 1, 1};
+    if ((rc = encode_map(&om, a.o.dtype, 4, a.o.ptr, dims, strides, box, "o"))) return rc;
+  }
+  if (a.k_cache.dtype == G4B_BF16) rc = launch_typed<__nv_bfloat16>(qm, km, vm, om, p, grid, pair, stage, short_items, p.n_splits > 1, st);
+  else rc = launch_typed<__half>(qm, km, vm, om, p, grid, pair, stage, short_items, p.n_splits > 1, st);
   if (rc != G4B_OK || p.n_splits == 1) return rc;
   G4bCombineArgs c{};
   c.partial_o = a.partial_o; c.partial_l = a.partial_l; c.partial_m = a.partial_m; c.o = a.o;
