@@ -917,6 +917,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     // tile), when the read has long ended, instead of waiting for it in the epilogue.  (Giving
     // the slot back before the first tile instead cost 1.5 % on long items: the wait sits in
     // front of the tile that the tensor pipe is waiting for.)
+    // Short items: the reference maximum a row ended the last item with is the first guess for
+    // the same row of the next one (another head or query tile of similar scores).  A guess
+    // at most 2^8 below or 2^4 above the first maximum the row really sees is kept -- any
+    // reference in that range is as good as the maximum itself -- so the first tile of an item can take the
+    // optimistic path too instead of waiting for the partner's maximum before the first exp.
+    float m_carry = -INFINITY;
     bool stage_held = false;
     auto release_stage = [&]() {
       if (!stage_held) return;
@@ -955,7 +961,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     const int qpos = q_t_base + m0 + r;
     const int hi_r = p.causal ? min(window, qpos + 1) : window;
     const int lo_r = p.sliding_window > 0 ? max(win_lo, qpos - p.sliding_window + 1) : win_lo;
-    float m_used = -INFINITY;   // reference maximum the accumulated O and l are scaled by
+    float m_used = (kShortItems && !few_keys) ? m_carry : -INFINITY;   // reference maximum the accumulated O and l are scaled by
+    bool anchored = false;      // m_used has been checked against a key this row sees
     float l_run = 0.f;          // this thread's half of the row sum
 
     for (int j = 0; j < n_tiles && ok; ++j) {
@@ -977,17 +984,23 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       ptx::tc_wait_ld();
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};
       if (need_mask) {
+        // the keys this row sees are one range [nlo, nhi) of the thread's 64: as one bit per key,
+        // so that an element costs a bit test and a select instead of two compares and a select
         const int nlo = lo_r - kbase - half * 64, nhi = hi_r - kbase - half * 64;
 #pragma unroll
-        for (int q2 = 0; q2 < 2; ++q2)
+        for (int q2 = 0; q2 < 2; ++q2) {
+          const int lo = min(max(nlo - 32 * q2, 0), 32), hi = min(max(nhi - 32 * q2, 0), 32);
+          const uint32_t below_hi = hi >= 32 ? 0xffffffffu : ((1u << hi) - 1u);
+          const uint32_t below_lo = lo >= 32 ? 0xffffffffu : ((1u << lo) - 1u);
+          const uint32_t bits = below_hi & ~below_lo;
 #pragma unroll
           for (int i = 0; i < 32; ++i) {
-            const int n = q2 * 32 + i;
             float x = __uint_as_float(sraw[q2][i]);
-            x = (n >= nlo && n < nhi) ? x : -INFINITY;
+            x = (bits & (1u << i)) ? x : -INFINITY;
             sraw[q2][i] = __float_as_uint(x);
             mx4[i & 3] = fmaxf(mx4[i & 3], x);
           }
+        }
       } else {
 #pragma unroll
         for (int q2 = 0; q2 < 2; ++q2)
@@ -1027,7 +1040,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       ++pair_phase;
       mx = fmaxf(mx, xm[(half ^ 1) * kBM + r]);
       const float m_blk = mx * p.scale_log2;
-      const bool exceed = m_blk > m_used + 8.f;
+      bool exceed = m_blk > m_used + 8.f;
+      bool first_seen = false;
+      if (kShortItems && !few_keys && !anchored && m_blk != -INFINITY) {
+        // the row's first visible key: a guess that lies too far ABOVE is replaced as well
+        // (nothing has been accumulated against it yet, so nothing is rescaled)
+        first_seen = anchored = true;
+        exceed = exceed || m_blk < m_used - 4.f;   // (f16 probabilities: keep them well above the subnormals)
+      }
       if (fast && __any_sync(0xffffffffu, exceed)) fast = false;   // same outcome in the partner warp
 
       if (fast) {
@@ -1065,7 +1085,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
         float alpha = 1.f;
         bool rescale = false;
         if (exceed) {
-          rescale = (m_used != -INFINITY);
+          rescale = (m_used != -INFINITY) && !first_seen;
           alpha = rescale ? ptx::ex2_approx(m_used - m_blk) : 1.f;
           m_used = m_blk;
         }
@@ -1175,6 +1195,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       arrive_issuer(bar_pb);
     }
 
+    if (kShortItems && !few_keys && m_used != -INFINITY) m_carry = m_used;
     // ---- epilogue: O / l -> global ----
     release_stage();   // (an item of one tile: its only V chunk may be the one that waits for the slot)
     if (ok) {
