@@ -1000,14 +1000,14 @@ def cpu_leg_in_child(argv):
 
 
 def cpu_baseline_of(wl, world, no_cpu):
-    """The workload's CPU baseline block: in this process on one GPU, in a child under torchrun."""
+    """The workload's CPU baseline block (one-GPU runs only)."""
     if no_cpu:
         return None
-    if world == 1:
-        v, sample = wl.cpu_sample()
-        return {"value": round(v, 5), "unit": wl.unit, "cores": torch.get_num_threads(), "kind": "port", "sample": sample}
-    line = cpu_leg_in_child(["--impl", "reference", "--port", "--workload", wl.name, "--steps", "2", "--warmup", "3"])
-    return line.get("cpu_baseline", line)
+    if world > 1:
+        # the other ranks spin in their barrier on the same cores: the CPU figure belongs to the one-GPU line
+        return None
+    v, sample = wl.cpu_sample()
+    return {"value": round(v, 5), "unit": wl.unit, "cores": torch.get_num_threads(), "kind": "port", "sample": sample}
 
 
 def cpu_config1():
@@ -1148,7 +1148,7 @@ def run_ours(args):
         if status != 0:
             raise SystemExit(f"device status word {status:#x} after the extra blocks")
         if rank == 0 and not args.no_cpu:
-            out["cpu_config1"] = cpu_config1() if world == 1 else cpu_leg_in_child(["--cpu-config1"])
+            out["cpu_config1"] = cpu_config1() if world == 1 else None
         if rank == 0 and not args.no_triton:
             try:
                 from baseline import triton_reference
@@ -1348,6 +1348,19 @@ def main():
         print(json.dumps(cpu_config1()))
         return
     if args.impl == "reference":
+        rank, world, _ = dist_env()
+        if world > 1:
+            # rank 0 alone measures, in a fresh interpreter with all host threads (see cpu_leg_in_child)
+            if rank == 0:
+                argv = ["--impl", "reference", "--workload", args.workload, "--steps", str(args.steps),
+                        "--warmup", str(args.warmup), "--gpus", str(args.gpus)] + (["--port"] if args.port else [])
+                line = cpu_leg_in_child(argv)
+                if "unavailable" in line:
+                    line = {"impl": "reference", **line}
+                else:
+                    line["n_gpus"] = world
+                print(json.dumps(line), flush=True)
+            return
         run_reference(args)
     else:
         run_ours(args)
