@@ -939,7 +939,7 @@ def roofline_of(wl, value, world, peaks, sustained=False):
     cap = captured_traffic(wl.name)
     traffic = None
     if cap is not None:     # per launch on one rank, scaled from the captured case by the units processed
-        traffic = cap["dram_bytes_per_algorithmic_unit"] * wl.units + cap.get("dram_bytes_per_batch_item", 0.0) * wl.B
+        traffic = cap["dram_bytes_per_algorithmic_unit"] * wl.units + cap.get("dram_bytes_per_batch_item", 0.0) * getattr(wl, "B", 0)
     kind = ("sustained" if sustained else "burst") if wl.bound == "tensor" else "copy"
     return {"bound": wl.bound, "achieved": round(per_gpu, 3), "peak": peak, "unit": wl.unit,
             "frac": round(per_gpu / peak, 4), "traffic": traffic, "peak_source": f"{peaks['source']} {kind}"}
