@@ -1532,7 +1532,7 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   if (n_items > 0x7fffffffLL) return fail(G4B_ERR_UNSUPPORTED, "prefill: too many work items");
   if (workers > n_items) workers = n_items;
   dim3 grid((unsigned)(pair ? 2 * workers : workers), 1, 1);
-  const bool stage = stage_out && p.n_splits == 1;   // partials are stored directly
+  bool stage = stage_out && p.n_splits == 1;   // partials are stored directly
   if (q_f32) {
     qm = km;   // never used by the kernel: q is converted on load
     p.q_f32 = (const float*)a.q.ptr;
@@ -1544,7 +1544,8 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
     const uint64_t dims[4] = {(uint64_t)D, (uint64_t)Tq, (uint64_t)H, (uint64_t)B};
     const uint64_t strides[3] = {(uint64_t)a.o.stride[2] * esz, (uint64_t)a.o.stride[1] * esz, (uint64_t)a.o.stride[0] * esz};
     const uint32_t box[4] = {64, 32, 1, 1};
-    if ((rc = encode_map(&om, a.o.dtype, 4, a.o.ptr, dims, strides, box, "o"))) return rc;
+    // an output layout the descriptor cannot express (the driver refuses it) is stored directly
+    if (encode_map(&om, a.o.dtype, 4, a.o.ptr, dims, strides, box, "o") != G4B_OK) { om = km; stage = false; }
   }
   if (a.k_cache.dtype == G4B_BF16) rc = launch_typed<__nv_bfloat16>(qm, km, vm, om, p, grid, pair, stage, short_items, p.n_splits > 1, st);
   else rc = launch_typed<__half>(qm, km, vm, om, p, grid, pair, stage, short_items, p.n_splits > 1, st);
