@@ -377,3 +377,24 @@ def test_sliding_window_unit_of_a_query_range_split(cuda):
         want = orc.attention_core(q[0, row:row + 1].permute(1, 0, 2).float().cpu(), kc[:, :pos + 1], vc[:, :pos + 1],
                                   scale=1 / 16, sliding_window=W)
         assert_close(o[0, row:row + 1].permute(1, 0, 2), want, f"row {row}")
+
+
+@pytest.mark.parametrize("layout", ["rows_padded", "heads_padded"])
+def test_prefill_output_view_leaves_its_surroundings_alone(cuda, layout):
+    """The output tile leaves through TMA boxes of 32 rows x 64 columns: a ragged Tq (200 = six
+    boxes and a quarter) written into a view of a larger buffer must not touch the rows past Tq
+    of a (slot, head), nor the padding between heads."""
+    B, H, G, Tq, T, D = 2, 8, 2, 200, 512, 256
+    case = make_ring_case(41, B=B, H=H, G=G, Tq=Tq, T=T, dtype=torch.bfloat16, times=[T, T - 100])
+    q_phys, k, v, time = (case[n].to(cuda) for n in ("q_phys", "k", "v", "time"))
+    if layout == "rows_padded":
+        big = torch.full((B, H, Tq + 56, D), 7.0, dtype=torch.bfloat16, device=cuda)     # [B,H,rows,D], 56 spare rows per head
+        o = big[:, :, :Tq]
+        spare = big[:, :, Tq:]
+    else:
+        big = torch.full((B, Tq, H + 3, D), 7.0, dtype=torch.bfloat16, device=cuda)      # [B,rows,heads,D], 3 spare heads per row
+        o = big[:, :, :H].permute(0, 2, 1, 3)
+        spare = big[:, :, H:]
+    fa2.flash_attention(q_phys.permute(0, 2, 1, 3), k, v, o, time, None, case["ctx_window"], fa2.PHASE_PREFILL, scale=1 / 16)
+    assert_close(o.cpu(), oracle(case), "output view")
+    assert bool((spare == 7.0).all()), "the kernel wrote outside the output view"
