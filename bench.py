@@ -27,6 +27,8 @@ parity check against the CPU oracle made in this run:
                  ranks (strong scaling, no communication)
     decode       configuration 4; on N > 1 GPUs ONE set of 256 sequences dealt over the ranks
                  longest-first (strong scaling, no communication)
+    decode_fp8   configuration 4 over 8-bit (e4m3) pages with a scale per (page, kv head); GB/s of
+                 the bytes it reads, half of configuration 4's
     decode_long  configuration 5; on N > 1 GPUs the KV range of the one sequence is split over
                  the ranks and the partials are merged through peer memory (strong scaling, the
                  one exchange step of the path); every rank checks its output against the oracle
@@ -755,6 +757,8 @@ class DecodeWorkload:
             self.config.update({"sequences_this_rank": B, "ctx_sum_this_rank": int(self.local_lens.sum())})
         self.config["step"] = ("one launch (append + attention + merge + exchange)" if self.merge_in_launch else
                                "two launches (append + attention, merge)") if fused else "three launches (append, attention, merge)"
+        if self.fp8:
+            self.config["step"] = "four launches (K rows quantised into their pages, V rows, attention, merge)"
         if self.long_split:
             self.config["merge"] = "all-gather + second merge launch (NCCL)" if nccl_gather else \
                 "inside the launch: local merge, exchange through peer memory, final merge"
@@ -1141,7 +1145,8 @@ def run_ours(args):
         if world > 1:
             out["prefill_strong"] = run_block("prefill_causal", dev, rank, world, peaks, args, k2, w2, strong=True, cpu=False)
             torch.cuda.empty_cache()
-        for key, name in (("swa", "prefill_swa"), ("decode", "decode_paged"), ("decode_long", "decode_long")):
+        for key, name in (("swa", "prefill_swa"), ("decode", "decode_paged"), ("decode_fp8", "decode_paged_fp8"),
+                          ("decode_long", "decode_long")):
             out[key] = run_block(name, dev, rank, world, peaks, args, k2, w2, strong=True)
             torch.cuda.empty_cache()
         status = _cabi.device_status()
