@@ -398,3 +398,35 @@ def test_prefill_output_view_leaves_its_surroundings_alone(cuda, layout):
     fa2.flash_attention(q_phys.permute(0, 2, 1, 3), k, v, o, time, None, case["ctx_window"], fa2.PHASE_PREFILL, scale=1 / 16)
     assert_close(o.cpu(), oracle(case), "output view")
     assert bool((spare == 7.0).all()), "the kernel wrote outside the output view"
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_sliding_window_items_with_wildly_different_score_scales(cuda, dtype):
+    """Short items start from the reference maximum the same row ended the worker's previous
+    item with.  Heads and positions whose scores differ by orders of magnitude (a guess far too
+    low, far too high, and rows whose first tile shows them no key at all) must give the same
+    output as the oracle: 256 work items over 74 workers, so every worker carries a guess
+    through several items."""
+    gen = torch.Generator().manual_seed(53)
+    B, S, H, G, D, W = 1, 4096, 16, 2, 256, 300
+    q_phys = randn(gen, B, S, H, D, dtype=torch.float32)
+    k = randn(gen, B, G, S, D, dtype=dtype)
+    v = randn(gen, B, G, S, D, dtype=dtype)
+    # per-head factors spanning 1e-2 .. 2e2 (scores up to ~ +-300 in log2 units after the 1/16),
+    # and per-position stripes of 128 rows that are almost silent
+    head_gain = torch.tensor([0.01, 200.0, 1.0, 60.0, 0.1, 120.0, 3.0, 0.02, 150.0, 0.5, 30.0, 0.01, 90.0, 1.0, 0.05, 180.0])
+    q_phys = q_phys * head_gain[None, None, :, None]
+    stripe = ((torch.arange(S) // 128) % 3 == 1).float() * 0.999
+    q_phys = (q_phys * (1.0 - stripe)[None, :, None, None]).to(dtype)
+    time = torch.full((B,), S, dtype=torch.int32)
+    qd = q_phys.to(cuda)
+    o = torch.zeros_like(qd)
+    fa2.flash_attention(qd.permute(0, 2, 1, 3), k.to(cuda), v.to(cuda), o.permute(0, 2, 1, 3), time.to(cuda), None,
+                        S, 1, scale=1 / 16, sliding_window=W)
+    got = o.permute(0, 2, 1, 3).cpu()
+    assert bool(torch.isfinite(got.float()).all())
+    rows = [0, 1, 127, 128, 129, 255, 256, 299, 300, 301, 383, 384, 1000, 2047, 2048, 2175, 2176, 3000, 4094, 4095]
+    for r in rows:
+        lo = max(0, r - W + 1)
+        want = orc.attention_core(q_phys[0, r:r + 1].permute(1, 0, 2), k[0, :, lo:r + 1], v[0, :, lo:r + 1], scale=1 / 16)
+        assert_close(got[0, :, r:r + 1], want, f"row={r}")
