@@ -350,7 +350,7 @@ decode_stream_kernel(const __grid_constant__ CUtensorMap k_map, const __grid_con
   const int R = p.H / p.G;                  // query heads per kv head (<= 8)
   uint8_t* ring = smem_raw;
   Ctl<kSt>* ctl = reinterpret_cast<Ctl<kSt>*>(smem_raw + Cfg::kRingBytes);
-  // after the stream the ring is scratch: warp accumulators / peers' partials, then merge weights
+  // after the stream the ring is scratch: the warps' accumulators, then the merging CTAs' reduction and the peers' pieces
   float* sm_o = reinterpret_cast<float*>(ring);                                   // [kConsumers][8][D + 4]
 
   // asked for before anything else: the split's key range, then its block-table entries, then
