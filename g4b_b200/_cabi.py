@@ -105,6 +105,13 @@ class G4bFp8AppendArgs(ctypes.Structure):
     ]
 
 
+class G4bFp8DequantArgs(ctypes.Structure):
+    _fields_ = [
+        ("cache", G4bTensor), ("scales", G4bTensor), ("out", G4bTensor), ("block_tables", G4bTensor),
+        ("time_dim_sizes", G4bTensor), ("user_phase", G4bTensor), ("phase", ctypes.c_int32), ("page_size", ctypes.c_int32),
+    ]
+
+
 class G4bAdvanceArgs(ctypes.Structure):
     _fields_ = [
         ("input_token_ids", G4bTensor), ("out_token_ids", G4bTensor), ("cache_offsets", G4bTensor),
@@ -120,6 +127,7 @@ EXPORTS = {
     "g4b_attn_decode_static_scratch": (ctypes.c_int, [ctypes.POINTER(G4bAttnArgs), ctypes.c_void_p]),
     "g4b_decode_step": (ctypes.c_int, [ctypes.POINTER(G4bDecodeStepArgs), ctypes.c_void_p]),
     "g4b_kv_append_fp8": (ctypes.c_int, [ctypes.POINTER(G4bFp8AppendArgs), ctypes.c_void_p]),
+    "g4b_kv_dequant_fp8": (ctypes.c_int, [ctypes.POINTER(G4bFp8DequantArgs), ctypes.c_void_p]),
     "g4b_flash_attention_fp8": (ctypes.c_int, [ctypes.POINTER(G4bAttnArgs), ctypes.POINTER(G4bTensor),
                                                ctypes.POINTER(G4bTensor), ctypes.c_void_p]),
     "g4b_attn_combine": (ctypes.c_int, [ctypes.POINTER(G4bCombineArgs), ctypes.c_void_p]),

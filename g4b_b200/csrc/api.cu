@@ -354,6 +354,40 @@ int g4b_kv_append_fp8(const G4bFp8AppendArgs* args, void* cuda_stream) {
   return launch_kv_append_fp8(a, (cudaStream_t)cuda_stream);
 }
 
+int g4b_kv_dequant_fp8(const G4bFp8DequantArgs* args, void* cuda_stream) {
+  if (args == nullptr) return fail(G4B_ERR_BAD_ARG, "args is null");
+  const G4bFp8DequantArgs& a = *args;
+  int rc;
+  if ((rc = check_tensor(a.cache, "cache", 4, true))) return rc;
+  if ((rc = check_tensor(a.scales, "scales", 2, false))) return rc;
+  if ((rc = check_tensor(a.out, "out", 4, true))) return rc;
+  if (!is_byte_dtype(a.cache.dtype)) return fail(G4B_ERR_BAD_DTYPE, "cache must hold one byte per element (e4m3)");
+  if (a.scales.dtype != G4B_F32) return fail(G4B_ERR_BAD_DTYPE, "scales must be f32");
+  if (a.out.dtype != G4B_F16 && a.out.dtype != G4B_BF16) return fail(G4B_ERR_BAD_DTYPE, "out must be f16 or bf16");
+  if (!contiguous_from(a.cache, 0) || !contiguous_from(a.out, 0)) return fail(G4B_ERR_BAD_STRIDE, "cache and out must be contiguous");
+  for (int i = 0; i < 4; ++i)
+    if (a.cache.shape[i] != a.out.shape[i]) return fail(G4B_ERR_BAD_ARG, "out must have the shape of cache");
+  if (!is_pow2(a.page_size) || a.cache.shape[2] != a.page_size) return fail(G4B_ERR_BAD_ARG, "pool dim 2 must equal page_size, a power of two");
+  if ((a.cache.shape[2] * a.cache.shape[3]) % 16 != 0) return fail(G4B_ERR_BAD_ARG, "page_size x D must be a multiple of 16");
+  if ((((uintptr_t)a.cache.ptr) & 15) || (((uintptr_t)a.out.ptr) & 15)) return fail(G4B_ERR_BAD_STRIDE, "cache and out must be 16-byte aligned");
+  if (a.scales.shape[0] != a.cache.shape[0] || a.scales.shape[1] != a.cache.shape[1]) return fail(G4B_ERR_BAD_ARG, "scales must be [num_pages, G]");
+  if (a.block_tables.ptr != nullptr) {
+    if ((rc = check_tensor(a.block_tables, "block_tables", 2, false))) return rc;
+    if (a.block_tables.dtype != G4B_I32) return fail(G4B_ERR_BAD_DTYPE, "block_tables must be int32");
+    if (a.time_dim_sizes.ptr == nullptr) return fail(G4B_ERR_BAD_ARG, "block_tables needs time_dim_sizes");
+    if ((rc = check_tensor(a.time_dim_sizes, "time_dim_sizes", 1, false))) return rc;
+    if (a.time_dim_sizes.dtype != G4B_I32 || a.time_dim_sizes.shape[0] != a.block_tables.shape[0])
+      return fail(G4B_ERR_BAD_ARG, "time_dim_sizes must be int32 [B]");
+    if (a.user_phase.ptr != nullptr) {
+      if ((rc = check_tensor(a.user_phase, "user_phase", 1, false))) return rc;
+      if (a.user_phase.dtype != G4B_U8 || a.user_phase.shape[0] != a.block_tables.shape[0]) return fail(G4B_ERR_BAD_ARG, "user_phase must be uint8 [B]");
+    }
+  } else if (a.time_dim_sizes.ptr != nullptr || a.user_phase.ptr != nullptr) {
+    return fail(G4B_ERR_BAD_ARG, "time_dim_sizes and user_phase are only read with block_tables");
+  }
+  return launch_kv_dequant_fp8(a, (cudaStream_t)cuda_stream);
+}
+
 int g4b_flash_attention_fp8(const G4bAttnArgs* args, const G4bTensor* k_scales, const G4bTensor* v_scales,
                             void* cuda_stream) {
   if (args == nullptr || k_scales == nullptr || v_scales == nullptr) return fail(G4B_ERR_BAD_ARG, "args or scales null");

@@ -71,6 +71,7 @@ bool decode_stream_supports(const G4bAttnArgs& a);                              
 int launch_decode_stream(const G4bAttnArgs& a, int num_splits, const G4bDecodeStepArgs* step, cudaStream_t st,
                          const G4bTensor* k_scales = nullptr, const G4bTensor* v_scales = nullptr);
 int launch_kv_append_fp8(const G4bFp8AppendArgs& a, cudaStream_t st);
+int launch_kv_dequant_fp8(const G4bFp8DequantArgs& a, cudaStream_t st);
 int launch_prefill(const G4bAttnArgs& a, cudaStream_t st);
 
 // ---------------------------------------------------------------------------------------

@@ -313,6 +313,94 @@ int launch_kv_append_fp8(const G4bFp8AppendArgs& a, cudaStream_t st) {
 }
 
 // ---------------------------------------------------------------------------------------
+// 8-bit pool -> 16-bit pool (for prefill chunks over an 8-bit cache)
+// ---------------------------------------------------------------------------------------
+struct Fp8DequantParams {
+  const uint8_t* cache; const float* scales; void* out;
+  const int32_t* block_tables; const int32_t* time_dim_sizes; const uint8_t* user_phase;
+  int64_t ss0, ss1, bt_s0, bt_s1, time_stride, phase_stride;
+  int G, num_pages, max_pages, page_shift, phase;
+  int64_t run_bytes;          // page_size x D: bytes of one (page, kv head) run of the 8-bit pool
+  int32_t* status;
+};
+
+// One block per (page, kv head) run: with block tables the grid is (max_pages * G, B) and a
+// block finds its page in the table (or leaves: past the slot's length, slot off phase, bad
+// entry); without them it is (num_pages * G, 1).  A thread turns 16 bytes into 16 values:
+// e4m3 -> f16 is exact, the product with the scale is taken in f32 and rounded once.
+template <typename T>
+__global__ void __launch_bounds__(256) kv_dequant_fp8_kernel(Fp8DequantParams p) {
+  const int g = (int)(blockIdx.x % (uint32_t)p.G);
+  int page = (int)(blockIdx.x / (uint32_t)p.G);
+  if (p.block_tables != nullptr) {
+    const int b = blockIdx.y, pg = page;
+    if (p.user_phase != nullptr && p.user_phase[b * p.phase_stride] != (uint8_t)p.phase) return;
+    const int time = p.time_dim_sizes[b * p.time_stride];
+    if (((int64_t)pg << p.page_shift) >= time) return;
+    page = p.block_tables[b * p.bt_s0 + pg * p.bt_s1];
+    if (page < 0 || page >= p.num_pages) {     // never follow a bad table entry
+      if (threadIdx.x == 0) atomicCAS(p.status, 0, 0x100 | 3);
+      return;
+    }
+  }
+  const float scale = p.scales[page * p.ss0 + g * p.ss1];
+  const int64_t run = ((int64_t)page * p.G + g) * p.run_bytes;
+  const uint8_t* src = p.cache + run;
+  T* dst = (T*)p.out + run;
+  for (int64_t i = 16 * (int64_t)threadIdx.x; i < p.run_bytes; i += 16 * 256) {
+    const uint4 raw = *reinterpret_cast<const uint4*>(src + i);
+    const uint32_t w[4] = {raw.x, raw.y, raw.z, raw.w};
+    uint32_t o[8];
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+#pragma unroll
+      for (int h = 0; h < 2; ++h) {
+        uint32_t two;
+        const uint16_t pair = (uint16_t)(h ? (w[j] >> 16) : (w[j] & 0xffffu));
+        asm("cvt.rn.f16x2.e4m3x2 %0, %1;" : "=r"(two) : "h"(pair));
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&two));
+        if constexpr (sizeof(T) == 2 && std::is_same<T, __half>::value) {
+          const __half2 r = __floats2half2_rn(f.x * scale, f.y * scale);
+          o[2 * j + h] = *reinterpret_cast<const uint32_t*>(&r);
+        } else {
+          const __nv_bfloat162 r = __floats2bfloat162_rn(f.x * scale, f.y * scale);
+          o[2 * j + h] = *reinterpret_cast<const uint32_t*>(&r);
+        }
+      }
+    }
+    *reinterpret_cast<uint4*>(dst + i) = make_uint4(o[0], o[1], o[2], o[3]);
+    *reinterpret_cast<uint4*>(dst + i + 8) = make_uint4(o[4], o[5], o[6], o[7]);
+  }
+}
+
+int launch_kv_dequant_fp8(const G4bFp8DequantArgs& a, cudaStream_t st) {
+  Fp8DequantParams p{};
+  p.cache = (const uint8_t*)a.cache.ptr; p.scales = (const float*)a.scales.ptr; p.out = a.out.ptr;
+  p.block_tables = (const int32_t*)a.block_tables.ptr; p.time_dim_sizes = (const int32_t*)a.time_dim_sizes.ptr;
+  p.user_phase = (const uint8_t*)a.user_phase.ptr;
+  p.ss0 = a.scales.stride[0]; p.ss1 = a.scales.stride[1];
+  p.bt_s0 = a.block_tables.stride[0]; p.bt_s1 = a.block_tables.stride[1];
+  p.time_stride = a.time_dim_sizes.stride[0]; p.phase_stride = a.user_phase.stride[0];
+  p.G = (int)a.cache.shape[1]; p.num_pages = (int)a.cache.shape[0];
+  p.max_pages = p.block_tables != nullptr ? (int)a.block_tables.shape[1] : 0;
+  while ((1 << p.page_shift) < a.page_size) ++p.page_shift;
+  p.phase = a.phase;
+  p.run_bytes = a.cache.shape[2] * a.cache.shape[3];
+  const int64_t B = p.block_tables != nullptr ? a.block_tables.shape[0] : 1;
+  const int64_t runs = (p.block_tables != nullptr ? (int64_t)p.max_pages : (int64_t)p.num_pages) * p.G;
+  if (runs == 0 || B == 0) return G4B_OK;
+  if (runs > 0x7fffffffLL || B > 65535) return fail(G4B_ERR_TOO_LARGE, "dequant: too many pages or slots for one launch");
+  G4B_STOP_IF_VALIDATE_ONLY();
+  p.status = device_status_ptr();
+  if (p.status == nullptr) return G4B_ERR_CUDA;
+  const dim3 grid((unsigned)runs, (unsigned)B, 1);
+  if (a.out.dtype == G4B_F16) kv_dequant_fp8_kernel<__half><<<grid, 256, 0, st>>>(p);
+  else kv_dequant_fp8_kernel<__nv_bfloat16><<<grid, 256, 0, st>>>(p);
+  G4B_CUDA_CHECK(cudaGetLastError());
+  return G4B_OK;
+}
+
+// ---------------------------------------------------------------------------------------
 // advance_decode_state
 // ---------------------------------------------------------------------------------------
 __global__ void advance_kernel(int32_t* in_tok, const int32_t* out_tok, int32_t* cache_offsets,

@@ -61,3 +61,25 @@ def add_kv_to_cache_fp8(x, cache, scales, cache_offsets, rmsnorm_eps, x_rsos=Non
     a.phase, a.page_size = int(phase), int(page_size)
     _cabi.check(_cabi.load().g4b_kv_append_fp8(ctypes.byref(a), ctypes.c_void_p(_cabi.current_stream(stream))))
     return None
+
+
+def dequantise_fp8_pool(cache, scales, out, *, block_tables=None, time_dim_sizes=None, user_phase=None, phase=0,
+                        page_size: int = 16, stream=None):
+    """An 8-bit (e4m3) page pool into a 16-bit pool of the same geometry, page for page
+    (``g4b_kv_dequant_fp8``): ``out[p] = round(e4m3(cache[p]) x scales[p])``, so the same block
+    tables address both and a prefill chunk (``fa2.flash_attention`` with Tq > 1) can attend to a
+    context that lives in 8 bits.  With ``block_tables`` and ``time_dim_sizes`` only the pages that
+    hold the slots' first ``time_dim_sizes[b]`` tokens are converted (of the slots in ``phase``,
+    when ``user_phase`` is given).  No counterpart in the reference."""
+    import ctypes
+
+    a = _cabi.G4bFp8DequantArgs()
+    a.cache = _cabi.as_tensor(cache)
+    a.scales = _cabi.as_tensor(scales)
+    a.out = _cabi.as_tensor(out)
+    a.block_tables = _cabi.as_tensor(block_tables)
+    a.time_dim_sizes = _cabi.as_tensor(time_dim_sizes)
+    a.user_phase = _cabi.as_tensor(user_phase)
+    a.phase, a.page_size = int(phase), int(page_size)
+    _cabi.check(_cabi.load().g4b_kv_dequant_fp8(ctypes.byref(a), ctypes.c_void_p(_cabi.current_stream(stream))))
+    return None

@@ -235,6 +235,15 @@ int g4b_advance_decode_state(const G4bAdvanceArgs* args, void* cuda_stream);
  * g4b_flash_attention_fp8: Tq == 1 attention over such pools (head dims 128, 256, 512; at most
  * 8 query heads per kv head), split-KV and merge as g4b_flash_attention.  q / o may be f32, f16
  * or bf16; products run in f16 with f32 accumulation.
+ *
+ * g4b_kv_dequant_fp8: for prefill chunks (Tq > 1) over such a cache.  Writes
+ * round-to-nearest(e4m3(byte) x scale) into a caller-owned f16 / bf16 pool of the same geometry,
+ * page p of the 8-bit pool into page p of `out`, so the same block tables address both and
+ * g4b_flash_attention runs over `out`.  With block_tables and time_dim_sizes only the pages that
+ * hold the first time_dim_sizes[b] tokens of the slots (of the slots in `phase`, when
+ * user_phase is given) are converted and every other page of `out` is left as it is; without
+ * them every page is.  A table entry outside the pool is skipped and reported (0x103 in the
+ * device status word).
  */
 typedef struct G4bFp8AppendArgs {
   G4bTensor x;             /* [B, G, Tq, D] view, last stride 1; f32, f16 or bf16 */
@@ -250,6 +259,17 @@ typedef struct G4bFp8AppendArgs {
   int32_t page_size;
 } G4bFp8AppendArgs;
 int g4b_kv_append_fp8(const G4bFp8AppendArgs* args, void* cuda_stream);
+typedef struct G4bFp8DequantArgs {
+  G4bTensor cache;          /* pool [num_pages, G, page_size, D], 1 byte per element */
+  G4bTensor scales;         /* f32 [num_pages, G] */
+  G4bTensor out;            /* pool [num_pages, G, page_size, D], f16 or bf16, contiguous */
+  G4bTensor block_tables;   /* optional int32 [B, max_pages] (then time_dim_sizes is required) */
+  G4bTensor time_dim_sizes; /* optional int32 [B] */
+  G4bTensor user_phase;     /* optional uint8 [B] (only with block_tables) */
+  int32_t phase;
+  int32_t page_size;
+} G4bFp8DequantArgs;
+int g4b_kv_dequant_fp8(const G4bFp8DequantArgs* args, void* cuda_stream);
 int g4b_flash_attention_fp8(const G4bAttnArgs* args, const G4bTensor* k_scales, const G4bTensor* v_scales,
                             void* cuda_stream);
 

@@ -167,3 +167,27 @@ def test_host_and_foreign_device_tensors_are_refused():
     with pytest.raises(ValueError, match="CUDA tensor"):
         akv.add_kv_to_cache(torch.zeros(2, 2, 3, 256), torch.zeros(2, 2, 17, 256, dtype=torch.float16),
                             torch.zeros(2, dtype=torch.int32), 1e-6, stream=0)
+
+
+def test_fp8_dequant_rejects_bad_arguments():
+    pool = torch.zeros(6, 2, 16, 256, dtype=torch.uint8)
+    sc = torch.zeros(6, 2)
+    out = torch.zeros(6, 2, 16, 256, dtype=torch.float16)
+    akv.dequantise_fp8_pool(pool, sc, out, stream=0)                    # valid: passes, launches nothing
+    bt, time = torch.zeros(2, 3, dtype=torch.int32), torch.zeros(2, dtype=torch.int32)
+    akv.dequantise_fp8_pool(pool, sc, out, block_tables=bt, time_dim_sizes=time, user_phase=torch.zeros(2, dtype=torch.uint8),
+                            phase=1, stream=0)
+    with pytest.raises(ValueError, match="shape of cache"):
+        akv.dequantise_fp8_pool(pool, sc, out[:5], stream=0)
+    with pytest.raises(ValueError, match="f16 or bf16"):
+        akv.dequantise_fp8_pool(pool, sc, out.float(), stream=0)
+    with pytest.raises(ValueError, match="one byte"):
+        akv.dequantise_fp8_pool(out, sc, out, stream=0)
+    with pytest.raises(ValueError, match=r"\[num_pages, G\]"):
+        akv.dequantise_fp8_pool(pool, sc[:, :1], out, stream=0)
+    with pytest.raises(ValueError, match="needs time_dim_sizes"):
+        akv.dequantise_fp8_pool(pool, sc, out, block_tables=bt, stream=0)
+    with pytest.raises(ValueError, match="only read with block_tables"):
+        akv.dequantise_fp8_pool(pool, sc, out, time_dim_sizes=time, stream=0)
+    with pytest.raises(ValueError, match="page_size"):
+        akv.dequantise_fp8_pool(pool, sc, out, page_size=32, stream=0)

@@ -124,3 +124,78 @@ def test_attention_over_fp8_pools(cuda, seed):
                             fa2.PHASE_DECODE, *parts, block_tables=bt.to(cuda), page_size=page, scale=1 / 16,
                             sliding_window=sw, num_kv_splits=S if S > 1 else None)
     assert_close(o, want, f"seed {seed}: D{D} H{H} G{G} page{page} lens{lens} S{S} sw{sw}")
+
+
+@pytest.mark.parametrize("out_dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("D,page", [(256, 16), (128, 32), (512, 16)])
+def test_dequantised_pool_is_bit_exact(cuda, out_dtype, D, page):
+    """Every byte value (NaN codes apart) under a spread of scales: out = round(e4m3 x scale),
+    whole pool and restricted to the pages of the slots in phase."""
+    from g4b_b200.kernels.add_kv_to_cache import dequantise_fp8_pool
+
+    gen = torch.Generator().manual_seed(D + page)
+    G, lens = 2, [3 * page + 5, page, 1, 2 * page]
+    bt, num_pages = _tables(gen, lens, page, extra=3)
+    pool = torch.randint(0, 256, (num_pages, G, page, D), generator=gen, dtype=torch.int16).to(torch.uint8)
+    pool[(pool & 0x7f) == 0x7f] = 0x3c                                   # no NaN codes
+    sc = torch.rand(num_pages, G, generator=gen) * torch.tensor([1e-3, 1.0, 37.0])[torch.randint(0, 3, (num_pages, G), generator=gen)]
+    want = orc.dequantise_fp8_pool(pool, sc).to(out_dtype)
+    out = torch.full((num_pages, G, page, D), 9.0, dtype=out_dtype, device=cuda)
+    dequantise_fp8_pool(pool.to(cuda), sc.to(cuda), out, page_size=page)
+    assert torch.equal(out.cpu(), want)
+    # restricted: slots 0 and 3 are in phase 1, slot 1 is not; slot 2 holds one token
+    out.fill_(9.0)
+    time = torch.tensor(lens, dtype=torch.int32)
+    ph = torch.tensor([1, 0, 1, 1], dtype=torch.uint8)
+    dequantise_fp8_pool(pool.to(cuda), sc.to(cuda), out, block_tables=bt.to(cuda), time_dim_sizes=time.to(cuda),
+                        user_phase=ph.to(cuda), phase=1, page_size=page)
+    live = torch.zeros(num_pages, dtype=torch.bool)
+    for b, n in enumerate(lens):
+        if ph[b] == 1:
+            live[bt[b, :(n + page - 1) // page].long()] = True
+    got = out.cpu()
+    assert torch.equal(got[live], want[live])
+    assert bool((got[~live] == 9.0).all()), "pages outside the request were written"
+
+
+def test_prefill_chunk_over_an_8_bit_context(cuda):
+    """A chunk of 96 new tokens attends to a context that lives in e4m3 pages: append (quantise)
+    the chunk, de-quantise the slots' pages into a 16-bit scratch pool, run the prefill kernel
+    over it with the same block tables; against the oracle's attention on the de-quantised values."""
+    from g4b_b200.kernels.add_kv_to_cache import dequantise_fp8_pool
+
+    gen = torch.Generator().manual_seed(77)
+    B, H, G, D, page, Tq = 2, 8, 2, 256, 16, 96
+    ctx = [700, 333]                                                       # tokens already cached
+    lens = [c + Tq for c in ctx]
+    bt, num_pages = _tables(gen, lens, page)
+    kp = torch.zeros(num_pages, G, page, D, dtype=torch.uint8)
+    vp = torch.zeros_like(kp)
+    ks, vs = torch.zeros(num_pages, G), torch.zeros(num_pages, G)
+    for b, n in enumerate(ctx):
+        kp, ks = orc.add_kv_to_cache_fp8(randn(gen, 1, G, n, D), kp, ks, torch.tensor([0]), 1e-6, block_tables=bt[b:b + 1], page_size=page)
+        vp, vs = orc.add_kv_to_cache_fp8(randn(gen, 1, G, n, D), vp, vs, torch.tensor([0]), 1e-6, block_tables=bt[b:b + 1], page_size=page)
+    k_new, v_new = randn(gen, B, G, Tq, D), randn(gen, B, G, Tq, D)
+    q = randn(gen, B, H, Tq, D, dtype=torch.bfloat16)
+    off = torch.tensor(ctx, dtype=torch.int32)
+    time = torch.tensor(lens, dtype=torch.int32)
+    # oracle: quantise the chunk, de-quantise everything, attend
+    wkp, wks = orc.add_kv_to_cache_fp8(k_new, kp.clone(), ks.clone(), off, 1e-6, block_tables=bt, page_size=page)
+    wvp, wvs = orc.add_kv_to_cache_fp8(v_new, vp.clone(), vs.clone(), off, 1e-6, block_tables=bt, page_size=page)
+    kd = orc.dequantise_fp8_pool(wkp, wks).to(torch.bfloat16).float()
+    vd = orc.dequantise_fp8_pool(wvp, wvs).to(torch.bfloat16).float()
+    cw = bt.shape[1] * page
+    want = orc.flash_attention(q, kd, vd, torch.zeros(B, H, Tq, D), time, None, cw, 1, scale=1 / 16, block_tables=bt, page_size=page)
+    # GPU
+    dkp, dvp, dks, dvs, dbt = kp.to(cuda), vp.to(cuda), ks.to(cuda), vs.to(cuda), bt.to(cuda)
+    add_kv_to_cache_fp8(k_new.to(cuda), dkp, dks, off.to(cuda), 1e-6, block_tables=dbt, page_size=page)
+    add_kv_to_cache_fp8(v_new.to(cuda), dvp, dvs, off.to(cuda), 1e-6, block_tables=dbt, page_size=page)
+    assert torch.equal(dkp.cpu(), wkp) and torch.equal(dvp.cpu(), wvp)
+    k16 = torch.zeros(num_pages, G, page, D, dtype=torch.bfloat16, device=cuda)
+    v16 = torch.zeros_like(k16)
+    dequantise_fp8_pool(dkp, dks, k16, block_tables=dbt, time_dim_sizes=time.to(cuda), page_size=page)
+    dequantise_fp8_pool(dvp, dvs, v16, block_tables=dbt, time_dim_sizes=time.to(cuda), page_size=page)
+    o = torch.zeros(B, H, Tq, D, dtype=torch.bfloat16, device=cuda)
+    fa2.flash_attention(q.to(cuda), k16, v16, o, time.to(cuda), None, cw, fa2.PHASE_PREFILL, scale=1 / 16,
+                        block_tables=dbt, page_size=page)
+    assert_close(o, want, "prefill chunk over an 8-bit context")
