@@ -199,3 +199,64 @@ def test_prefill_chunk_over_an_8_bit_context(cuda):
     fa2.flash_attention(q.to(cuda), k16, v16, o, time.to(cuda), None, cw, fa2.PHASE_PREFILL, scale=1 / 16,
                         block_tables=dbt, page_size=page)
     assert_close(o, want, "prefill chunk over an 8-bit context")
+
+
+def test_serving_loop_over_8_bit_pages(cuda):
+    """Two requests through chunked prefill and decode with nothing but 8-bit pages behind them:
+    every chunk is quantised into the pages, the slot's pages are converted into a 16-bit scratch
+    pool and the prefill kernel attends over it; every decode step appends one row per slot and
+    attends over the bytes.  After every step the pools equal the CPU quantiser's bit for bit and
+    the attention output equals the oracle's attention over the de-quantised values."""
+    from g4b_b200.kernels.add_kv_to_cache import dequantise_fp8_pool
+
+    gen = torch.Generator().manual_seed(2024)
+    B, H, G, D, page, CHUNK, n_decode = 2, 8, 2, 256, 16, 32, 5
+    prompts = [70, 45]
+    bt, num_pages = _tables(gen, [n + n_decode for n in prompts], page)
+    cw = bt.shape[1] * page
+    # CPU twins of the pools, advanced by the oracle's quantiser
+    wk, wv = torch.zeros(num_pages, G, page, D, dtype=torch.uint8), torch.zeros(num_pages, G, page, D, dtype=torch.uint8)
+    wks, wvs = torch.zeros(num_pages, G), torch.zeros(num_pages, G)
+    dk, dv, dks, dvs = wk.to(cuda), wv.to(cuda), wks.to(cuda), wvs.to(cuda)
+    k16 = torch.zeros(num_pages, G, page, D, dtype=torch.bfloat16, device=cuda)
+    v16 = torch.zeros_like(k16)
+    dbt = bt.to(cuda)
+    for b, n in enumerate(prompts):                      # ---- chunked prefill, one slot at a time
+        for s in range(0, n, CHUNK):
+            e = min(n, s + CHUNK)
+            kx, vx = randn(gen, 1, G, e - s, D), randn(gen, 1, G, e - s, D)
+            q = randn(gen, 1, H, e - s, D, dtype=torch.bfloat16)
+            off, time = torch.tensor([s], dtype=torch.int32), torch.tensor([e], dtype=torch.int32)
+            wk, wks = orc.add_kv_to_cache_fp8(kx, wk, wks, off, 1e-6, block_tables=bt[b:b + 1], page_size=page)
+            wv, wvs = orc.add_kv_to_cache_fp8(vx, wv, wvs, off, 1e-6, block_tables=bt[b:b + 1], page_size=page)
+            add_kv_to_cache_fp8(kx.to(cuda), dk, dks, off.to(cuda), 1e-6, block_tables=dbt[b:b + 1], page_size=page)
+            add_kv_to_cache_fp8(vx.to(cuda), dv, dvs, off.to(cuda), 1e-6, block_tables=dbt[b:b + 1], page_size=page)
+            assert torch.equal(dk.cpu(), wk) and torch.equal(dv.cpu(), wv), f"slot {b} chunk at {s}: bytes differ"
+            dequantise_fp8_pool(dk, dks, k16, block_tables=dbt[b:b + 1], time_dim_sizes=time.to(cuda), page_size=page)
+            dequantise_fp8_pool(dv, dvs, v16, block_tables=dbt[b:b + 1], time_dim_sizes=time.to(cuda), page_size=page)
+            o = torch.zeros(1, H, e - s, D, dtype=torch.bfloat16, device=cuda)
+            fa2.flash_attention(q.to(cuda), k16, v16, o, time.to(cuda), None, cw, fa2.PHASE_PREFILL, scale=1 / 16,
+                                block_tables=dbt[b:b + 1], page_size=page)
+            kd = orc.dequantise_fp8_pool(wk, wks).to(torch.bfloat16).float()
+            vd = orc.dequantise_fp8_pool(wv, wvs).to(torch.bfloat16).float()
+            want = orc.flash_attention(q, kd, vd, torch.zeros(1, H, e - s, D), time, None, cw, 1, scale=1 / 16,
+                                       block_tables=bt[b:b + 1], page_size=page)
+            assert_close(o, want, f"slot {b} prefill chunk [{s}, {e})")
+    pos = torch.tensor(prompts, dtype=torch.int32)       # ---- decode, both slots per step
+    parts = (torch.empty(3, B, H, 1, D, device=cuda), torch.empty(3, B, H, 1, device=cuda), torch.empty(3, B, H, 1, device=cuda))
+    for step in range(n_decode):
+        kx, vx = randn(gen, B, G, 1, D), randn(gen, B, G, 1, D)
+        q = randn(gen, B, H, 1, D, dtype=torch.float16)
+        wk, wks = orc.add_kv_to_cache_fp8(kx, wk, wks, pos, 1e-6, block_tables=bt, page_size=page)
+        wv, wvs = orc.add_kv_to_cache_fp8(vx, wv, wvs, pos, 1e-6, block_tables=bt, page_size=page)
+        add_kv_to_cache_fp8(kx.to(cuda), dk, dks, pos.to(cuda), 1e-6, block_tables=dbt, page_size=page)
+        add_kv_to_cache_fp8(vx.to(cuda), dv, dvs, pos.to(cuda), 1e-6, block_tables=dbt, page_size=page)
+        assert torch.equal(dk.cpu(), wk) and torch.equal(dv.cpu(), wv) and torch.equal(dks.cpu(), wks), f"decode step {step}: pools differ"
+        time = pos + 1
+        o = torch.zeros(B, H, 1, D, dtype=torch.float16, device=cuda)
+        fa2.flash_attention_fp8(q.to(cuda), dk, dv, dks, dvs, o, time.to(cuda), None, cw, fa2.PHASE_DECODE, *parts,
+                                block_tables=dbt, page_size=page, scale=1 / 16, num_kv_splits=3)
+        want = orc.flash_attention(q, orc.dequantise_fp8_pool(wk, wks), orc.dequantise_fp8_pool(wv, wvs),
+                                   torch.zeros(B, H, 1, D), time, None, cw, 2, scale=1 / 16, block_tables=bt, page_size=page)
+        assert_close(o, want, f"decode step {step}")
+        pos = pos + 1
