@@ -88,8 +88,8 @@ static int validate_attn(const G4bAttnArgs& a, bool need_partials, int splits, b
   if (a.k_cache.shape[3] != D) return fail(G4B_ERR_BAD_ARG, "head dim of q and cache differ");
   const int64_t G = a.k_cache.shape[1];
   if (G <= 0 || H % G != 0) return fail(G4B_ERR_BAD_ARG, "query heads must be a multiple of kv heads");
-  if (D != 256 && !(tq1 && (D == 128 || D == 512)))
-    return fail(G4B_ERR_UNSUPPORTED, "head dim %lld not supported (Tq == 1: 128, 256, 512; Tq > 1: 256)", (long long)D);
+  if (D != 256 && D != 128 && !(tq1 && D == 512))
+    return fail(G4B_ERR_UNSUPPORTED, "head dim %lld not supported (Tq == 1: 128, 256, 512; Tq > 1: 128, 256)", (long long)D);
   if ((((uintptr_t)a.k_cache.ptr) | ((uintptr_t)a.v_cache.ptr)) & 15)
     return fail(G4B_ERR_BAD_STRIDE, "k_cache/v_cache must be 16-byte aligned");
   if (a.stage != G4B_STAGE_CAUSAL && a.stage != G4B_STAGE_FULL)

@@ -1,4 +1,5 @@
-// Flash-attention forward for Tq > 1 (prefill chunks), head dim 256, f16 / bf16, on the
+// Flash-attention forward for Tq > 1 (prefill chunks), head dim 256 (and 128, on tiles whose
+// upper half is the TMA's zero fill: the time of head dim 256), f16 / bf16, on the
 // 5th-generation tensor cores: tcgen05.mma with accumulators in tensor memory, operands
 // staged in shared memory by TMA, online softmax in registers.
 //
@@ -84,6 +85,7 @@ struct PrefillParams {
   int64_t time_stride, phase_stride, bt_s0, bt_s1;
   int page_shift, num_pages, max_pages;      // paged mode
   int B, H, G, Tq, T;
+  int D;                                     // head dim in memory: 256, or 128 (the upper half of every tile is then zero fill)
   // split-KV for chunks that would leave most SMs idle: work items are (item, key range),
   // un-normalised (acc, l, m) go to the caller's partial buffers and a merge launch follows
   float* po; float* pl; float* pm;
@@ -178,19 +180,20 @@ struct KeySource {
   int ring_start, Trows;    // ring
   int G, g, page_shift, num_pages, max_pages;   // paged
   int window;               // keys [0, window) exist
+  int D;                    // elements per row in memory
   bool paged;
   __device__ __forceinline__ const T* row(int key) const {
     if (key < 0 || key >= window) return nullptr;
     if (!paged) {
       int pr = ring_start + key;
       if (pr >= Trows) pr -= Trows;
-      return base + (int64_t)pr * kHD;
+      return base + (int64_t)pr * D;
     }
     const int pg = key >> page_shift;
     if (pg >= max_pages) return nullptr;
     const int page = bt[pg * bt_s1];
     if (page < 0 || page >= num_pages) return nullptr;
-    return base + ((((int64_t)page * G + g) << page_shift) + (key & ((1 << page_shift) - 1))) * kHD;
+    return base + ((((int64_t)page * G + g) << page_shift) + (key & ((1 << page_shift) - 1))) * D;
   }
 };
 
@@ -208,7 +211,7 @@ __device__ __forceinline__ void manual_chunk(uint8_t* dst, const KeySource<T>& s
     const int r = idx / chunks_per_row, ch = idx % chunks_per_row;
     uint4 val = make_uint4(0u, 0u, 0u, 0u);
     const T* rp = src.row(key0 + r);
-    if (rp != nullptr) val = *reinterpret_cast<const uint4*>(rp + d0 + ch * 8);
+    if (rp != nullptr && d0 + ch * 8 < src.D) val = *reinterpret_cast<const uint4*>(rp + d0 + ch * 8);   // (columns past the head dim: zero, like the TMA fill)
     const int slab = ch >> 3, c16 = ch & 7;
     uint8_t* p = dst + slab * (slab_rows * 128) + r * 128 + ((c16 ^ (r & 7)) << 4);
     *reinterpret_cast<uint4*>(p) = val;
@@ -256,11 +259,14 @@ template <> struct PackT<__half> {
 //   each CTA stages only half of every tile (K: half the keys, V: half the head dim), so the
 //   ring covers twice the time and Q.K^T reads 96 instead of 128 bytes of shared memory per
 //   cycle -- the two things that starve the single-CTA form.
-template <typename T, bool kPair, bool kStageOut, bool kShortItems, bool kSplit>
+template <typename T, bool kPair, bool kStageOut, bool kShortItems, bool kSplit, bool kNarrow>
 __global__ void __launch_bounds__(kThreads, 1)
 prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
                const __grid_constant__ CUtensorMap v_map, const __grid_constant__ CUtensorMap o_map, PrefillParams p) {
   extern __shared__ __align__(1024) uint8_t smem_raw[];
+  // head dim in memory: 256, or (kNarrow) 128 -- the tiles stay 256 wide, their upper half is
+  // the TMA's zero fill and the accumulator's upper half is never stored
+  constexpr int kD = kNarrow ? 128 : kHD;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // kStageOut: the epilogue turns the output block through shared memory to store whole
   // 128-byte row segments.  It borrows the ring slot of the item's last V chunk: that slot is
@@ -385,12 +391,12 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     G4B_ITEM_GEOMETRY(item);
     if (n_tiles <= 0) continue;
     KeySource<T> ksrc, vsrc;
-    ksrc.paged = paged; ksrc.window = window; ksrc.ring_start = ring_start; ksrc.Trows = p.T;
+    ksrc.paged = paged; ksrc.window = window; ksrc.ring_start = ring_start; ksrc.Trows = p.T; ksrc.D = kD;
     ksrc.G = p.G; ksrc.g = g; ksrc.page_shift = p.page_shift; ksrc.num_pages = p.num_pages;
     ksrc.max_pages = p.max_pages; ksrc.bt = paged ? p.block_tables + b * p.bt_s0 : nullptr; ksrc.bt_s1 = p.bt_s1;
-    ksrc.base = paged ? (const T*)p.k : (const T*)p.k + ((int64_t)b * p.G + g) * p.T * kHD;
+    ksrc.base = paged ? (const T*)p.k : (const T*)p.k + ((int64_t)b * p.G + g) * p.T * kD;
     vsrc = ksrc;
-    vsrc.base = paged ? (const T*)p.v : (const T*)p.v + ((int64_t)b * p.G + g) * p.T * kHD;
+    vsrc.base = paged ? (const T*)p.v : (const T*)p.v + ((int64_t)b * p.G + g) * p.T * kD;
     const int bg = b * p.G + g;
     // The previous item's epilogue borrows the slot of its last V chunk (chunk cc - 1), which
     // chunk cc + 4 refills.  stage_free completes once per item, so it must also be waited for
@@ -422,7 +428,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
 #pragma unroll 4
       for (int r = 0; r < kBM; ++r) {
         uint4 w = make_uint4(0u, 0u, 0u, 0u);
-        if (m0 + r < p.Tq) {
+        if (m0 + r < p.Tq && lane * 8 < kD) {
           const float4* src = reinterpret_cast<const float4*>(q0 + (int64_t)(m0 + r) * p.q_s2 + lane * 8);
           const float4 a = src[0], c = src[1];
           w = make_uint4(PackT<T>::pack(a.x, a.y), PackT<T>::pack(a.z, a.w), PackT<T>::pack(c.x, c.y), PackT<T>::pack(c.z, c.w));
@@ -951,7 +957,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       // no visible key for any row of this tile: the output rows are defined as zero
       if (active && half == 0 && r < rows_valid) {
         const int64_t off = b * p.o_s0 + h * p.o_s1 + (int64_t)(m0 + r) * p.o_s2;
-        for (int d = 0; d < kHD; ++d) {
+        for (int d = 0; d < kD; ++d) {
           if (p.o_dtype == G4B_F32) ((float*)p.o)[off + d] = 0.f;
           else ((uint16_t*)p.o)[off + d] = 0;
         }
@@ -1211,7 +1217,8 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     }
     if (ok) {
       const float inv_l = l_run > 0.f ? 1.f / l_run : 0.f;
-      const bool row_ok = r < rows_valid;
+      // (head dim 128: the accumulator's columns 128..255 are zeros nobody stores)
+      const bool row_ok = r < rows_valid && half * 128 < kD;
       const uint64_t pol_o = ptx::policy_evict_first();   // the output is not read again here
       const int64_t off = b * p.o_s0 + h * p.o_s1 + (int64_t)(m0 + r) * p.o_s2 + half * 128;
       if constexpr (kSplit) {
@@ -1295,7 +1302,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
             }
             ptx::fence_proxy_async_smem();
             __syncwarp();
-            if (lane == 0 && lane_base < rows_valid) {   // (a box wholly past Tq is not issued at all)
+            if (lane == 0 && lane_base < rows_valid && half * 128 < kD) {   // (a box wholly past Tq or the head dim is not issued at all)
               ptx::tma_store_4d_hint(&o_map, ptx::smem_u32(stage), half * 128 + cp * 64, m0 + lane_base, h, b, pol_o);
               ptx::bulk_commit();
             }
@@ -1358,14 +1365,14 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
 // ---------------------------------------------------------------------------------------
 // host side: tensor maps + launch
 // ---------------------------------------------------------------------------------------
-template <typename T, bool kPair, bool kStageOut, bool kShortItems, bool kSplit>
+template <typename T, bool kPair, bool kStageOut, bool kShortItems, bool kSplit, bool kNarrow>
 static int launch_variant(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const CUtensorMap& om,
                           const PrefillParams& p, dim3 grid, cudaStream_t st) {
   static bool attr_set[64] = {false};
   int dev = 0;
   G4B_CUDA_CHECK(cudaGetDevice(&dev));
   if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    G4B_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<T, kPair, kStageOut, kShortItems, kSplit>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
+    G4B_CUDA_CHECK(cudaFuncSetAttribute(prefill_kernel<T, kPair, kStageOut, kShortItems, kSplit, kNarrow>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes));
     attr_set[dev] = true;
   }
   cudaLaunchConfig_t cfg = {};
@@ -1380,22 +1387,30 @@ static int launch_variant(const CUtensorMap& qm, const CUtensorMap& km, const CU
   attr[0].val.clusterDim.z = 1;
   cfg.attrs = attr;
   cfg.numAttrs = 1;
-  G4B_CUDA_CHECK(cudaLaunchKernelEx(&cfg, prefill_kernel<T, kPair, kStageOut, kShortItems, kSplit>, qm, km, vm, om, p));
+  G4B_CUDA_CHECK(cudaLaunchKernelEx(&cfg, prefill_kernel<T, kPair, kStageOut, kShortItems, kSplit, kNarrow>, qm, km, vm, om, p));
   return G4B_OK;
+}
+
+template <typename T, bool kNarrow>
+static int launch_width(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const CUtensorMap& om,
+                        const PrefillParams& p, dim3 grid, bool pair, bool stage_out, bool short_items, bool split,
+                        cudaStream_t st) {
+  if (split) {
+    if (pair) return launch_variant<T, true, false, false, true, kNarrow>(qm, km, vm, om, p, grid, st);
+    return launch_variant<T, false, false, false, true, kNarrow>(qm, km, vm, om, p, grid, st);
+  }
+  if (pair && stage_out && short_items) return launch_variant<T, true, true, true, false, kNarrow>(qm, km, vm, om, p, grid, st);
+  if (pair && stage_out) return launch_variant<T, true, true, false, false, kNarrow>(qm, km, vm, om, p, grid, st);
+  if (pair) return launch_variant<T, true, false, false, false, kNarrow>(qm, km, vm, om, p, grid, st);
+  return launch_variant<T, false, false, false, false, kNarrow>(qm, km, vm, om, p, grid, st);
 }
 
 template <typename T>
 static int launch_typed(const CUtensorMap& qm, const CUtensorMap& km, const CUtensorMap& vm, const CUtensorMap& om,
                         const PrefillParams& p, dim3 grid, bool pair, bool stage_out, bool short_items, bool split,
                         cudaStream_t st) {
-  if (split) {
-    if (pair) return launch_variant<T, true, false, false, true>(qm, km, vm, om, p, grid, st);
-    return launch_variant<T, false, false, false, true>(qm, km, vm, om, p, grid, st);
-  }
-  if (pair && stage_out && short_items) return launch_variant<T, true, true, true, false>(qm, km, vm, om, p, grid, st);
-  if (pair && stage_out) return launch_variant<T, true, true, false, false>(qm, km, vm, om, p, grid, st);
-  if (pair) return launch_variant<T, true, false, false, false>(qm, km, vm, om, p, grid, st);
-  return launch_variant<T, false, false, false, false>(qm, km, vm, om, p, grid, st);
+  if (p.D == 128) return launch_width<T, true>(qm, km, vm, om, p, grid, pair, stage_out, short_items, split, st);
+  return launch_width<T, false>(qm, km, vm, om, p, grid, pair, stage_out, short_items, split, st);
 }
 
 }  // namespace
@@ -1458,6 +1473,7 @@ int launch_prefill(const G4bAttnArgs& a, cudaStream_t st) {
   p.o_s0 = a.o.stride[0]; p.o_s1 = a.o.stride[1]; p.o_s2 = a.o.stride[2];
   p.time_stride = a.time_dim_sizes.stride[0]; p.phase_stride = a.user_phase.stride[0];
   p.B = (int)B; p.H = (int)H; p.G = (int)G; p.Tq = (int)Tq; p.T = paged ? 1 : (int)T;
+  p.D = (int)D;
   p.n_q_tiles = (int)n_q_tiles;
   p.by_units.set((uint32_t)(pair ? B * H / 2 : B * H));
   p.by_H.set((uint32_t)H);

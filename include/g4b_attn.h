@@ -105,14 +105,15 @@ typedef struct G4bAttnArgs {
 
 /* Head dims: the Tq == 1 path (g4b_attn_decode, g4b_decode_step, g4b_attn_combine, and
  * g4b_flash_attention when Tq == 1 with at most 8 query heads per kv head) takes 128, 256 and
- * 512; the Tq > 1 kernel (g4b_attn_prefill) takes 256. */
+ * 512; the Tq > 1 kernel (g4b_attn_prefill) takes 256 and 128 (128 on the 256-wide tiles, so at
+ * the time of 256). */
 
 /* replaces flash_attention() as a whole (fa2.py:634-715): picks the prefill or the
  * decode kernel, the split count, and runs the combine when splits > 1. */
 int g4b_flash_attention(const G4bAttnArgs* args, void* cuda_stream);
 
 /* replaces the launch of _attn_kernel for Tq > 1 (fa2.py:256-480, 672-690):
- * tcgen05 / TMEM / TMA flash-attention forward, head dim 256, f16 or bf16 caches, q and o in
+ * tcgen05 / TMEM / TMA flash-attention forward, head dim 256 or 128, f16 or bf16 caches, q and o in
  * the cache dtype or f32.  If the partial triple is given (f32, [S,B,H,Tq,D] / [S,B,H,Tq]) and
  * the chunk has too few (slot, head, 128-row tile) units to occupy the GPU, every unit's key
  * range is split over up to S pieces (num_kv_splits forces a count) and merged by a second

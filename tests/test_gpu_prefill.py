@@ -430,3 +430,59 @@ def test_sliding_window_items_with_wildly_different_score_scales(cuda, dtype):
         lo = max(0, r - W + 1)
         want = orc.attention_core(q_phys[0, r:r + 1].permute(1, 0, 2), k[0, :, lo:r + 1], v[0, :, lo:r + 1], scale=1 / 16)
         assert_close(got[0, :, r:r + 1], want, f"row={r}")
+
+
+
+# ------------------------------------------------------------------------------------------
+# head dim 128 (the kernel's tiles are 256 wide: the upper half is zero fill, never stored)
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("B,H,G,Tq,T", [(2, 8, 2, 256, 1024), (1, 3, 3, 200, 333), (2, 4, 2, 130, 517)])
+def test_prefill_head_dim_128_over_ring_cache(cuda, dtype, B, H, G, Tq, T):
+    """CTA pairs and the one-CTA form (odd head count), wrapped rings (the tile that crosses the
+    end of the ring is staged by ordinary loads), ragged Tq; the memory after every output row
+    (the next head's row) must stay as it was."""
+    case = make_ring_case(60, B=B, H=H, G=G, Tq=Tq, T=T, D=128, dtype=dtype,
+                          times=[T if b % 2 == 0 else T + 17 for b in range(B)])
+    assert_close(run(case, cuda), oracle(case), "head dim 128 over ring")
+
+
+def test_prefill_head_dim_128_windows_f32_and_full_stage(cuda):
+    case = make_ring_case(61, B=2, H=8, G=2, Tq=384, T=384, D=128, dtype=torch.bfloat16, times=[384, 384])
+    assert_close(run(case, cuda, sliding_window=100), oracle(case, sliding_window=100), "head dim 128, sliding window")
+    assert_close(run(case, cuda, stage=fa2.STAGE_FULL), oracle(case, stage=fa2.STAGE_FULL), "head dim 128, full stage")
+    assert_close(run(case, cuda, o_dtype=torch.float32), oracle(case), "head dim 128, f32 output")
+    # f32 q (rounded to the cache type on load)
+    q32 = case["q_phys"].float().to(cuda)
+    o = torch.zeros(2, 384, 8, 128, dtype=torch.bfloat16, device=cuda)
+    fa2.flash_attention(q32.permute(0, 2, 1, 3), case["k"].to(cuda), case["v"].to(cuda), o.permute(0, 2, 1, 3),
+                        case["time"].to(cuda), None, 384, fa2.PHASE_PREFILL, scale=1 / 16)
+    assert_close(o.permute(0, 2, 1, 3).cpu(), oracle(case), "head dim 128, f32 q")
+
+
+def test_prefill_head_dim_128_paged_and_split(cuda):
+    """Over a paged cache (16-row TMA boxes per page), and a short chunk over a long context
+    with the key range split and merged."""
+    from helpers import make_paged_case
+
+    times, Tq, H, G = [640, 37 + 256, 513], 256, 8, 2
+    case = make_paged_case(62, lens=times, H=H, G=G, D=128, dtype=torch.bfloat16)
+    gen = torch.Generator().manual_seed(63)
+    q_phys = randn(gen, 3, Tq, H, 128, dtype=torch.bfloat16)
+    o = torch.zeros_like(q_phys).to(cuda)
+    fa2.flash_attention(q_phys.to(cuda).permute(0, 2, 1, 3), case["k_pool"].to(cuda), case["v_pool"].to(cuda),
+                        o.permute(0, 2, 1, 3), case["time"].to(cuda), None, case["max_len"], 1, scale=1 / 16,
+                        block_tables=case["block_tables"].to(cuda), page_size=16)
+    want = orc.flash_attention(q_phys.permute(0, 2, 1, 3), case["k_pool"].float(), case["v_pool"].float(),
+                               torch.zeros(3, H, Tq, 128), case["time"], None, case["max_len"], 1, scale=1 / 16,
+                               block_tables=case["block_tables"], page_size=16)
+    assert_close(o.permute(0, 2, 1, 3).cpu(), want, "head dim 128, paged")
+    # split-KV chunk: B1 H8 G2, 128 rows over 4096 keys, 4 splits
+    ring = make_ring_case(64, B=1, H=8, G=2, Tq=128, T=4096, D=128, dtype=torch.bfloat16, times=[4096])
+    q, k, v, time = (ring[n].to(cuda) for n in ("q_phys", "k", "v", "time"))
+    po = torch.empty(4, 1, 8, 128, 128, device=cuda)
+    pl, pm = torch.empty(4, 1, 8, 128, device=cuda), torch.empty(4, 1, 8, 128, device=cuda)
+    o2 = torch.zeros(1, 128, 8, 128, dtype=torch.bfloat16, device=cuda)
+    fa2.flash_attention(q.permute(0, 2, 1, 3), k, v, o2.permute(0, 2, 1, 3), time, None, 4096, fa2.PHASE_PREFILL,
+                        po, pl, pm, scale=1 / 16, num_kv_splits=4)
+    assert_close(o2.permute(0, 2, 1, 3).cpu(), oracle(ring), "head dim 128, split-KV chunk")

@@ -90,11 +90,10 @@ def test_reference_head_dim_128_decode_case(cuda, with_splits):
     assert_close(o, want, "decode_small_w1024")
 
 
-def test_prefill_head_dim_128_is_refused(cuda):
-    """The Tq > 1 kernel is built for head dim 256 only; other head dims must be refused, not
-    computed."""
-    q = torch.zeros(1, 8, 64, 128, dtype=torch.float16, device=cuda)
-    k = torch.zeros(1, 2, 1024, 128, dtype=torch.float16, device=cuda)
+def test_prefill_head_dim_512_is_refused(cuda):
+    """The Tq > 1 kernel takes head dims 128 and 256; others must be refused, not computed."""
+    q = torch.zeros(1, 8, 64, 512, dtype=torch.float16, device=cuda)
+    k = torch.zeros(1, 2, 1024, 512, dtype=torch.float16, device=cuda)
     time = torch.full((1,), 1024, dtype=torch.int32, device=cuda)
     with pytest.raises(ValueError, match="head dim"):
         fa2.flash_attention(q, k, k.clone(), torch.zeros_like(q), time, None, 1024, fa2.PHASE_PREFILL)
