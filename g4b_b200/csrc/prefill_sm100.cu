@@ -923,7 +923,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     // tile), when the read has long ended, instead of waiting for it in the epilogue.  (Giving
     // the slot back before the first tile instead cost 1.5 % on long items: the wait sits in
     // front of the tile that the tensor pipe is waiting for.)
-    // Short items: the reference maximum a row ended the last item with is the first guess for
+    // The reference maximum a row ended the last item with is the first guess for
     // the same row of the next one (another head or query tile of similar scores).  A guess
     // at most 2^8 below or 2^4 above the first maximum the row really sees is kept -- any
     // reference in that range is as good as the maximum itself -- so the first tile of an item can take the
@@ -967,7 +967,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
     const int qpos = q_t_base + m0 + r;
     const int hi_r = p.causal ? min(window, qpos + 1) : window;
     const int lo_r = p.sliding_window > 0 ? max(win_lo, qpos - p.sliding_window + 1) : win_lo;
-    float m_used = (kShortItems && !few_keys) ? m_carry : -INFINITY;   // reference maximum the accumulated O and l are scaled by
+    float m_used = !few_keys ? m_carry : -INFINITY;   // reference maximum the accumulated O and l are scaled by
     bool anchored = false;      // m_used has been checked against a key this row sees
     float l_run = 0.f;          // this thread's half of the row sum
 
@@ -1048,7 +1048,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       const float m_blk = mx * p.scale_log2;
       bool exceed = m_blk > m_used + 8.f;
       bool first_seen = false;
-      if (kShortItems && !few_keys && !anchored && m_blk != -INFINITY) {
+      if (!few_keys && !anchored && m_blk != -INFINITY) {
         // the row's first visible key: a guess that lies too far ABOVE is replaced as well
         // (nothing has been accumulated against it yet, so nothing is rescaled)
         first_seen = anchored = true;
@@ -1145,7 +1145,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       float alpha = 1.f;
       bool rescale = false;
       if (exceed) {
-        rescale = (m_used != -INFINITY);
+        rescale = (m_used != -INFINITY) && !first_seen;
         alpha = rescale ? ptx::ex2_approx(m_used - m_blk) : 1.f;
         m_used = m_blk;
       }
@@ -1201,7 +1201,7 @@ prefill_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant_
       arrive_issuer(bar_pb);
     }
 
-    if (kShortItems && !few_keys && m_used != -INFINITY) m_carry = m_used;
+    if (!few_keys && m_used != -INFINITY) m_carry = m_used;
     // ---- epilogue: O / l -> global ----
     release_stage();   // (an item of one tile: its only V chunk may be the one that waits for the slot)
     if (ok) {

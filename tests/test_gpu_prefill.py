@@ -486,3 +486,30 @@ def test_prefill_head_dim_128_paged_and_split(cuda):
     fa2.flash_attention(q.permute(0, 2, 1, 3), k, v, o2.permute(0, 2, 1, 3), time, None, 4096, fa2.PHASE_PREFILL,
                         po, pl, pm, scale=1 / 16, num_kv_splits=4)
     assert_close(o2.permute(0, 2, 1, 3).cpu(), oracle(ring), "head dim 128, split-KV chunk")
+
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+def test_causal_items_with_wildly_different_score_scales(cuda, dtype):
+    """The same for long (causal) items, whose first tile takes the general path when the
+    carried maximum does not hold: 256 items over 74 workers, heads whose scores differ by
+    orders of magnitude, stripes of almost silent rows."""
+    gen = torch.Generator().manual_seed(54)
+    B, S, H, G, D = 1, 4096, 16, 2, 256
+    q_phys = randn(gen, B, S, H, D, dtype=torch.float32)
+    k = randn(gen, B, G, S, D, dtype=dtype)
+    v = randn(gen, B, G, S, D, dtype=dtype)
+    head_gain = torch.tensor([150.0, 0.01, 60.0, 1.0, 0.02, 200.0, 0.1, 3.0, 0.5, 90.0, 0.01, 30.0, 180.0, 0.05, 1.0, 120.0])
+    q_phys = q_phys * head_gain[None, None, :, None]
+    stripe = ((torch.arange(S) // 128) % 3 == 2).float() * 0.999
+    q_phys = (q_phys * (1.0 - stripe)[None, :, None, None]).to(dtype)
+    time = torch.full((B,), S, dtype=torch.int32)
+    qd = q_phys.to(cuda)
+    o = torch.zeros_like(qd)
+    fa2.flash_attention(qd.permute(0, 2, 1, 3), k.to(cuda), v.to(cuda), o.permute(0, 2, 1, 3), time.to(cuda), None,
+                        S, 1, scale=1 / 16)
+    got = o.permute(0, 2, 1, 3).cpu()
+    assert bool(torch.isfinite(got.float()).all())
+    for r in [0, 1, 63, 64, 127, 128, 129, 255, 256, 383, 384, 1000, 2047, 2048, 2175, 3000, 4094, 4095]:
+        want = orc.attention_core(q_phys[0, r:r + 1].permute(1, 0, 2), k[0, :, :r + 1], v[0, :, :r + 1], scale=1 / 16)
+        assert_close(got[0, :, r:r + 1], want, f"row={r}")
